@@ -1,0 +1,162 @@
+/*
+ * polarquant_b200 - C ABI of the B200 (sm_100a) polar key-cache hot path.
+ *
+ * Every entry point takes raw device pointers (unless its name ends in _host),
+ * explicit sizes and strides, and a CUDA stream handle (cudaStream_t passed as
+ * void*).  Work is enqueued on that stream and the call returns without
+ * synchronising.  The library owns no memory: outputs and scratch are the
+ * caller's.  Return value: PQ_OK (0) or a negative pq_status; nothing throws or
+ * aborts.  Strides are in ELEMENTS of the tensor's dtype.
+ *
+ * The reference project (ericshwu/PolarQuant) is Python; the interface each
+ * function stands behind is cited as file:line of that project.
+ */
+#ifndef POLARQUANT_B200_H
+#define POLARQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { PQ_F16 = 0, PQ_BF16 = 1, PQ_F32 = 2 } pq_dtype;
+
+typedef enum {
+  PQ_OK = 0,
+  PQ_ERR_INVALID = -1,     /* bad shape, null pointer, rbits + tbits > 8, ...   */
+  PQ_ERR_UNSUPPORTED = -2, /* valid for the reference, not built into this lib  */
+  PQ_ERR_WORKSPACE = -3,   /* scratch buffer missing or too small               */
+  PQ_ERR_CUDA = -4,        /* a CUDA runtime call failed (see pq_last_cuda_error) */
+  PQ_ERR_ALIGNMENT = -5    /* a pointer or stride breaks a 16-byte requirement  */
+} pq_status;
+
+/* pq_quantize flag bits */
+#define PQ_QUANT_WRAP_DTYPE 1u /* add RN_dtype(2*pi) to negative angles (what torch does on CPU) \
+                                  instead of float32(2*pi) (what torch does on CUDA, the default) */
+#define PQ_QUANT_NORM_SEPARATE 2u /* fp32 keys only: radius^2 = RN(x*x) + RN(y*y) instead of fma(y, y, x*x) */
+
+/*
+ * Polar key quantizer.  Replaces the method quantize_and_pack_nbit
+ * (models/modeling_llama_polar.py:135-157, models/modeling_qwen_polar.py:134-156).
+ *
+ * keys: (B, Nk, L, hd) of `dtype`, strides[4] in elements with strides[3] == 1;
+ * pair d is channels (d, d + hd/2).  L % G == 0, rbits + tbits <= 8, hd == 128.
+ * Outputs are contiguous: codes (B, Nk, L/G, G, hd/2) uint8 with
+ * code = (rho << tbits) + theta; rscale, rmn, tscale, tmn (B, Nk, L/G, 1, hd/2)
+ * of `dtype`.  Bit-exact with the reference ops executed by torch on CUDA.
+ */
+int pq_quantize(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G,
+                int rbits, int tbits, int dtype, unsigned flags,
+                uint8_t* codes, void* rscale, void* rmn, void* tscale, void* tmn, void* stream);
+
+/*
+ * Un-scaled fp32 query-key logits over the packed keys.  Replaces
+ * attention_decode_forward_triton_impl and its Triton kernel
+ * (models/kernel4group.py:14-109).
+ *
+ * q: (B, N, 2*D) of `dtype` with element strides q_stride_b / q_stride_h and unit
+ * inner stride; codes (B, Nk, Nb, G, D) and the four scale tensors (B, Nk, Nb, D)
+ * contiguous; out (B, N, Nb*G) fp32 contiguous.  Query head kvh*(N/Nk)+h reads
+ * kv head kvh.  D == 64, G % 16 == 0, 1 <= tbits <= 4.
+ */
+int pq_qk_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                 const uint8_t* codes, const void* rscale, const void* rmn,
+                 const void* tscale, const void* tmn, float* out,
+                 int B, int N, int Nk, int Nb, int G, int D, int rbits, int tbits, int dtype,
+                 void* stream);
+
+/*
+ * Fused decode attention over the polar cache: lookup-table QK over the packed
+ * keys + QK over the full-precision residual keys + scale + optional mask +
+ * online softmax + P.V, split over the sequence with a log-sum-exp merge.
+ * Replaces the decode branch of the patched attention forward
+ * (models/modeling_llama_polar.py:61-101, models/modeling_qwen_polar.py:60-100),
+ * i.e. the composition of the call at :66-75 with the eager ops at :77-99.
+ */
+typedef struct pq_decode_params {
+  /* query (B, N, hd), dtype qk_dtype */
+  const void* q;
+  int64_t q_stride_b, q_stride_h;
+  /* packed keys: codes (B, Nk, Nb, G, hd/2) uint8; unit (b, kvh) starts at
+     b * codes_stride_b + kvh * codes_stride_h bytes and holds Nb*G*(hd/2)
+     contiguous bytes.  NULL allowed when Nb == 0. */
+  const uint8_t* codes;
+  int64_t codes_stride_b, codes_stride_h;
+  /* scales (B, Nk, Nb, hd/2), dtype qk_dtype; unit (b, kvh) starts at
+     b * scale_stride_b + kvh * scale_stride_h elements, rows contiguous */
+  const void* rscale;
+  const void* rmn;
+  const void* tscale;
+  const void* tmn;
+  int64_t scale_stride_b, scale_stride_h;
+  /* full-precision residual keys (B, Nk, R, hd), dtype qk_dtype, including the
+     current token.  NULL allowed when R == 0. */
+  const void* k_res;
+  int64_t kres_stride_b, kres_stride_h, kres_stride_t;
+  /* values (B, Nk, Nb*G + R, hd), dtype v_dtype (PQ_F16 or PQ_BF16) */
+  const void* v;
+  int64_t v_stride_b, v_stride_h, v_stride_t;
+  /* optional key mask (B, Nb*G + R) uint8, 1 = attend, 0 = masked; NULL = none */
+  const uint8_t* mask;
+  int64_t mask_stride_b;
+  /* output (B, N, hd) of out_dtype; optional natural-log log-sum-exp (B, N) fp32 */
+  void* out;
+  int64_t out_stride_b, out_stride_h;
+  float* lse;
+  /* caller-owned scratch of at least pq_decode_workspace_bytes(...) bytes, 256-byte aligned */
+  void* workspace;
+  size_t workspace_bytes;
+  int B, N, Nk, Nb, G, R, hd;
+  int rbits, tbits;
+  int qk_dtype, v_dtype, out_dtype;
+  float sm_scale;  /* logits multiplier; 0 means 1/sqrt(hd) as at modeling_llama_polar.py:80 */
+  int num_ctas;    /* 0 = choose from the device's SM count */
+} pq_decode_params;
+
+int pq_decode_attention(const pq_decode_params* p, void* stream);
+/* sizeof(pq_decode_params) as this library was compiled, for bindings to verify their mirror of the struct */
+size_t pq_decode_params_size(void);
+
+/* Scratch bytes pq_decode_attention needs for this problem on the current device. */
+size_t pq_decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int num_ctas);
+
+/*
+ * Merge P partial attention results over disjoint key ranges (sequence split
+ * across chunks or GPUs).  outs (P, rows, hd) fp32 softmax-normalised, lses
+ * (P, rows) fp32 natural log; out (rows, hd) of out_dtype, lse_out (rows) fp32 or
+ * NULL.  No counterpart in the reference, which never splits the sequence.
+ */
+int pq_merge_lse(const float* outs, const float* lses, int P, int64_t rows, int hd,
+                 void* out, int out_dtype, float* lse_out, void* stream);
+
+/*
+ * Host-buffer forms: the same operations for callers whose tensors live in host
+ * memory.  Inputs are copied to the device staging area the caller provides,
+ * the kernels run, results are copied back; everything is enqueued on `stream`
+ * (the caller synchronises).  Host buffers should be pinned for the copies to
+ * overlap.  staging must hold pq_*_host_staging_bytes bytes.
+ */
+int pq_quantize_host(const void* keys_host, int B, int Nk, int L, int hd, int G, int rbits, int tbits,
+                     int dtype, unsigned flags, uint8_t* codes_host, void* rscale_host, void* rmn_host,
+                     void* tscale_host, void* tmn_host, void* staging, size_t staging_bytes, void* stream);
+size_t pq_quantize_host_staging_bytes(int B, int Nk, int L, int hd, int G, int dtype);
+
+/* p holds HOST pointers for q, codes, scales, k_res, v, mask, out, lse (contiguous
+   tensors; the stride fields are ignored and recomputed); workspace fields are
+   ignored, scratch is carved from staging. */
+int pq_decode_attention_host(const pq_decode_params* p, void* staging, size_t staging_bytes, void* stream);
+size_t pq_decode_host_staging_bytes(int B, int N, int Nk, int Nb, int G, int R, int hd,
+                                    int qk_dtype, int v_dtype, int out_dtype, int has_mask);
+
+const char* pq_strerror(int status);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread */
+int pq_last_cuda_error(void);
+/* library ABI version, bumped when a signature or struct layout changes */
+int pq_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLARQUANT_B200_H */

@@ -1,0 +1,328 @@
+"""CPU oracle for the polar key-cache hot path.  TEST INFRASTRUCTURE ONLY.
+
+Nothing in the shipped package imports this module.  Only the tests, the smoke
+check and the CPU-baseline legs of the benchmark call it, and only as the
+checker (or as the timed CPU arm), never as a fallback for the CUDA kernels.
+
+It restates, in plain torch/numpy on whatever device the inputs live on, the
+algorithm of the reference project (ericshwu/PolarQuant):
+
+* ``quantize_ops``      - the op sequence of ``quantize_and_pack_nbit``
+                          (models/modeling_llama_polar.py:135-157, same body at
+                          models/modeling_qwen_polar.py:134-156).
+* ``quantize_chain``    - the same quantizer written as an explicit chain of
+                          "fp32 operation, then round to the key dtype" steps,
+                          the form the CUDA kernel implements.  The constant
+                          added to negative angles is a parameter because torch
+                          rounds the Python scalar 2*pi to the tensor dtype on
+                          CPU and keeps it in fp32 on CUDA.
+* ``dequantize``        - models/kernel4group.py:151-153, evaluated in fp32 on
+                          the stored scale values (what the reference Triton
+                          kernel does at models/kernel4group.py:67,73).
+* ``qk_logits_lut``     - the lookup-table form of the reference kernel
+                          ``_kernel`` (models/kernel4group.py:37-80).
+* ``qk_logits``         - dequantise-then-matmul, models/kernel4group.py:151-155.
+* ``decode_attention``  - the decode branch of the patched attention forward
+                          (models/modeling_llama_polar.py:77-99, Qwen copy at
+                          models/modeling_qwen_polar.py:76-98) composed with the
+                          fp32 logits above.
+* ``merge_lse``         - log-sum-exp merge of partial attention results; it has
+                          no counterpart in the reference (the reference never
+                          splits the sequence) and is defined by softmax algebra.
+
+Parity pin: the reference ships no golden vectors or tests for this path.  The
+functions here are pinned against the reference's own code executed on CPU (its
+quantizer method, its Triton kernel under the Triton interpreter, and its
+unmodified attention forward); the outputs of those runs are the fixtures under
+tests/golden/, produced by tests/golden/make_golden.py.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+TWO_PI = 2.0 * math.pi
+
+
+def _rn(x: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
+    """Round an fp32 tensor to ``dt`` (nearest even) and return it as fp32."""
+    return x.to(dt).to(torch.float32)
+
+
+def _sqrt_ieee(x: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 square root.  torch.sqrt on CPU goes through a vector
+    math library that is not always correctly rounded; numpy's and CUDA's are."""
+    if x.is_cuda:
+        return torch.sqrt(x)
+    return torch.from_numpy(np.sqrt(x.contiguous().numpy()))
+
+
+# ----------------------------------------------------------------------------
+# quantizer
+# ----------------------------------------------------------------------------
+def quantize_ops(key_states: torch.Tensor, rbits: int = 4, tbits: int = 4, group_size: int = 128):
+    """Polar quantizer as the reference's sequence of tensor ops in the key dtype.
+
+    Follows models/modeling_llama_polar.py:137-157 step for step: the
+    (2, head_dim/2) view pairs channel d with channel d+head_dim/2 (:141), the
+    angle is atan2 wrapped into [0, 2*pi) (:143-144), angle and radius are
+    min/max quantised over each group of ``group_size`` tokens (:146-153) and
+    packed as ``(rho << tbits) + theta`` in one byte per pair (:155).
+
+    Runs on CPU or CUDA; on a given device it executes the same ATen kernels the
+    reference would, so it is the bit-exact yardstick for that device.
+    """
+    bsz, heads, length, hd = key_states.shape
+    if hd % 2 or length % group_size or rbits + tbits > 8:
+        raise AssertionError("head_dim must be even, length a multiple of the group, rbits+tbits <= 8")
+    half, grp = hd // 2, group_size
+    pairs = key_states.view(bsz, heads, length // grp, grp, 2, half)
+    first, second = pairs[..., 0, :], pairs[..., 1, :]
+
+    angle = torch.atan2(second, first)
+    angle = torch.where(angle < 0, angle + TWO_PI, angle)
+    a_hi = angle.max(dim=-2, keepdim=True).values
+    a_lo = angle.min(dim=-2, keepdim=True).values
+    a_step = (a_hi - a_lo) / (2 ** tbits)
+    a_code = torch.clamp(torch.floor((angle - a_lo) / a_step).to(torch.uint8), 0, 2 ** tbits - 1)
+
+    radius = torch.norm(pairs, p=2, dim=-2)
+    r_hi = radius.max(dim=-2, keepdim=True).values
+    r_lo = radius.min(dim=-2, keepdim=True).values
+    r_step = (r_hi - r_lo) / (2 ** rbits)
+    r_code = torch.clamp(torch.floor((radius - r_lo) / r_step).to(torch.uint8), 0, 2 ** rbits - 1)
+
+    codes = (r_code << tbits) + a_code
+    return codes, r_step, r_lo, a_step, a_lo
+
+
+def quantize_chain(key_states: torch.Tensor, rbits: int = 4, tbits: int = 4, group_size: int = 128,
+                   wrap_constant: str = "dtype", atan2_fn=None):
+    """The quantizer as explicit fp32 arithmetic with a rounding after every op.
+
+    Every reference op (models/modeling_llama_polar.py:143-155) computes in fp32
+    and rounds its result to the key dtype; this function spells that out, which
+    is the arithmetic the CUDA kernel performs per (token, pair):
+
+      phi   = RN(atan2f(y, x));  phi < 0 -> RN(phi + C)                    (:143-144)
+      tstep = RN(RN(max phi - min phi) / 2^tbits)                           (:146-147)
+      theta = min(u8(floor(RN(RN(phi - min phi) / tstep))), 2^tbits - 1)   (:148)
+      r     = RN(sqrtf(x*x + y*y)),  same min/max/step/floor/clamp          (:150-153)
+      code  = (rho << tbits) + theta                                        (:155)
+
+    ``wrap_constant`` selects C: "dtype" rounds 2*pi to the key dtype first
+    (torch on CPU), "fp32" keeps float32(2*pi) (torch on CUDA).
+    ``atan2_fn(y, x)`` supplies the fp32 arctangent (default ``torch.atan2``);
+    different math libraries differ in the last fp32 bit, which can move a
+    rounded angle across a representable value.
+    """
+    dt = key_states.dtype
+    bsz, heads, length, hd = key_states.shape
+    if hd % 2 or length % group_size or rbits + tbits > 8:
+        raise AssertionError("head_dim must be even, length a multiple of the group, rbits+tbits <= 8")
+    half, grp = hd // 2, group_size
+    k32 = key_states.to(torch.float32).view(bsz, heads, length // grp, grp, 2, half)
+    x, y = k32[..., 0, :], k32[..., 1, :]
+    atan2_fn = atan2_fn or torch.atan2
+
+    if wrap_constant == "dtype":
+        wrap = float(torch.tensor(TWO_PI, dtype=torch.float64).to(dt).to(torch.float32))
+    elif wrap_constant == "fp32":
+        wrap = float(torch.tensor(TWO_PI, dtype=torch.float64).to(torch.float32))
+    else:
+        raise ValueError("wrap_constant must be 'dtype' or 'fp32'")
+
+    phi = _rn(atan2_fn(y, x), dt)
+    phi = torch.where(phi < 0, _rn(phi + torch.tensor(wrap, dtype=torch.float32), dt), phi)
+
+    def minmax_code(val: torch.Tensor, bits: int):
+        hi = val.amax(dim=-2, keepdim=True)
+        lo = val.amin(dim=-2, keepdim=True)
+        step = _rn(_rn(hi - lo, dt) / float(2 ** bits), dt)
+        quot = torch.floor(_rn(_rn(val - lo, dt) / step, dt))
+        # float -> int64 -> uint8 like ATen's cast: NaN (0/0 in a constant group) gives 0
+        as_int = torch.nan_to_num(quot, nan=0.0, posinf=255.0, neginf=0.0).to(torch.int64)
+        code = torch.clamp(as_int & 0xFF, 0, 2 ** bits - 1).to(torch.uint8)
+        return code, step, lo
+
+    theta, tstep, tlo = minmax_code(phi, tbits)
+    radius = _rn(_sqrt_ieee(x * x + y * y), dt)
+    rho, rstep, rlo = minmax_code(radius, rbits)
+    codes = ((rho.to(torch.int32) << tbits) + theta.to(torch.int32)).to(torch.uint8)
+    return codes, rstep.to(dt), rlo.to(dt), tstep.to(dt), tlo.to(dt)
+
+
+# ----------------------------------------------------------------------------
+# dequantise / QK logits
+# ----------------------------------------------------------------------------
+def dequantize(codes, rscale, rmn, tscale, tmn, rbits: int = 4, tbits: int = 4) -> torch.Tensor:
+    """Reconstructed keys (B, Nk, Nb*G, head_dim) in fp32.
+
+    models/kernel4group.py:151-153: angle and radius are the bin centres
+    ``code * step + step / 2 + min``; the key is ``[r cos(phi) | r sin(phi)]``
+    with the cosines in channels 0..63 and the sines in channels 64..127.  The
+    scales are upcast to fp32 before any arithmetic, as the reference kernel
+    does (models/kernel4group.py:67,73).
+    """
+    bsz, kvh, nb, grp, half = codes.shape
+    c = codes.to(torch.int32)
+    theta = (c & ((1 << tbits) - 1)).to(torch.float32)
+    rho = (c >> tbits).to(torch.float32)
+    ts, tm = tscale.to(torch.float32), tmn.to(torch.float32)
+    rs, rm = rscale.to(torch.float32), rmn.to(torch.float32)
+    phi = ts * (theta + 0.5) + tm
+    rad = rs * (rho + 0.5) + rm
+    keys = torch.stack([rad * torch.cos(phi), rad * torch.sin(phi)], dim=-2)
+    return keys.reshape(bsz, kvh, nb * grp, 2 * half)
+
+
+def _expand_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
+    """Query head i reads kv head i // n_rep (HF ``repeat_kv`` as used at
+    models/modeling_llama_polar.py:79,99)."""
+    if n_rep == 1:
+        return x
+    b, h, l, d = x.shape
+    return x[:, :, None].expand(b, h, n_rep, l, d).reshape(b, h * n_rep, l, d)
+
+
+def qk_logits(query, codes, rscale, rmn, tscale, tmn, rbits: int = 4, tbits: int = 4) -> torch.Tensor:
+    """Un-scaled fp32 logits (B, N, 1, Nb*G): dequantise, then matmul
+    (models/kernel4group.py:151-155)."""
+    n_rep = query.shape[1] // codes.shape[1]
+    keys = _expand_kv(dequantize(codes, rscale, rmn, tscale, tmn, rbits, tbits), n_rep)
+    return torch.matmul(query.to(torch.float32), keys.transpose(2, 3))
+
+
+def qk_logits_lut(query, codes, rscale, rmn, tscale, tmn, rbits: int = 4, tbits: int = 4) -> torch.Tensor:
+    """The same logits in the lookup-table form of the reference Triton kernel.
+
+    models/kernel4group.py:67-77: per (batch, kv head, group, pair) build the
+    table ``T[h, d, a] = q_x[h, d] cos(phi_a) + q_y[h, d] sin(phi_a)`` over the
+    angle levels a, gather it by the angle code, multiply by the radius level
+    gathered by the radius code, and sum over the pairs d.  Query pair layout
+    x = q[d], y = q[d + 64] (:64); query head kvh * (N / Nk) + h belongs to kv
+    head kvh (:40,50).
+    """
+    bsz, kvh, nb, grp, half = codes.shape
+    nq = query.shape[1]
+    n_rep = nq // kvh
+    q = query.to(torch.float32).reshape(bsz, kvh, n_rep, 2, half)
+    qx, qy = q[..., 0, :], q[..., 1, :]                                   # (B, Nk, rep, D)
+    levels_t = torch.arange(1 << tbits, dtype=torch.float32, device=codes.device) + 0.5
+    levels_r = torch.arange(1 << rbits, dtype=torch.float32, device=codes.device) + 0.5
+    ts, tm = tscale.to(torch.float32)[..., 0, :], tmn.to(torch.float32)[..., 0, :]   # (B, Nk, Nb, D)
+    rs, rm = rscale.to(torch.float32)[..., 0, :], rmn.to(torch.float32)[..., 0, :]
+    phi = ts[..., None] * levels_t + tm[..., None]                        # (B, Nk, Nb, D, A)
+    table = (qx[:, :, :, None, :, None] * torch.cos(phi)[:, :, None]
+             + qy[:, :, :, None, :, None] * torch.sin(phi)[:, :, None])   # (B, Nk, rep, Nb, D, A)
+    radii = rs[..., None] * levels_r + rm[..., None]                      # (B, Nk, Nb, D, R)
+    c = codes.to(torch.int64)
+    a_idx = (c & ((1 << tbits) - 1)).transpose(-1, -2)                    # (B, Nk, Nb, D, G)
+    r_idx = (c >> tbits).transpose(-1, -2)
+    picked = torch.gather(table, -1, a_idx[:, :, None].expand(bsz, kvh, n_rep, nb, half, grp))
+    rad = torch.gather(radii, -1, r_idx)                                  # (B, Nk, Nb, D, G)
+    out = (picked * rad[:, :, None]).sum(dim=-2)                          # (B, Nk, rep, Nb, G)
+    return out.reshape(bsz, nq, 1, nb * grp)
+
+
+# ----------------------------------------------------------------------------
+# fused decode attention (composition of the reference's decode branch)
+# ----------------------------------------------------------------------------
+def decode_attention(query, key_residual, codes, rscale, rmn, tscale, tmn, values,
+                     attention_mask=None, rbits: int = 4, tbits: int = 4, sm_scale: float | None = None,
+                     faithful_rounding: bool = True, return_lse: bool = False):
+    """One decode step of polar attention, as the reference's eager ops compute it.
+
+    models/modeling_llama_polar.py:77-99 with the quantised-part logits from
+    ``qk_logits`` (fp32):
+
+      w_res = fp32(RN_q(q @ K_res^T))          residual keys, incl. the new token  (:79)
+      w     = [w_quant | w_res] / sqrt(head_dim)                                   (:80)
+      w    += (1 - mask) * finfo(fp32).min     only when a mask is given           (:94-95)
+      p     = RN_q(softmax_fp32(w))                                                (:97)
+      out   = RN_q(p @ V)                      V incl. the new token               (:99)
+
+    ``query`` (B, N, 1, hd); ``key_residual`` (B, Nk, R, hd) or None; ``codes``
+    (B, Nk, Nb, G, hd/2) or None; ``values`` (B, Nk, Nb*G + R, hd).  With
+    ``faithful_rounding=False`` the three RN_q roundings are skipped (all-fp32
+    arithmetic), which is the noise-free target a fused kernel approximates.
+    Returns (B, N, 1, hd) in the query dtype (fp32 when not faithful), plus the
+    natural-log log-sum-exp (B, N) when ``return_lse``.
+    """
+    qdt = query.dtype
+    bsz, nq, _, hd = query.shape
+    kvh = values.shape[1]
+    n_rep = nq // kvh
+    scale = (1.0 / math.sqrt(hd)) if sm_scale is None else sm_scale
+    parts = []
+    if codes is not None and codes.shape[2] > 0:
+        parts.append(qk_logits(query, codes, rscale, rmn, tscale, tmn, rbits, tbits))
+    if key_residual is not None and key_residual.shape[2] > 0:
+        kr = _expand_kv(key_residual, n_rep)
+        if faithful_rounding:
+            w_res = torch.matmul(query, kr.to(qdt).transpose(2, 3)).to(torch.float32)
+        else:
+            w_res = torch.matmul(query.to(torch.float32), kr.to(torch.float32).transpose(2, 3))
+        parts.append(w_res)
+    w = torch.cat(parts, dim=-1)
+    # the reference divides by sqrt(head_dim); a caller-supplied scale multiplies
+    w = w / math.sqrt(hd) if sm_scale is None else w * scale
+    if attention_mask is not None:
+        m = attention_mask.to(torch.float32)
+        w = w + (1.0 - m[:, None, None, :]) * torch.finfo(torch.float32).min
+    lse = torch.logsumexp(w, dim=-1)[:, :, 0]
+    p = torch.softmax(w, dim=-1)
+    vv = _expand_kv(values, n_rep)
+    if faithful_rounding:
+        out = torch.matmul(p.to(qdt), vv.to(qdt))
+    else:
+        out = torch.matmul(p, vv.to(torch.float32))
+    return (out, lse) if return_lse else out
+
+
+def merge_lse(outs: torch.Tensor, lses: torch.Tensor):
+    """Merge partial attention results computed over disjoint key ranges.
+
+    ``outs`` (P, ..., hd) are softmax-normalised partial outputs, ``lses``
+    (P, ...) their natural-log log-sum-exps.  With L = logsumexp_p(lse_p) the
+    result is ``sum_p exp(lse_p - L) * out_p`` and its log-sum-exp is L.
+    """
+    lses = lses.to(torch.float32)
+    total = torch.logsumexp(lses, dim=0)
+    w = torch.exp(lses - total[None])
+    w = torch.where(torch.isfinite(w), w, torch.zeros_like(w))
+    return (w[..., None] * outs.to(torch.float32)).sum(dim=0), total
+
+
+# ----------------------------------------------------------------------------
+# seeded synthetic inputs with the shapes and value distributions of the
+# benchmark configurations
+# ----------------------------------------------------------------------------
+def synth_keys(bsz, kvh, length, hd, dtype, seed, kind="loguniform", device="cpu"):
+    """Seeded synthetic keys.  kind="loguniform": randn times a per-(kv head,
+    channel) scale drawn log-uniformly from [0.5, 8].  kind="outlier": randn with
+    four seeded pair indices per head whose two channels are scaled by 10."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    k = torch.randn(bsz, kvh, length, hd, generator=g, dtype=torch.float32)
+    if kind == "loguniform":
+        s = torch.exp(torch.empty(kvh, hd).uniform_(math.log(0.5), math.log(8.0), generator=g))
+        k = k * s[None, :, None, :]
+    elif kind == "outlier":
+        half = hd // 2
+        for h in range(kvh):
+            idx = torch.randperm(half, generator=g)[:4]
+            k[:, h, :, idx] *= 10.0
+            k[:, h, :, idx + half] *= 10.0
+    elif kind != "randn":
+        raise ValueError(kind)
+    return k.to(dtype).to(device)
+
+
+def as_numpy(t: torch.Tensor) -> np.ndarray:
+    """Bit-preserving numpy view: bf16 tensors come back as uint16 words."""
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()

@@ -1,0 +1,773 @@
+// Decode-time kernels over the packed polar key cache (sm_100a):
+//   * qk_decode_kernel        - un-scaled fp32 logits q.K^T over the codes
+//                               (the reference's Triton kernel, models/kernel4group.py:14-80)
+//   * decode_attention_kernel - fused: logits over codes + logits over the
+//                               full-precision residual keys + scale + mask +
+//                               online softmax + P.V, one partial per warp segment
+//                               (models/modeling_llama_polar.py:66-99)
+//   * merge_partials_kernel / merge_lse_kernel - log-sum-exp merges.
+//
+// Work decomposition.  A "step" is 16 consecutive tokens of one (batch, kv head)
+// unit.  All steps of all units form one flat sequence that is cut into equal
+// contiguous ranges, one per warp; warps never synchronise with each other.
+// A warp whose range crosses a unit boundary emits one partial (m, l, O) per
+// unit it touched; the merge kernel finds a unit's partials by the same
+// arithmetic, so no counters, atomics or zero-initialised scratch are needed.
+//
+// Per step (one warp, 16 tokens, all query heads of the kv head):
+//   1. 128-bit loads of the 16 x 64 code bytes: lane (g, t) [g = lane / 4,
+//      t = lane % 4] gets the codes of pairs 16t..16t+15 of tokens g and g+8.
+//   2. Dequantise in registers: the angle code indexes a per-group table of
+//      (cos, sin) half2 entries in shared memory (64 pairs x 2^tbits levels,
+//      rebuilt per token group because the angle step and offset are per
+//      (group, pair), models/kernel4group.py:67); the radius code becomes a
+//      half directly through an exponent trick and one HFMA2.  The products
+//      land in the A-fragment layout of mma.m16n8k16 (tokens x pair-channels).
+//   3. S^T[token, head] = K^[token, :] . q[head, :] on the tensor cores, the
+//      query heads of the kv head (<= 8) as the N dimension.  The lookup-table
+//      form of the reference (one table per query head) needs one shared-memory
+//      gather per (token, pair, head); the dequantise-then-MMA form needs one
+//      per (token, pair) whatever the GQA group size.
+//   4. Online softmax in the log2 domain on the accumulator fragment, warp
+//      shuffles across the eight token rows.
+//   5. P^T is transposed in registers (movmatrix) into the B operand and
+//      O^T[channel, head] += V^T[channel, token] . P^T[token, head]; V goes from
+//      global memory straight into A fragments (128-bit loads + byte permutes),
+//      never through shared memory, which is kept for the table gathers.
+//
+// tcgen05/TMEM is not used: one decode query per head gives M = 16 tokens x
+// N <= 8 heads tiles, far below the 64-row minimum of tcgen05.mma, and the path
+// is bound by HBM and the shared-memory gathers, not by tensor throughput.
+#include "pq_common.cuh"
+
+namespace pq {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
+constexpr int kStep = 16;          // tokens per step
+constexpr int kHeadTile = 8;       // query heads per unit (N of the MMA)
+constexpr int kPartialFloats = kHeadDim * kHeadTile;   // O^T partial, [channel][head]
+
+struct DecodeArgs {
+  const void* q; int64_t q_sb, q_sh;
+  const uint8_t* codes; int64_t c_sb, c_sh;
+  const void *rscale, *rmn, *tscale, *tmn; int64_t s_sb, s_sh;
+  const void* kres; int64_t kr_sb, kr_sh, kr_st;
+  const void* v; int64_t v_sb, v_sh, v_st;
+  const uint8_t* mask; int64_t m_sb;
+  float* part_o;        // [slot][128][8]
+  float2* part_ml;      // [slot][8]  (running max in log2 units, running sum)
+  float* logits;        // qk-only output (B, N, Nb*G)
+  int B, N, Nk, Nb, G, R;
+  int nrep, head_tiles;
+  int spg;              // steps per token group = G / 16
+  int nq, nr, slots_per_unit;   // quantised steps, residual steps, nq + 2*nr
+  long long total_slots; int total_warps; int max_seg;
+  float scale_log2;     // sm_scale * log2(e)
+};
+
+__device__ __forceinline__ long long range_lo(long long w, long long total, int nwarps) {
+  return (w * total) / nwarps;
+}
+
+// ---- shared-memory table of (cos, sin) bin centres for one token group ----------
+// word index = (row_pos << TBITS) + level, row_pos = 4 * (d % 16) + d / 16, so the
+// four rows a warp gathers from in one instruction (pairs 16t + m, t = 0..3) are
+// adjacent and the lane-dependent part of the byte offset fits in the low byte.
+template <int TBITS, int SDT>
+__device__ __forceinline__ void build_angle_table(uint32_t* tbl, float* scr, const void* tscale_row,
+                                                  const void* tmn_row, int lane) {
+  constexpr int A = 1 << TBITS;
+  __syncwarp();
+  if constexpr (SDT == PQ_F32) {
+    const float* ts = static_cast<const float*>(tscale_row);
+    const float* tm = static_cast<const float*>(tmn_row);
+    scr[lane] = ts[lane]; scr[lane + 32] = ts[lane + 32];
+    scr[64 + lane] = tm[lane]; scr[96 + lane] = tm[lane + 32];
+  } else {
+    const uint32_t* ts = static_cast<const uint32_t*>(tscale_row);
+    const uint32_t* tm = static_cast<const uint32_t*>(tmn_row);
+    float2 a = unpack2<SDT>(ts[lane]), b = unpack2<SDT>(tm[lane]);
+    scr[2 * lane] = a.x; scr[2 * lane + 1] = a.y;
+    scr[64 + 2 * lane] = b.x; scr[64 + 2 * lane + 1] = b.y;
+  }
+  __syncwarp();
+#pragma unroll 4
+  for (int it = 0; it < 2 * A; ++it) {
+    const int idx = it * 32 + lane;
+    const int pos = idx >> TBITS, lvl = idx & (A - 1);
+    const int d = 16 * (pos & 3) + (pos >> 2);
+    float phi = fmaf(scr[d], static_cast<float>(lvl) + 0.5f, scr[64 + d]);
+    // reduce to [-pi, pi] before the hardware approximations
+    float n = rintf(phi * 0.15915494309189535f);
+    phi = fmaf(n, -6.28318548202514648f, phi);
+    phi = fmaf(n, 1.7484555e-7f, phi);
+    tbl[idx] = pack2<PQ_F16>(__cosf(phi), __sinf(phi));
+  }
+  __syncwarp();
+}
+
+template <int SDT> __device__ __forceinline__ void load16f(const void* p, float (&v)[16]) {
+  if constexpr (SDT == PQ_F32) {
+    const float4* f = static_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 x = f[i];
+      v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
+    }
+  } else {
+    const uint4* u = static_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 x = u[i];
+      float2 a = unpack2<SDT>(x.x), b = unpack2<SDT>(x.y), c = unpack2<SDT>(x.z), d = unpack2<SDT>(x.w);
+      v[8 * i] = a.x; v[8 * i + 1] = a.y; v[8 * i + 2] = b.x; v[8 * i + 3] = b.y;
+      v[8 * i + 4] = c.x; v[8 * i + 5] = c.y; v[8 * i + 6] = d.x; v[8 * i + 7] = d.y;
+    }
+  }
+}
+
+// Radius constants of this lane's 16 pairs for one group.  The radius code rho is
+// turned into the half value 2^RBITS + rho by OR-ing it into the mantissa of
+// 2^RBITS, so r = rscale * (rho + 0.5) + rmn = rscale * (2^RBITS + rho) + c with
+// c = rmn + (0.5 - 2^RBITS) * rscale.  rs2/rc2[w][e] hold the constants of pairs
+// (4w + e, 4w + e + 2), the two code bytes one HFMA2 handles.
+template <int RBITS, int SDT>
+__device__ __forceinline__ void load_radius_consts(const void* rscale_row, const void* rmn_row, int t,
+                                                   uint32_t (&rs2)[4][2], uint32_t (&rc2)[4][2]) {
+  float rs[16], rm[16];
+  load16f<SDT>(static_cast<const char*>(rscale_row) + 16 * t * (SDT == PQ_F32 ? 4 : 2), rs);
+  load16f<SDT>(static_cast<const char*>(rmn_row) + 16 * t * (SDT == PQ_F32 ? 4 : 2), rm);
+  const float k = 0.5f - static_cast<float>(1 << RBITS);
+#pragma unroll
+  for (int w = 0; w < 4; ++w)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int a = 4 * w + e, b = a + 2;
+      rs2[w][e] = pack2<PQ_F16>(rs[a], rs[b]);
+      rc2[w][e] = pack2<PQ_F16>(fmaf(k, rs[a], rm[a]), fmaf(k, rs[b], rm[b]));
+    }
+}
+
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+  __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b),
+                      *reinterpret_cast<__half2*>(&c));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t hmul2_lo(uint32_t cs, uint32_t rr) {   // cs * (rr.lo, rr.lo)
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&cs), __low2half2(*reinterpret_cast<__half2*>(&rr)));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t hmul2_hi(uint32_t cs, uint32_t rr) {   // cs * (rr.hi, rr.hi)
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&cs), __high2half2(*reinterpret_cast<__half2*>(&rr)));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// S^T (16 tokens x 8 heads) += K^ (16 tokens x 128 pair-channels) . q^T for one step.
+// cg / ch: this lane's 16 code bytes of tokens g and g + 8.
+template <int RBITS, int TBITS>
+__device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, const uint4& ch4,
+                                              const char* tbl, uint32_t lane_off,
+                                              const uint32_t (&rs2)[4][2], const uint32_t (&rc2)[4][2],
+                                              const uint32_t (&qb)[8][2]) {
+  constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
+  constexpr int MSH = 10 - RBITS;                                // mantissa shift of rho
+  constexpr uint32_t RM = (((1u << RBITS) - 1u) << MSH) * 0x00010001u;
+  constexpr uint32_t MAGIC = (static_cast<uint32_t>(15 + RBITS) << 10) * 0x00010001u;
+  const uint32_t cg[4] = {cg4.x, cg4.y, cg4.z, cg4.w};
+  const uint32_t ch[4] = {ch4.x, ch4.y, ch4.z, ch4.w};
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t og = ((cg[w] << 2) & TM4) | lane_off;
+    const uint32_t oh = ((ch[w] << 2) & TM4) | lane_off;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int sr = 8 * e + TBITS + RBITS - 10;                  // compile-time after unrolling
+      const uint32_t hg = ((sr >= 0 ? cg[w] >> sr : cg[w] << -sr) & RM) | MAGIC;
+      const uint32_t hh = ((sr >= 0 ? ch[w] >> sr : ch[w] << -sr) & RM) | MAGIC;
+      const uint32_t rg = hfma2_u(hg, rs2[w][e], rc2[w][e]);
+      const uint32_t rh = hfma2_u(hh, rs2[w][e], rc2[w][e]);
+      const char* rowA = tbl + ((4 * w + e) << (TBITS + 4));
+      const char* rowB = tbl + ((4 * w + e + 2) << (TBITS + 4));
+      const uint32_t csAg = *reinterpret_cast<const uint32_t*>(rowA + __byte_perm(og, 0, 0x4440 | e));
+      const uint32_t csBg = *reinterpret_cast<const uint32_t*>(rowB + __byte_perm(og, 0, 0x4440 | (e + 2)));
+      const uint32_t csAh = *reinterpret_cast<const uint32_t*>(rowA + __byte_perm(oh, 0, 0x4440 | e));
+      const uint32_t csBh = *reinterpret_cast<const uint32_t*>(rowB + __byte_perm(oh, 0, 0x4440 | (e + 2)));
+      mma_16816_f16(S, hmul2_lo(csAg, rg), hmul2_lo(csAh, rh), hmul2_hi(csBg, rg), hmul2_hi(csBh, rh),
+                    qb[2 * w + e][0], qb[2 * w + e][1]);
+    }
+  }
+}
+
+// Query B fragments for the quantised path: k-step s = 2w + e pairs lanes' slots with
+// pairs pA = 16t + 4w + e and pB = pA + 2; a register holds (q[p], q[p + 64]) as half2.
+template <int QDT>
+__device__ __forceinline__ void load_q_quant(const void* q_head, bool valid, int t, uint32_t (&qb)[8][2]) {
+#pragma unroll
+  for (int s = 0; s < 8; ++s)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int p = 16 * t + 4 * (s >> 1) + (s & 1) + 2 * j;
+      float x = 0.f, y = 0.f;
+      if (valid) {
+        if constexpr (QDT == PQ_F32) {
+          x = static_cast<const float*>(q_head)[p]; y = static_cast<const float*>(q_head)[p + kPairs];
+        } else if constexpr (QDT == PQ_F16) {
+          x = __half2float(static_cast<const __half*>(q_head)[p]);
+          y = __half2float(static_cast<const __half*>(q_head)[p + kPairs]);
+        } else {
+          x = __bfloat162float(static_cast<const __nv_bfloat16*>(q_head)[p]);
+          y = __bfloat162float(static_cast<const __nv_bfloat16*>(q_head)[p + kPairs]);
+        }
+      }
+      qb[s][j] = pack2<PQ_F16>(x, y);
+    }
+}
+
+// eight consecutive elements at p as four packed 16-bit pairs; fp32 is rounded to fp16
+template <int DT> __device__ __forceinline__ uint4 load8_as16(const void* p, bool valid) {
+  uint4 r = make_uint4(0, 0, 0, 0);
+  if (valid) {
+    if constexpr (DT == PQ_F32) {
+      const float4* f = static_cast<const float4*>(p);
+      float4 a = f[0], b = f[1];
+      r.x = pack2<PQ_F16>(a.x, a.y); r.y = pack2<PQ_F16>(a.z, a.w);
+      r.z = pack2<PQ_F16>(b.x, b.y); r.w = pack2<PQ_F16>(b.z, b.w);
+    } else {
+      r = ldg_stream(p);
+    }
+  }
+  return r;
+}
+
+// element size helper for byte arithmetic on typed-by-tag buffers
+__device__ __forceinline__ constexpr int esize(int dt) { return dt == PQ_F32 ? 4 : 2; }
+
+struct SoftmaxState { float m0, m1, l0, l1; };
+
+// Online-softmax update for one step.  S holds logits of tokens (g, g+8) x heads
+// (2t, 2t+1).  Returns the P^T B-fragment (b0, b1) in the value dtype and rescales O.
+template <int VDT>
+__device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bool ok_g, bool ok_h,
+                                             bool masked_g, bool masked_h, SoftmaxState& st,
+                                             float (&O)[8][4], uint32_t& b0, uint32_t& b1) {
+  constexpr float kMasked = -1.0e30f;   // finite stand-in for "+ finfo.min": an all-masked row stays uniform
+  float x0 = S[0] * scale_log2, x1 = S[1] * scale_log2, x2 = S[2] * scale_log2, x3 = S[3] * scale_log2;
+  if (masked_g) { x0 = kMasked; x1 = kMasked; }
+  if (masked_h) { x2 = kMasked; x3 = kMasked; }
+  if (!ok_g) { x0 = -INFINITY; x1 = -INFINITY; }
+  if (!ok_h) { x2 = -INFINITY; x3 = -INFINITY; }
+  float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+#pragma unroll
+  for (int o = 4; o <= 16; o <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+  }
+  const float n0 = fmaxf(st.m0, mx0), n1 = fmaxf(st.m1, mx1);
+  const bool grew = (n0 > st.m0) || (n1 > st.m1);
+  if (__any_sync(0xffffffffu, grew)) {
+    const float a0 = exp2_approx(st.m0 - n0), a1 = exp2_approx(st.m1 - n1);
+    st.l0 *= a0; st.l1 *= a1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { O[j][0] *= a0; O[j][1] *= a1; O[j][2] *= a0; O[j][3] *= a1; }
+    st.m0 = n0; st.m1 = n1;
+  }
+  const float p0 = exp2_approx(x0 - n0), p1 = exp2_approx(x1 - n1);
+  const float p2 = exp2_approx(x2 - n0), p3 = exp2_approx(x3 - n1);
+  st.l0 += p0 + p2; st.l1 += p1 + p3;
+  b0 = movmatrix_trans(pack2<VDT>(p0, p1));
+  b1 = movmatrix_trans(pack2<VDT>(p2, p3));
+}
+
+// O^T[channel, head] += V^T . P^T for m-tiles [J0, J0 + 4): V registers v[tok][reg] hold, for
+// tokens (2t, 2t+1, 2t+8, 2t+9), channels 8g + 2*reg (+1) of one 64-channel half.
+template <int VDT>
+__device__ __forceinline__ void pv_half(float (&O)[8][4], int J0, const uint4 (&v)[4], uint32_t b0, uint32_t b1) {
+  const uint32_t va[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+  const uint32_t vb[4] = {v[1].x, v[1].y, v[1].z, v[1].w};
+  const uint32_t vc[4] = {v[2].x, v[2].y, v[2].z, v[2].w};
+  const uint32_t vd[4] = {v[3].x, v[3].y, v[3].z, v[3].w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t a0 = __byte_perm(va[j], vb[j], 0x5410);   // channel 2j   of tokens (2t, 2t+1)
+    const uint32_t a1 = __byte_perm(va[j], vb[j], 0x7632);   // channel 2j+1
+    const uint32_t a2 = __byte_perm(vc[j], vd[j], 0x5410);   // tokens (2t+8, 2t+9)
+    const uint32_t a3 = __byte_perm(vc[j], vd[j], 0x7632);
+    mma_16816<VDT>(O[J0 + j], a0, a1, a2, a3, b0, b1);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// fused decode attention
+// ---------------------------------------------------------------------------------
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
+__global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : 3)
+decode_kernel(const DecodeArgs a) {
+  constexpr int A = 1 << TBITS;
+  __shared__ __align__(16) uint32_t s_tbl[kWarps][kPairs * A];
+  __shared__ float s_scr[kWarps][128];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const long long gw = static_cast<long long>(blockIdx.x) * kWarps + warp;
+  long long lo = range_lo(gw, a.total_slots, a.total_warps);
+  const long long hi = range_lo(gw + 1, a.total_slots, a.total_warps);
+  if (lo >= hi) return;
+
+  const char* tbl = reinterpret_cast<const char*>(s_tbl[warp]);
+  const uint32_t lane_off = (static_cast<uint32_t>(t) << (TBITS + 2)) * 0x01010101u;
+  constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
+  constexpr int KRDT = QDT == PQ_BF16 ? PQ_BF16 : PQ_F16;   // MMA type of the residual-key product
+
+  long long unit = lo / a.slots_per_unit;
+  int pos = static_cast<int>(lo - unit * a.slots_per_unit);
+  int seg = 0;
+
+  while (lo < hi) {
+    const long long unit_end = (unit + 1) * a.slots_per_unit;
+    const long long seg_hi = hi < unit_end ? hi : unit_end;
+    const int pos_end = pos + static_cast<int>(seg_hi - lo);
+
+    const int ht = static_cast<int>(unit % a.head_tiles);
+    const long long bk = unit / a.head_tiles;
+    const int kvh = static_cast<int>(bk % a.Nk);
+    const int b = static_cast<int>(bk / a.Nk);
+    const int head0 = kvh * a.nrep + ht * kHeadTile;
+    const int nheads = min(kHeadTile, a.nrep - ht * kHeadTile);
+    const bool head_ok = g < nheads;
+    const char* q_head = static_cast<const char*>(a.q) + (b * a.q_sb + (head0 + g) * a.q_sh) * QES;
+
+    SoftmaxState st = {-INFINITY, -INFINITY, 0.f, 0.f};
+    float O[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { O[j][0] = O[j][1] = O[j][2] = O[j][3] = 0.f; }
+
+    const char* v_unit = static_cast<const char*>(a.v) + (b * a.v_sb + kvh * a.v_sh) * 2;
+    const int64_t v_row = a.v_st * 2;                       // bytes between tokens
+    const uint8_t* mask_row = a.mask ? a.mask + b * a.m_sb : nullptr;
+    const int Lq = a.Nb * a.G;
+
+    // ------------------------------ quantised steps ------------------------------
+    const int qs_end = pos_end < a.nq ? pos_end : a.nq;
+    if (pos < qs_end) {
+      uint32_t qb[8][2];
+      load_q_quant<QDT>(q_head, head_ok, t, qb);
+      const uint8_t* c_unit = a.codes + b * a.c_sb + kvh * a.c_sh;
+      const char* rs_unit = static_cast<const char*>(a.rscale) + (b * a.s_sb + kvh * a.s_sh) * QES;
+      const char* rm_unit = static_cast<const char*>(a.rmn) + (b * a.s_sb + kvh * a.s_sh) * QES;
+      const char* ts_unit = static_cast<const char*>(a.tscale) + (b * a.s_sb + kvh * a.s_sh) * QES;
+      const char* tm_unit = static_cast<const char*>(a.tmn) + (b * a.s_sb + kvh * a.s_sh) * QES;
+      uint32_t rs2[4][2], rc2[4][2];
+
+      // lane's code bytes: token row * 64 + 16 t
+      const uint8_t* c_lane = c_unit + static_cast<int64_t>(pos) * kStep * kPairs + g * kPairs + 16 * t;
+      uint4 cg = ldg_stream(c_lane), ch = ldg_stream(c_lane + 8 * kPairs);
+      uint4 v0[4], v1[4];
+      // lane's value bytes: tokens (2t, 2t+1, 2t+8, 2t+9), channels 8g.. and 64+8g..
+      const char* v_lane = nullptr;
+      if constexpr (!QK_ONLY) {
+        v_lane = v_unit + static_cast<int64_t>(pos) * kStep * v_row + (2 * t) * v_row + 16 * g;
+        v0[0] = ldg_stream(v_lane);               v1[0] = ldg_stream(v_lane + 128);
+        v0[1] = ldg_stream(v_lane + v_row);       v1[1] = ldg_stream(v_lane + v_row + 128);
+        v0[2] = ldg_stream(v_lane + 8 * v_row);   v1[2] = ldg_stream(v_lane + 8 * v_row + 128);
+        v0[3] = ldg_stream(v_lane + 9 * v_row);   v1[3] = ldg_stream(v_lane + 9 * v_row + 128);
+      }
+
+      int in_group = pos % a.spg;
+      int grp = pos / a.spg;
+      bool fresh = true;
+      for (int s = pos; s < qs_end; ++s) {
+        if (fresh || in_group == 0) {
+          const int64_t row = static_cast<int64_t>(grp) * kPairs * QES;
+          build_angle_table<TBITS, QDT>(s_tbl[warp], s_scr[warp], ts_unit + row, tm_unit + row, lane);
+          load_radius_consts<RBITS, QDT>(rs_unit + row, rm_unit + row, t, rs2, rc2);
+          fresh = false;
+        }
+        const bool more = s + 1 < qs_end;
+        uint4 ng = cg, nh = ch;
+        c_lane += kStep * kPairs;
+        if (more) { ng = ldg_stream(c_lane); nh = ldg_stream(c_lane + 8 * kPairs); }
+
+        float S[4] = {0.f, 0.f, 0.f, 0.f};
+        qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl, lane_off, rs2, rc2, qb);
+
+        if constexpr (QK_ONLY) {
+          // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
+          const int tok = s * kStep + g;
+          float* orow = a.logits + (static_cast<int64_t>(b) * a.N + head0 + 2 * t) * Lq + tok;
+          if (2 * t < nheads) { orow[0] = S[0]; orow[8] = S[2]; }
+          if (2 * t + 1 < nheads) { orow[Lq] = S[1]; orow[Lq + 8] = S[3]; }
+        } else {
+          bool mg = false, mh = false;
+          if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
+          uint32_t b0, b1;
+          softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
+          v_lane += kStep * v_row;
+          pv_half<VDT>(O, 0, v0, b0, b1);
+          if (more) {
+            v0[0] = ldg_stream(v_lane);             v0[1] = ldg_stream(v_lane + v_row);
+            v0[2] = ldg_stream(v_lane + 8 * v_row); v0[3] = ldg_stream(v_lane + 9 * v_row);
+          }
+          pv_half<VDT>(O, 4, v1, b0, b1);
+          if (more) {
+            v1[0] = ldg_stream(v_lane + 128);             v1[1] = ldg_stream(v_lane + v_row + 128);
+            v1[2] = ldg_stream(v_lane + 8 * v_row + 128); v1[3] = ldg_stream(v_lane + 9 * v_row + 128);
+          }
+        }
+        cg = ng; ch = nh;
+        if (++in_group == a.spg) { in_group = 0; ++grp; }
+      }
+    }
+
+    // ------------------------------ residual steps -------------------------------
+    if constexpr (!QK_ONLY) {
+      const int rv0 = pos > a.nq ? pos - a.nq : 0;          // virtual residual slots [rv0, rv1)
+      const int rv1 = pos_end - a.nq;
+      if (rv1 > rv0) {
+        // query fragments in natural channel order: chunk c = channels 8t + 32c .. +7
+        uint4 qr[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) qr[c] = load8_as16<QDT>(q_head + (8 * t + 32 * c) * QES, head_ok);
+        const char* kr_unit = static_cast<const char*>(a.kres) + (b * a.kr_sb + kvh * a.kr_sh) * QES;
+        const int64_t kr_row = a.kr_st * QES;
+        for (int rv = rv0 + (rv0 & 1); rv < rv1; rv += 2) {   // a step is owned by its even slot
+          const int r0 = (rv >> 1) * kStep;
+          const bool ok_g = r0 + g < a.R, ok_h = r0 + g + 8 < a.R;
+          uint4 kg[4], kh[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            kg[c] = load8_as16<QDT>(kr_unit + (r0 + g) * kr_row + (8 * t + 32 * c) * QES, ok_g);
+            kh[c] = load8_as16<QDT>(kr_unit + (r0 + g + 8) * kr_row + (8 * t + 32 * c) * QES, ok_h);
+          }
+          uint4 v0[4], v1[4];
+          {
+            const char* vl = v_unit + static_cast<int64_t>(Lq + r0 + 2 * t) * v_row + 16 * g;
+            const int tk[4] = {0, 1, 8, 9};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const bool ok = r0 + 2 * t + tk[i] < a.R;
+              v0[i] = ok ? ldg_stream(vl + tk[i] * v_row) : make_uint4(0, 0, 0, 0);
+              v1[i] = ok ? ldg_stream(vl + tk[i] * v_row + 128) : make_uint4(0, 0, 0, 0);
+            }
+          }
+          float S[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            mma_16816<KRDT>(S, kg[c].x, kh[c].x, kg[c].y, kh[c].y, qr[c].x, qr[c].y);
+            mma_16816<KRDT>(S, kg[c].z, kh[c].z, kg[c].w, kh[c].w, qr[c].z, qr[c].w);
+          }
+          bool mg = false, mh = false;
+          if (mask_row) {
+            mg = ok_g && mask_row[Lq + r0 + g] == 0;
+            mh = ok_h && mask_row[Lq + r0 + g + 8] == 0;
+          }
+          uint32_t b0, b1;
+          softmax_step<VDT>(S, a.scale_log2, ok_g, ok_h, mg, mh, st, O, b0, b1);
+          pv_half<VDT>(O, 0, v0, b0, b1);
+          pv_half<VDT>(O, 4, v1, b0, b1);
+        }
+      }
+
+      // ------------------------------ emit the partial -----------------------------
+#pragma unroll
+      for (int o = 4; o <= 16; o <<= 1) {
+        st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, o);
+        st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, o);
+      }
+      const long long slot = gw * a.max_seg + seg;
+      float* po = a.part_o + slot * kPartialFloats;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // m-tile j: row g is channel 64*(j/4) + 8g + 2*(j%4), row g+8 the next channel
+        const int chn = 64 * (j >> 2) + 8 * g + 2 * (j & 3);
+        *reinterpret_cast<float2*>(po + chn * kHeadTile + 2 * t) = make_float2(O[j][0], O[j][1]);
+        *reinterpret_cast<float2*>(po + (chn + 1) * kHeadTile + 2 * t) = make_float2(O[j][2], O[j][3]);
+      }
+      if (g == 0) {
+        a.part_ml[slot * kHeadTile + 2 * t] = make_float2(st.m0, st.l0);
+        a.part_ml[slot * kHeadTile + 2 * t + 1] = make_float2(st.m1, st.l1);
+      }
+    }
+
+    lo = seg_hi; ++unit; pos = 0; ++seg;
+  }
+}
+
+// warp that owns flat slot x: the largest w with range_lo(w) <= x
+__device__ __forceinline__ long long warp_of(long long x, long long total, int nwarps) {
+  return ((x + 1) * nwarps - 1) / total;
+}
+
+// One CTA per unit: combine the unit's partials, normalise, write out (and lse).
+template <int ODT>
+__global__ void __launch_bounds__(kHeadDim)
+merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, int64_t o_sh,
+                      float* __restrict__ lse) {
+  const long long unit = blockIdx.x;
+  const int ch = threadIdx.x;
+  const int ht = static_cast<int>(unit % a.head_tiles);
+  const long long bk = unit / a.head_tiles;
+  const int kvh = static_cast<int>(bk % a.Nk), b = static_cast<int>(bk / a.Nk);
+  const int head0 = kvh * a.nrep + ht * kHeadTile;
+  const int nheads = min(kHeadTile, a.nrep - ht * kHeadTile);
+
+  const long long first = unit * a.slots_per_unit, last = first + a.slots_per_unit - 1;
+  const long long w0 = warp_of(first, a.total_slots, a.total_warps);
+  const long long w1 = warp_of(last, a.total_slots, a.total_warps);
+
+  float M[kHeadTile], L[kHeadTile], acc[kHeadTile];
+#pragma unroll
+  for (int h = 0; h < kHeadTile; ++h) { M[h] = -INFINITY; L[h] = 0.f; acc[h] = 0.f; }
+
+  for (int pass = 0; pass < 2; ++pass) {
+    for (long long w = w0; w <= w1; ++w) {
+      const long long wlo = range_lo(w, a.total_slots, a.total_warps);
+      const long long whi = range_lo(w + 1, a.total_slots, a.total_warps);
+      if (wlo >= whi) continue;                              // warp without work
+      const int seg = static_cast<int>(unit - wlo / a.slots_per_unit);
+      const long long slot = w * a.max_seg + seg;
+      const float4* ml = reinterpret_cast<const float4*>(a.part_ml + slot * kHeadTile);
+      float2 mlv[kHeadTile];
+#pragma unroll
+      for (int i = 0; i < kHeadTile / 2; ++i) {
+        float4 x = ml[i];
+        mlv[2 * i] = make_float2(x.x, x.y); mlv[2 * i + 1] = make_float2(x.z, x.w);
+      }
+      if (pass == 0) {
+#pragma unroll
+        for (int h = 0; h < kHeadTile; ++h) M[h] = fmaxf(M[h], mlv[h].x);
+      } else {
+        const float4* po = reinterpret_cast<const float4*>(a.part_o + slot * kPartialFloats + ch * kHeadTile);
+        float4 o0 = po[0], o1 = po[1];
+        const float ov[kHeadTile] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+        for (int h = 0; h < kHeadTile; ++h) {
+          const float wgt = mlv[h].x == -INFINITY ? 0.f : exp2_approx(mlv[h].x - M[h]);
+          L[h] = fmaf(wgt, mlv[h].y, L[h]);
+          acc[h] = fmaf(wgt, ov[h], acc[h]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < kHeadTile; ++h) {
+    if (h < nheads) {
+      const float val = acc[h] / L[h];
+      const int64_t off = b * o_sb + (head0 + h) * o_sh + ch;
+      if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = val;
+      else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(val);
+      else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
+      if (lse && ch == 0)
+        lse[static_cast<int64_t>(b) * a.N + head0 + h] = (M[h] + log2f(L[h])) * 0.6931471805599453f;
+    }
+  }
+}
+
+// Merge P normalised partial results (outs (P, rows, 128), lses (P, rows)).
+template <int ODT>
+__global__ void __launch_bounds__(kHeadDim)
+merge_lse_kernel(const float* __restrict__ outs, const float* __restrict__ lses, int P, int64_t rows,
+                 void* __restrict__ out, float* __restrict__ lse_out) {
+  const int64_t row = blockIdx.x;
+  const int ch = threadIdx.x;
+  float M = -INFINITY;
+  for (int p = 0; p < P; ++p) M = fmaxf(M, lses[p * rows + row]);
+  float L = 0.f, acc = 0.f;
+  for (int p = 0; p < P; ++p) {
+    const float l = lses[p * rows + row];
+    const float w = l == -INFINITY ? 0.f : __expf(l - M);
+    L += w;
+    acc = fmaf(w, outs[(p * rows + row) * kHeadDim + ch], acc);
+  }
+  const float val = acc / L;
+  const int64_t off = row * kHeadDim + ch;
+  if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = val;
+  else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(val);
+  else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
+  if (lse_out && ch == 0) lse_out[row] = M + __logf(L);
+}
+
+// ---------------------------------------------------------------------------------
+// host side: partition, dispatch
+// ---------------------------------------------------------------------------------
+int sm_count() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached = n; cached_dev = dev;
+  }
+  return cached;
+}
+
+constexpr int kMinSlotsPerWarp = 16;   // below this a partial costs more than the work it covers
+
+void plan(DecodeArgs& a, int ctas_per_sm, int num_ctas) {
+  a.nrep = a.N / a.Nk;
+  a.head_tiles = (a.nrep + kHeadTile - 1) / kHeadTile;
+  a.spg = a.G / kStep;
+  a.nq = a.Nb * a.spg;
+  a.nr = (a.R + kStep - 1) / kStep;
+  a.slots_per_unit = a.nq + 2 * a.nr;
+  const long long units = static_cast<long long>(a.B) * a.Nk * a.head_tiles;
+  a.total_slots = units * a.slots_per_unit;
+  long long ctas = num_ctas > 0 ? num_ctas : static_cast<long long>(sm_count()) * ctas_per_sm;
+  const long long useful = (a.total_slots + static_cast<long long>(kMinSlotsPerWarp) * kWarps - 1) /
+                           (static_cast<long long>(kMinSlotsPerWarp) * kWarps);
+  if (num_ctas <= 0 && ctas > useful) ctas = useful;
+  if (ctas < 1) ctas = 1;
+  a.total_warps = static_cast<int>(ctas * kWarps);
+  const long long per_warp = (a.total_slots + a.total_warps - 1) / a.total_warps;
+  a.max_seg = static_cast<int>((per_warp + a.slots_per_unit - 1) / (a.slots_per_unit > 0 ? a.slots_per_unit : 1)) + 1;
+}
+
+size_t workspace_bytes_for(const DecodeArgs& a) {
+  const size_t slots = static_cast<size_t>(a.total_warps) * a.max_seg;
+  return slots * (kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2));
+}
+
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
+int launch_decode(const DecodeArgs& a, cudaStream_t s) {
+  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<a.total_warps / kWarps, kThreads, 0, s>>>(a);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
+template <int RBITS, int TBITS, bool QK_ONLY>
+int dispatch_dtypes(const DecodeArgs& a, int qdt, int vdt, cudaStream_t s) {
+#define PQ_CASE(Q, V) if (qdt == Q && vdt == V) return launch_decode<RBITS, TBITS, Q, V, QK_ONLY>(a, s)
+  if constexpr (QK_ONLY) {
+    PQ_CASE(PQ_F16, PQ_F16); PQ_CASE(PQ_BF16, PQ_F16); PQ_CASE(PQ_F32, PQ_F16);
+  } else {
+    PQ_CASE(PQ_F16, PQ_F16); PQ_CASE(PQ_BF16, PQ_BF16); PQ_CASE(PQ_F32, PQ_F16);
+    PQ_CASE(PQ_F32, PQ_BF16); PQ_CASE(PQ_F16, PQ_BF16); PQ_CASE(PQ_BF16, PQ_F16);
+  }
+#undef PQ_CASE
+  return PQ_ERR_UNSUPPORTED;
+}
+
+template <bool QK_ONLY>
+int dispatch_bits(const DecodeArgs& a, int rbits, int tbits, int qdt, int vdt, cudaStream_t s) {
+#define PQ_BITS(R, T) if (rbits == R && tbits == T) return dispatch_dtypes<R, T, QK_ONLY>(a, qdt, vdt, s)
+  PQ_BITS(4, 4); PQ_BITS(3, 3); PQ_BITS(2, 4);
+  PQ_BITS(4, 3); PQ_BITS(3, 4); PQ_BITS(2, 2); PQ_BITS(2, 3); PQ_BITS(3, 2); PQ_BITS(4, 2);
+#undef PQ_BITS
+  return PQ_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
+                     const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
+                     int Nb, int G, int D, int rbits, int tbits, int dtype, cudaStream_t stream) {
+  if (B < 0 || N <= 0 || Nk <= 0 || Nb < 0 || G <= 0 || N % Nk != 0) return PQ_ERR_INVALID;
+  if (rbits < 0 || tbits < 0 || rbits + tbits > 8 || !dtype_ok(dtype)) return PQ_ERR_INVALID;
+  if (D != kPairs || G % kStep != 0) return PQ_ERR_UNSUPPORTED;
+  if (B == 0 || Nb == 0) return PQ_OK;
+  if (!q || !codes || !rscale || !rmn || !tscale || !tmn || !out) return PQ_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(codes) % 16 || reinterpret_cast<uintptr_t>(rscale) % 16 ||
+      reinterpret_cast<uintptr_t>(rmn) % 16 || reinterpret_cast<uintptr_t>(tscale) % 16 ||
+      reinterpret_cast<uintptr_t>(tmn) % 16)
+    return PQ_ERR_ALIGNMENT;
+  DecodeArgs a{};
+  a.q = q; a.q_sb = q_sb; a.q_sh = q_sh;
+  a.codes = codes; a.c_sh = static_cast<int64_t>(Nb) * G * kPairs; a.c_sb = a.c_sh * Nk;
+  a.rscale = rscale; a.rmn = rmn; a.tscale = tscale; a.tmn = tmn;
+  a.s_sh = static_cast<int64_t>(Nb) * kPairs; a.s_sb = a.s_sh * Nk;
+  a.logits = out;
+  a.B = B; a.N = N; a.Nk = Nk; a.Nb = Nb; a.G = G; a.R = 0;
+  plan(a, 4, 0);
+  return dispatch_bits<true>(a, rbits, tbits, dtype, PQ_F16, stream);
+}
+
+size_t decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int num_ctas) {
+  if (B <= 0 || N <= 0 || Nk <= 0 || Nb < 0 || G <= 0 || R < 0 || N % Nk != 0 || G % kStep != 0) return 0;
+  DecodeArgs a{};
+  a.B = B; a.N = N; a.Nk = Nk; a.Nb = Nb; a.G = G; a.R = R;
+  plan(a, 3, num_ctas);
+  return workspace_bytes_for(a);
+}
+
+int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
+  if (!p) return PQ_ERR_INVALID;
+  if (p->B < 0 || p->N <= 0 || p->Nk <= 0 || p->Nb < 0 || p->G <= 0 || p->R < 0 || p->N % p->Nk != 0)
+    return PQ_ERR_INVALID;
+  if (p->rbits < 0 || p->tbits < 0 || p->rbits + p->tbits > 8) return PQ_ERR_INVALID;
+  if (!dtype_ok(p->qk_dtype) || !dtype_ok(p->out_dtype)) return PQ_ERR_INVALID;
+  if (p->v_dtype != PQ_F16 && p->v_dtype != PQ_BF16) return PQ_ERR_UNSUPPORTED;
+  if (p->hd != kHeadDim || p->G % kStep != 0) return PQ_ERR_UNSUPPORTED;
+  if (p->B == 0) return PQ_OK;
+  if (p->Nb == 0 && p->R == 0) return PQ_ERR_INVALID;          // softmax over nothing
+  if (!p->q || !p->v || !p->out) return PQ_ERR_INVALID;
+  if (p->Nb > 0 && (!p->codes || !p->rscale || !p->rmn || !p->tscale || !p->tmn)) return PQ_ERR_INVALID;
+  if (p->R > 0 && !p->k_res) return PQ_ERR_INVALID;
+  const int qes = static_cast<int>(dtype_bytes(p->qk_dtype));
+  auto mis = [](const void* ptr, size_t al) { return reinterpret_cast<uintptr_t>(ptr) % al != 0; };
+  // 128-bit loads: pointers 16-byte aligned, strides multiples of 16 bytes
+  if (mis(p->v, 16) || (p->v_stride_b * 2) % 16 || (p->v_stride_h * 2) % 16 || (p->v_stride_t * 2) % 16)
+    return PQ_ERR_ALIGNMENT;
+  if (mis(p->q, 16) || (p->q_stride_b * qes) % 16 || (p->q_stride_h * qes) % 16) return PQ_ERR_ALIGNMENT;
+  if (p->Nb > 0) {
+    if (mis(p->codes, 16) || p->codes_stride_b % 16 || p->codes_stride_h % 16) return PQ_ERR_ALIGNMENT;
+    if (mis(p->rscale, 16) || mis(p->rmn, 16) || mis(p->tscale, 16) || mis(p->tmn, 16) ||
+        (p->scale_stride_b * qes) % 16 || (p->scale_stride_h * qes) % 16)
+      return PQ_ERR_ALIGNMENT;
+  }
+  if (p->R > 0 && (mis(p->k_res, 16) || (p->kres_stride_b * qes) % 16 || (p->kres_stride_h * qes) % 16 ||
+                   (p->kres_stride_t * qes) % 16))
+    return PQ_ERR_ALIGNMENT;
+
+  DecodeArgs a{};
+  a.q = p->q; a.q_sb = p->q_stride_b; a.q_sh = p->q_stride_h;
+  a.codes = p->codes; a.c_sb = p->codes_stride_b; a.c_sh = p->codes_stride_h;
+  a.rscale = p->rscale; a.rmn = p->rmn; a.tscale = p->tscale; a.tmn = p->tmn;
+  a.s_sb = p->scale_stride_b; a.s_sh = p->scale_stride_h;
+  a.kres = p->k_res; a.kr_sb = p->kres_stride_b; a.kr_sh = p->kres_stride_h; a.kr_st = p->kres_stride_t;
+  a.v = p->v; a.v_sb = p->v_stride_b; a.v_sh = p->v_stride_h; a.v_st = p->v_stride_t;
+  a.mask = p->mask; a.m_sb = p->mask_stride_b;
+  a.B = p->B; a.N = p->N; a.Nk = p->Nk; a.Nb = p->Nb; a.G = p->G; a.R = p->R;
+  plan(a, 3, p->num_ctas);
+  const size_t need = workspace_bytes_for(a);
+  if (!p->workspace || p->workspace_bytes < need) return PQ_ERR_WORKSPACE;
+  if (mis(p->workspace, 256)) return PQ_ERR_ALIGNMENT;
+  const size_t slots = static_cast<size_t>(a.total_warps) * a.max_seg;
+  a.part_o = static_cast<float*>(p->workspace);
+  a.part_ml = reinterpret_cast<float2*>(a.part_o + slots * kPartialFloats);
+  const float sm = p->sm_scale != 0.f ? p->sm_scale : 0.08838834764831845f;   // 1/sqrt(128)
+  a.scale_log2 = sm * 1.4426950408889634f;
+
+  // a kernel instance exists per (rbits, tbits); without packed keys any instance serves
+  const int rb = p->Nb > 0 ? p->rbits : 4, tb = p->Nb > 0 ? p->tbits : 4;
+  int rc = dispatch_bits<false>(a, rb, tb, p->qk_dtype, p->v_dtype, stream);
+  if (rc != PQ_OK) return rc;
+  const unsigned units = static_cast<unsigned>(static_cast<long long>(a.B) * a.Nk * a.head_tiles);
+  switch (p->out_dtype) {
+    case PQ_F16: merge_partials_kernel<PQ_F16><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    case PQ_BF16: merge_partials_kernel<PQ_BF16><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    default: merge_partials_kernel<PQ_F32><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+  }
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
+int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out,
+                     int out_dtype, float* lse_out, cudaStream_t stream) {
+  if (P <= 0 || rows < 0 || !dtype_ok(out_dtype)) return PQ_ERR_INVALID;
+  if (hd != kHeadDim) return PQ_ERR_UNSUPPORTED;
+  if (rows == 0) return PQ_OK;
+  if (!outs || !lses || !out) return PQ_ERR_INVALID;
+  if (rows > 0x7fffffffLL) return PQ_ERR_UNSUPPORTED;
+  const unsigned grid = static_cast<unsigned>(rows);
+  switch (out_dtype) {
+    case PQ_F16: merge_lse_kernel<PQ_F16><<<grid, kHeadDim, 0, stream>>>(outs, lses, P, rows, out, lse_out); break;
+    case PQ_BF16: merge_lse_kernel<PQ_BF16><<<grid, kHeadDim, 0, stream>>>(outs, lses, P, rows, out, lse_out); break;
+    default: merge_lse_kernel<PQ_F32><<<grid, kHeadDim, 0, stream>>>(outs, lses, P, rows, out, lse_out); break;
+  }
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
+}  // namespace pq

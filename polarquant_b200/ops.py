@@ -1,0 +1,264 @@
+"""Tensor-level entry points over the C ABI: quantizer, QK logits, fused decode attention, LSE merge.
+
+Every function takes CUDA tensors, enqueues on the current torch stream of the
+tensors' device and returns without synchronising.  torch only supplies device
+memory and the stream handle.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float16: _lib.PQ_F16, torch.bfloat16: _lib.PQ_BF16, torch.float32: _lib.PQ_F32}
+
+
+def _dtype_code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise ValueError(f"{what}: dtype {t.dtype} is not supported (float16, bfloat16, float32)") from None
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("polarquant_b200 runs on CUDA tensors only; there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError("all tensors must live on the same CUDA device")
+    return dev
+
+
+def _stream(dev: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _vec_ok(t: torch.Tensor, elems: int) -> bool:
+    """True when 4/8-element vector loads are legal on every row of ``t``."""
+    if t.stride(-1) != 1:
+        return False
+    es = t.element_size()
+    if t.data_ptr() % (elems * es):
+        return False
+    return all(s % elems == 0 for s in t.stride()[:-1])
+
+
+def quantize_and_pack_nbit(key_states: torch.Tensor, rbits: int = 4, tbits: int = 4, group_size: int = 128,
+                           flags: int = 0):
+    """Polar-quantise keys (B, Nk, L, 128); same contract as the reference method.
+
+    Reference: ``quantize_and_pack_nbit`` at models/modeling_llama_polar.py:135-157.
+    Returns ``(indices, rscale, rmn, tscale, tmn)`` with shapes (B, Nk, L/G, G, 64)
+    uint8 and four (B, Nk, L/G, 1, 64) tensors in the key dtype.  Strided inputs
+    (the (B, L, Nk, hd) layout the prefill hands over) are read in place.
+    """
+    if key_states.dim() != 4:
+        raise ValueError("key_states must be (batch, kv_heads, length, head_dim)")
+    bsz, heads, length, hd = key_states.shape
+    # the reference's assertion (models/modeling_llama_polar.py:138)
+    assert hd % 2 == 0 and length % group_size == 0 and rbits + tbits <= 8
+    dev = _require_cuda(key_states)
+    dt = _dtype_code(key_states, "quantize_and_pack_nbit")
+    if not _vec_ok(key_states, 4):
+        key_states = key_states.contiguous()
+    nb = length // group_size
+    codes = torch.empty((bsz, heads, nb, group_size, hd // 2), dtype=torch.uint8, device=dev)
+    scales = [torch.empty((bsz, heads, nb, 1, hd // 2), dtype=key_states.dtype, device=dev) for _ in range(4)]
+    strides = (ctypes.c_int64 * 4)(*key_states.stride())
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.pq_quantize(key_states.data_ptr(), strides, bsz, heads, length, hd, group_size, rbits, tbits, dt,
+                             flags, codes.data_ptr(), scales[0].data_ptr(), scales[1].data_ptr(),
+                             scales[2].data_ptr(), scales[3].data_ptr(), _stream(dev))
+    _lib.check(rc, "pq_quantize")
+    return (codes, *scales)
+
+
+def qk_decode(query_states: torch.Tensor, indices: torch.Tensor, rscale, rmn, tscale, tmn,
+              rbits: int = 4, tbits: int = 4) -> torch.Tensor:
+    """Un-scaled fp32 logits (B, N, 1, Nb*G) over the packed keys.
+
+    Reference: ``attention_decode_forward_triton_impl`` at models/kernel4group.py:83-109.
+    ``Nk = indices.shape[1]`` and query head ``kvh * (N // Nk) + h`` reads kv head kvh.
+    """
+    bsz, kvh, nb, grp, half = indices.shape
+    nq = query_states.shape[1]
+    dev = _require_cuda(query_states, indices, rscale, rmn, tscale, tmn)
+    dt = _dtype_code(query_states, "attention_decode_forward")
+    if nq % kvh:
+        raise ValueError("query heads must be a multiple of the kv heads of the code tensor")
+    if indices.dtype != torch.uint8:
+        raise ValueError("indices must be uint8")
+    q = query_states.reshape(bsz, nq, 2 * half)
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    indices = indices.contiguous()
+    scales = []
+    for s in (rscale, rmn, tscale, tmn):
+        if s.dtype != query_states.dtype:
+            s = s.to(query_states.dtype)
+        scales.append(s.contiguous())
+    out = torch.empty((bsz, nq, 1, nb * grp), dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.pq_qk_decode(q.data_ptr(), q.stride(0), q.stride(1), indices.data_ptr(), scales[0].data_ptr(),
+                              scales[1].data_ptr(), scales[2].data_ptr(), scales[3].data_ptr(), out.data_ptr(),
+                              bsz, nq, kvh, nb, grp, half, rbits, tbits, dt, _stream(dev))
+    _lib.check(rc, "pq_qk_decode")
+    return out
+
+
+_workspaces: dict = {}
+
+
+def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) scratch, grown on demand and reused across calls."""
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def _unit_strides(t: torch.Tensor, inner: int):
+    """(stride_b, stride_h) of a (B, Nk, ...) tensor whose trailing dims are dense, else None."""
+    expect = 1
+    for size, stride in zip(reversed(t.shape[2:]), reversed(t.stride()[2:])):
+        if size != 1 and stride != expect:
+            return None
+        expect *= size
+    return t.stride(0), t.stride(1)
+
+
+def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, rmn, tscale, tmn,
+                     value_states: torch.Tensor, attention_mask=None, rbits: int = 4, tbits: int = 4,
+                     sm_scale: float | None = None, out_dtype: torch.dtype | None = None,
+                     return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0):
+    """One fused decode-attention step over the polar cache.
+
+    Computes what the reference's decode branch computes with separate ops
+    (models/modeling_llama_polar.py:66-99): logits over the packed keys, logits
+    over the full-precision residual keys (which already include the current
+    token), ``/ sqrt(head_dim)``, optional key mask, softmax, and the product with
+    the values (which already include the current token).
+
+    query_states (B, N, 1, 128); key_residual (B, Nk, R, 128) or None; indices
+    (B, Nk, Nb, G, 64) uint8 or None with scales (B, Nk, Nb, 1, 64);
+    value_states (B, Nk, Nb*G + R, 128) fp16/bf16, any batch/head/token strides;
+    attention_mask (B, Nb*G + R), nonzero = attend.  Returns (B, N, 1, 128) in
+    ``out_dtype`` (default: the query dtype) and, with ``return_lse``, the
+    natural-log log-sum-exp (B, N) fp32.
+    """
+    dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask)
+    bsz, nq, qlen, hd = query_states.shape
+    if qlen != 1:
+        raise ValueError("decode attention takes exactly one query position")
+    kvh = value_states.shape[1]
+    qdt = _dtype_code(query_states, "decode_attention")
+    vdt = _dtype_code(value_states, "decode_attention")
+    out_dtype = out_dtype or query_states.dtype
+    nb = grp = 0
+    if indices is not None and indices.shape[2] > 0:
+        _, _, nb, grp, _ = indices.shape
+    else:
+        indices = None
+        grp = 128
+    res = 0 if key_residual is None else key_residual.shape[2]
+    ctx = nb * grp + res
+    if value_states.shape[2] != ctx:
+        raise ValueError(f"value_states holds {value_states.shape[2]} tokens, keys hold {ctx}")
+
+    p = _lib.DecodeParams()
+    q = query_states.reshape(bsz, nq, hd)
+    if not _vec_ok(q, 8):
+        q = q.contiguous()
+    p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    keep = [q]
+    if indices is not None:
+        if indices.dtype != torch.uint8:
+            raise ValueError("indices must be uint8")
+        if _unit_strides(indices, 1) is None or indices.data_ptr() % 16 or indices.stride(0) % 16 or indices.stride(1) % 16:
+            indices = indices.contiguous()
+        p.codes, (p.codes_stride_b, p.codes_stride_h) = indices.data_ptr(), _unit_strides(indices, 1)
+        sc = []
+        for s in (rscale, rmn, tscale, tmn):
+            if s.dtype != query_states.dtype:
+                s = s.to(query_states.dtype)
+            if _unit_strides(s, 1) is None or not _vec_ok(s, 8):
+                s = s.contiguous()
+            sc.append(s)
+        if len({(s.stride(0), s.stride(1)) for s in sc}) != 1:
+            sc = [s.contiguous() for s in sc]
+        p.rscale, p.rmn, p.tscale, p.tmn = (s.data_ptr() for s in sc)
+        p.scale_stride_b, p.scale_stride_h = sc[0].stride(0), sc[0].stride(1)
+        keep += [indices, *sc]
+    if res:
+        kr = key_residual
+        if kr.dtype != query_states.dtype:
+            kr = kr.to(query_states.dtype)
+        if not _vec_ok(kr, 8):
+            kr = kr.contiguous()
+        p.k_res = kr.data_ptr()
+        p.kres_stride_b, p.kres_stride_h, p.kres_stride_t = kr.stride(0), kr.stride(1), kr.stride(2)
+        keep.append(kr)
+    v = value_states
+    if vdt == _lib.PQ_F32:
+        v = v.to(torch.float16 if query_states.dtype != torch.bfloat16 else torch.bfloat16)
+        vdt = _DT[v.dtype]
+    if not _vec_ok(v, 8):
+        v = v.contiguous()
+    p.v, p.v_stride_b, p.v_stride_h, p.v_stride_t = v.data_ptr(), v.stride(0), v.stride(1), v.stride(2)
+    keep.append(v)
+    if attention_mask is not None:
+        m = (attention_mask != 0).to(torch.uint8)
+        if m.shape != (bsz, ctx):
+            raise ValueError(f"attention_mask must be (batch, {ctx})")
+        m = m.contiguous()
+        p.mask, p.mask_stride_b = m.data_ptr(), m.stride(0)
+        keep.append(m)
+    out = torch.empty((bsz, nq, 1, hd), dtype=out_dtype, device=dev)
+    p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    lse = torch.empty((bsz, nq), dtype=torch.float32, device=dev) if return_lse else None
+    p.lse = lse.data_ptr() if return_lse else None
+    p.B, p.N, p.Nk, p.Nb, p.G, p.R, p.hd = bsz, nq, kvh, nb, grp, res, hd
+    p.rbits, p.tbits = rbits, tbits
+    p.qk_dtype, p.v_dtype, p.out_dtype = qdt, vdt, _DT[out_dtype]
+    p.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
+    p.num_ctas = num_ctas
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        need = lib.pq_decode_workspace_bytes(bsz, nq, kvh, nb, grp, res, num_ctas)
+        ws = workspace if workspace is not None else _workspace(dev, need)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+        rc = lib.pq_decode_attention(ctypes.byref(p), _stream(dev))
+    _lib.check(rc, "pq_decode_attention")
+    del keep
+    return (out, lse) if return_lse else out
+
+
+def merge_lse(outs: torch.Tensor, lses: torch.Tensor, out_dtype: torch.dtype = torch.float32,
+              return_lse: bool = False):
+    """Merge P partial results: outs (P, ..., 128) fp32 normalised, lses (P, ...) fp32 natural log."""
+    dev = _require_cuda(outs, lses)
+    outs = outs.to(torch.float32).contiguous()
+    lses = lses.to(torch.float32).contiguous()
+    parts = outs.shape[0]
+    hd = outs.shape[-1]
+    rows = lses[0].numel()
+    out = torch.empty(outs.shape[1:], dtype=out_dtype, device=dev)
+    lse = torch.empty(lses.shape[1:], dtype=torch.float32, device=dev) if return_lse else None
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.pq_merge_lse(outs.data_ptr(), lses.data_ptr(), parts, rows, hd, out.data_ptr(), _DT[out_dtype],
+                              lse.data_ptr() if return_lse else None, _stream(dev))
+    _lib.check(rc, "pq_merge_lse")
+    return (out, lse) if return_lse else out
