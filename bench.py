@@ -1,0 +1,405 @@
+"""Benchmark of the polar key-cache hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one fused decode-attention call (packed-key logits + residual-key logits + softmax + P.V)
+over the whole batch of the Llama-3.1-8B-shaped configuration: batch 16, 32 query / 8 kv heads, head_dim 128,
+context 32768 = 255 packed groups of 128 tokens + 128 full-precision residual keys, bf16, polar 4/4.
+Inputs are seeded synthetic tensors (keys randn times a per-channel log-uniform scale in [0.5, 8], packed by
+the CUDA quantizer; queries and values randn); the inputs of one step (1.36 GB) exceed the 126 MB L2.
+
+It prints ONE JSON line.  `value` is algorithmic GB/s with the cache resident in HBM; `e2e` is the same metric
+through the host-buffer C entry point with every input copied from pinned host memory and the output copied
+back inside the timed region; `roofline` is the attention kernel alone (CUDA events around it on its stream);
+`cpu_baseline` is the CPU oracle (a port of the reference's eager path) on a bounded sample.
+With N > 1 (launched by torch.distributed.run) every rank holds its own batch of 16 sequences (weak scaling,
+the path shards by batch / kv head without any collective) and the time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "polar-KV decode-attn GB/s (% HBM peak) & µs/step @32k ctx; e2e decode tokens/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    # smaller cases for profiler captures; the defaults are the benchmark configuration
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--group", type=int, default=128)
+    ap.add_argument("--rbits", type=int, default=4)
+    ap.add_argument("--tbits", type=int, default=4)
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--no-extras", action="store_true", help="skip e2e, quantizer and CPU legs (profiler runs)")
+    return ap.parse_args()
+
+
+def algorithmic_bytes(B, N, Nk, Nb, G, R, e=2, e_out=2):
+    """Bytes one decode step must move: codes + scales + residual keys + values + query + output."""
+    lq = Nb * G
+    return B * Nk * (lq * 64 + Nb * 4 * 64 * e + R * 128 * e + (lq + R) * 128 * e) + B * N * 128 * (e + e_out)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                clocks.append(float(r[0])); maxes.append(float(r[1]))
+                for name, flag in zip(names, r[3:7]):
+                    if flag.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def make_inputs(args, device, seed):
+    """Seeded synthetic cache for one rank: packed keys (CUDA quantizer), residual keys, values, query."""
+    import torch
+    import polarquant_b200 as pq
+    B, N, Nk, G = args.batch, args.q_heads, args.kv_heads, args.group
+    R = 128
+    Nb = (args.ctx - R) // G
+    g = torch.Generator(device=device).manual_seed(seed)
+    scale = torch.exp(torch.empty(Nk, 128, device=device).uniform_(math.log(0.5), math.log(8.0), generator=g))
+    q = torch.randn(B, N, 1, 128, device=device, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Nk, Nb * G + R, 128, device=device, generator=g).to(torch.bfloat16)
+    kres = (torch.randn(B, Nk, R, 128, device=device, generator=g) * scale[None, :, None]).to(torch.bfloat16)
+    packed = [[] for _ in range(5)]
+    for b in range(B):
+        kb = (torch.randn(1, Nk, Nb * G, 128, device=device, generator=g) * scale[None, :, None]).to(torch.bfloat16)
+        for lst, t in zip(packed, pq.quantize_and_pack_nbit(kb, args.rbits, args.tbits, G)):
+            lst.append(t)
+    packed = [torch.cat(lst, dim=0) for lst in packed]
+    return dict(q=q, kres=kres, packed=packed, v=v, B=B, N=N, Nk=Nk, Nb=Nb, G=G, R=R)
+
+
+def oracle_cpu_step(sample, args):
+    """The reference's eager decode path (dequantise -> matmul -> softmax -> P.V) on host cores."""
+    from oracle import polar_oracle as oracle
+    return oracle.decode_attention(sample["q"], sample["kres"], *sample["packed"], sample["v"],
+                                   rbits=args.rbits, tbits=args.tbits)
+
+
+def cpu_sample(args, seed=1002):
+    """One batch element of the benchmark configuration, built on the CPU with the oracle's quantizer."""
+    import torch
+    from oracle import polar_oracle as oracle
+    N, Nk, G, R = args.q_heads, args.kv_heads, args.group, 128
+    Nb = (args.ctx - R) // G
+    g = torch.Generator().manual_seed(seed)
+    keys = oracle.synth_keys(1, Nk, Nb * G + R, 128, torch.bfloat16, seed=seed)
+    q = torch.randn(1, N, 1, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, Nk, Nb * G + R, 128, generator=g).to(torch.bfloat16)
+    packed = oracle.quantize_ops(keys[:, :, :Nb * G].contiguous(), args.rbits, args.tbits, G)
+    return dict(q=q, kres=keys[:, :, Nb * G:].contiguous(), packed=list(packed), v=v), \
+        algorithmic_bytes(1, N, Nk, Nb, G, R)
+
+
+def time_cpu(args, budget_s=20.0, max_reps=10):
+    import torch
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample, nbytes = cpu_sample(args)
+    oracle_cpu_step(sample, args)                        # warm-up
+    times, t_end = [], time.perf_counter() + budget_s
+    while len(times) < max_reps and (time.perf_counter() < t_end or len(times) < 2):
+        t0 = time.perf_counter()
+        oracle_cpu_step(sample, args)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"1 of {args.batch} batch elements of the workload ({nbytes / 1e6:.1f} MB per step), "
+                      f"best of {len(times)} runs, torch CPU eager ops, {cores} threads",
+            "ms_per_sample_step": best * 1e3}
+
+
+def run_reference_arm(args, rank):
+    """--impl reference: the reference's own eager path for this step, timed on host cores (CPU oracle port)."""
+    if rank != 0:
+        return
+    import torch
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample, nbytes = cpu_sample(args)
+    for _ in range(min(args.warmup, 2)):
+        oracle_cpu_step(sample, args)
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle_cpu_step(sample, args)
+    dt = (time.perf_counter() - t0) / steps
+    val = nbytes / dt / 1e9
+    sample_txt = (f"each step = 1 of {args.batch} batch elements of the workload ({nbytes / 1e6:.1f} MB), "
+                  f"{steps} timed steps, torch CPU eager ops, {cores} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample_txt},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(args):
+    return {"workload": f"Llama-3.1-8B-shaped GQA decode attention: batch {args.batch} per GPU, {args.q_heads} q / "
+                        f"{args.kv_heads} kv heads, head_dim 128, ctx {args.ctx}, polar {args.rbits}/{args.tbits}, "
+                        f"group {args.group}, residual 128, bf16",
+            "l2": "inputs of one step (1.36 GB at the default size) exceed the 126 MB L2; no flush needed",
+            "sharding": "batch per GPU, no collective in the step"}
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import polarquant_b200 as pq
+    from polarquant_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+
+    inp = make_inputs(args, device, seed=1002 + rank)
+    B, N, Nk, Nb, G, R = (inp[k] for k in ("B", "N", "Nk", "Nb", "G", "R"))
+    nbytes = algorithmic_bytes(B, N, Nk, Nb, G, R)
+    ws = torch.empty(lib.pq_decode_workspace_bytes(B, N, Nk, Nb, G, R, 0) + 256, dtype=torch.uint8, device=device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+    def new_event():
+        e = ctypes.c_void_p()
+        assert lib.pq_event_create(ctypes.byref(e)) == 0
+        return e
+
+    def step(mid=None):
+        return pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"], rbits=args.rbits,
+                                   tbits=args.tbits, workspace=ws, mid_event=mid)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    K = args.steps
+    ev_a = [new_event() for _ in range(K)]
+    ev_m = [new_event() for _ in range(K)]
+    ev_end = new_event()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    for i in range(K):
+        lib.pq_event_record(ev_a[i], stream)
+        step(ev_m[i])
+    lib.pq_event_record(ev_end, stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = ctypes.c_float()
+    lib.pq_event_elapsed_ms(ev_a[0], ev_end, ctypes.byref(ms))
+    total_ms = ms.value
+    kern_ms = []
+    for i in range(K):
+        lib.pq_event_elapsed_ms(ev_a[i], ev_m[i], ctypes.byref(ms))
+        kern_ms.append(ms.value)
+    if world > 1:
+        t = torch.tensor([total_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / K
+    value = nbytes * world / (ms_per_step * 1e-3) / 1e9
+
+    result = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        kavg = sum(kern_ms) / len(kern_ms)
+        achieved = nbytes / (kavg * 1e-3) / 1e9
+        result = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
+            "us_per_step": ms_per_step * 1e3, "algorithmic_mb_per_step_per_gpu": nbytes / 1e6,
+            "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_HBM_GBS,
+            "pct_of_measured_copy_peak": 100.0 * value / world / peak,
+            "clocks": clocks, "gpu_launches": 2 * K,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "decode_kernel (fused attention over packed keys)",
+                         "peak_source": f"{peak_kind} copy bandwidth", "kernel_us": kavg * 1e3,
+                         "kernel_us_median": statistics.median(kern_ms) * 1e3},
+        }
+
+    if not args.no_extras:
+        extras = run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event)
+        if rank == 0:
+            result.update(extras)
+    if rank == 0:
+        if not args.no_extras:
+            result["cpu_baseline"] = time_cpu(args)
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
+    """End-to-end leg (host buffers through the C ABI) and the quantizer timing."""
+    import torch
+    import torch.distributed as dist
+    import polarquant_b200 as pq
+    from polarquant_b200 import _lib
+    B, N, Nk, Nb, G, R = (inp[k] for k in ("B", "N", "Nk", "Nb", "G", "R"))
+    out = {}
+
+    # ---- e2e: every input in pinned host memory, H2D + kernels + D2H inside the timed region ----
+    host = {k: inp[k].cpu().contiguous().pin_memory() for k in ("q", "kres", "v")}
+    hpacked = [t.cpu().contiguous().pin_memory() for t in inp["packed"]]
+    hout = torch.empty(B, N, 1, 128, dtype=torch.bfloat16).pin_memory()
+    p = _lib.DecodeParams()
+    p.q, p.k_res, p.v, p.out = host["q"].data_ptr(), host["kres"].data_ptr(), host["v"].data_ptr(), hout.data_ptr()
+    p.codes, p.rscale, p.rmn, p.tscale, p.tmn = (t.data_ptr() for t in hpacked)
+    p.B, p.N, p.Nk, p.Nb, p.G, p.R, p.hd = B, N, Nk, Nb, G, R, 128
+    p.rbits, p.tbits = args.rbits, args.tbits
+    p.qk_dtype = p.v_dtype = p.out_dtype = _lib.PQ_BF16
+    need = lib.pq_decode_host_staging_bytes(B, N, Nk, Nb, G, R, 128, _lib.PQ_BF16, _lib.PQ_BF16, _lib.PQ_BF16, 0)
+    staging = torch.empty(need, dtype=torch.uint8, device=device)
+    h2d = sum(t.numel() * t.element_size() for t in [*host.values(), *hpacked])
+    d2h = hout.numel() * hout.element_size()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        rc = lib.pq_decode_attention_host(ctypes.byref(p), staging.data_ptr(), need, stream)
+        assert rc == 0, lib.pq_strerror(rc)
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    a, b = new_event(), new_event()
+    lib.pq_event_record(a, stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    lib.pq_event_record(b, stream)
+    torch.cuda.synchronize(device)
+    ms = ctypes.c_float()
+    lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
+    e2e_ms = ms.value / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    got = pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"], rbits=args.rbits, tbits=args.tbits)
+    assert torch.equal(hout.to(device), got), "host-buffer entry point disagrees with the device entry point"
+    out["e2e"] = {"value": nbytes * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                  "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                  "note": "pq_decode_attention_host: the whole cache of the step is copied from pinned host memory "
+                          "each step, so this leg is bound by the host link, not by the kernels"}
+    del staging, host, hpacked
+
+    # ---- quantizer at a 32k-token prefill, strided (B, L, Nk, hd) layout as the prefill hands it over ----
+    if rank == 0:
+        L = args.ctx
+        g = torch.Generator(device=device).manual_seed(7)
+        base = torch.randn(B, L, Nk, 128, device=device, generator=g).to(torch.bfloat16)
+        keys = base.transpose(1, 2)
+        for _ in range(3):
+            pq.quantize_and_pack_nbit(keys, args.rbits, args.tbits, G)
+        torch.cuda.synchronize(device)
+        a, b = new_event(), new_event()
+        reps = 10
+        lib.pq_event_record(a, stream)
+        for _ in range(reps):
+            pq.quantize_and_pack_nbit(keys, args.rbits, args.tbits, G)
+        lib.pq_event_record(b, stream)
+        lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
+        q_ms = ms.value / reps
+        q_bytes = B * Nk * L * 128 * 2 + B * Nk * (L * 64 + (L // G) * 4 * 64 * 2)
+        peak, _ = measured_peak()
+        out["quantizer"] = {"workload": f"{L}-token prefill, batch {B}, {Nk} kv heads, bf16, strided (B, L, Nk, hd)",
+                            "us": q_ms * 1e3, "algorithmic_mb": q_bytes / 1e6,
+                            "gbs": q_bytes / (q_ms * 1e-3) / 1e9, "frac_of_peak": q_bytes / (q_ms * 1e-3) / 1e9 / peak}
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -35,7 +35,8 @@ typedef enum {
 /* pq_quantize flag bits */
 #define PQ_QUANT_WRAP_DTYPE 1u /* add RN_dtype(2*pi) to negative angles (what torch does on CPU) \
                                   instead of float32(2*pi) (what torch does on CUDA, the default) */
-#define PQ_QUANT_NORM_SEPARATE 2u /* fp32 keys only: radius^2 = RN(x*x) + RN(y*y) instead of fma(y, y, x*x) */
+#define PQ_QUANT_NORM_FMA 2u /* fp32 keys only: radius^2 = fma(y, y, RN(x*x)) instead of RN(x*x) + RN(y*y), the \
+                                 form torch evaluates on both CPU and CUDA (for 16-bit keys the two coincide) */
 
 /*
  * Polar key quantizer.  Replaces the method quantize_and_pack_nbit
@@ -113,6 +114,7 @@ typedef struct pq_decode_params {
   int qk_dtype, v_dtype, out_dtype;
   float sm_scale;  /* logits multiplier; 0 means 1/sqrt(hd) as at modeling_llama_polar.py:80 */
   int num_ctas;    /* 0 = choose from the device's SM count */
+  void* mid_event; /* optional cudaEvent_t recorded between the attention kernel and the merge kernel */
 } pq_decode_params;
 
 int pq_decode_attention(const pq_decode_params* p, void* stream);
@@ -149,6 +151,16 @@ size_t pq_quantize_host_staging_bytes(int B, int Nk, int L, int hd, int G, int d
 int pq_decode_attention_host(const pq_decode_params* p, void* staging, size_t staging_bytes, void* stream);
 size_t pq_decode_host_staging_bytes(int B, int N, int Nk, int Nb, int G, int R, int hd,
                                     int qk_dtype, int v_dtype, int out_dtype, int has_mask);
+
+/*
+ * CUDA-event helpers so a host program without its own CUDA binding can time the
+ * kernels on the stream they are launched on.  pq_event_elapsed_ms synchronises
+ * on `end` first.
+ */
+int pq_event_create(void** event);
+int pq_event_destroy(void* event);
+int pq_event_record(void* event, void* stream);
+int pq_event_elapsed_ms(void* start, void* end, float* ms);
 
 const char* pq_strerror(int status);
 /* cudaError_t of the most recent failing CUDA call made by this library on the calling thread */

@@ -16,12 +16,13 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libpolarquant_b200.so")
 PQ_F16, PQ_BF16, PQ_F32 = 0, 1, 2
 PQ_OK = 0
 PQ_QUANT_WRAP_DTYPE = 1
-PQ_QUANT_NORM_SEPARATE = 2
+PQ_QUANT_NORM_FMA = 2
 
 EXPORTED_SYMBOLS = (
     "pq_quantize", "pq_qk_decode", "pq_decode_attention", "pq_decode_workspace_bytes", "pq_merge_lse",
     "pq_quantize_host", "pq_quantize_host_staging_bytes", "pq_decode_attention_host",
     "pq_decode_host_staging_bytes", "pq_strerror", "pq_last_cuda_error", "pq_abi_version", "pq_decode_params_size",
+    "pq_event_create", "pq_event_destroy", "pq_event_record", "pq_event_elapsed_ms",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -45,6 +46,7 @@ class DecodeParams(ctypes.Structure):
         ("qk_dtype", _int), ("v_dtype", _int), ("out_dtype", _int),
         ("sm_scale", _f32),
         ("num_ctas", _int),
+        ("mid_event", _vp),
     ]
 
 
@@ -70,6 +72,14 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_decode_attention_host.argtypes = [ctypes.POINTER(DecodeParams), _vp, _sz, _vp]
     lib.pq_decode_host_staging_bytes.restype = _sz
     lib.pq_decode_host_staging_bytes.argtypes = [_int] * 11
+    lib.pq_event_create.restype = _int
+    lib.pq_event_create.argtypes = [ctypes.POINTER(_vp)]
+    lib.pq_event_destroy.restype = _int
+    lib.pq_event_destroy.argtypes = [_vp]
+    lib.pq_event_record.restype = _int
+    lib.pq_event_record.argtypes = [_vp, _vp]
+    lib.pq_event_elapsed_ms.restype = _int
+    lib.pq_event_elapsed_ms.argtypes = [_vp, _vp, ctypes.POINTER(_f32)]
     lib.pq_strerror.restype = ctypes.c_char_p
     lib.pq_strerror.argtypes = [_int]
     lib.pq_last_cuda_error.restype = _int

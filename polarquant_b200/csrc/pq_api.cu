@@ -77,6 +77,30 @@ int pq_merge_lse(const float* outs, const float* lses, int P, int64_t rows, int 
   return merge_lse_device(outs, lses, P, rows, hd, out, out_dtype, lse_out, static_cast<cudaStream_t>(stream));
 }
 
+int pq_event_create(void** event) {
+  if (!event) return PQ_ERR_INVALID;
+  cudaEvent_t e;
+  PQ_CUDA_TRY(cudaEventCreate(&e));
+  *event = e;
+  return PQ_OK;
+}
+int pq_event_destroy(void* event) {
+  if (!event) return PQ_OK;
+  PQ_CUDA_TRY(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return PQ_OK;
+}
+int pq_event_record(void* event, void* stream) {
+  if (!event) return PQ_ERR_INVALID;
+  PQ_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+  return PQ_OK;
+}
+int pq_event_elapsed_ms(void* start, void* end, float* ms) {
+  if (!start || !end || !ms) return PQ_ERR_INVALID;
+  PQ_CUDA_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(end)));
+  PQ_CUDA_TRY(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(end)));
+  return PQ_OK;
+}
+
 // ----------------------------- host-buffer forms -----------------------------
 
 size_t pq_quantize_host_staging_bytes(int B, int Nk, int L, int hd, int G, int dtype) {
@@ -160,6 +184,7 @@ int pq_decode_attention_host(const pq_decode_params* hp, void* staging, size_t s
   d.workspace_bytes = decode_workspace_bytes(B, N, Nk, Nb, G, R, 0);
   d.workspace = c.take(d.workspace_bytes);
   d.num_ctas = 0;
+  d.mid_event = nullptr;
 
   PQ_CUDA_TRY(cudaMemcpyAsync(dq, hp->q, q_b, cudaMemcpyHostToDevice, s));
   if (Nb > 0) {

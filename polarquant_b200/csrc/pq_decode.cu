@@ -743,6 +743,7 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   const int rb = p->Nb > 0 ? p->rbits : 4, tb = p->Nb > 0 ? p->tbits : 4;
   int rc = dispatch_bits<false>(a, rb, tb, p->qk_dtype, p->v_dtype, stream);
   if (rc != PQ_OK) return rc;
+  if (p->mid_event) PQ_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(p->mid_event), stream));
   const unsigned units = static_cast<unsigned>(static_cast<long long>(a.B) * a.Nk * a.head_tiles);
   switch (p->out_dtype) {
     case PQ_F16: merge_partials_kernel<PQ_F16><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;

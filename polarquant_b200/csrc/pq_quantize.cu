@@ -9,7 +9,7 @@
 //   phi   = RN(atan2f(y, x));  if phi < 0: phi = RN(phi + float(2*pi))       (:143-144)
 //   tstep = RN(RN(max phi - min phi) / 2^tbits)                              (:146-147)
 //   theta = min(u8(floor(RN(RN(phi - min phi) / tstep))), 2^tbits - 1)       (:148)
-//   r     = RN(sqrtf(x*x + y*y)), then the same min/max/step/floor/clamp     (:150-153)
+//   r     = RN(sqrtf(RN(x*x) + RN(y*y))), same min/max/step/floor/clamp     (:150-153)
 //   code  = (rho << tbits) + theta                                           (:155)
 //
 // Pair d is channels (d, d + 64) (the (2, 64) view at :141).  Traffic is the
@@ -95,7 +95,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   const T* base = keys + b * sb + h * sh + static_cast<int64_t>(j) * G * sl;
 
   const float wrap = (flags & PQ_QUANT_WRAP_DTYPE) ? E::round(6.283185307179586f) : 6.283185307179586f;
-  const bool norm_sep = (flags & PQ_QUANT_NORM_SEPARATE) != 0;
+  const bool norm_sep = (flags & PQ_QUANT_NORM_FMA) == 0;
 
   constexpr int NR = NI > 0 ? NI : 1;
   float phi[NR][4], rad[NR][4];

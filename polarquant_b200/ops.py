@@ -142,7 +142,8 @@ def _unit_strides(t: torch.Tensor, inner: int):
 def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, rmn, tscale, tmn,
                      value_states: torch.Tensor, attention_mask=None, rbits: int = 4, tbits: int = 4,
                      sm_scale: float | None = None, out_dtype: torch.dtype | None = None,
-                     return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0):
+                     return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0,
+                     mid_event=None):
     """One fused decode-attention step over the polar cache.
 
     Computes what the reference's decode branch computes with separate ops
@@ -234,6 +235,7 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     p.qk_dtype, p.v_dtype, p.out_dtype = qdt, vdt, _DT[out_dtype]
     p.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
     p.num_ctas = num_ctas
+    p.mid_event = mid_event
     lib = _lib.load()
     with torch.cuda.device(dev):
         need = lib.pq_decode_workspace_bytes(bsz, nq, kvh, nb, grp, res, num_ctas)

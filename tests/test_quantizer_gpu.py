@@ -38,7 +38,7 @@ def test_cpu_convention_flag_reproduces_reference_cpu_fixtures(name):
     from polarquant_b200 import _lib
     g = load_golden(name)
     rb, tb, grp = g["meta"]
-    flags = _lib.PQ_QUANT_WRAP_DTYPE | (_lib.PQ_QUANT_NORM_SEPARATE if g["keys"].dtype == torch.float32 else 0)
+    flags = _lib.PQ_QUANT_WRAP_DTYPE
     got = pq.quantize_and_pack_nbit(g["keys"].cuda(), rb, tb, grp, flags=flags)
     mism = float((got[0].cpu() != g["indices"]).float().mean())
     assert mism <= 2e-3, f"{mism:.2e} of the codes differ from the CPU fixture"
