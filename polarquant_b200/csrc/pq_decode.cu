@@ -48,6 +48,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kStep = 16;          // tokens per step
 constexpr int kHeadTile = 8;       // query heads per unit (N of the MMA)
 constexpr int kPartialFloats = kHeadDim * kHeadTile;   // O^T partial, [channel][head]
+constexpr int kPrefetch = 4;       // steps between the L2 prefetch and the use of a tile
 
 struct DecodeArgs {
   const void* q; int64_t q_sb, q_sh;
@@ -164,11 +165,20 @@ __device__ __forceinline__ uint32_t hmul2_hi(uint32_t cs, uint32_t rr) {   // cs
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
 // S^T (16 tokens x 8 heads) += K^ (16 tokens x 128 pair-channels) . q^T for one step.
-// cg / ch: this lane's 16 code bytes of tokens g and g + 8.
+// cg4 / ch4: this lane's 16 code bytes of tokens g and g + 8.  tbl_addr is the 32-bit
+// shared-memory address of the warp's table, 256-byte aligned, so one byte permute
+// builds a full gather address: byte 0 = (theta << 2) | (t << (TBITS + 2)), bytes 1..3
+// from the table address of the row block.
 template <int RBITS, int TBITS>
 __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, const uint4& ch4,
-                                              const char* tbl, uint32_t lane_off,
+                                              uint32_t tbl_addr, uint32_t lane_off,
                                               const uint32_t (&rs2)[4][2], const uint32_t (&rc2)[4][2],
                                               const uint32_t (&qb)[8][2]) {
   constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
@@ -188,16 +198,31 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
       const uint32_t hh = ((sr >= 0 ? ch[w] >> sr : ch[w] << -sr) & RM) | MAGIC;
       const uint32_t rg = hfma2_u(hg, rs2[w][e], rc2[w][e]);
       const uint32_t rh = hfma2_u(hh, rs2[w][e], rc2[w][e]);
-      const char* rowA = tbl + ((4 * w + e) << (TBITS + 4));
-      const char* rowB = tbl + ((4 * w + e + 2) << (TBITS + 4));
-      const uint32_t csAg = *reinterpret_cast<const uint32_t*>(rowA + __byte_perm(og, 0, 0x4440 | e));
-      const uint32_t csBg = *reinterpret_cast<const uint32_t*>(rowB + __byte_perm(og, 0, 0x4440 | (e + 2)));
-      const uint32_t csAh = *reinterpret_cast<const uint32_t*>(rowA + __byte_perm(oh, 0, 0x4440 | e));
-      const uint32_t csBh = *reinterpret_cast<const uint32_t*>(rowB + __byte_perm(oh, 0, 0x4440 | (e + 2)));
+      // row blocks are (16 << TBITS) bytes apart: a multiple of 32, added to a 256-byte aligned base
+      const uint32_t rowA = tbl_addr + ((4 * w + e) << (TBITS + 4));
+      const uint32_t rowB = tbl_addr + ((4 * w + e + 2) << (TBITS + 4));
+      uint32_t csAg, csBg, csAh, csBh;
+      if constexpr (TBITS == 4) {
+        // the row offset is a multiple of 256: OR-able, the permute splices the address
+        csAg = lds_u32(__byte_perm(og, rowA, 0x7650 | e));
+        csBg = lds_u32(__byte_perm(og, rowB, 0x7650 | (e + 2)));
+        csAh = lds_u32(__byte_perm(oh, rowA, 0x7650 | e));
+        csBh = lds_u32(__byte_perm(oh, rowB, 0x7650 | (e + 2)));
+      } else {
+        csAg = lds_u32(rowA + __byte_perm(og, 0, 0x4440 | e));
+        csBg = lds_u32(rowB + __byte_perm(og, 0, 0x4440 | (e + 2)));
+        csAh = lds_u32(rowA + __byte_perm(oh, 0, 0x4440 | e));
+        csBh = lds_u32(rowB + __byte_perm(oh, 0, 0x4440 | (e + 2)));
+      }
       mma_16816_f16(S, hmul2_lo(csAg, rg), hmul2_lo(csAh, rh), hmul2_hi(csBg, rg), hmul2_hi(csBh, rh),
                     qb[2 * w + e][0], qb[2 * w + e][1]);
     }
   }
+}
+
+// Ask the L2 to fetch `bytes` (a multiple of 16) starting at the 16-byte aligned address p.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
 // Query B fragments for the quantised path: k-step s = 2w + e pairs lanes' slots with
@@ -305,17 +330,18 @@ template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
 __global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : 3)
 decode_kernel(const DecodeArgs a) {
   constexpr int A = 1 << TBITS;
-  __shared__ __align__(16) uint32_t s_tbl[kWarps][kPairs * A];
+  __shared__ __align__(256) uint32_t s_tbl[kWarps][kPairs * A];
   __shared__ float s_scr[kWarps][128];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const long long gw = static_cast<long long>(blockIdx.x) * kWarps + warp;
+  if (gw >= a.total_warps) return;
   long long lo = range_lo(gw, a.total_slots, a.total_warps);
   const long long hi = range_lo(gw + 1, a.total_slots, a.total_warps);
   if (lo >= hi) return;
 
-  const char* tbl = reinterpret_cast<const char*>(s_tbl[warp]);
+  const uint32_t tbl_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tbl[warp]));
   const uint32_t lane_off = (static_cast<uint32_t>(t) << (TBITS + 2)) * 0x01010101u;
   constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
   constexpr int KRDT = QDT == PQ_BF16 ? PQ_BF16 : PQ_F16;   // MMA type of the residual-key product
@@ -374,10 +400,26 @@ decode_kernel(const DecodeArgs a) {
         v0[3] = ldg_stream(v_lane + 9 * v_row);   v1[3] = ldg_stream(v_lane + 9 * v_row + 128);
       }
 
+      // The register loads run one step ahead; the L2 is asked for the tiles kPrefetch steps
+      // ahead so those loads find their lines on chip.  One lane issues a bulk prefetch per
+      // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
+      const bool v_dense = v_row == kHeadDim * 2;
+      auto prefetch_step = [&](int step) {
+        if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, kStep * kPairs);
+        if constexpr (!QK_ONLY) {
+          const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row;
+          if (v_dense) { if (lane == 1) prefetch_l2(vt, kStep * kHeadDim * 2); }
+          else if (lane < kStep) prefetch_l2(vt + lane * v_row, kHeadDim * 2);
+        }
+      };
+      for (int ahead = 2; ahead < kPrefetch; ++ahead)
+        if (pos + ahead < qs_end) prefetch_step(pos + ahead);
+
       int in_group = pos % a.spg;
       int grp = pos / a.spg;
       bool fresh = true;
       for (int s = pos; s < qs_end; ++s) {
+        if (s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
         if (fresh || in_group == 0) {
           const int64_t row = static_cast<int64_t>(grp) * kPairs * QES;
           build_angle_table<TBITS, QDT>(s_tbl[warp], s_scr[warp], ts_unit + row, tm_unit + row, lane);
@@ -390,7 +432,7 @@ decode_kernel(const DecodeArgs a) {
         if (more) { ng = ldg_stream(c_lane); nh = ldg_stream(c_lane + 8 * kPairs); }
 
         float S[4] = {0.f, 0.f, 0.f, 0.f};
-        qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl, lane_off, rs2, rc2, qb);
+        qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_off, rs2, rc2, qb);
 
         if constexpr (QK_ONLY) {
           // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
@@ -457,6 +499,12 @@ decode_kernel(const DecodeArgs a) {
             mma_16816<KRDT>(S, kg[c].x, kh[c].x, kg[c].y, kh[c].y, qr[c].x, qr[c].y);
             mma_16816<KRDT>(S, kg[c].z, kh[c].z, kg[c].w, kh[c].w, qr[c].z, qr[c].w);
           }
+          if constexpr (QDT != PQ_F32) {
+            // the reference computes these logits with a matmul in the query dtype and only then
+            // casts to fp32 (models/modeling_llama_polar.py:79): one rounding to that dtype
+            const float2 lo2 = unpack2<QDT>(pack2<QDT>(S[0], S[1])), hi2 = unpack2<QDT>(pack2<QDT>(S[2], S[3]));
+            S[0] = lo2.x; S[1] = lo2.y; S[2] = hi2.x; S[3] = hi2.y;
+          }
           bool mg = false, mh = false;
           if (mask_row) {
             mg = ok_g && mask_row[Lq + r0 + g] == 0;
@@ -499,13 +547,23 @@ __device__ __forceinline__ long long warp_of(long long x, long long total, int n
   return ((x + 1) * nwarps - 1) / total;
 }
 
-// One CTA per unit: combine the unit's partials, normalise, write out (and lse).
+// One CTA per unit combines the unit's partials, normalises and writes out (and lse).
+// kMergeGroups groups of 128 threads (one thread per channel) stride over the partials;
+// every range is non-empty (total_warps <= total_slots), so the partials of a unit are the
+// consecutive warps w0..w1, all with segment 0 except possibly the first.
+constexpr int kMergeGroups = 8;
+static_assert(kMergeGroups == kHeadTile, "each thread group finishes one head");
+
 template <int ODT>
-__global__ void __launch_bounds__(kHeadDim)
+__global__ void __launch_bounds__(kHeadDim * kMergeGroups)
 merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, int64_t o_sh,
                       float* __restrict__ lse) {
+  __shared__ float s_max[kMergeGroups * 4][kHeadTile];
+  __shared__ float s_acc[kMergeGroups][kHeadTile][kHeadDim];
+  __shared__ float s_l[kMergeGroups][kHeadTile];
+
   const long long unit = blockIdx.x;
-  const int ch = threadIdx.x;
+  const int ch = threadIdx.x & (kHeadDim - 1), grp = threadIdx.x >> 7;
   const int ht = static_cast<int>(unit % a.head_tiles);
   const long long bk = unit / a.head_tiles;
   const int kvh = static_cast<int>(bk % a.Nk), b = static_cast<int>(bk / a.Nk);
@@ -515,51 +573,80 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   const long long first = unit * a.slots_per_unit, last = first + a.slots_per_unit - 1;
   const long long w0 = warp_of(first, a.total_slots, a.total_warps);
   const long long w1 = warp_of(last, a.total_slots, a.total_warps);
+  const int seg0 = static_cast<int>(unit - range_lo(w0, a.total_slots, a.total_warps) / a.slots_per_unit);
+  const int n = static_cast<int>(w1 - w0 + 1);
+  auto slot_of = [&](int i) { return (w0 + i) * a.max_seg + (i == 0 ? seg0 : 0); };
 
-  float M[kHeadTile], L[kHeadTile], acc[kHeadTile];
+  // pass 1: per-head maximum of the partial maxima
+  float M[kHeadTile];
 #pragma unroll
-  for (int h = 0; h < kHeadTile; ++h) { M[h] = -INFINITY; L[h] = 0.f; acc[h] = 0.f; }
-
-  for (int pass = 0; pass < 2; ++pass) {
-    for (long long w = w0; w <= w1; ++w) {
-      const long long wlo = range_lo(w, a.total_slots, a.total_warps);
-      const long long whi = range_lo(w + 1, a.total_slots, a.total_warps);
-      if (wlo >= whi) continue;                              // warp without work
-      const int seg = static_cast<int>(unit - wlo / a.slots_per_unit);
-      const long long slot = w * a.max_seg + seg;
-      const float4* ml = reinterpret_cast<const float4*>(a.part_ml + slot * kHeadTile);
-      float2 mlv[kHeadTile];
+  for (int h = 0; h < kHeadTile; ++h) M[h] = -INFINITY;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float4* ml = reinterpret_cast<const float4*>(a.part_ml + slot_of(i) * kHeadTile);
 #pragma unroll
-      for (int i = 0; i < kHeadTile / 2; ++i) {
-        float4 x = ml[i];
-        mlv[2 * i] = make_float2(x.x, x.y); mlv[2 * i + 1] = make_float2(x.z, x.w);
-      }
-      if (pass == 0) {
-#pragma unroll
-        for (int h = 0; h < kHeadTile; ++h) M[h] = fmaxf(M[h], mlv[h].x);
-      } else {
-        const float4* po = reinterpret_cast<const float4*>(a.part_o + slot * kPartialFloats + ch * kHeadTile);
-        float4 o0 = po[0], o1 = po[1];
-        const float ov[kHeadTile] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-#pragma unroll
-        for (int h = 0; h < kHeadTile; ++h) {
-          const float wgt = mlv[h].x == -INFINITY ? 0.f : exp2_approx(mlv[h].x - M[h]);
-          L[h] = fmaf(wgt, mlv[h].y, L[h]);
-          acc[h] = fmaf(wgt, ov[h], acc[h]);
-        }
-      }
+    for (int k = 0; k < kHeadTile / 2; ++k) {
+      const float4 x = ml[k];
+      M[2 * k] = fmaxf(M[2 * k], x.x); M[2 * k + 1] = fmaxf(M[2 * k + 1], x.z);
     }
   }
 #pragma unroll
   for (int h = 0; h < kHeadTile; ++h) {
-    if (h < nheads) {
-      const float val = acc[h] / L[h];
-      const int64_t off = b * o_sb + (head0 + h) * o_sh + ch;
-      if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = val;
-      else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(val);
-      else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
-      if (lse && ch == 0)
-        lse[static_cast<int64_t>(b) * a.N + head0 + h] = (M[h] + log2f(L[h])) * 0.6931471805599453f;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) M[h] = fmaxf(M[h], __shfl_xor_sync(0xffffffffu, M[h], o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int h = 0; h < kHeadTile; ++h) s_max[threadIdx.x >> 5][h] = M[h];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < kHeadTile; ++h) {
+    float m = s_max[0][h];
+    for (int w = 1; w < kMergeGroups * 4; ++w) m = fmaxf(m, s_max[w][h]);
+    M[h] = m;
+  }
+
+  // pass 2: weighted sums, the groups striding over the partials
+  float L[kHeadTile], acc[kHeadTile];
+#pragma unroll
+  for (int h = 0; h < kHeadTile; ++h) { L[h] = 0.f; acc[h] = 0.f; }
+  for (int i = grp; i < n; i += kMergeGroups) {
+    const long long slot = slot_of(i);
+    const float4* ml = reinterpret_cast<const float4*>(a.part_ml + slot * kHeadTile);
+    const float4* po = reinterpret_cast<const float4*>(a.part_o + slot * kPartialFloats + ch * kHeadTile);
+    const float4 o0 = po[0], o1 = po[1];
+    const float ov[kHeadTile] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+    for (int k = 0; k < kHeadTile / 2; ++k) {
+      const float4 x = ml[k];
+      const float wa = x.x == -INFINITY ? 0.f : exp2_approx(x.x - M[2 * k]);
+      const float wb = x.z == -INFINITY ? 0.f : exp2_approx(x.z - M[2 * k + 1]);
+      L[2 * k] = fmaf(wa, x.y, L[2 * k]); L[2 * k + 1] = fmaf(wb, x.w, L[2 * k + 1]);
+      acc[2 * k] = fmaf(wa, ov[2 * k], acc[2 * k]); acc[2 * k + 1] = fmaf(wb, ov[2 * k + 1], acc[2 * k + 1]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < kHeadTile; ++h) s_acc[grp][h][ch] = acc[h];
+  if (ch == 0) {
+#pragma unroll
+    for (int h = 0; h < kHeadTile; ++h) s_l[grp][h] = L[h];
+  }
+  __syncthreads();
+  // group g finishes head g (kMergeGroups == kHeadTile)
+  const int h = grp;
+  if (h < nheads) {
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMergeGroups; ++k) { l += s_l[k][h]; o += s_acc[k][h][ch]; }
+    const float val = o / l;
+    const int64_t off = b * o_sb + (head0 + h) * o_sh + ch;
+    if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = val;
+    else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(val);
+    else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
+    if (lse && ch == 0) {
+      float mh = s_max[0][h];
+      for (int w = 1; w < kMergeGroups * 4; ++w) mh = fmaxf(mh, s_max[w][h]);
+      lse[static_cast<int64_t>(b) * a.N + head0 + h] = (mh + log2f(l)) * 0.6931471805599453f;
     }
   }
 }
@@ -619,7 +706,9 @@ void plan(DecodeArgs& a, int ctas_per_sm, int num_ctas) {
                            (static_cast<long long>(kMinSlotsPerWarp) * kWarps);
   if (num_ctas <= 0 && ctas > useful) ctas = useful;
   if (ctas < 1) ctas = 1;
-  a.total_warps = static_cast<int>(ctas * kWarps);
+  long long warps = ctas * kWarps;
+  if (warps > a.total_slots) warps = a.total_slots > 0 ? a.total_slots : 1;   // every warp range is non-empty
+  a.total_warps = static_cast<int>(warps);
   const long long per_warp = (a.total_slots + a.total_warps - 1) / a.total_warps;
   a.max_seg = static_cast<int>((per_warp + a.slots_per_unit - 1) / (a.slots_per_unit > 0 ? a.slots_per_unit : 1)) + 1;
 }
@@ -631,7 +720,7 @@ size_t workspace_bytes_for(const DecodeArgs& a) {
 
 template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
 int launch_decode(const DecodeArgs& a, cudaStream_t s) {
-  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<a.total_warps / kWarps, kThreads, 0, s>>>(a);
+  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, 0, s>>>(a);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
@@ -746,9 +835,9 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (p->mid_event) PQ_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(p->mid_event), stream));
   const unsigned units = static_cast<unsigned>(static_cast<long long>(a.B) * a.Nk * a.head_tiles);
   switch (p->out_dtype) {
-    case PQ_F16: merge_partials_kernel<PQ_F16><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
-    case PQ_BF16: merge_partials_kernel<PQ_BF16><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
-    default: merge_partials_kernel<PQ_F32><<<units, kHeadDim, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    case PQ_F16: merge_partials_kernel<PQ_F16><<<units, kHeadDim * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    case PQ_BF16: merge_partials_kernel<PQ_BF16><<<units, kHeadDim * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    default: merge_partials_kernel<PQ_F32><<<units, kHeadDim * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
   }
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;

