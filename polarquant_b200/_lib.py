@@ -11,7 +11,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libpolarquant_b200.so")
+# POLARQUANT_B200_LIB points at an alternative build of the same library (kernel tuning experiments)
+LIB_PATH = os.environ.get("POLARQUANT_B200_LIB") or os.path.join(_HERE, "csrc", "libpolarquant_b200.so")
 
 PQ_F16, PQ_BF16, PQ_F32 = 0, 1, 2
 PQ_OK = 0

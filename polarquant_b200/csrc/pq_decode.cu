@@ -48,7 +48,10 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kStep = 16;          // tokens per step
 constexpr int kHeadTile = 8;       // query heads per unit (N of the MMA)
 constexpr int kPartialFloats = kHeadDim * kHeadTile;   // O^T partial, [channel][head]
-constexpr int kPrefetch = 4;       // steps between the L2 prefetch and the use of a tile
+#ifndef PQ_PREFETCH_STEPS
+#define PQ_PREFETCH_STEPS 4
+#endif
+constexpr int kPrefetch = PQ_PREFETCH_STEPS;   // steps between the L2 prefetch and the use of a tile (0 = off)
 
 struct DecodeArgs {
   const void* q; int64_t q_sb, q_sh;
@@ -72,39 +75,65 @@ __device__ __forceinline__ long long range_lo(long long w, long long total, int 
   return (w * total) / nwarps;
 }
 
-// ---- shared-memory table of (cos, sin) bin centres for one token group ----------
-// word index = (row_pos << TBITS) + level, row_pos = 4 * (d % 16) + d / 16, so the
-// four rows a warp gathers from in one instruction (pairs 16t + m, t = 0..3) are
-// adjacent and the lane-dependent part of the byte offset fits in the low byte.
-template <int TBITS, int SDT>
-__device__ __forceinline__ void build_angle_table(uint32_t* tbl, float* scr, const void* tscale_row,
-                                                  const void* tmn_row, int lane) {
-  constexpr int A = 1 << TBITS;
-  __syncwarp();
-  if constexpr (SDT == PQ_F32) {
-    const float* ts = static_cast<const float*>(tscale_row);
-    const float* tm = static_cast<const float*>(tmn_row);
-    scr[lane] = ts[lane]; scr[lane + 32] = ts[lane + 32];
-    scr[64 + lane] = tm[lane]; scr[96 + lane] = tm[lane + 32];
-  } else {
-    const uint32_t* ts = static_cast<const uint32_t*>(tscale_row);
-    const uint32_t* tm = static_cast<const uint32_t*>(tmn_row);
-    float2 a = unpack2<SDT>(ts[lane]), b = unpack2<SDT>(tm[lane]);
-    scr[2 * lane] = a.x; scr[2 * lane + 1] = a.y;
-    scr[64 + 2 * lane] = b.x; scr[64 + 2 * lane + 1] = b.y;
+// ---- per-group constants staged in shared memory ------------------------------------
+// The four scale rows of a token group (rscale, rmn, tscale, tmn: 4 x 64 elements) are
+// copied global -> shared with cp.async one group ahead of their use, double-buffered,
+// so the dependent table build never waits on DRAM.
+template <int SDT>
+__device__ __forceinline__ void stage_scales_async(uint32_t dst_addr, const char* rs_row, const char* rm_row,
+                                                   const char* ts_row, const char* tm_row, int lane) {
+  constexpr int kChunks = (SDT == PQ_F32 ? 16 : 8);          // 16-byte chunks per row
+#pragma unroll
+  for (int i = lane; i < 4 * kChunks; i += 32) {
+    const int tensor = i / kChunks, chunk = i % kChunks;
+    const char* src = (tensor == 0 ? rs_row : tensor == 1 ? rm_row : tensor == 2 ? ts_row : tm_row) + 16 * chunk;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_addr + 16u * i), "l"(src) : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void wait_staged() {
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncwarp();
-#pragma unroll 4
-  for (int it = 0; it < 2 * A; ++it) {
-    const int idx = it * 32 + lane;
-    const int pos = idx >> TBITS, lvl = idx & (A - 1);
-    const int d = 16 * (pos & 3) + (pos >> 2);
-    float phi = fmaf(scr[d], static_cast<float>(lvl) + 0.5f, scr[64 + d]);
-    // reduce to [-pi, pi] before the hardware approximations
-    float n = rintf(phi * 0.15915494309189535f);
-    phi = fmaf(n, -6.28318548202514648f, phi);
-    phi = fmaf(n, 1.7484555e-7f, phi);
-    tbl[idx] = pack2<PQ_F16>(__cosf(phi), __sinf(phi));
+}
+
+// ---- shared-memory table of (cos, sin) bin centres for one token group ----------
+// word index = (row_pos << TBITS) + (level ^ x), row_pos = 4 * (d % 16) + d / 16, so the
+// four rows a warp gathers from in one instruction (pairs 16t + m, t = 0..3) are adjacent
+// and the lane-dependent part of the byte offset fits in the low byte.  The XOR with
+// x = (m / 2 + 8 * (t / 2)) mod 2^TBITS (m = d % 16, t = d / 16) spreads the stores of the
+// build, where lane l owns pairs 2l and 2l + 1, over all banks; the gather side folds
+// the same XOR into the constant it already applies to the code bytes.
+template <int TBITS> __device__ __forceinline__ uint32_t table_xor(int m, int t) {
+  return static_cast<uint32_t>((m >> 1) + 8 * (t >> 1)) & ((1u << TBITS) - 1u);
+}
+
+template <int TBITS, int SDT>
+__device__ __forceinline__ void build_angle_table(uint32_t tbl_addr, const char* sc, int lane) {
+  constexpr int A = 1 << TBITS;
+  constexpr int ROW = 64 * (SDT == PQ_F32 ? 4 : 2);          // bytes per staged scale row
+  float ts[2], tm[2];
+  if constexpr (SDT == PQ_F32) {
+    const float2 a = *reinterpret_cast<const float2*>(sc + 2 * ROW + 8 * lane);
+    const float2 b = *reinterpret_cast<const float2*>(sc + 3 * ROW + 8 * lane);
+    ts[0] = a.x; ts[1] = a.y; tm[0] = b.x; tm[1] = b.y;
+  } else {
+    const float2 a = unpack2<SDT>(*reinterpret_cast<const uint32_t*>(sc + 2 * ROW + 4 * lane));
+    const float2 b = unpack2<SDT>(*reinterpret_cast<const uint32_t*>(sc + 3 * ROW + 4 * lane));
+    ts[0] = a.x; ts[1] = a.y; tm[0] = b.x; tm[1] = b.y;
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int d = 2 * lane + half, m = d & 15, t = d >> 4;
+    const uint32_t base = tbl_addr + (static_cast<uint32_t>(4 * m + t) << (TBITS + 2));
+    const uint32_t bx = base ^ (table_xor<TBITS>(m, t) << 2);
+#pragma unroll
+    for (int k = 0; k < A; ++k) {
+      // |phi| stays small (a quantiser emits [0, 2 pi]); the hardware sine/cosine take the
+      // fraction of phi / (2 pi), precise to ~1e-6 for |phi| < 100, far below fp16 spacing
+      const float phi = fmaf(ts[half], static_cast<float>(k) + 0.5f, tm[half]);
+      const uint32_t cs = pack2<PQ_F16>(__cosf(phi), __sinf(phi));
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(bx ^ (static_cast<uint32_t>(k) << 2)), "r"(cs) : "memory");
+    }
   }
   __syncwarp();
 }
@@ -135,11 +164,12 @@ template <int SDT> __device__ __forceinline__ void load16f(const void* p, float 
 // c = rmn + (0.5 - 2^RBITS) * rscale.  rs2/rc2[w][e] hold the constants of pairs
 // (4w + e, 4w + e + 2), the two code bytes one HFMA2 handles.
 template <int RBITS, int SDT>
-__device__ __forceinline__ void load_radius_consts(const void* rscale_row, const void* rmn_row, int t,
+__device__ __forceinline__ void load_radius_consts(const char* sc, int t,
                                                    uint32_t (&rs2)[4][2], uint32_t (&rc2)[4][2]) {
+  constexpr int ES = SDT == PQ_F32 ? 4 : 2;
   float rs[16], rm[16];
-  load16f<SDT>(static_cast<const char*>(rscale_row) + 16 * t * (SDT == PQ_F32 ? 4 : 2), rs);
-  load16f<SDT>(static_cast<const char*>(rmn_row) + 16 * t * (SDT == PQ_F32 ? 4 : 2), rm);
+  load16f<SDT>(sc + 16 * t * ES, rs);
+  load16f<SDT>(sc + 64 * ES + 16 * t * ES, rm);
   const float k = 0.5f - static_cast<float>(1 << RBITS);
 #pragma unroll
   for (int w = 0; w < 4; ++w)
@@ -174,11 +204,12 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
 // S^T (16 tokens x 8 heads) += K^ (16 tokens x 128 pair-channels) . q^T for one step.
 // cg4 / ch4: this lane's 16 code bytes of tokens g and g + 8.  tbl_addr is the 32-bit
 // shared-memory address of the warp's table, 256-byte aligned, so one byte permute
-// builds a full gather address: byte 0 = (theta << 2) | (t << (TBITS + 2)), bytes 1..3
-// from the table address of the row block.
+// builds a full gather address: byte 0 = ((theta ^ x) << 2) | (t << (TBITS + 2)), bytes 1..3
+// from the table address of the row block.  lane_xor[w] carries, per code byte of word w,
+// (x << 2) | (t << (TBITS + 2)) for this lane's t.
 template <int RBITS, int TBITS>
 __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, const uint4& ch4,
-                                              uint32_t tbl_addr, uint32_t lane_off,
+                                              uint32_t tbl_addr, const uint32_t (&lane_xor)[4],
                                               const uint32_t (&rs2)[4][2], const uint32_t (&rc2)[4][2],
                                               const uint32_t (&qb)[8][2]) {
   constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
@@ -189,8 +220,8 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
   const uint32_t ch[4] = {ch4.x, ch4.y, ch4.z, ch4.w};
 #pragma unroll
   for (int w = 0; w < 4; ++w) {
-    const uint32_t og = ((cg[w] << 2) & TM4) | lane_off;
-    const uint32_t oh = ((ch[w] << 2) & TM4) | lane_off;
+    const uint32_t og = ((cg[w] << 2) & TM4) ^ lane_xor[w];
+    const uint32_t oh = ((ch[w] << 2) & TM4) ^ lane_xor[w];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int sr = 8 * e + TBITS + RBITS - 10;                  // compile-time after unrolling
@@ -330,8 +361,10 @@ template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
 __global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : 3)
 decode_kernel(const DecodeArgs a) {
   constexpr int A = 1 << TBITS;
+  constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
+  constexpr int kStageBytes = 4 * kPairs * QES;   // four scale rows of one group
   __shared__ __align__(256) uint32_t s_tbl[kWarps][kPairs * A];
-  __shared__ float s_scr[kWarps][128];
+  __shared__ __align__(16) char s_sc[kWarps][2][kStageBytes];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -342,8 +375,13 @@ decode_kernel(const DecodeArgs a) {
   if (lo >= hi) return;
 
   const uint32_t tbl_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tbl[warp]));
-  const uint32_t lane_off = (static_cast<uint32_t>(t) << (TBITS + 2)) * 0x01010101u;
-  constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
+  uint32_t lane_xor[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    lane_xor[w] = (static_cast<uint32_t>(t) << (TBITS + 2)) * 0x01010101u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) lane_xor[w] |= (table_xor<TBITS>(4 * w + i, t) << 2) << (8 * i);
+  }
   constexpr int KRDT = QDT == PQ_BF16 ? PQ_BF16 : PQ_F16;   // MMA type of the residual-key product
 
   long long unit = lo / a.slots_per_unit;
@@ -417,13 +455,25 @@ decode_kernel(const DecodeArgs a) {
 
       int in_group = pos % a.spg;
       int grp = pos / a.spg;
+      const int last_grp = (qs_end - 1) / a.spg;
+      const uint32_t sc_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_sc[warp][0]));
+      auto stage_group = [&](int gidx, int buf) {
+        const int64_t row = static_cast<int64_t>(gidx) * kPairs * QES;
+        stage_scales_async<QDT>(sc_addr + buf * kStageBytes, rs_unit + row, rm_unit + row, ts_unit + row,
+                                tm_unit + row, lane);
+      };
+      __syncwarp();                       // earlier readers of the staging buffers are done
+      int buf = 0;
+      stage_group(grp, buf);
       bool fresh = true;
       for (int s = pos; s < qs_end; ++s) {
-        if (s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
+        if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
         if (fresh || in_group == 0) {
-          const int64_t row = static_cast<int64_t>(grp) * kPairs * QES;
-          build_angle_table<TBITS, QDT>(s_tbl[warp], s_scr[warp], ts_unit + row, tm_unit + row, lane);
-          load_radius_consts<RBITS, QDT>(rs_unit + row, rm_unit + row, t, rs2, rc2);
+          wait_staged();                  // this group's scales have landed; all lanes are past the old table
+          if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
+          build_angle_table<TBITS, QDT>(tbl_addr, s_sc[warp][buf], lane);
+          load_radius_consts<RBITS, QDT>(s_sc[warp][buf], t, rs2, rc2);
+          buf ^= 1;
           fresh = false;
         }
         const bool more = s + 1 < qs_end;
@@ -432,7 +482,7 @@ decode_kernel(const DecodeArgs a) {
         if (more) { ng = ldg_stream(c_lane); nh = ldg_stream(c_lane + 8 * kPairs); }
 
         float S[4] = {0.f, 0.f, 0.f, 0.f};
-        qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_off, rs2, rc2, qb);
+        qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
 
         if constexpr (QK_ONLY) {
           // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
