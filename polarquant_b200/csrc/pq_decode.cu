@@ -186,69 +186,69 @@ __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) 
                       *reinterpret_cast<__half2*>(&c));
   return *reinterpret_cast<uint32_t*>(&r);
 }
-__device__ __forceinline__ uint32_t hmul2_lo(uint32_t cs, uint32_t rr) {   // cs * (rr.lo, rr.lo)
+// cs * (rr.lo, rr.lo) and cs * (rr.hi, rr.hi): the half selection folds into the multiply
+__device__ __forceinline__ uint32_t hmul2_lo(uint32_t cs, uint32_t rr) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&cs), __low2half2(*reinterpret_cast<__half2*>(&rr)));
   return *reinterpret_cast<uint32_t*>(&r);
 }
-__device__ __forceinline__ uint32_t hmul2_hi(uint32_t cs, uint32_t rr) {   // cs * (rr.hi, rr.hi)
+__device__ __forceinline__ uint32_t hmul2_hi(uint32_t cs, uint32_t rr) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&cs), __high2half2(*reinterpret_cast<__half2*>(&rr)));
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+template <int IMM> __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
   return v;
 }
 
+// One k-step of S^T += K^ . q^T: code bytes E and E + 2 of word W of the two tokens this
+// lane holds (pairs 16t + 4W + E and + 2), dequantised and fed to one MMA.
+//   * gather address = byte permute splicing ((theta ^ x) << 2) | (t << (TBITS + 2)) from the
+//     prepared code word into the low byte of the 256-byte aligned table address; the row
+//     block offset (4W + E) << (TBITS + 4) rides in the load's immediate field;
+//   * radius = HFMA2 on the two code bytes at once; the multiply selects the half it needs.
+template <int RBITS, int TBITS, int W, int E>
+__device__ __forceinline__ void qk_kstep(float (&S)[4], uint32_t cgw, uint32_t chw, uint32_t og, uint32_t oh,
+                                         uint32_t tbl_addr, uint32_t rs, uint32_t rc, uint32_t qb0, uint32_t qb1) {
+  constexpr int MSH = 10 - RBITS;                                // mantissa shift of rho
+  constexpr uint32_t RM = (((1u << RBITS) - 1u) << MSH) * 0x00010001u;
+  constexpr uint32_t MAGIC = (static_cast<uint32_t>(15 + RBITS) << 10) * 0x00010001u;
+  constexpr int SR = 8 * E + TBITS + RBITS - 10;
+  constexpr int ROW_A = (4 * W + E) << (TBITS + 4), ROW_B = (4 * W + E + 2) << (TBITS + 4);
+  const uint32_t hg = ((SR >= 0 ? cgw >> (SR >= 0 ? SR : 0) : cgw << (SR < 0 ? -SR : 0)) & RM) | MAGIC;
+  const uint32_t hh = ((SR >= 0 ? chw >> (SR >= 0 ? SR : 0) : chw << (SR < 0 ? -SR : 0)) & RM) | MAGIC;
+  const uint32_t rg = hfma2_u(hg, rs, rc);
+  const uint32_t rh = hfma2_u(hh, rs, rc);
+  const uint32_t csAg = lds_u32_imm<ROW_A>(__byte_perm(og, tbl_addr, 0x7650 | E));
+  const uint32_t csBg = lds_u32_imm<ROW_B>(__byte_perm(og, tbl_addr, 0x7650 | (E + 2)));
+  const uint32_t csAh = lds_u32_imm<ROW_A>(__byte_perm(oh, tbl_addr, 0x7650 | E));
+  const uint32_t csBh = lds_u32_imm<ROW_B>(__byte_perm(oh, tbl_addr, 0x7650 | (E + 2)));
+  mma_16816_f16(S, hmul2_lo(csAg, rg), hmul2_lo(csAh, rh), hmul2_hi(csBg, rg), hmul2_hi(csBh, rh), qb0, qb1);
+}
+
 // S^T (16 tokens x 8 heads) += K^ (16 tokens x 128 pair-channels) . q^T for one step.
-// cg4 / ch4: this lane's 16 code bytes of tokens g and g + 8.  tbl_addr is the 32-bit
-// shared-memory address of the warp's table, 256-byte aligned, so one byte permute
-// builds a full gather address: byte 0 = ((theta ^ x) << 2) | (t << (TBITS + 2)), bytes 1..3
-// from the table address of the row block.  lane_xor[w] carries, per code byte of word w,
-// (x << 2) | (t << (TBITS + 2)) for this lane's t.
+// cg4 / ch4: this lane's 16 code bytes of tokens g and g + 8.  lane_xor[w] carries, per code
+// byte of word w, (x << 2) | (t << (TBITS + 2)) for this lane's t (x: the table's bank swizzle).
 template <int RBITS, int TBITS>
 __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, const uint4& ch4,
                                               uint32_t tbl_addr, const uint32_t (&lane_xor)[4],
                                               const uint32_t (&rs2)[4][2], const uint32_t (&rc2)[4][2],
                                               const uint32_t (&qb)[8][2]) {
   constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
-  constexpr int MSH = 10 - RBITS;                                // mantissa shift of rho
-  constexpr uint32_t RM = (((1u << RBITS) - 1u) << MSH) * 0x00010001u;
-  constexpr uint32_t MAGIC = (static_cast<uint32_t>(15 + RBITS) << 10) * 0x00010001u;
-  const uint32_t cg[4] = {cg4.x, cg4.y, cg4.z, cg4.w};
-  const uint32_t ch[4] = {ch4.x, ch4.y, ch4.z, ch4.w};
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    const uint32_t og = ((cg[w] << 2) & TM4) ^ lane_xor[w];
-    const uint32_t oh = ((ch[w] << 2) & TM4) ^ lane_xor[w];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int sr = 8 * e + TBITS + RBITS - 10;                  // compile-time after unrolling
-      const uint32_t hg = ((sr >= 0 ? cg[w] >> sr : cg[w] << -sr) & RM) | MAGIC;
-      const uint32_t hh = ((sr >= 0 ? ch[w] >> sr : ch[w] << -sr) & RM) | MAGIC;
-      const uint32_t rg = hfma2_u(hg, rs2[w][e], rc2[w][e]);
-      const uint32_t rh = hfma2_u(hh, rs2[w][e], rc2[w][e]);
-      // row blocks are (16 << TBITS) bytes apart: a multiple of 32, added to a 256-byte aligned base
-      const uint32_t rowA = tbl_addr + ((4 * w + e) << (TBITS + 4));
-      const uint32_t rowB = tbl_addr + ((4 * w + e + 2) << (TBITS + 4));
-      uint32_t csAg, csBg, csAh, csBh;
-      if constexpr (TBITS == 4) {
-        // the row offset is a multiple of 256: OR-able, the permute splices the address
-        csAg = lds_u32(__byte_perm(og, rowA, 0x7650 | e));
-        csBg = lds_u32(__byte_perm(og, rowB, 0x7650 | (e + 2)));
-        csAh = lds_u32(__byte_perm(oh, rowA, 0x7650 | e));
-        csBh = lds_u32(__byte_perm(oh, rowB, 0x7650 | (e + 2)));
-      } else {
-        csAg = lds_u32(rowA + __byte_perm(og, 0, 0x4440 | e));
-        csBg = lds_u32(rowB + __byte_perm(og, 0, 0x4440 | (e + 2)));
-        csAh = lds_u32(rowA + __byte_perm(oh, 0, 0x4440 | e));
-        csBh = lds_u32(rowB + __byte_perm(oh, 0, 0x4440 | (e + 2)));
-      }
-      mma_16816_f16(S, hmul2_lo(csAg, rg), hmul2_lo(csAh, rh), hmul2_hi(csBg, rg), hmul2_hi(csBh, rh),
-                    qb[2 * w + e][0], qb[2 * w + e][1]);
-    }
+#define PQ_WORD(W, CG, CH)                                                                                     \
+  {                                                                                                            \
+    const uint32_t og = (((CG) << 2) & TM4) ^ lane_xor[W];                                                     \
+    const uint32_t oh = (((CH) << 2) & TM4) ^ lane_xor[W];                                                     \
+    qk_kstep<RBITS, TBITS, W, 0>(S, CG, CH, og, oh, tbl_addr, rs2[W][0], rc2[W][0], qb[2 * W][0], qb[2 * W][1]); \
+    qk_kstep<RBITS, TBITS, W, 1>(S, CG, CH, og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0],           \
+                                 qb[2 * W + 1][1]);                                                            \
   }
+  PQ_WORD(0, cg4.x, ch4.x)
+  PQ_WORD(1, cg4.y, ch4.y)
+  PQ_WORD(2, cg4.z, ch4.z)
+  PQ_WORD(3, cg4.w, ch4.w)
+#undef PQ_WORD
 }
 
 // Ask the L2 to fetch `bytes` (a multiple of 16) starting at the 16-byte aligned address p.
@@ -429,13 +429,13 @@ decode_kernel(const DecodeArgs a) {
       uint4 cg = ldg_stream(c_lane), ch = ldg_stream(c_lane + 8 * kPairs);
       uint4 v0[4], v1[4];
       // lane's value bytes: tokens (2t, 2t+1, 2t+8, 2t+9), channels 8g.. and 64+8g..
-      const char* v_lane = nullptr;
+      const char* vp[4] = {nullptr, nullptr, nullptr, nullptr};
+      const int64_t v_step = kStep * v_row;
       if constexpr (!QK_ONLY) {
-        v_lane = v_unit + static_cast<int64_t>(pos) * kStep * v_row + (2 * t) * v_row + 16 * g;
-        v0[0] = ldg_stream(v_lane);               v1[0] = ldg_stream(v_lane + 128);
-        v0[1] = ldg_stream(v_lane + v_row);       v1[1] = ldg_stream(v_lane + v_row + 128);
-        v0[2] = ldg_stream(v_lane + 8 * v_row);   v1[2] = ldg_stream(v_lane + 8 * v_row + 128);
-        v0[3] = ldg_stream(v_lane + 9 * v_row);   v1[3] = ldg_stream(v_lane + 9 * v_row + 128);
+        const char* v_lane = v_unit + static_cast<int64_t>(pos) * kStep * v_row + (2 * t) * v_row + 16 * g;
+        vp[0] = v_lane; vp[1] = v_lane + v_row; vp[2] = v_lane + 8 * v_row; vp[3] = v_lane + 9 * v_row;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { v0[i] = ldg_stream(vp[i]); v1[i] = ldg_stream(vp[i] + 128); }
       }
 
       // The register loads run one step ahead; the L2 is asked for the tiles kPrefetch steps
@@ -476,10 +476,10 @@ decode_kernel(const DecodeArgs a) {
           buf ^= 1;
           fresh = false;
         }
+        // next tile; the last step of the segment re-reads its own tile rather than branching
         const bool more = s + 1 < qs_end;
-        uint4 ng = cg, nh = ch;
-        c_lane += kStep * kPairs;
-        if (more) { ng = ldg_stream(c_lane); nh = ldg_stream(c_lane + 8 * kPairs); }
+        if (more) c_lane += kStep * kPairs;
+        const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
 
         float S[4] = {0.f, 0.f, 0.f, 0.f};
         qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
@@ -495,17 +495,16 @@ decode_kernel(const DecodeArgs a) {
           if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
           uint32_t b0, b1;
           softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
-          v_lane += kStep * v_row;
+          if (more) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) vp[i] += v_step;
+          }
           pv_half<VDT>(O, 0, v0, b0, b1);
-          if (more) {
-            v0[0] = ldg_stream(v_lane);             v0[1] = ldg_stream(v_lane + v_row);
-            v0[2] = ldg_stream(v_lane + 8 * v_row); v0[3] = ldg_stream(v_lane + 9 * v_row);
-          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v0[i] = ldg_stream(vp[i]);
           pv_half<VDT>(O, 4, v1, b0, b1);
-          if (more) {
-            v1[0] = ldg_stream(v_lane + 128);             v1[1] = ldg_stream(v_lane + v_row + 128);
-            v1[2] = ldg_stream(v_lane + 8 * v_row + 128); v1[3] = ldg_stream(v_lane + 9 * v_row + 128);
-          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v1[i] = ldg_stream(vp[i] + 128);
         }
         cg = ng; ch = nh;
         if (++in_group == a.spg) { in_group = 0; ++grp; }
@@ -597,23 +596,31 @@ __device__ __forceinline__ long long warp_of(long long x, long long total, int n
   return ((x + 1) * nwarps - 1) / total;
 }
 
-// One CTA per unit combines the unit's partials, normalises and writes out (and lse).
-// kMergeGroups groups of 128 threads (one thread per channel) stride over the partials;
-// every range is non-empty (total_warps <= total_slots), so the partials of a unit are the
-// consecutive warps w0..w1, all with segment 0 except possibly the first.
+// Combine a unit's partials, normalise, write out (and lse).  Grid (units, 2): each CTA owns
+// 64 of the 128 channels.  Pass 1 finds the per-head maximum over the unit's partials; pass 2
+// stages, chunk by chunk, the weights 2^(m_i - M) and weighted sums once per (partial, head)
+// in shared memory, and 8 groups of 64 threads stride over the partial rows, four rows in
+// flight per thread, with one FMA per (partial, head, channel).  Every warp range of the
+// attention kernel is non-empty (total_warps <= total_slots), so the partials of a unit are
+// the consecutive warps w0..w1, all with segment 0 except possibly the first.
 constexpr int kMergeGroups = 8;
+constexpr int kMergeCh = 64;
+constexpr int kMergeChunk = 128;      // partials whose weights are staged at a time
 static_assert(kMergeGroups == kHeadTile, "each thread group finishes one head");
 
 template <int ODT>
-__global__ void __launch_bounds__(kHeadDim * kMergeGroups)
+__global__ void __launch_bounds__(kMergeCh * kMergeGroups)
 merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, int64_t o_sh,
                       float* __restrict__ lse) {
-  __shared__ float s_max[kMergeGroups * 4][kHeadTile];
-  __shared__ float s_acc[kMergeGroups][kHeadTile][kHeadDim];
-  __shared__ float s_l[kMergeGroups][kHeadTile];
+  constexpr int kThreadsM = kMergeCh * kMergeGroups;
+  __shared__ float s_w[kMergeChunk][kHeadTile];                // weight of partial i for head h
+  __shared__ float s_red[kThreadsM / 32][kHeadTile];
+  __shared__ float s_acc[kMergeGroups][kHeadTile][kMergeCh];
+  __shared__ float s_max[kHeadTile], s_sum[kHeadTile];
 
   const long long unit = blockIdx.x;
-  const int ch = threadIdx.x & (kHeadDim - 1), grp = threadIdx.x >> 7;
+  const int chl = threadIdx.x & (kMergeCh - 1), grp = threadIdx.x / kMergeCh;
+  const int ch = blockIdx.y * kMergeCh + chl;
   const int ht = static_cast<int>(unit % a.head_tiles);
   const long long bk = unit / a.head_tiles;
   const int kvh = static_cast<int>(bk % a.Nk), b = static_cast<int>(bk / a.Nk);
@@ -627,77 +634,84 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   const int n = static_cast<int>(w1 - w0 + 1);
   auto slot_of = [&](int i) { return (w0 + i) * a.max_seg + (i == 0 ? seg0 : 0); };
 
-  // pass 1: per-head maximum of the partial maxima
-  float M[kHeadTile];
-#pragma unroll
-  for (int h = 0; h < kHeadTile; ++h) M[h] = -INFINITY;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float4* ml = reinterpret_cast<const float4*>(a.part_ml + slot_of(i) * kHeadTile);
-#pragma unroll
-    for (int k = 0; k < kHeadTile / 2; ++k) {
-      const float4 x = ml[k];
-      M[2 * k] = fmaxf(M[2 * k], x.x); M[2 * k + 1] = fmaxf(M[2 * k + 1], x.z);
+  // ---- pass 1: per-head maximum; thread (i, h) pairs stride over the n x 8 (m, l) entries ----
+  {
+    const int h = threadIdx.x & (kHeadTile - 1);
+    float m = -INFINITY;
+    for (int i = threadIdx.x >> 3; i < n; i += kThreadsM >> 3) m = fmaxf(m, a.part_ml[slot_of(i) * kHeadTile + h].x);
+    // lanes with equal (lane & 7) hold the same head
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+    if ((threadIdx.x & 31) < kHeadTile) s_red[threadIdx.x >> 5][h] = m;
+    __syncthreads();
+    if (threadIdx.x < kHeadTile) {
+      float mm = s_red[0][threadIdx.x];
+      for (int w = 1; w < kThreadsM / 32; ++w) mm = fmaxf(mm, s_red[w][threadIdx.x]);
+      s_max[threadIdx.x] = mm;
+      s_sum[threadIdx.x] = 0.f;
     }
-  }
-#pragma unroll
-  for (int h = 0; h < kHeadTile; ++h) {
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) M[h] = fmaxf(M[h], __shfl_xor_sync(0xffffffffu, M[h], o));
-  }
-  if ((threadIdx.x & 31) == 0) {
-#pragma unroll
-    for (int h = 0; h < kHeadTile; ++h) s_max[threadIdx.x >> 5][h] = M[h];
-  }
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < kHeadTile; ++h) {
-    float m = s_max[0][h];
-    for (int w = 1; w < kMergeGroups * 4; ++w) m = fmaxf(m, s_max[w][h]);
-    M[h] = m;
+    __syncthreads();
   }
 
-  // pass 2: weighted sums, the groups striding over the partials
-  float L[kHeadTile], acc[kHeadTile];
+  // ---- pass 2 ----
+  float acc[kHeadTile];
 #pragma unroll
-  for (int h = 0; h < kHeadTile; ++h) { L[h] = 0.f; acc[h] = 0.f; }
-  for (int i = grp; i < n; i += kMergeGroups) {
-    const long long slot = slot_of(i);
-    const float4* ml = reinterpret_cast<const float4*>(a.part_ml + slot * kHeadTile);
-    const float4* po = reinterpret_cast<const float4*>(a.part_o + slot * kPartialFloats + ch * kHeadTile);
-    const float4 o0 = po[0], o1 = po[1];
-    const float ov[kHeadTile] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+  for (int h = 0; h < kHeadTile; ++h) acc[h] = 0.f;
+  float lsum = 0.f;                                             // thread (i, h): sum of w * l
+  for (int c0 = 0; c0 < n; c0 += kMergeChunk) {
+    const int cn = min(kMergeChunk, n - c0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < cn * kHeadTile; e += kThreadsM) {
+      const int i = e >> 3, h = e & (kHeadTile - 1);
+      const float2 ml = a.part_ml[slot_of(c0 + i) * kHeadTile + h];
+      const float w = ml.x == -INFINITY ? 0.f : exp2_approx(ml.x - s_max[h]);
+      s_w[i][h] = w;
+      lsum = fmaf(w, ml.y, lsum);
+    }
+    __syncthreads();
+    for (int i0 = grp; i0 < cn; i0 += 4 * kMergeGroups) {
+      float4 o[4][2];
 #pragma unroll
-    for (int k = 0; k < kHeadTile / 2; ++k) {
-      const float4 x = ml[k];
-      const float wa = x.x == -INFINITY ? 0.f : exp2_approx(x.x - M[2 * k]);
-      const float wb = x.z == -INFINITY ? 0.f : exp2_approx(x.z - M[2 * k + 1]);
-      L[2 * k] = fmaf(wa, x.y, L[2 * k]); L[2 * k + 1] = fmaf(wb, x.w, L[2 * k + 1]);
-      acc[2 * k] = fmaf(wa, ov[2 * k], acc[2 * k]); acc[2 * k + 1] = fmaf(wb, ov[2 * k + 1], acc[2 * k + 1]);
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kMergeGroups;
+        if (i < cn) {
+          const float4* po = reinterpret_cast<const float4*>(a.part_o + slot_of(c0 + i) * kPartialFloats + ch * kHeadTile);
+          o[u][0] = po[0]; o[u][1] = po[1];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kMergeGroups;
+        if (i < cn) {
+          const float4 wa = *reinterpret_cast<const float4*>(&s_w[i][0]);
+          const float4 wb = *reinterpret_cast<const float4*>(&s_w[i][4]);
+          acc[0] = fmaf(wa.x, o[u][0].x, acc[0]); acc[1] = fmaf(wa.y, o[u][0].y, acc[1]);
+          acc[2] = fmaf(wa.z, o[u][0].z, acc[2]); acc[3] = fmaf(wa.w, o[u][0].w, acc[3]);
+          acc[4] = fmaf(wb.x, o[u][1].x, acc[4]); acc[5] = fmaf(wb.y, o[u][1].y, acc[5]);
+          acc[6] = fmaf(wb.z, o[u][1].z, acc[6]); acc[7] = fmaf(wb.w, o[u][1].w, acc[7]);
+        }
+      }
     }
   }
+  // reduce sum(w * l): thread's head is (threadIdx.x & 7) in every chunk
+  lsum += __shfl_xor_sync(0xffffffffu, lsum, 8);
+  lsum += __shfl_xor_sync(0xffffffffu, lsum, 16);
+  if ((threadIdx.x & 31) < kHeadTile) atomicAdd(&s_sum[threadIdx.x & (kHeadTile - 1)], lsum);
 #pragma unroll
-  for (int h = 0; h < kHeadTile; ++h) s_acc[grp][h][ch] = acc[h];
-  if (ch == 0) {
-#pragma unroll
-    for (int h = 0; h < kHeadTile; ++h) s_l[grp][h] = L[h];
-  }
+  for (int h = 0; h < kHeadTile; ++h) s_acc[grp][h][chl] = acc[h];
   __syncthreads();
-  // group g finishes head g (kMergeGroups == kHeadTile)
-  const int h = grp;
+  const int h = grp;                                            // group g finishes head g
   if (h < nheads) {
-    float l = 0.f, o = 0.f;
+    float o = 0.f;
 #pragma unroll
-    for (int k = 0; k < kMergeGroups; ++k) { l += s_l[k][h]; o += s_acc[k][h][ch]; }
+    for (int k = 0; k < kMergeGroups; ++k) o += s_acc[k][h][chl];
+    const float l = s_sum[h];
     const float val = o / l;
     const int64_t off = b * o_sb + (head0 + h) * o_sh + ch;
     if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = val;
     else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(val);
     else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
-    if (lse && ch == 0) {
-      float mh = s_max[0][h];
-      for (int w = 1; w < kMergeGroups * 4; ++w) mh = fmaxf(mh, s_max[w][h]);
-      lse[static_cast<int64_t>(b) * a.N + head0 + h] = (mh + log2f(l)) * 0.6931471805599453f;
-    }
+    if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + h] = (s_max[h] + log2f(l)) * 0.6931471805599453f;
   }
 }
 
@@ -885,9 +899,9 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (p->mid_event) PQ_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(p->mid_event), stream));
   const unsigned units = static_cast<unsigned>(static_cast<long long>(a.B) * a.Nk * a.head_tiles);
   switch (p->out_dtype) {
-    case PQ_F16: merge_partials_kernel<PQ_F16><<<units, kHeadDim * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
-    case PQ_BF16: merge_partials_kernel<PQ_BF16><<<units, kHeadDim * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
-    default: merge_partials_kernel<PQ_F32><<<units, kHeadDim * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    case PQ_F16: merge_partials_kernel<PQ_F16><<<dim3(units, kHeadDim / kMergeCh), kMergeCh * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    case PQ_BF16: merge_partials_kernel<PQ_BF16><<<dim3(units, kHeadDim / kMergeCh), kMergeCh * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    default: merge_partials_kernel<PQ_F32><<<dim3(units, kHeadDim / kMergeCh), kMergeCh * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
   }
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
