@@ -1,0 +1,82 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/polarquant_b200.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "polarquant_b200.h")
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = _declared_functions()
+    for must in ("pq_quantize", "pq_qk_decode", "pq_decode_attention", "pq_decode_workspace_bytes", "pq_merge_lse",
+                 "pq_quantize_host", "pq_decode_attention_host", "pq_strerror"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from polarquant_b200 import _lib
+    lib = _lib.load()
+    for name in _declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    for name in _lib.EXPORTED_SYMBOLS:
+        assert name in _declared_functions(), f"{name} is bound in Python but missing from the header"
+
+
+def test_struct_mirror_and_status_strings():
+    from polarquant_b200 import _lib
+    lib = _lib.load()
+    assert lib.pq_abi_version() == 1
+    assert lib.pq_decode_params_size() == ctypes.sizeof(_lib.DecodeParams)
+    for code in (0, -1, -2, -3, -4, -5):
+        assert lib.pq_strerror(code)
+    assert b"unknown" in lib.pq_strerror(-99)
+
+
+def test_argument_validation_needs_no_gpu():
+    """Bad arguments are rejected before any CUDA call, so these run on a CPU-only box."""
+    from polarquant_b200 import _lib
+    lib = _lib.load()
+    st = (ctypes.c_int64 * 4)(128 * 256, 256 * 128, 128, 1)
+    assert lib.pq_quantize(None, st, 1, 1, 256, 128, 128, 5, 4, _lib.PQ_BF16, 0, None, None, None, None, None, None) == -1
+    assert lib.pq_quantize(None, st, 1, 1, 200, 128, 128, 4, 4, _lib.PQ_BF16, 0, None, None, None, None, None, None) == -1
+    assert lib.pq_quantize(None, st, 1, 1, 256, 64, 128, 4, 4, _lib.PQ_BF16, 0, None, None, None, None, None, None) == -2
+    assert lib.pq_quantize(None, st, 0, 1, 256, 128, 128, 4, 4, _lib.PQ_BF16, 0, None, None, None, None, None, None) == 0
+    assert lib.pq_qk_decode(None, 0, 0, None, None, None, None, None, None, 1, 6, 4, 1, 128, 64, 4, 4, 0, None) == -1
+    p = _lib.DecodeParams()
+    p.B, p.N, p.Nk, p.Nb, p.G, p.R, p.hd = 1, 8, 2, 1, 128, 0, 128
+    p.rbits, p.tbits = 4, 5
+    assert lib.pq_decode_attention(ctypes.byref(p), None) == -1           # rbits + tbits > 8
+    p.tbits = 4
+    p.v_dtype = _lib.PQ_F32
+    assert lib.pq_decode_attention(ctypes.byref(p), None) == -2           # fp32 values are not built
+    assert lib.pq_decode_workspace_bytes(16, 32, 8, 255, 128, 128, 0) > 0
+    assert lib.pq_decode_workspace_bytes(16, 32, 6, 255, 128, 128, 0) == 0
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    import polarquant_b200 as pq
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pq.quantize_and_pack_nbit(torch.zeros(1, 1, 128, 128, dtype=torch.bfloat16), 4, 4, 128)
+    q = torch.zeros(1, 2, 1, 128, dtype=torch.float16)
+    idx = torch.zeros(1, 2, 1, 32, 64, dtype=torch.uint8)
+    s = torch.zeros(1, 2, 1, 1, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pq.attention_decode_forward_triton_impl(q, idx, s, s, s, s)
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from polarquant_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libpolarquant_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _lib.load()
