@@ -29,7 +29,8 @@ typedef enum {
   PQ_ERR_UNSUPPORTED = -2, /* valid for the reference, not built into this lib  */
   PQ_ERR_WORKSPACE = -3,   /* scratch buffer missing or too small               */
   PQ_ERR_CUDA = -4,        /* a CUDA runtime call failed (see pq_last_cuda_error) */
-  PQ_ERR_ALIGNMENT = -5    /* a pointer or stride breaks a 16-byte requirement  */
+  PQ_ERR_ALIGNMENT = -5,   /* a pointer or stride breaks a 16-byte requirement  */
+  PQ_ERR_SCRATCH_LIMIT = -6 /* problem needs more scratch than the built-in array of pq_decode_attention_static holds */
 } pq_status;
 
 /* pq_quantize flag bits */
@@ -123,6 +124,28 @@ size_t pq_decode_params_size(void);
 
 /* Scratch bytes pq_decode_attention needs for this problem on the current device. */
 size_t pq_decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int num_ctas);
+
+/*
+ * pq_decode_attention for callers that cannot provide scratch memory or call an allocator
+ * at all (a runtime that hands out its whole device heap at start-up, a plugin host that
+ * forbids allocation after initialisation).  It has no counterpart in the reference, whose
+ * Python code allocates freely.  Same arguments and results as pq_decode_attention; the
+ * workspace fields of `p` are ignored.  The partial results go to an array built into the
+ * library image: pq_decode_static_scratch_bytes() bytes (16 MiB) of device memory, held on
+ * every GPU that loads the library until the process exits.  A problem whose
+ * pq_decode_workspace_bytes() exceeds that is refused with PQ_ERR_SCRATCH_LIMIT before any
+ * work is enqueued.  The call itself performs no cudaMalloc / cudaFree and calls no
+ * allocating library routine.
+ *
+ * The first call on each device looks up the array's device address (with that device
+ * current) and caches it; make that first call outside any CUDA stream capture.
+ * All calls on a device share the one array, and it keeps whatever the previous call left
+ * in it.  Nothing in it has to start at zero: every slot a call reads was written earlier
+ * by the same call.  Two calls whose kernels overlap in time on the same GPU (different
+ * streams, or different host threads) would overwrite each other's partials: serialise them.
+ */
+int pq_decode_attention_static(const pq_decode_params* p, void* stream);
+size_t pq_decode_static_scratch_bytes(void);
 
 /*
  * Merge P partial attention results over disjoint key ranges (sequence split

@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "pq_quantize_host", "pq_quantize_host_staging_bytes", "pq_decode_attention_host",
     "pq_decode_host_staging_bytes", "pq_strerror", "pq_last_cuda_error", "pq_abi_version", "pq_decode_params_size",
     "pq_event_create", "pq_event_destroy", "pq_event_record", "pq_event_elapsed_ms",
+    "pq_decode_attention_static", "pq_decode_static_scratch_bytes",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -60,6 +61,10 @@ def _declare(lib: ctypes.CDLL) -> None:
                                  _int, _int, _int, _int, _int, _int, _int, _int, _int, _vp]
     lib.pq_decode_attention.restype = _int
     lib.pq_decode_attention.argtypes = [ctypes.POINTER(DecodeParams), _vp]
+    lib.pq_decode_attention_static.restype = _int
+    lib.pq_decode_attention_static.argtypes = [ctypes.POINTER(DecodeParams), _vp]
+    lib.pq_decode_static_scratch_bytes.restype = _sz
+    lib.pq_decode_static_scratch_bytes.argtypes = []
     lib.pq_decode_workspace_bytes.restype = _sz
     lib.pq_decode_workspace_bytes.argtypes = [_int] * 7
     lib.pq_merge_lse.restype = _int

@@ -16,6 +16,8 @@ int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* c
                      int Nb, int G, int D, int rbits, int tbits, int dtype, cudaStream_t stream);
 size_t decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int num_ctas);
 int decode_attention_device(const pq_decode_params* p, cudaStream_t stream);
+int decode_attention_static_device(const pq_decode_params* p, cudaStream_t stream);
+size_t decode_static_scratch_bytes();
 int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out, int out_dtype,
                      float* lse_out, cudaStream_t stream);
 
@@ -46,6 +48,7 @@ const char* pq_strerror(int status) {
     case PQ_ERR_WORKSPACE: return "workspace missing or smaller than pq_decode_workspace_bytes()";
     case PQ_ERR_CUDA: return "a CUDA runtime call failed (pq_last_cuda_error() has the code)";
     case PQ_ERR_ALIGNMENT: return "pointer or stride is not aligned for vector loads";
+    case PQ_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the built-in 16 MiB array of pq_decode_attention_static; use pq_decode_attention with a caller-provided workspace";
     default: return "unknown status";
   }
 }
@@ -71,6 +74,11 @@ size_t pq_decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int
 int pq_decode_attention(const pq_decode_params* p, void* stream) {
   return decode_attention_device(p, static_cast<cudaStream_t>(stream));
 }
+
+int pq_decode_attention_static(const pq_decode_params* p, void* stream) {
+  return decode_attention_static_device(p, static_cast<cudaStream_t>(stream));
+}
+size_t pq_decode_static_scratch_bytes(void) { return decode_static_scratch_bytes(); }
 
 int pq_merge_lse(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out, int out_dtype,
                  float* lse_out, void* stream) {

@@ -38,6 +38,8 @@
 // tcgen05/TMEM is not used: one decode query per head gives M = 16 tokens x
 // N <= 8 heads tiles, far below the 64-row minimum of tcgen05.mma, and the path
 // is bound by HBM and the shared-memory gathers, not by tensor throughput.
+#include <mutex>
+
 #include "pq_common.cuh"
 
 namespace pq {
@@ -922,6 +924,58 @@ int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, 
   }
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// Fused decode attention for callers that must not allocate.
+//
+// Some hosts of this library cannot hand over scratch memory: a serving runtime whose
+// device heap is fully carved up at start-up, a plugin loaded into a process that forbids
+// allocation calls after initialisation, code running inside a region where any allocator
+// call (the CUDA runtime's or a framework's caching allocator) is off limits.  For them the
+// partial results of the split-sequence kernel live in a fixed array inside the library
+// image instead of a caller-provided buffer.  The array costs kStaticScratchBytes of device
+// memory on every GPU whose context loads the library, until the process exits.
+//
+// In host code the array's name is only a handle, not a device address, so the address is
+// looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
+// ---------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;     // 16 MiB; the 32k-context benchmark shape needs 14.8 MB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {};
+}  // namespace
+
+size_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int decode_attention_static_device(const pq_decode_params* p, cudaStream_t stream) {
+  if (!p) return PQ_ERR_INVALID;
+  // the size check needs only the dimensions and comes first, so an oversized problem is
+  // refused before anything touches the device
+  const size_t need = decode_workspace_bytes(p->B, p->N, p->Nk, p->Nb, p->G, p->R, p->num_ctas);
+  if (need > kStaticScratchBytes) return PQ_ERR_SCRATCH_LIMIT;
+  int dev = -1;
+  PQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return PQ_ERR_UNSUPPORTED;
+  void* addr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    addr = g_scratch_addr[dev];
+    if (!addr) {
+      // first call on this device: resolve the device address of the array (no allocation;
+      // it may load the library's device code, so make this call before any stream capture)
+      PQ_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+      if (!addr) return PQ_ERR_CUDA;
+      g_scratch_addr[dev] = addr;
+    }
+  }
+  pq_decode_params q = *p;
+  q.workspace = addr;
+  q.workspace_bytes = kStaticScratchBytes;
+  return decode_attention_device(&q, stream);
 }
 
 }  // namespace pq
