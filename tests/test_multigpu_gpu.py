@@ -1,0 +1,60 @@
+"""Sequence-split decode attention over NCCL on 2+ GPUs of one node (skipped on a single-GPU box).
+
+Each rank holds a slice of the keys, runs the fused CUDA kernel on it, all-gathers one (output, log-sum-exp) pair
+per query head and merges with the CUDA merge kernel; the result must equal single-GPU attention over all keys."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, queue):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import polarquant_b200 as pq
+        from polarquant_b200 import distributed as pqd
+        from oracle import polar_oracle as oracle
+        B, N, Nk, Nb, G, R = 2, 16, 4, 10, 128, 45
+        keys = oracle.synth_keys(B, Nk, Nb * G + R, 128, torch.bfloat16, seed=21).to(dev)
+        g = torch.Generator().manual_seed(22)
+        q = torch.randn(B, N, 1, 128, generator=g).to(torch.bfloat16).to(dev)
+        v = torch.randn(B, Nk, Nb * G + R, 128, generator=g).to(torch.bfloat16).to(dev)
+        packed = pq.quantize_and_pack_nbit(keys[:, :, :Nb * G].contiguous(), 4, 4, G)
+        kres = keys[:, :, Nb * G:].contiguous()
+        full = pq.decode_attention(q, kres, *packed, v, out_dtype=torch.float32)
+        g0, g1, owns = pqd.split_sequence(Nb, R, rank, world)
+        mine = [t[:, :, g0:g1].contiguous() for t in packed] if g1 > g0 else None
+        my_v = [v[:, :, g0 * G:g1 * G]] + ([v[:, :, Nb * G:]] if owns else [])
+        got = pqd.sequence_parallel_decode(q, kres if owns else None, mine, torch.cat(my_v, dim=2).contiguous(),
+                                           out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        queue.put((rank, float((got - full).abs().max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_sequence_split_over_nccl_equals_single_gpu_attention():
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = 33500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    for _ in range(world):
+        _, err = queue.get(timeout=5)
+        assert err <= 2e-3
