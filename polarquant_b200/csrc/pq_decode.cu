@@ -238,12 +238,19 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
                                               const uint32_t (&rs2)[4][2], const uint32_t (&rc2)[4][2],
                                               const uint32_t (&qb)[8][2]) {
   constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
+  // two accumulator sets halve the chain of dependent MMAs
+  float S2[4] = {0.f, 0.f, 0.f, 0.f};
+#ifdef PQ_SINGLE_S
+#define PQ_S2 S
+#else
+#define PQ_S2 S2
+#endif
 #define PQ_WORD(W, CG, CH)                                                                                     \
   {                                                                                                            \
     const uint32_t og = (((CG) << 2) & TM4) ^ lane_xor[W];                                                     \
     const uint32_t oh = (((CH) << 2) & TM4) ^ lane_xor[W];                                                     \
     qk_kstep<RBITS, TBITS, W, 0>(S, CG, CH, og, oh, tbl_addr, rs2[W][0], rc2[W][0], qb[2 * W][0], qb[2 * W][1]); \
-    qk_kstep<RBITS, TBITS, W, 1>(S, CG, CH, og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0],           \
+    qk_kstep<RBITS, TBITS, W, 1>(PQ_S2, CG, CH, og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0],       \
                                  qb[2 * W + 1][1]);                                                            \
   }
   PQ_WORD(0, cg4.x, ch4.x)
@@ -251,6 +258,11 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
   PQ_WORD(2, cg4.z, ch4.z)
   PQ_WORD(3, cg4.w, ch4.w)
 #undef PQ_WORD
+#undef PQ_S2
+#ifndef PQ_SINGLE_S
+#pragma unroll
+  for (int i = 0; i < 4; ++i) S[i] += S2[i];
+#endif
 }
 
 // Ask the L2 to fetch `bytes` (a multiple of 16) starting at the 16-byte aligned address p.
@@ -359,8 +371,11 @@ __device__ __forceinline__ void pv_half(float (&O)[8][4], int J0, const uint4 (&
 // ---------------------------------------------------------------------------------
 // fused decode attention
 // ---------------------------------------------------------------------------------
+#ifndef PQ_MIN_CTAS
+#define PQ_MIN_CTAS 3
+#endif
 template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
-__global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : 3)
+__global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : PQ_MIN_CTAS)
 decode_kernel(const DecodeArgs a) {
   constexpr int A = 1 << TBITS;
   constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
@@ -445,12 +460,21 @@ decode_kernel(const DecodeArgs a) {
       // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
       const bool v_dense = v_row == kHeadDim * 2;
       auto prefetch_step = [&](int step) {
+#ifdef PQ_PREFETCH_LANES
+        // one 128-byte line per lane
+        if (lane < 8) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_unit + static_cast<int64_t>(step) * kStep * kPairs + 128 * lane));
+        if constexpr (!QK_ONLY) {
+          const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row + (lane >> 1) * v_row + 128 * (lane & 1);
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(vt));
+        }
+#else
         if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, kStep * kPairs);
         if constexpr (!QK_ONLY) {
           const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row;
           if (v_dense) { if (lane == 1) prefetch_l2(vt, kStep * kHeadDim * 2); }
           else if (lane < kStep) prefetch_l2(vt + lane * v_row, kHeadDim * 2);
         }
+#endif
       };
       for (int ahead = 2; ahead < kPrefetch; ++ahead)
         if (pos + ahead < qs_end) prefetch_step(pos + ahead);
@@ -467,49 +491,56 @@ decode_kernel(const DecodeArgs a) {
       __syncwarp();                       // earlier readers of the staging buffers are done
       int buf = 0;
       stage_group(grp, buf);
-      bool fresh = true;
-      for (int s = pos; s < qs_end; ++s) {
-        if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
-        if (fresh || in_group == 0) {
-          wait_staged();                  // this group's scales have landed; all lanes are past the old table
-          if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
-          build_angle_table<TBITS, QDT>(tbl_addr, s_sc[warp][buf], lane);
-          load_radius_consts<RBITS, QDT>(s_sc[warp][buf], t, rs2, rc2);
-          buf ^= 1;
-          fresh = false;
-        }
-        // next tile; the last step of the segment re-reads its own tile rather than branching
-        const bool more = s + 1 < qs_end;
-        if (more) c_lane += kStep * kPairs;
-        const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
+      int s = pos;
+      while (s < qs_end) {
+        // ---- one run of steps inside one token group: constants first, then a lean step loop ----
+        const int run_end = min(qs_end, s - in_group + a.spg);
+        wait_staged();                    // this group's scales have landed; all lanes are past the old table
+        if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
+        build_angle_table<TBITS, QDT>(tbl_addr, s_sc[warp][buf], lane);
+        load_radius_consts<RBITS, QDT>(s_sc[warp][buf], t, rs2, rc2);
+        buf ^= 1;
+#ifdef PQ_UNROLL2
+#pragma unroll 2
+#else
+#pragma unroll 1
+#endif
+        for (; s < run_end; ++s) {
+          if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
+          // next tile; the last step of the segment re-reads its own tile rather than branching
+          const bool more = s + 1 < qs_end;
+          if (more) c_lane += kStep * kPairs;
+          const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
 
-        float S[4] = {0.f, 0.f, 0.f, 0.f};
-        qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
+          float S[4] = {0.f, 0.f, 0.f, 0.f};
+          qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
 
-        if constexpr (QK_ONLY) {
-          // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
-          const int tok = s * kStep + g;
-          float* orow = a.logits + (static_cast<int64_t>(b) * a.N + head0 + 2 * t) * Lq + tok;
-          if (2 * t < nheads) { orow[0] = S[0]; orow[8] = S[2]; }
-          if (2 * t + 1 < nheads) { orow[Lq] = S[1]; orow[Lq + 8] = S[3]; }
-        } else {
-          bool mg = false, mh = false;
-          if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
-          uint32_t b0, b1;
-          softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
-          if (more) {
+          if constexpr (QK_ONLY) {
+            // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
+            const int tok = s * kStep + g;
+            float* orow = a.logits + (static_cast<int64_t>(b) * a.N + head0 + 2 * t) * Lq + tok;
+            if (2 * t < nheads) { orow[0] = S[0]; orow[8] = S[2]; }
+            if (2 * t + 1 < nheads) { orow[Lq] = S[1]; orow[Lq + 8] = S[3]; }
+          } else {
+            bool mg = false, mh = false;
+            if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
+            uint32_t b0, b1;
+            softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
+            if (more) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) vp[i] += v_step;
+              for (int i = 0; i < 4; ++i) vp[i] += v_step;
+            }
+            pv_half<VDT>(O, 0, v0, b0, b1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v0[i] = ldg_stream(vp[i]);
+            pv_half<VDT>(O, 4, v1, b0, b1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v1[i] = ldg_stream(vp[i] + 128);
           }
-          pv_half<VDT>(O, 0, v0, b0, b1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) v0[i] = ldg_stream(vp[i]);
-          pv_half<VDT>(O, 4, v1, b0, b1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) v1[i] = ldg_stream(vp[i] + 128);
+          cg = ng; ch = nh;
         }
-        cg = ng; ch = nh;
-        if (++in_group == a.spg) { in_group = 0; ++grp; }
+        in_group = 0;
+        ++grp;
       }
     }
 
@@ -842,7 +873,7 @@ size_t decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int nu
   if (B <= 0 || N <= 0 || Nk <= 0 || Nb < 0 || G <= 0 || R < 0 || N % Nk != 0 || G % kStep != 0) return 0;
   DecodeArgs a{};
   a.B = B; a.N = N; a.Nk = Nk; a.Nb = Nb; a.G = G; a.R = R;
-  plan(a, 3, num_ctas);
+  plan(a, PQ_MIN_CTAS, num_ctas);
   return workspace_bytes_for(a);
 }
 
@@ -884,7 +915,7 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   a.v = p->v; a.v_sb = p->v_stride_b; a.v_sh = p->v_stride_h; a.v_st = p->v_stride_t;
   a.mask = p->mask; a.m_sb = p->mask_stride_b;
   a.B = p->B; a.N = p->N; a.Nk = p->Nk; a.Nb = p->Nb; a.G = p->G; a.R = p->R;
-  plan(a, 3, p->num_ctas);
+  plan(a, PQ_MIN_CTAS, p->num_ctas);
   const size_t need = workspace_bytes_for(a);
   if (!p->workspace || p->workspace_bytes < need) return PQ_ERR_WORKSPACE;
   if (mis(p->workspace, 256)) return PQ_ERR_ALIGNMENT;
