@@ -81,7 +81,7 @@ __device__ __forceinline__ long long range_lo(long long w, long long total, int 
 // The four scale rows of a token group (rscale, rmn, tscale, tmn: 4 x 64 elements) are
 // copied global -> shared with cp.async one group ahead of their use, double-buffered,
 // so the dependent table build never waits on DRAM.
-template <int SDT>
+template <int SDT, bool COMMIT = true>
 __device__ __forceinline__ void stage_scales_async(uint32_t dst_addr, const char* rs_row, const char* rm_row,
                                                    const char* ts_row, const char* tm_row, int lane) {
   constexpr int kChunks = (SDT == PQ_F32 ? 16 : 8);          // 16-byte chunks per row
@@ -91,7 +91,7 @@ __device__ __forceinline__ void stage_scales_async(uint32_t dst_addr, const char
     const char* src = (tensor == 0 ? rs_row : tensor == 1 ? rm_row : tensor == 2 ? ts_row : tm_row) + 16 * chunk;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_addr + 16u * i), "l"(src) : "memory");
   }
-  asm volatile("cp.async.commit_group;" ::: "memory");
+  if constexpr (COMMIT) asm volatile("cp.async.commit_group;" ::: "memory");
 }
 __device__ __forceinline__ void wait_staged() {
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -368,6 +368,54 @@ __device__ __forceinline__ void pv_half(float (&O)[8][4], int J0, const uint4 (&
   }
 }
 
+
+#ifdef PQ_V_SMEM
+// ---- value tiles through shared memory ------------------------------------------------
+// A value tile is 16 token rows of 256 bytes.  It is copied global -> shared with cp.async
+// (16 bytes per lane, 8 per lane per tile) into rows padded to 272 bytes, so that the eight
+// rows of every 8x8 block ldmatrix reads fall in eight different 16-byte bank groups.
+constexpr int kVRowSmem = 272;
+constexpr int kVTileSmem = kStep * kVRowSmem;      // 4352 bytes
+#ifndef PQ_V_STAGES
+#define PQ_V_STAGES 3
+#endif
+constexpr int kVStages = PQ_V_STAGES;              // value tiles in flight per warp: kVStages - 1
+__device__ __forceinline__ void load_v_tile_async(uint32_t stage_addr, const char* tile, int64_t v_row,
+                                                  int valid_rows, int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = i * 32 + lane, row = c >> 4, col = c & 15;
+    const bool ok = row < valid_rows;
+    const char* src = tile + (ok ? row : 0) * v_row + col * 16;
+    const uint32_t dst = stage_addr + row * kVRowSmem + col * 16;
+    const int bytes = ok ? 16 : 0;                 // rows past the end are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// O^T[channel, head] += V^T . P^T for all eight 16-channel tiles of one staged value tile.
+// ldmatrix.trans hands lane (g, t) the pairs {V[2t][c], V[2t+1][c]}: m-tile j row g is channel
+// 16j + g, row g + 8 channel 16j + 8 + g.
+template <int VDT>
+__device__ __forceinline__ void pv_from_smem(float (&O)[8][4], uint32_t stage_addr, int lane, uint32_t b0, uint32_t b1) {
+  // lane supplies the row address of matrix (lane / 8), row (lane % 8):
+  // matrices: (tokens 0-7, ch +0), (tokens 0-7, ch +8), (tokens 8-15, ch +0), (tokens 8-15, ch +8)
+  const int mi = lane >> 3, r = lane & 7;
+  const uint32_t base = stage_addr + (r + 8 * (mi >> 1)) * kVRowSmem + (mi & 1) * 16;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t a0, a1, a2, a3;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                 : "r"(base + j * 32));
+    mma_16816<VDT>(O[j], a0, a1, a2, a3, b0, b1);
+  }
+}
+#endif
+
 // ---------------------------------------------------------------------------------
 // fused decode attention
 // ---------------------------------------------------------------------------------
@@ -380,8 +428,18 @@ decode_kernel(const DecodeArgs a) {
   constexpr int A = 1 << TBITS;
   constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
   constexpr int kStageBytes = 4 * kPairs * QES;   // four scale rows of one group
+#ifdef PQ_V_SMEM
+  extern __shared__ __align__(256) unsigned char smem_dyn[];
+  constexpr int kWarpSmem = kPairs * A * 4 + 2 * kStageBytes + (QK_ONLY ? 0 : kVStages * kVTileSmem);
+  unsigned char* warp_smem = smem_dyn + (threadIdx.x >> 5) * kWarpSmem;
+  uint32_t* s_tbl_w = reinterpret_cast<uint32_t*>(warp_smem);
+  char* s_sc_w = reinterpret_cast<char*>(warp_smem + kPairs * A * 4);
+#else
   __shared__ __align__(256) uint32_t s_tbl[kWarps][kPairs * A];
   __shared__ __align__(16) char s_sc[kWarps][2][kStageBytes];
+  uint32_t* s_tbl_w = s_tbl[threadIdx.x >> 5];
+  char* s_sc_w = s_sc[threadIdx.x >> 5][0];
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -391,7 +449,10 @@ decode_kernel(const DecodeArgs a) {
   const long long hi = range_lo(gw + 1, a.total_slots, a.total_warps);
   if (lo >= hi) return;
 
-  const uint32_t tbl_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tbl[warp]));
+  const uint32_t tbl_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tbl_w));
+#ifdef PQ_V_SMEM
+  const uint32_t vst_addr = tbl_addr + kPairs * A * 4 + 2 * kStageBytes;   // two value stages
+#endif
   uint32_t lane_xor[4];
 #pragma unroll
   for (int w = 0; w < 4; ++w) {
@@ -444,6 +505,19 @@ decode_kernel(const DecodeArgs a) {
       // lane's code bytes: token row * 64 + 16 t
       const uint8_t* c_lane = c_unit + static_cast<int64_t>(pos) * kStep * kPairs + g * kPairs + 16 * t;
       uint4 cg = ldg_stream(c_lane), ch = ldg_stream(c_lane + 8 * kPairs);
+#ifdef PQ_V_SMEM
+      // value tiles go global -> shared (cp.async) one step ahead, two stages per warp
+      const char* v_tile = v_unit + static_cast<int64_t>(pos) * kStep * v_row;
+      const int64_t v_step = kStep * v_row;
+      int vstage = 0;
+      if constexpr (!QK_ONLY) {
+        cp_async_wait<0>();               // nothing of an earlier segment may still be landing in the stages
+        __syncwarp();
+        load_v_tile_async(vst_addr, v_tile, v_row, kStep, lane);      // committed with the first scales below
+      }
+      const int last_tile = qs_end - 1;   // tiles past the segment are never fetched: the last one is re-read
+      int next_tile = pos;
+#else
       uint4 v0[4], v1[4];
       // lane's value bytes: tokens (2t, 2t+1, 2t+8, 2t+9), channels 8g.. and 64+8g..
       const char* vp[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -454,6 +528,7 @@ decode_kernel(const DecodeArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) { v0[i] = ldg_stream(vp[i]); v1[i] = ldg_stream(vp[i] + 128); }
       }
+#endif
 
       // The register loads run one step ahead; the L2 is asked for the tiles kPrefetch steps
       // ahead so those loads find their lines on chip.  One lane issues a bulk prefetch per
@@ -482,23 +557,47 @@ decode_kernel(const DecodeArgs a) {
       int in_group = pos % a.spg;
       int grp = pos / a.spg;
       const int last_grp = (qs_end - 1) / a.spg;
-      const uint32_t sc_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_sc[warp][0]));
+      const uint32_t sc_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_sc_w));
+#ifdef PQ_V_SMEM
+      constexpr bool kCommitScales = QK_ONLY;   // fused kernel: the scale copies join the next value-tile group
+#else
+      constexpr bool kCommitScales = true;
+#endif
       auto stage_group = [&](int gidx, int buf) {
         const int64_t row = static_cast<int64_t>(gidx) * kPairs * QES;
-        stage_scales_async<QDT>(sc_addr + buf * kStageBytes, rs_unit + row, rm_unit + row, ts_unit + row,
-                                tm_unit + row, lane);
+        stage_scales_async<QDT, kCommitScales>(sc_addr + buf * kStageBytes, rs_unit + row, rm_unit + row,
+                                               ts_unit + row, tm_unit + row, lane);
       };
       __syncwarp();                       // earlier readers of the staging buffers are done
       int buf = 0;
       stage_group(grp, buf);
+#ifdef PQ_V_SMEM
+      if constexpr (!QK_ONLY) {
+        cp_async_commit();                           // first value tile + first scales
+#pragma unroll
+        for (int d = 1; d < kVStages - 1; ++d) {     // fill the pipeline: tiles pos+1 .. pos+kVStages-2
+          if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
+          load_v_tile_async(vst_addr + d * kVTileSmem, v_tile, v_row, kStep, lane);
+          cp_async_commit();
+        }
+      }
+#endif
       int s = pos;
       while (s < qs_end) {
         // ---- one run of steps inside one token group: constants first, then a lean step loop ----
         const int run_end = min(qs_end, s - in_group + a.spg);
-        wait_staged();                    // this group's scales have landed; all lanes are past the old table
+        // this group's scale rows must have landed.  In the fused kernel they rode in the value-tile
+        // group committed one token group (spg steps) ago; when that is older than the kVStages - 1
+        // groups allowed in flight nothing needs draining.
+#ifdef PQ_V_SMEM
+        if (!QK_ONLY && s != pos && a.spg >= kVStages) { cp_async_wait<kVStages - 1>(); __syncwarp(); }
+        else wait_staged();
+#else
+        wait_staged();
+#endif
         if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
-        build_angle_table<TBITS, QDT>(tbl_addr, s_sc[warp][buf], lane);
-        load_radius_consts<RBITS, QDT>(s_sc[warp][buf], t, rs2, rc2);
+        build_angle_table<TBITS, QDT>(tbl_addr, s_sc_w + buf * kStageBytes, lane);
+        load_radius_consts<RBITS, QDT>(s_sc_w + buf * kStageBytes, t, rs2, rc2);
         buf ^= 1;
 #ifdef PQ_UNROLL2
 #pragma unroll 2
@@ -511,6 +610,15 @@ decode_kernel(const DecodeArgs a) {
           const bool more = s + 1 < qs_end;
           if (more) c_lane += kStep * kPairs;
           const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
+#ifdef PQ_V_SMEM
+          if constexpr (!QK_ONLY) {
+            if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
+            int fill = vstage + kVStages - 1;
+            if (fill >= kVStages) fill -= kVStages;
+            load_v_tile_async(vst_addr + fill * kVTileSmem, v_tile, v_row, kStep, lane);
+            cp_async_commit();              // also carries scale rows staged since the last commit
+          }
+#endif
 
           float S[4] = {0.f, 0.f, 0.f, 0.f};
           qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
@@ -526,6 +634,13 @@ decode_kernel(const DecodeArgs a) {
             if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
             uint32_t b0, b1;
             softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
+#ifdef PQ_V_SMEM
+            cp_async_wait<kVStages - 1>();  // this step's tile has landed; the newer ones may be in flight
+            __syncwarp();
+            pv_from_smem<VDT>(O, vst_addr + vstage * kVTileSmem, lane, b0, b1);
+            __syncwarp();                   // every lane is done with the stage before it is refilled
+            if (++vstage == kVStages) vstage = 0;
+#else
             if (more) {
 #pragma unroll
               for (int i = 0; i < 4; ++i) vp[i] += v_step;
@@ -536,12 +651,16 @@ decode_kernel(const DecodeArgs a) {
             pv_half<VDT>(O, 4, v1, b0, b1);
 #pragma unroll
             for (int i = 0; i < 4; ++i) v1[i] = ldg_stream(vp[i] + 128);
+#endif
           }
           cg = ng; ch = nh;
         }
         in_group = 0;
         ++grp;
       }
+#ifdef PQ_V_SMEM
+      cp_async_wait<0>();                 // the last (redundant) prefetch of the segment
+#endif
     }
 
     // ------------------------------ residual steps -------------------------------
@@ -564,6 +683,12 @@ decode_kernel(const DecodeArgs a) {
             kg[c] = load8_as16<QDT>(kr_unit + (r0 + g) * kr_row + (8 * t + 32 * c) * QES, ok_g);
             kh[c] = load8_as16<QDT>(kr_unit + (r0 + g + 8) * kr_row + (8 * t + 32 * c) * QES, ok_h);
           }
+#ifdef PQ_V_SMEM
+          cp_async_wait<0>();
+          __syncwarp();
+          load_v_tile_async(vst_addr, v_unit + static_cast<int64_t>(Lq + r0) * v_row, v_row, a.R - r0, lane);
+          cp_async_commit();
+#else
           uint4 v0[4], v1[4];
           {
             const char* vl = v_unit + static_cast<int64_t>(Lq + r0 + 2 * t) * v_row + 16 * g;
@@ -575,6 +700,7 @@ decode_kernel(const DecodeArgs a) {
               v1[i] = ok ? ldg_stream(vl + tk[i] * v_row + 128) : make_uint4(0, 0, 0, 0);
             }
           }
+#endif
           float S[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -594,8 +720,15 @@ decode_kernel(const DecodeArgs a) {
           }
           uint32_t b0, b1;
           softmax_step<VDT>(S, a.scale_log2, ok_g, ok_h, mg, mh, st, O, b0, b1);
+#ifdef PQ_V_SMEM
+          cp_async_wait<0>();
+          __syncwarp();
+          pv_from_smem<VDT>(O, vst_addr, lane, b0, b1);
+          __syncwarp();
+#else
           pv_half<VDT>(O, 0, v0, b0, b1);
           pv_half<VDT>(O, 4, v1, b0, b1);
+#endif
         }
       }
 
@@ -609,10 +742,15 @@ decode_kernel(const DecodeArgs a) {
       float* po = a.part_o + slot * kPartialFloats;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
+#ifdef PQ_V_SMEM
+        // m-tile j: row g is channel 16j + g, row g+8 channel 16j + 8 + g
+        const int chn = 16 * j + g, chn2 = chn + 8;
+#else
         // m-tile j: row g is channel 64*(j/4) + 8g + 2*(j%4), row g+8 the next channel
-        const int chn = 64 * (j >> 2) + 8 * g + 2 * (j & 3);
+        const int chn = 64 * (j >> 2) + 8 * g + 2 * (j & 3), chn2 = chn + 1;
+#endif
         *reinterpret_cast<float2*>(po + chn * kHeadTile + 2 * t) = make_float2(O[j][0], O[j][1]);
-        *reinterpret_cast<float2*>(po + (chn + 1) * kHeadTile + 2 * t) = make_float2(O[j][2], O[j][3]);
+        *reinterpret_cast<float2*>(po + chn2 * kHeadTile + 2 * t) = make_float2(O[j][2], O[j][3]);
       }
       if (g == 0) {
         a.part_ml[slot * kHeadTile + 2 * t] = make_float2(st.m0, st.l0);
@@ -817,7 +955,17 @@ size_t workspace_bytes_for(const DecodeArgs& a) {
 
 template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
 int launch_decode(const DecodeArgs& a, cudaStream_t s) {
+#ifdef PQ_V_SMEM
+  constexpr int kStageBytes = 4 * kPairs * (QDT == PQ_F32 ? 4 : 2);
+  constexpr int kWarpSmem = kPairs * (1 << TBITS) * 4 + 2 * kStageBytes + (QK_ONLY ? 0 : kVStages * kVTileSmem);
+  constexpr int kSmem = kWarps * kWarpSmem;
+  if (kSmem > 48 * 1024)
+    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, kSmem, s>>>(a);
+#else
   decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, 0, s>>>(a);
+#endif
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
