@@ -31,9 +31,10 @@
 //   4. Online softmax in the log2 domain on the accumulator fragment, warp
 //      shuffles across the eight token rows.
 //   5. P^T is transposed in registers (movmatrix) into the B operand and
-//      O^T[channel, head] += V^T[channel, token] . P^T[token, head]; V goes from
-//      global memory straight into A fragments (128-bit loads + byte permutes),
-//      never through shared memory, which is kept for the table gathers.
+//      O^T[channel, head] += V^T[channel, token] . P^T[token, head]; value tiles are
+//      copied global -> shared with cp.async two steps ahead (three stages per
+//      warp, rows padded to 272 bytes) and read as A fragments with
+//      ldmatrix.trans, which needs no registers while the tile is in flight.
 //
 // tcgen05/TMEM is not used: one decode query per head gives M = 16 tokens x
 // N <= 8 heads tiles, far below the 64-row minimum of tcgen05.mma, and the path
@@ -240,17 +241,12 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
   constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
   // two accumulator sets halve the chain of dependent MMAs
   float S2[4] = {0.f, 0.f, 0.f, 0.f};
-#ifdef PQ_SINGLE_S
-#define PQ_S2 S
-#else
-#define PQ_S2 S2
-#endif
 #define PQ_WORD(W, CG, CH)                                                                                     \
   {                                                                                                            \
     const uint32_t og = (((CG) << 2) & TM4) ^ lane_xor[W];                                                     \
     const uint32_t oh = (((CH) << 2) & TM4) ^ lane_xor[W];                                                     \
     qk_kstep<RBITS, TBITS, W, 0>(S, CG, CH, og, oh, tbl_addr, rs2[W][0], rc2[W][0], qb[2 * W][0], qb[2 * W][1]); \
-    qk_kstep<RBITS, TBITS, W, 1>(PQ_S2, CG, CH, og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0],       \
+    qk_kstep<RBITS, TBITS, W, 1>(S2, CG,     CH, og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0],       \
                                  qb[2 * W + 1][1]);                                                            \
   }
   PQ_WORD(0, cg4.x, ch4.x)
@@ -258,11 +254,8 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
   PQ_WORD(2, cg4.z, ch4.z)
   PQ_WORD(3, cg4.w, ch4.w)
 #undef PQ_WORD
-#undef PQ_S2
-#ifndef PQ_SINGLE_S
 #pragma unroll
   for (int i = 0; i < 4; ++i) S[i] += S2[i];
-#endif
 }
 
 // Ask the L2 to fetch `bytes` (a multiple of 16) starting at the 16-byte aligned address p.
@@ -350,26 +343,6 @@ __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bo
   b1 = movmatrix_trans(pack2<VDT>(p2, p3));
 }
 
-// O^T[channel, head] += V^T . P^T for m-tiles [J0, J0 + 4): V registers v[tok][reg] hold, for
-// tokens (2t, 2t+1, 2t+8, 2t+9), channels 8g + 2*reg (+1) of one 64-channel half.
-template <int VDT>
-__device__ __forceinline__ void pv_half(float (&O)[8][4], int J0, const uint4 (&v)[4], uint32_t b0, uint32_t b1) {
-  const uint32_t va[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
-  const uint32_t vb[4] = {v[1].x, v[1].y, v[1].z, v[1].w};
-  const uint32_t vc[4] = {v[2].x, v[2].y, v[2].z, v[2].w};
-  const uint32_t vd[4] = {v[3].x, v[3].y, v[3].z, v[3].w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t a0 = __byte_perm(va[j], vb[j], 0x5410);   // channel 2j   of tokens (2t, 2t+1)
-    const uint32_t a1 = __byte_perm(va[j], vb[j], 0x7632);   // channel 2j+1
-    const uint32_t a2 = __byte_perm(vc[j], vd[j], 0x5410);   // tokens (2t+8, 2t+9)
-    const uint32_t a3 = __byte_perm(vc[j], vd[j], 0x7632);
-    mma_16816<VDT>(O[J0 + j], a0, a1, a2, a3, b0, b1);
-  }
-}
-
-
-#ifdef PQ_V_SMEM
 // ---- value tiles through shared memory ------------------------------------------------
 // A value tile is 16 token rows of 256 bytes.  It is copied global -> shared with cp.async
 // (16 bytes per lane, 8 per lane per tile) into rows padded to 272 bytes, so that the eight
@@ -414,7 +387,6 @@ __device__ __forceinline__ void pv_from_smem(float (&O)[8][4], uint32_t stage_ad
     mma_16816<VDT>(O[j], a0, a1, a2, a3, b0, b1);
   }
 }
-#endif
 
 // ---------------------------------------------------------------------------------
 // fused decode attention
@@ -428,19 +400,15 @@ decode_kernel(const DecodeArgs a) {
   constexpr int A = 1 << TBITS;
   constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
   constexpr int kStageBytes = 4 * kPairs * QES;   // four scale rows of one group
-#ifdef PQ_V_SMEM
   extern __shared__ __align__(256) unsigned char smem_dyn[];
   constexpr int kWarpSmem = kPairs * A * 4 + 2 * kStageBytes + (QK_ONLY ? 0 : kVStages * kVTileSmem);
   unsigned char* warp_smem = smem_dyn + (threadIdx.x >> 5) * kWarpSmem;
   uint32_t* s_tbl_w = reinterpret_cast<uint32_t*>(warp_smem);
   char* s_sc_w = reinterpret_cast<char*>(warp_smem + kPairs * A * 4);
-#else
-  __shared__ __align__(256) uint32_t s_tbl[kWarps][kPairs * A];
-  __shared__ __align__(16) char s_sc[kWarps][2][kStageBytes];
-  uint32_t* s_tbl_w = s_tbl[threadIdx.x >> 5];
-  char* s_sc_w = s_sc[threadIdx.x >> 5][0];
-#endif
 
+  // A grid launched behind this one with programmatic stream serialisation (the merge kernel) may be
+  // set up now; it waits for this grid's completion itself before it reads the partials.
+  asm volatile("griddepcontrol.launch_dependents;");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const long long gw = static_cast<long long>(blockIdx.x) * kWarps + warp;
@@ -450,9 +418,7 @@ decode_kernel(const DecodeArgs a) {
   if (lo >= hi) return;
 
   const uint32_t tbl_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tbl_w));
-#ifdef PQ_V_SMEM
   const uint32_t vst_addr = tbl_addr + kPairs * A * 4 + 2 * kStageBytes;   // two value stages
-#endif
   uint32_t lane_xor[4];
 #pragma unroll
   for (int w = 0; w < 4; ++w) {
@@ -505,7 +471,6 @@ decode_kernel(const DecodeArgs a) {
       // lane's code bytes: token row * 64 + 16 t
       const uint8_t* c_lane = c_unit + static_cast<int64_t>(pos) * kStep * kPairs + g * kPairs + 16 * t;
       uint4 cg = ldg_stream(c_lane), ch = ldg_stream(c_lane + 8 * kPairs);
-#ifdef PQ_V_SMEM
       // value tiles go global -> shared (cp.async) one step ahead, two stages per warp
       const char* v_tile = v_unit + static_cast<int64_t>(pos) * kStep * v_row;
       const int64_t v_step = kStep * v_row;
@@ -517,39 +482,18 @@ decode_kernel(const DecodeArgs a) {
       }
       const int last_tile = qs_end - 1;   // tiles past the segment are never fetched: the last one is re-read
       int next_tile = pos;
-#else
-      uint4 v0[4], v1[4];
-      // lane's value bytes: tokens (2t, 2t+1, 2t+8, 2t+9), channels 8g.. and 64+8g..
-      const char* vp[4] = {nullptr, nullptr, nullptr, nullptr};
-      const int64_t v_step = kStep * v_row;
-      if constexpr (!QK_ONLY) {
-        const char* v_lane = v_unit + static_cast<int64_t>(pos) * kStep * v_row + (2 * t) * v_row + 16 * g;
-        vp[0] = v_lane; vp[1] = v_lane + v_row; vp[2] = v_lane + 8 * v_row; vp[3] = v_lane + 9 * v_row;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { v0[i] = ldg_stream(vp[i]); v1[i] = ldg_stream(vp[i] + 128); }
-      }
-#endif
 
       // The register loads run one step ahead; the L2 is asked for the tiles kPrefetch steps
       // ahead so those loads find their lines on chip.  One lane issues a bulk prefetch per
       // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
       const bool v_dense = v_row == kHeadDim * 2;
       auto prefetch_step = [&](int step) {
-#ifdef PQ_PREFETCH_LANES
-        // one 128-byte line per lane
-        if (lane < 8) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_unit + static_cast<int64_t>(step) * kStep * kPairs + 128 * lane));
-        if constexpr (!QK_ONLY) {
-          const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row + (lane >> 1) * v_row + 128 * (lane & 1);
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(vt));
-        }
-#else
         if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, kStep * kPairs);
         if constexpr (!QK_ONLY) {
           const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row;
           if (v_dense) { if (lane == 1) prefetch_l2(vt, kStep * kHeadDim * 2); }
           else if (lane < kStep) prefetch_l2(vt + lane * v_row, kHeadDim * 2);
         }
-#endif
       };
       for (int ahead = 2; ahead < kPrefetch; ++ahead)
         if (pos + ahead < qs_end) prefetch_step(pos + ahead);
@@ -558,11 +502,7 @@ decode_kernel(const DecodeArgs a) {
       int grp = pos / a.spg;
       const int last_grp = (qs_end - 1) / a.spg;
       const uint32_t sc_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_sc_w));
-#ifdef PQ_V_SMEM
       constexpr bool kCommitScales = QK_ONLY;   // fused kernel: the scale copies join the next value-tile group
-#else
-      constexpr bool kCommitScales = true;
-#endif
       auto stage_group = [&](int gidx, int buf) {
         const int64_t row = static_cast<int64_t>(gidx) * kPairs * QES;
         stage_scales_async<QDT, kCommitScales>(sc_addr + buf * kStageBytes, rs_unit + row, rm_unit + row,
@@ -571,7 +511,6 @@ decode_kernel(const DecodeArgs a) {
       __syncwarp();                       // earlier readers of the staging buffers are done
       int buf = 0;
       stage_group(grp, buf);
-#ifdef PQ_V_SMEM
       if constexpr (!QK_ONLY) {
         cp_async_commit();                           // first value tile + first scales
 #pragma unroll
@@ -581,7 +520,6 @@ decode_kernel(const DecodeArgs a) {
           cp_async_commit();
         }
       }
-#endif
       int s = pos;
       while (s < qs_end) {
         // ---- one run of steps inside one token group: constants first, then a lean step loop ----
@@ -589,28 +527,19 @@ decode_kernel(const DecodeArgs a) {
         // this group's scale rows must have landed.  In the fused kernel they rode in the value-tile
         // group committed one token group (spg steps) ago; when that is older than the kVStages - 1
         // groups allowed in flight nothing needs draining.
-#ifdef PQ_V_SMEM
         if (!QK_ONLY && s != pos && a.spg >= kVStages) { cp_async_wait<kVStages - 1>(); __syncwarp(); }
         else wait_staged();
-#else
-        wait_staged();
-#endif
         if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
         build_angle_table<TBITS, QDT>(tbl_addr, s_sc_w + buf * kStageBytes, lane);
         load_radius_consts<RBITS, QDT>(s_sc_w + buf * kStageBytes, t, rs2, rc2);
         buf ^= 1;
-#ifdef PQ_UNROLL2
-#pragma unroll 2
-#else
 #pragma unroll 1
-#endif
         for (; s < run_end; ++s) {
           if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
           // next tile; the last step of the segment re-reads its own tile rather than branching
           const bool more = s + 1 < qs_end;
           if (more) c_lane += kStep * kPairs;
           const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
-#ifdef PQ_V_SMEM
           if constexpr (!QK_ONLY) {
             if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
             int fill = vstage + kVStages - 1;
@@ -618,7 +547,6 @@ decode_kernel(const DecodeArgs a) {
             load_v_tile_async(vst_addr + fill * kVTileSmem, v_tile, v_row, kStep, lane);
             cp_async_commit();              // also carries scale rows staged since the last commit
           }
-#endif
 
           float S[4] = {0.f, 0.f, 0.f, 0.f};
           qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
@@ -634,33 +562,18 @@ decode_kernel(const DecodeArgs a) {
             if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
             uint32_t b0, b1;
             softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
-#ifdef PQ_V_SMEM
             cp_async_wait<kVStages - 1>();  // this step's tile has landed; the newer ones may be in flight
             __syncwarp();
             pv_from_smem<VDT>(O, vst_addr + vstage * kVTileSmem, lane, b0, b1);
             __syncwarp();                   // every lane is done with the stage before it is refilled
             if (++vstage == kVStages) vstage = 0;
-#else
-            if (more) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) vp[i] += v_step;
-            }
-            pv_half<VDT>(O, 0, v0, b0, b1);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v0[i] = ldg_stream(vp[i]);
-            pv_half<VDT>(O, 4, v1, b0, b1);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v1[i] = ldg_stream(vp[i] + 128);
-#endif
           }
           cg = ng; ch = nh;
         }
         in_group = 0;
         ++grp;
       }
-#ifdef PQ_V_SMEM
       cp_async_wait<0>();                 // the last (redundant) prefetch of the segment
-#endif
     }
 
     // ------------------------------ residual steps -------------------------------
@@ -683,24 +596,10 @@ decode_kernel(const DecodeArgs a) {
             kg[c] = load8_as16<QDT>(kr_unit + (r0 + g) * kr_row + (8 * t + 32 * c) * QES, ok_g);
             kh[c] = load8_as16<QDT>(kr_unit + (r0 + g + 8) * kr_row + (8 * t + 32 * c) * QES, ok_h);
           }
-#ifdef PQ_V_SMEM
           cp_async_wait<0>();
           __syncwarp();
           load_v_tile_async(vst_addr, v_unit + static_cast<int64_t>(Lq + r0) * v_row, v_row, a.R - r0, lane);
           cp_async_commit();
-#else
-          uint4 v0[4], v1[4];
-          {
-            const char* vl = v_unit + static_cast<int64_t>(Lq + r0 + 2 * t) * v_row + 16 * g;
-            const int tk[4] = {0, 1, 8, 9};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const bool ok = r0 + 2 * t + tk[i] < a.R;
-              v0[i] = ok ? ldg_stream(vl + tk[i] * v_row) : make_uint4(0, 0, 0, 0);
-              v1[i] = ok ? ldg_stream(vl + tk[i] * v_row + 128) : make_uint4(0, 0, 0, 0);
-            }
-          }
-#endif
           float S[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -720,15 +619,10 @@ decode_kernel(const DecodeArgs a) {
           }
           uint32_t b0, b1;
           softmax_step<VDT>(S, a.scale_log2, ok_g, ok_h, mg, mh, st, O, b0, b1);
-#ifdef PQ_V_SMEM
           cp_async_wait<0>();
           __syncwarp();
           pv_from_smem<VDT>(O, vst_addr, lane, b0, b1);
           __syncwarp();
-#else
-          pv_half<VDT>(O, 0, v0, b0, b1);
-          pv_half<VDT>(O, 4, v1, b0, b1);
-#endif
         }
       }
 
@@ -742,13 +636,8 @@ decode_kernel(const DecodeArgs a) {
       float* po = a.part_o + slot * kPartialFloats;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-#ifdef PQ_V_SMEM
         // m-tile j: row g is channel 16j + g, row g+8 channel 16j + 8 + g
         const int chn = 16 * j + g, chn2 = chn + 8;
-#else
-        // m-tile j: row g is channel 64*(j/4) + 8g + 2*(j%4), row g+8 the next channel
-        const int chn = 64 * (j >> 2) + 8 * g + 2 * (j & 3), chn2 = chn + 1;
-#endif
         *reinterpret_cast<float2*>(po + chn * kHeadTile + 2 * t) = make_float2(O[j][0], O[j][1]);
         *reinterpret_cast<float2*>(po + chn2 * kHeadTile + 2 * t) = make_float2(O[j][2], O[j][3]);
       }
@@ -789,6 +678,9 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   __shared__ float s_acc[kMergeGroups][kHeadTile][kMergeCh];
   __shared__ float s_max[kHeadTile], s_sum[kHeadTile];
 
+  // no-op unless launched with programmatic stream serialisation: wait until the attention kernel has
+  // completed and its partials are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long unit = blockIdx.x;
   const int chl = threadIdx.x & (kMergeCh - 1), grp = threadIdx.x / kMergeCh;
   const int ch = blockIdx.y * kMergeCh + chl;
@@ -805,15 +697,37 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   const int n = static_cast<int>(w1 - w0 + 1);
   auto slot_of = [&](int i) { return (w0 + i) * a.max_seg + (i == 0 ? seg0 : 0); };
 
-  // ---- pass 1: per-head maximum; thread (i, h) pairs stride over the n x 8 (m, l) entries ----
+  // The first batch of partial rows is requested before anything else so that its DRAM round trip
+  // overlaps the one of the (m, l) entries.
+  float4 o_first[4][2];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = grp + u * kMergeGroups;
+    if (i < n) {
+      const float4* po = reinterpret_cast<const float4*>(a.part_o + slot_of(i) * kPartialFloats + ch * kHeadTile);
+      o_first[u][0] = po[0]; o_first[u][1] = po[1];
+    }
+  }
+
+  // ---- pass 1: per-head maximum; thread (i, h) pairs stride over the n x 8 (m, l) entries.
+  // The entries of the first chunk stay in registers for pass 2. ----
+  constexpr int kKeep = kMergeChunk * kHeadTile / kThreadsM;     // entries per thread in one chunk
+  float2 kept[kKeep];
+  const int h_mine = threadIdx.x & (kHeadTile - 1);
   {
-    const int h = threadIdx.x & (kHeadTile - 1);
     float m = -INFINITY;
-    for (int i = threadIdx.x >> 3; i < n; i += kThreadsM >> 3) m = fmaxf(m, a.part_ml[slot_of(i) * kHeadTile + h].x);
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k) {
+      const int i = (threadIdx.x >> 3) + k * (kThreadsM >> 3);
+      kept[k] = i < n ? a.part_ml[slot_of(i) * kHeadTile + h_mine] : make_float2(-INFINITY, 0.f);
+      m = fmaxf(m, kept[k].x);
+    }
+    for (int i = (threadIdx.x >> 3) + kKeep * (kThreadsM >> 3); i < n; i += kThreadsM >> 3)
+      m = fmaxf(m, a.part_ml[slot_of(i) * kHeadTile + h_mine].x);
     // lanes with equal (lane & 7) hold the same head
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
-    if ((threadIdx.x & 31) < kHeadTile) s_red[threadIdx.x >> 5][h] = m;
+    if ((threadIdx.x & 31) < kHeadTile) s_red[threadIdx.x >> 5][h_mine] = m;
     __syncthreads();
     if (threadIdx.x < kHeadTile) {
       float mm = s_red[0][threadIdx.x];
@@ -832,12 +746,24 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   for (int c0 = 0; c0 < n; c0 += kMergeChunk) {
     const int cn = min(kMergeChunk, n - c0);
     __syncthreads();
-    for (int e = threadIdx.x; e < cn * kHeadTile; e += kThreadsM) {
-      const int i = e >> 3, h = e & (kHeadTile - 1);
-      const float2 ml = a.part_ml[slot_of(c0 + i) * kHeadTile + h];
-      const float w = ml.x == -INFINITY ? 0.f : exp2_approx(ml.x - s_max[h]);
-      s_w[i][h] = w;
-      lsum = fmaf(w, ml.y, lsum);
+    if (c0 == 0) {
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k) {
+        const int i = (threadIdx.x >> 3) + k * (kThreadsM >> 3);
+        if (i < cn) {
+          const float w = kept[k].x == -INFINITY ? 0.f : exp2_approx(kept[k].x - s_max[h_mine]);
+          s_w[i][h_mine] = w;
+          lsum = fmaf(w, kept[k].y, lsum);
+        }
+      }
+    } else {
+      for (int e = threadIdx.x; e < cn * kHeadTile; e += kThreadsM) {
+        const int i = e >> 3;
+        const float2 ml = a.part_ml[slot_of(c0 + i) * kHeadTile + h_mine];
+        const float w = ml.x == -INFINITY ? 0.f : exp2_approx(ml.x - s_max[h_mine]);
+        s_w[i][h_mine] = w;
+        lsum = fmaf(w, ml.y, lsum);
+      }
     }
     __syncthreads();
     for (int i0 = grp; i0 < cn; i0 += 4 * kMergeGroups) {
@@ -845,7 +771,8 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * kMergeGroups;
-        if (i < cn) {
+        if (c0 == 0 && i0 == grp) { o[u][0] = o_first[u][0]; o[u][1] = o_first[u][1]; }
+        else if (i < cn) {
           const float4* po = reinterpret_cast<const float4*>(a.part_o + slot_of(c0 + i) * kPartialFloats + ch * kHeadTile);
           o[u][0] = po[0]; o[u][1] = po[1];
         }
@@ -955,7 +882,6 @@ size_t workspace_bytes_for(const DecodeArgs& a) {
 
 template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
 int launch_decode(const DecodeArgs& a, cudaStream_t s) {
-#ifdef PQ_V_SMEM
   constexpr int kStageBytes = 4 * kPairs * (QDT == PQ_F32 ? 4 : 2);
   constexpr int kWarpSmem = kPairs * (1 << TBITS) * 4 + 2 * kStageBytes + (QK_ONLY ? 0 : kVStages * kVTileSmem);
   constexpr int kSmem = kWarps * kWarpSmem;
@@ -963,9 +889,6 @@ int launch_decode(const DecodeArgs& a, cudaStream_t s) {
     PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, kSmem, s>>>(a);
-#else
-  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, 0, s>>>(a);
-#endif
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
@@ -1079,12 +1002,26 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (rc != PQ_OK) return rc;
   if (p->mid_event) PQ_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(p->mid_event), stream));
   const unsigned units = static_cast<unsigned>(static_cast<long long>(a.B) * a.Nk * a.head_tiles);
+  // The merge is launched with programmatic stream serialisation when it directly follows the attention
+  // kernel in the stream, so its launch overlaps that kernel's tail; with an event in between it is a plain launch.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units, kHeadDim / kMergeCh);
+  cfg.blockDim = dim3(kMergeCh * kMergeGroups);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p->mid_event ? 0 : 1;
+  void* out_ptr = p->out;
+  int64_t osb = p->out_stride_b, osh = p->out_stride_h;
+  float* lse_ptr = p->lse;
   switch (p->out_dtype) {
-    case PQ_F16: merge_partials_kernel<PQ_F16><<<dim3(units, kHeadDim / kMergeCh), kMergeCh * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
-    case PQ_BF16: merge_partials_kernel<PQ_BF16><<<dim3(units, kHeadDim / kMergeCh), kMergeCh * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
-    default: merge_partials_kernel<PQ_F32><<<dim3(units, kHeadDim / kMergeCh), kMergeCh * kMergeGroups, 0, stream>>>(a, p->out, p->out_stride_b, p->out_stride_h, p->lse); break;
+    case PQ_F16: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_F16>, a, out_ptr, osb, osh, lse_ptr)); break;
+    case PQ_BF16: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_BF16>, a, out_ptr, osb, osh, lse_ptr)); break;
+    default: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_F32>, a, out_ptr, osb, osh, lse_ptr)); break;
   }
-  PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
 
