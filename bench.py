@@ -379,7 +379,10 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     got = pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"], rbits=args.rbits, tbits=args.tbits)
-    assert torch.equal(hout.to(device), got), "host-buffer entry point disagrees with the device entry point"
+    if not torch.equal(hout.to(device), got):
+        d = (hout.to(device).float() - got.float()).abs()
+        raise AssertionError(f"host-buffer entry point disagrees with the device entry point: "
+                             f"{int((hout.to(device) != got).sum())} elements, max |diff| {float(d.max()):.3e}")
     out["e2e"] = {"value": nbytes * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                   "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
                   "note": "pq_decode_attention_host: the whole cache of the step is copied from pinned host memory "

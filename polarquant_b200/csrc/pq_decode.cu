@@ -39,6 +39,8 @@
 // tcgen05/TMEM is not used: one decode query per head gives M = 16 tokens x
 // N <= 8 heads tiles, far below the 64-row minimum of tcgen05.mma, and the path
 // is bound by HBM and the shared-memory gathers, not by tensor throughput.
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "pq_common.cuh"
@@ -521,14 +523,17 @@ decode_kernel(const DecodeArgs a) {
         }
       }
       int s = pos;
+      int prev_run = 0;
       while (s < qs_end) {
         // ---- one run of steps inside one token group: constants first, then a lean step loop ----
         const int run_end = min(qs_end, s - in_group + a.spg);
         // this group's scale rows must have landed.  In the fused kernel they rode in the value-tile
-        // group committed one token group (spg steps) ago; when that is older than the kVStages - 1
-        // groups allowed in flight nothing needs draining.
-        if (!QK_ONLY && s != pos && a.spg >= kVStages) { cp_async_wait<kVStages - 1>(); __syncwarp(); }
+        // group committed at the first step of the previous run; when that run had at least kVStages
+        // steps the group is older than the kVStages - 1 groups allowed in flight and nothing needs
+        // draining.  (The first run of a segment may be shorter than a token group.)
+        if (!QK_ONLY && prev_run >= kVStages) { cp_async_wait<kVStages - 1>(); __syncwarp(); }
         else wait_staged();
+        prev_run = run_end - s;
         if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
         build_angle_table<TBITS, QDT>(tbl_addr, s_sc_w + buf * kStageBytes, lane);
         load_radius_consts<RBITS, QDT>(s_sc_w + buf * kStageBytes, t, rs2, rc2);
@@ -794,9 +799,16 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   // reduce sum(w * l): thread's head is (threadIdx.x & 7) in every chunk
   lsum += __shfl_xor_sync(0xffffffffu, lsum, 8);
   lsum += __shfl_xor_sync(0xffffffffu, lsum, 16);
-  if ((threadIdx.x & 31) < kHeadTile) atomicAdd(&s_sum[threadIdx.x & (kHeadTile - 1)], lsum);
+  // per-warp sums are combined in a fixed order so that results do not depend on timing
+  if ((threadIdx.x & 31) < kHeadTile) s_red[threadIdx.x >> 5][threadIdx.x & (kHeadTile - 1)] = lsum;
 #pragma unroll
   for (int h = 0; h < kHeadTile; ++h) s_acc[grp][h][chl] = acc[h];
+  __syncthreads();
+  if (threadIdx.x < kHeadTile) {
+    float l = 0.f;
+    for (int w = 0; w < kThreadsM / 32; ++w) l += s_red[w][threadIdx.x];
+    s_sum[threadIdx.x] = l;
+  }
   __syncthreads();
   const int h = grp;                                            // group g finishes head g
   if (h < nheads) {
@@ -1013,7 +1025,8 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = p->mid_event ? 0 : 1;
+  static const bool no_pdl = getenv("POLARQUANT_B200_NO_PDL") != nullptr;   // field switch: plain launches only
+  cfg.numAttrs = (p->mid_event || no_pdl) ? 0 : 1;
   void* out_ptr = p->out;
   int64_t osb = p->out_stride_b, osh = p->out_stride_h;
   float* lse_ptr = p->lse;

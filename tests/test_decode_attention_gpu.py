@@ -133,6 +133,17 @@ def test_result_does_not_depend_on_the_work_split(num_ctas):
     _check(got, want, f"num_ctas={num_ctas}")
 
 
+def test_results_are_bitwise_reproducible_from_call_to_call():
+    """No atomics, no timing-dependent reduction order: the same inputs give the same bits every time."""
+    import polarquant_b200 as pq
+    for shape in ((4, 32, 8, 64, 128, 128), (5, 16, 4, 19, 16, 77), (3, 28, 4, 37, 32, 5)):
+        q, kres, quant, v = _make(*shape, torch.bfloat16, 4, 4, seed=194)
+        ref, lse = pq.decode_attention(q, kres, *quant, v, out_dtype=torch.float32, return_lse=True)
+        for _ in range(40):
+            got, lse2 = pq.decode_attention(q, kres, *quant, v, out_dtype=torch.float32, return_lse=True)
+            assert torch.equal(got, ref) and torch.equal(lse2, lse)
+
+
 def test_custom_softmax_scale_and_fp32_output():
     import polarquant_b200 as pq
     q, kres, quant, v = _make(1, 8, 2, 2, 128, 9, torch.float16, 4, 4, seed=95)
