@@ -313,23 +313,28 @@ struct SoftmaxState { float m0, m1, l0, l1; };
 
 // Online-softmax update for one step.  S holds logits of tokens (g, g+8) x heads
 // (2t, 2t+1).  Returns the P^T B-fragment (b0, b1) in the value dtype and rescales O.
-template <int VDT>
+// The running maximum lives in the scaled log2 domain; the scale is applied inside the
+// exponent's FMA.  GUARDED adds the per-token validity / mask handling (residual window,
+// masked batches); the unguarded form is the hot loop's.
+template <int VDT, bool GUARDED>
 __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bool ok_g, bool ok_h,
                                              bool masked_g, bool masked_h, SoftmaxState& st,
                                              float (&O)[8][4], uint32_t& b0, uint32_t& b1) {
-  constexpr float kMasked = -1.0e30f;   // finite stand-in for "+ finfo.min": an all-masked row stays uniform
-  float x0 = S[0] * scale_log2, x1 = S[1] * scale_log2, x2 = S[2] * scale_log2, x3 = S[3] * scale_log2;
-  if (masked_g) { x0 = kMasked; x1 = kMasked; }
-  if (masked_h) { x2 = kMasked; x3 = kMasked; }
-  if (!ok_g) { x0 = -INFINITY; x1 = -INFINITY; }
-  if (!ok_h) { x2 = -INFINITY; x3 = -INFINITY; }
-  float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+  if constexpr (GUARDED) {
+    // a finite stand-in for "+ finfo.min" keeps an all-masked row uniform, as in the reference
+    const float kMasked = -1.0e30f / scale_log2;
+    if (masked_g) { S[0] = kMasked; S[1] = kMasked; }
+    if (masked_h) { S[2] = kMasked; S[3] = kMasked; }
+    if (!ok_g) { S[0] = -INFINITY; S[1] = -INFINITY; }
+    if (!ok_h) { S[2] = -INFINITY; S[3] = -INFINITY; }
+  }
+  float mx0 = fmaxf(S[0], S[2]), mx1 = fmaxf(S[1], S[3]);
 #pragma unroll
   for (int o = 4; o <= 16; o <<= 1) {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
   }
-  const float n0 = fmaxf(st.m0, mx0), n1 = fmaxf(st.m1, mx1);
+  const float n0 = fmaxf(st.m0, mx0 * scale_log2), n1 = fmaxf(st.m1, mx1 * scale_log2);   // scale > 0
   const bool grew = (n0 > st.m0) || (n1 > st.m1);
   if (__any_sync(0xffffffffu, grew)) {
     const float a0 = exp2_approx(st.m0 - n0), a1 = exp2_approx(st.m1 - n1);
@@ -338,8 +343,8 @@ __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bo
     for (int j = 0; j < 8; ++j) { O[j][0] *= a0; O[j][1] *= a1; O[j][2] *= a0; O[j][3] *= a1; }
     st.m0 = n0; st.m1 = n1;
   }
-  const float p0 = exp2_approx(x0 - n0), p1 = exp2_approx(x1 - n1);
-  const float p2 = exp2_approx(x2 - n0), p3 = exp2_approx(x3 - n1);
+  const float p0 = exp2_approx(fmaf(S[0], scale_log2, -n0)), p1 = exp2_approx(fmaf(S[1], scale_log2, -n1));
+  const float p2 = exp2_approx(fmaf(S[2], scale_log2, -n0)), p3 = exp2_approx(fmaf(S[3], scale_log2, -n1));
   st.l0 += p0 + p2; st.l1 += p1 + p3;
   b0 = movmatrix_trans(pack2<VDT>(p0, p1));
   b1 = movmatrix_trans(pack2<VDT>(p2, p3));
@@ -367,6 +372,21 @@ __device__ __forceinline__ void load_v_tile_async(uint32_t stage_addr, const cha
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
   }
 }
+// Hot-loop form: dst_lane = stage address + this lane's fixed offset, src_lane = tile address + this lane's
+// fixed offset; the eight copies of a lane are two rows apart.  With dense token rows (256 bytes) every
+// offset is an immediate.
+template <bool DENSE>
+__device__ __forceinline__ void load_v_tile_fast(uint32_t dst_lane, const char* src_lane, int64_t two_rows) {
+#define PQ_CP(I)                                                                                              \
+  if constexpr (DENSE)                                                                                        \
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(dst_lane), "l"(src_lane),          \
+                 "n"((I) * 2 * kVRowSmem), "n"((I) * 2 * kHeadDim * 2) : "memory");                           \
+  else                                                                                                        \
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst_lane), "l"(src_lane + (I) * two_rows), \
+                 "n"((I) * 2 * kVRowSmem) : "memory");
+  PQ_CP(0) PQ_CP(1) PQ_CP(2) PQ_CP(3) PQ_CP(4) PQ_CP(5) PQ_CP(6) PQ_CP(7)
+#undef PQ_CP
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -374,20 +394,24 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // O^T[channel, head] += V^T . P^T for all eight 16-channel tiles of one staged value tile.
 // ldmatrix.trans hands lane (g, t) the pairs {V[2t][c], V[2t+1][c]}: m-tile j row g is channel
 // 16j + g, row g + 8 channel 16j + 8 + g.
-template <int VDT>
-__device__ __forceinline__ void pv_from_smem(float (&O)[8][4], uint32_t stage_addr, int lane, uint32_t b0, uint32_t b1) {
-  // lane supplies the row address of matrix (lane / 8), row (lane % 8):
-  // matrices: (tokens 0-7, ch +0), (tokens 0-7, ch +8), (tokens 8-15, ch +0), (tokens 8-15, ch +8)
+// lane supplies the row address of matrix (lane / 8), row (lane % 8); the matrices are
+// (tokens 0-7, ch +0), (tokens 0-7, ch +8), (tokens 8-15, ch +0), (tokens 8-15, ch +8)
+__device__ __forceinline__ uint32_t ldsm_lane_offset(int lane) {
   const int mi = lane >> 3, r = lane & 7;
-  const uint32_t base = stage_addr + (r + 8 * (mi >> 1)) * kVRowSmem + (mi & 1) * 16;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint32_t a0, a1, a2, a3;
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
-                 : "r"(base + j * 32));
-    mma_16816<VDT>(O[j], a0, a1, a2, a3, b0, b1);
+  return (r + 8 * (mi >> 1)) * kVRowSmem + (mi & 1) * 16;
+}
+template <int VDT>
+__device__ __forceinline__ void pv_from_smem(float (&O)[8][4], uint32_t base, uint32_t b0, uint32_t b1) {
+#define PQ_PV(J)                                                                                   \
+  {                                                                                                \
+    uint32_t a0, a1, a2, a3;                                                                       \
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"         \
+                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)                                          \
+                 : "r"(base), "n"((J) * 32));                                                      \
+    mma_16816<VDT>(O[J], a0, a1, a2, a3, b0, b1);                                                  \
   }
+  PQ_PV(0) PQ_PV(1) PQ_PV(2) PQ_PV(3) PQ_PV(4) PQ_PV(5) PQ_PV(6) PQ_PV(7)
+#undef PQ_PV
 }
 
 // ---------------------------------------------------------------------------------
@@ -474,13 +498,21 @@ decode_kernel(const DecodeArgs a) {
       const uint8_t* c_lane = c_unit + static_cast<int64_t>(pos) * kStep * kPairs + g * kPairs + 16 * t;
       uint4 cg = ldg_stream(c_lane), ch = ldg_stream(c_lane + 8 * kPairs);
       // value tiles go global -> shared (cp.async) one step ahead, two stages per warp
-      const char* v_tile = v_unit + static_cast<int64_t>(pos) * kStep * v_row;
-      const int64_t v_step = kStep * v_row;
+      // this lane's fixed part of the copy addresses: row lane / 16 (+ 2 per copy), 16-byte column lane % 16
+      const char* v_tile = v_unit + static_cast<int64_t>(pos) * kStep * v_row + (lane >> 4) * v_row + (lane & 15) * 16;
+      const uint32_t cp_dst = vst_addr + (lane >> 4) * kVRowSmem + (lane & 15) * 16;
+      const uint32_t ldsm_base = vst_addr + ldsm_lane_offset(lane);
+      const int64_t v_step = kStep * v_row, two_rows = 2 * v_row;
+      const bool v_dense = v_row == kHeadDim * 2;
       int vstage = 0;
+      auto fetch_tile = [&](int stage) {
+        if (v_dense) load_v_tile_fast<true>(cp_dst + stage * kVTileSmem, v_tile, two_rows);
+        else load_v_tile_fast<false>(cp_dst + stage * kVTileSmem, v_tile, two_rows);
+      };
       if constexpr (!QK_ONLY) {
         cp_async_wait<0>();               // nothing of an earlier segment may still be landing in the stages
         __syncwarp();
-        load_v_tile_async(vst_addr, v_tile, v_row, kStep, lane);      // committed with the first scales below
+        fetch_tile(0);                    // committed with the first scales below
       }
       const int last_tile = qs_end - 1;   // tiles past the segment are never fetched: the last one is re-read
       int next_tile = pos;
@@ -488,7 +520,6 @@ decode_kernel(const DecodeArgs a) {
       // The register loads run one step ahead; the L2 is asked for the tiles kPrefetch steps
       // ahead so those loads find their lines on chip.  One lane issues a bulk prefetch per
       // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
-      const bool v_dense = v_row == kHeadDim * 2;
       auto prefetch_step = [&](int step) {
         if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, kStep * kPairs);
         if constexpr (!QK_ONLY) {
@@ -518,7 +549,7 @@ decode_kernel(const DecodeArgs a) {
 #pragma unroll
         for (int d = 1; d < kVStages - 1; ++d) {     // fill the pipeline: tiles pos+1 .. pos+kVStages-2
           if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
-          load_v_tile_async(vst_addr + d * kVTileSmem, v_tile, v_row, kStep, lane);
+          fetch_tile(d);
           cp_async_commit();
         }
       }
@@ -549,7 +580,7 @@ decode_kernel(const DecodeArgs a) {
             if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
             int fill = vstage + kVStages - 1;
             if (fill >= kVStages) fill -= kVStages;
-            load_v_tile_async(vst_addr + fill * kVTileSmem, v_tile, v_row, kStep, lane);
+            fetch_tile(fill);
             cp_async_commit();              // also carries scale rows staged since the last commit
           }
 
@@ -563,13 +594,16 @@ decode_kernel(const DecodeArgs a) {
             if (2 * t < nheads) { orow[0] = S[0]; orow[8] = S[2]; }
             if (2 * t + 1 < nheads) { orow[Lq] = S[1]; orow[Lq + 8] = S[3]; }
           } else {
-            bool mg = false, mh = false;
-            if (mask_row) { mg = mask_row[s * kStep + g] == 0; mh = mask_row[s * kStep + g + 8] == 0; }
             uint32_t b0, b1;
-            softmax_step<VDT>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
+            if (mask_row) {
+              const bool mg = mask_row[s * kStep + g] == 0, mh = mask_row[s * kStep + g + 8] == 0;
+              softmax_step<VDT, true>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
+            } else {
+              softmax_step<VDT, false>(S, a.scale_log2, true, true, false, false, st, O, b0, b1);
+            }
             cp_async_wait<kVStages - 1>();  // this step's tile has landed; the newer ones may be in flight
             __syncwarp();
-            pv_from_smem<VDT>(O, vst_addr + vstage * kVTileSmem, lane, b0, b1);
+            pv_from_smem<VDT>(O, ldsm_base + vstage * kVTileSmem, b0, b1);
             __syncwarp();                   // every lane is done with the stage before it is refilled
             if (++vstage == kVStages) vstage = 0;
           }
@@ -623,10 +657,10 @@ decode_kernel(const DecodeArgs a) {
             mh = ok_h && mask_row[Lq + r0 + g + 8] == 0;
           }
           uint32_t b0, b1;
-          softmax_step<VDT>(S, a.scale_log2, ok_g, ok_h, mg, mh, st, O, b0, b1);
+          softmax_step<VDT, true>(S, a.scale_log2, ok_g, ok_h, mg, mh, st, O, b0, b1);
           cp_async_wait<0>();
           __syncwarp();
-          pv_from_smem<VDT>(O, vst_addr, lane, b0, b1);
+          pv_from_smem<VDT>(O, vst_addr + ldsm_lane_offset(lane), b0, b1);
           __syncwarp();
         }
       }
