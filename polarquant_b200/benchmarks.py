@@ -1,0 +1,96 @@
+"""Secondary timings of the polar key-cache kernels (the headline number is bench.py at the repository root).
+
+    python -m polarquant_b200.benchmarks qk        # the reference's QK micro-benchmark grid
+    python -m polarquant_b200.benchmarks sweep     # fused decode attention over bit widths / group sizes / shapes
+    python -m polarquant_b200.benchmarks quant     # quantizer at prefill sizes
+
+`qk` reproduces the grid of the reference's benchmark/benchmark_matmul.py (`test4polar`, lines 89-120: 32 heads on
+the code tensor, D = 64, fp16, random codes in [0, 250) and randn scales, batch 1/2/4/8, length 4096..131072), but
+times with CUDA events over back-to-back launches instead of a host timer around each synchronised call.
+Every line printed is one JSON object.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import ops
+
+
+def _time_us(fn, reps: int = 20, warm: int = 3) -> float:
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps * 1e3
+
+
+def qk_grid(group_size: int = 32, rbits: int = 4, tbits: int = 4, batches=(1, 2, 4, 8),
+            lengths=(4096, 8192, 16384, 32768, 65536, 131072)):
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(2)
+    for B in batches:
+        for L in lengths:
+            N = 32
+            q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.float16)
+            idx = torch.randint(0, 250, (B, N, L // group_size, group_size, 64), device=dev, generator=g,
+                                dtype=torch.uint8)
+            sc = [torch.randn(B, N, L // group_size, 1, 64, device=dev, generator=g).to(torch.float16)
+                  for _ in range(4)]
+            us = _time_us(lambda: ops.qk_decode(q, idx, *sc, rbits=rbits, tbits=tbits))
+            nbytes = idx.numel() + 4 * sc[0].numel() * 2 + q.numel() * 2 + B * N * L * 4
+            print(json.dumps({"bench": "qk", "batch": B, "length": L, "group": group_size, "bits": f"{rbits}/{tbits}",
+                              "ms": us / 1e3, "gbs": nbytes / us / 1e3}))
+            del idx, sc
+
+
+def decode_sweep():
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1003)
+    shapes = [("llama3-8b B16 ctx32k", 16, 32, 8, 32768), ("qwen2.5-7b B64 ctx8k", 64, 28, 4, 8192),
+              ("llama2-7b MHA B1 ctx4k", 1, 32, 32, 4096), ("70b-shaped 1 kv head/GPU B8 ctx128k", 8, 8, 1, 131072)]
+    for name, B, N, Nk, ctx in shapes:
+        for (rb, tb) in ((4, 4), (3, 3), (2, 4)):
+            for G in (128, 32):
+                R = 128
+                Nb = (ctx - R) // G
+                q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.bfloat16)
+                v = torch.randn(B, Nk, ctx, 128, device=dev, generator=g).to(torch.bfloat16)
+                kres = torch.randn(B, Nk, R, 128, device=dev, generator=g).to(torch.bfloat16)
+                keys = torch.randn(B, Nk, Nb * G, 128, device=dev, generator=g).to(torch.bfloat16)
+                packed = ops.quantize_and_pack_nbit(keys, rb, tb, G)
+                del keys
+                us = _time_us(lambda: ops.decode_attention(q, kres, *packed, v, rbits=rb, tbits=tb), reps=20)
+                nbytes = (packed[0].numel() + 4 * packed[1].numel() * 2 + kres.numel() * 2 + v.numel() * 2
+                          + q.numel() * 4)
+                print(json.dumps({"bench": "decode", "shape": name, "bits": f"{rb}/{tb}", "group": G, "us": us,
+                                  "mb": nbytes / 1e6, "gbs": nbytes / us / 1e3}))
+                del packed, v
+
+
+def quant_sizes():
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(7)
+    for (B, Nk, L, G, dt) in ((16, 8, 32768, 128, torch.bfloat16), (64, 4, 8192, 128, torch.bfloat16),
+                              (64, 4, 8192, 32, torch.bfloat16), (16, 8, 32768, 128, torch.float16),
+                              (16, 8, 128, 128, torch.bfloat16)):
+        base = torch.randn(B, L, Nk, 128, device=dev, generator=g).to(dt)
+        keys = base.transpose(1, 2)
+        us = _time_us(lambda: ops.quantize_and_pack_nbit(keys, 4, 4, G), reps=10)
+        es = base.element_size()
+        nbytes = B * Nk * L * 128 * es + B * Nk * (L * 64 + (L // G) * 4 * 64 * es)
+        print(json.dumps({"bench": "quantize", "batch": B, "kv_heads": Nk, "tokens": L, "group": G,
+                          "dtype": str(dt).split(".")[-1], "us": us, "mb": nbytes / 1e6, "gbs": nbytes / us / 1e3}))
+        del base, keys
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "sweep"
+    {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes}[what]()
