@@ -54,6 +54,16 @@ int pq_quantize(const void* keys, const int64_t strides[4], int B, int Nk, int L
                 uint8_t* codes, void* rscale, void* rmn, void* tscale, void* tmn, void* stream);
 
 /*
+ * Self-test of the quantizer's fast paths (no reference counterpart).  The kernel replaces atan2f, sqrtf and the
+ * IEEE division by cheaper approximations wherever the approximation provably rounds to the same 16-bit value,
+ * and calls the exact routine otherwise.  This entry point checks that claim exhaustively on the device: for all
+ * 2^32 pairs of 16-bit patterns of `dtype` (PQ_F16 or PQ_BF16) it compares the fast-path result with the
+ * exact-only result - which = 0: angle and radius of the key pair (x, y); which = 1: quantisation level of value
+ * x with step y - and writes the number of disagreeing pairs to *mismatches_dev (device memory, 8 bytes).
+ */
+int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream);
+
+/*
  * Un-scaled fp32 query-key logits over the packed keys.  Replaces
  * attention_decode_forward_triton_impl and its Triton kernel
  * (models/kernel4group.py:14-109).

@@ -11,6 +11,7 @@ int& last_cuda_error() {
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
                     int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
                     void* tmn, cudaStream_t stream);
+int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
                      const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
                      int Nb, int G, int D, int rbits, int tbits, int dtype, cudaStream_t stream);
@@ -58,6 +59,10 @@ int pq_quantize(const void* keys, const int64_t strides[4], int B, int Nk, int L
                 void* tmn, void* stream) {
   return quantize_device(keys, strides, B, Nk, L, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale,
                          tmn, static_cast<cudaStream_t>(stream));
+}
+
+int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream) {
+  return selftest_quantizer_device(dtype, which, mismatches_dev, static_cast<cudaStream_t>(stream));
 }
 
 int pq_qk_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* codes, const void* rscale,

@@ -54,24 +54,137 @@ template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bflo
   v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-template <typename T>
-__device__ __forceinline__ void polar_of(float x, float y, float wrap, bool norm_separate,
-                                         float& phi, float& rad) {
-  using E = Elem<T>;
-  float a = E::round(atan2f(y, x));
-  if (a < 0.0f) a = E::round(__fadd_rn(a, wrap));
-  phi = a;
-  float s = norm_separate ? __fadd_rn(__fmul_rn(x, x), __fmul_rn(y, y)) : __fmaf_rn(y, y, __fmul_rn(x, x));
-  rad = E::round(__fsqrt_rn(s));
+// ---------------------------------------------------------------------------------------------
+// Fast paths with an exact fallback.
+//
+// The reference's results are roundings to a 16-bit type of fp32 library results (atan2f, sqrtf, an
+// IEEE division).  A cheaper fp32 approximation gives the same 16-bit result whenever it lies farther
+// from the nearest rounding tie than its own error; only the remaining fraction of a percent takes the
+// library call.  `rounds_safely` implements that test; the margins are validated exhaustively over
+// every pair of 16-bit inputs by pq_selftest_quantizer (see tests/test_quantizer_gpu.py).
+// fp32 keys always take the exact path.  The exact routines are kept out of line so the unrolled hot
+// code stays small enough for the instruction cache.
+// ---------------------------------------------------------------------------------------------
+constexpr unsigned kTieMargin = 24;     // fp32 units in the last place kept clear on both sides of a tie
+
+template <typename T> __device__ __forceinline__ bool rounds_safely(float v);
+template <> __device__ __forceinline__ bool rounds_safely<__nv_bfloat16>(float v) {
+  // bf16 keeps the top 16 bits: ties sit at 0x8000 in the low half
+  const unsigned low = __float_as_uint(v) & 0xffffu;
+  return (low - (0x8000u - kTieMargin)) > 2u * kTieMargin;
+}
+template <> __device__ __forceinline__ bool rounds_safely<__half>(float v) {
+  // fp16 keeps 10 mantissa bits: ties sit at 0x1000 in the low 13 bits, for values in its normal range
+  const unsigned bits = __float_as_uint(v);
+  const unsigned low = bits & 0x1fffu;
+  const unsigned mag = bits & 0x7fffffffu;
+  const bool normal = mag >= 0x38800000u && mag < 0x47000000u;     // 2^-14 <= |v| < 32768
+  return normal && (low - (0x1000u - kTieMargin)) > 2u * kTieMargin;
+}
+template <> __device__ __forceinline__ bool rounds_safely<float>(float) { return false; }
+
+__device__ __forceinline__ bool mid_range_bits(unsigned mag) {      // 2^-100 < |v| < 2^100: no flush, no overflow, no NaN
+  return mag > 0x0d800000u && mag < 0x71800000u;
+}
+__device__ __forceinline__ bool mid_range(float v) { return mid_range_bits(__float_as_uint(v) & 0x7fffffffu); }
+
+__device__ __noinline__ float atan2_exact(float y, float x) { return atan2f(y, x); }
+__device__ __noinline__ float sqrt_exact(float s) { return __fsqrt_rn(s); }
+__device__ __noinline__ float div_exact(float a, float b) { return __fdiv_rn(a, b); }
+// float -> int64 -> uint8, the cast ATen performs: NaN gives 0, +inf and anything past 2^63 give 0xff
+__device__ __noinline__ unsigned cast_exact(float q) { return static_cast<unsigned>(static_cast<long long>(q)) & 0xffu; }
+
+// round two fp32 values to T and back with one packed conversion (full-rate pipe, unlike the scalar cvt)
+template <typename T> __device__ __forceinline__ void round2(float a, float b, float& ra, float& rb) {
+  if constexpr (Elem<T>::kDtype == PQ_F32) { ra = a; rb = b; }
+  else { const float2 f = unpack2<Elem<T>::kDtype>(pack2<Elem<T>::kDtype>(a, b)); ra = f.x; rb = f.y; }
 }
 
-template <typename T>
-__device__ __forceinline__ unsigned level_of(float v, float lo, float step, unsigned top) {
-  using E = Elem<T>;
-  float q = floorf(E::round(__fdiv_rn(E::round(__fsub_rn(v, lo)), step)));
-  // float -> int64 -> uint8, the cast ATen performs: NaN gives 0, +inf gives 0xff
-  unsigned u = static_cast<unsigned>(static_cast<long long>(q)) & 0xffu;
-  return u < top ? u : top;
+// atan2 by the odd polynomial atan(z) = z * P(z^2) on z = min/max in [0, 1] (relative error 2.4e-7 when
+// evaluated in fp32) and the usual octant fix-ups.  `ok` is false where the approximation is not trusted:
+// zeros, NaN/inf, magnitudes outside 2^+-100, ratios that underflow.
+__device__ __forceinline__ float atan2_approx(float y, float x, bool& ok) {
+  const unsigned ix = __float_as_uint(x) & 0x7fffffffu, iy = __float_as_uint(y) & 0x7fffffffu;
+  const unsigned imx = max(ix, iy), imn = min(ix, iy);            // integer order == order of magnitudes; NaN sorts last
+  const float mx = __uint_as_float(imx), mn = __uint_as_float(imn);
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(mx));
+  const float z = mn * r, u = z * z;
+  ok = mid_range_bits(imx) && z > 1e-30f;
+  float p = -0.004780454095453024f;
+  p = fmaf(p, u, 0.024557121098041534f);
+  p = fmaf(p, u, -0.059904709458351135f);
+  p = fmaf(p, u, 0.09942758828401566f);
+  p = fmaf(p, u, -0.14029419422149658f);
+  p = fmaf(p, u, 0.19971375167369843f);
+  p = fmaf(p, u, -0.3333209455013275f);
+  p = fmaf(p, u, 0.9999999403953552f);
+  float a = p * z;
+  if (iy > ix) a = 1.5707963267948966f - a;
+  if (x < 0.0f) a = 3.141592653589793f - a;
+  return y < 0.0f ? -a : a;
+}
+
+// angle and radius of two pairs at once (the roundings are packed two by two)
+template <typename T, bool FAST = true>
+__device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[2], float wrap, bool norm_separate,
+                                          float (&phi)[2], float (&rad)[2]) {
+  constexpr bool kFast = FAST && !(Elem<T>::kDtype == PQ_F32);
+  float a[2], r[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    bool ok = false;
+    if constexpr (kFast) {
+      a[k] = atan2_approx(y[k], x[k], ok);
+      ok = ok && rounds_safely<T>(a[k]);
+    }
+    if (!ok) a[k] = atan2_exact(y[k], x[k]);
+    // for 16-bit keys the two products are exact in fp32, so both forms of the sum agree
+    const float s = norm_separate ? __fadd_rn(__fmul_rn(x[k], x[k]), __fmul_rn(y[k], y[k]))
+                                  : __fmaf_rn(y[k], y[k], __fmul_rn(x[k], x[k]));
+    ok = false;
+    if constexpr (kFast) {
+      float rs;
+      asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(rs) : "f"(s));
+      r[k] = s * rs;
+      ok = mid_range(s) && rounds_safely<T>(r[k]);
+    }
+    if (!ok) r[k] = sqrt_exact(s);
+  }
+  round2<T>(a[0], a[1], a[0], a[1]);
+  float w[2];
+  round2<T>(__fadd_rn(a[0], wrap), __fadd_rn(a[1], wrap), w[0], w[1]);
+  phi[0] = a[0] < 0.0f ? w[0] : a[0];
+  phi[1] = a[1] < 0.0f ? w[1] : a[1];
+  round2<T>(r[0], r[1], rad[0], rad[1]);
+}
+
+// floor(RN(RN(v - lo) / step)) clamped to [0, top], for two values.  `rstep` is the correctly rounded
+// reciprocal of `step`; the product is within 1.5 ulp of the IEEE quotient and is used when it rounds safely.
+template <typename T, bool FAST = true>
+__device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)[2], const float (&step)[2],
+                                          const float (&rstep)[2], unsigned top, unsigned (&lvl)[2]) {
+  constexpr bool kFast = FAST && !(Elem<T>::kDtype == PQ_F32);
+  float d[2], q[2];
+  round2<T>(__fsub_rn(v[0], lo[0]), __fsub_rn(v[1], lo[1]), d[0], d[1]);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    bool ok = false;
+    if constexpr (kFast) {
+      q[k] = d[k] * rstep[k];
+      ok = mid_range(step[k]) && rounds_safely<T>(q[k]);
+    }
+    if (!ok) q[k] = div_exact(d[k], step[k]);
+  }
+  round2<T>(q[0], q[1], q[0], q[1]);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    // in [0, 256) truncation to int is the floor and equals the reference's cast chain
+    unsigned u;
+    if (q[k] >= 0.0f && q[k] < 256.0f) u = static_cast<unsigned>(__float2int_rz(q[k]));
+    else u = cast_exact(floorf(q[k]));
+    lvl[k] = u < top ? u : top;
+  }
 }
 
 // NI > 0: the thread keeps phi and r of its NI tokens x 4 pairs in registers
@@ -112,8 +225,14 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
       load4<T>(row + p0, x);
       load4<T>(row + p0 + kPairs, y);
 #pragma unroll
+      for (int p = 0; p < 4; p += 2) {
+        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
+        float ph[2], rd[2];
+        polar_of2<T>(xx, yy, wrap, norm_sep, ph, rd);
+        phi[i][p] = ph[0]; phi[i][p + 1] = ph[1]; rad[i][p] = rd[0]; rad[i][p + 1] = rd[1];
+      }
+#pragma unroll
       for (int p = 0; p < 4; ++p) {
-        polar_of<T>(x[p], y[p], wrap, norm_sep, phi[i][p], rad[i][p]);
         tmx[p] = max_nan(tmx[p], phi[i][p]); tmn[p] = min_nan(tmn[p], phi[i][p]);
         rmx[p] = max_nan(rmx[p], rad[i][p]); rmn[p] = min_nan(rmn[p], rad[i][p]);
       }
@@ -125,11 +244,15 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
       load4<T>(row + p0, x);
       load4<T>(row + p0 + kPairs, y);
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        float a, r;
-        polar_of<T>(x[p], y[p], wrap, norm_sep, a, r);
-        tmx[p] = max_nan(tmx[p], a); tmn[p] = min_nan(tmn[p], a);
-        rmx[p] = max_nan(rmx[p], r); rmn[p] = min_nan(rmn[p], r);
+      for (int p = 0; p < 4; p += 2) {
+        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
+        float ph[2], rd[2];
+        polar_of2<T>(xx, yy, wrap, norm_sep, ph, rd);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          tmx[p + k] = max_nan(tmx[p + k], ph[k]); tmn[p + k] = min_nan(tmn[p + k], ph[k]);
+          rmx[p + k] = max_nan(rmx[p + k], rd[k]); rmn[p + k] = min_nan(rmn[p + k], rd[k]);
+        }
       }
     }
   }
@@ -160,7 +283,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   }
   __syncthreads();
 
-  float tstep[4], rstep[4];
+  float tstep[4], rstep[4], trcp[4], rrcp[4];
   const float inv_t = 1.0f / static_cast<float>(1 << tbits), inv_r = 1.0f / static_cast<float>(1 << rbits);
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
@@ -169,6 +292,8 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
     // dividing by a power of two equals multiplying by its exact reciprocal
     tstep[p] = E::round(__fmul_rn(E::round(__fsub_rn(tmx[p], tmn[p])), inv_t));
     rstep[p] = E::round(__fmul_rn(E::round(__fsub_rn(rmx[p], rmn[p])), inv_r));
+    trcp[p] = __frcp_rn(tstep[p]);
+    rrcp[p] = __frcp_rn(rstep[p]);
   }
   if (warp == 0 && tsub == 0) {
     const int64_t so = static_cast<int64_t>(tile) * kPairs + p0;
@@ -186,10 +311,15 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
     for (int i = 0; i < NI; ++i) {
       uint32_t word = 0;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        unsigned th = level_of<T>(phi[i][p], tmn[p], tstep[p], ttop);
-        unsigned rh = level_of<T>(rad[i][p], rmn[p], rstep[p], rtop);
-        word |= (((rh << tbits) + th) & 0xffu) << (8 * p);
+      for (int p = 0; p < 4; p += 2) {
+        const float pv[2] = {phi[i][p], phi[i][p + 1]}, rv[2] = {rad[i][p], rad[i][p + 1]};
+        const float tl[2] = {tmn[p], tmn[p + 1]}, ts[2] = {tstep[p], tstep[p + 1]}, tr[2] = {trcp[p], trcp[p + 1]};
+        const float rl[2] = {rmn[p], rmn[p + 1]}, rs[2] = {rstep[p], rstep[p + 1]}, rr[2] = {rrcp[p], rrcp[p + 1]};
+        unsigned th[2], rh[2];
+        level_of2<T>(pv, tl, ts, tr, ttop, th);
+        level_of2<T>(rv, rl, rs, rr, rtop, rh);
+        word |= (((rh[0] << tbits) + th[0]) & 0xffu) << (8 * p);
+        word |= (((rh[1] << tbits) + th[1]) & 0xffu) << (8 * p + 8);
       }
       *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok0 + 16 * i) * kPairs) = word;
     }
@@ -201,16 +331,53 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
       load4<T>(row + p0 + kPairs, y);
       uint32_t word = 0;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        float a, r;
-        polar_of<T>(x[p], y[p], wrap, norm_sep, a, r);
-        unsigned th = level_of<T>(a, tmn[p], tstep[p], ttop);
-        unsigned rh = level_of<T>(r, rmn[p], rstep[p], rtop);
-        word |= (((rh << tbits) + th) & 0xffu) << (8 * p);
+      for (int p = 0; p < 4; p += 2) {
+        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
+        float pv[2], rv[2];
+        polar_of2<T>(xx, yy, wrap, norm_sep, pv, rv);
+        const float tl[2] = {tmn[p], tmn[p + 1]}, ts[2] = {tstep[p], tstep[p + 1]}, tr[2] = {trcp[p], trcp[p + 1]};
+        const float rl[2] = {rmn[p], rmn[p + 1]}, rs[2] = {rstep[p], rstep[p + 1]}, rr[2] = {rrcp[p], rrcp[p + 1]};
+        unsigned th[2], rh[2];
+        level_of2<T>(pv, tl, ts, tr, ttop, th);
+        level_of2<T>(rv, rl, rs, rr, rtop, rh);
+        word |= (((rh[0] << tbits) + th[0]) & 0xffu) << (8 * p);
+        word |= (((rh[1] << tbits) + th[1]) & 0xffu) << (8 * p + 8);
       }
       *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok) * kPairs) = word;
     }
   }
+}
+
+// Exhaustive self-test: for every pair of 16-bit patterns, the fast-path functions must return exactly what the
+// exact-only functions return.  which = 0: angle and radius of the key pair (x, y); which = 1: quantisation
+// level of value x with step y.  Counts the disagreeing pairs.
+template <typename T>
+__global__ void selftest_kernel(int which, unsigned long long* mismatches) {
+  using E = Elem<T>;
+  unsigned long long bad = 0;
+  const unsigned long long total = 1ull << 32;
+  for (unsigned long long i = blockIdx.x * static_cast<unsigned long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
+    const unsigned short xb = static_cast<unsigned short>(i & 0xffffu), yb = static_cast<unsigned short>(i >> 16);
+    const float x = E::to_float(*reinterpret_cast<const T*>(&xb)), y = E::to_float(*reinterpret_cast<const T*>(&yb));
+    if (which == 0) {
+      const float xx[2] = {x, y}, yy[2] = {y, x};             // the pair and its mirror image
+      float p0[2], r0[2], p1[2], r1[2];
+      polar_of2<T, true>(xx, yy, 6.283185307179586f, true, p0, r0);
+      polar_of2<T, false>(xx, yy, 6.283185307179586f, true, p1, r1);
+      // values compare equal or both NaN; +0 and -0 count as equal, as they do for torch.equal
+      const bool same_p = (p0[0] == p1[0]) || (p0[0] != p0[0] && p1[0] != p1[0]);
+      const bool same_r = (r0[0] == r1[0]) || (r0[0] != r0[0] && r1[0] != r1[0]);
+      bad += !(same_p && same_r);
+    } else {
+      const float v[2] = {x, x}, lo[2] = {0.0f, 0.0f}, st[2] = {y, y}, rc[2] = {__frcp_rn(y), __frcp_rn(y)};
+      unsigned a[2], b[2];
+      level_of2<T, true>(v, lo, st, rc, 255u, a);
+      level_of2<T, false>(v, lo, st, rc, 255u, b);
+      bad += a[0] != b[0];
+    }
+  }
+  if (bad) atomicAdd(mismatches, bad);
 }
 
 template <typename T>
@@ -239,6 +406,16 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
 }
 
 }  // namespace
+
+int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream) {
+  if (!mismatches_dev || which < 0 || which > 1) return PQ_ERR_INVALID;
+  if (dtype != PQ_F16 && dtype != PQ_BF16) return PQ_ERR_INVALID;
+  PQ_CUDA_TRY(cudaMemsetAsync(mismatches_dev, 0, sizeof(unsigned long long), stream));
+  if (dtype == PQ_F16) selftest_kernel<__half><<<148 * 8, 256, 0, stream>>>(which, mismatches_dev);
+  else selftest_kernel<__nv_bfloat16><<<148 * 8, 256, 0, stream>>>(which, mismatches_dev);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
 
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G,
                     int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn,

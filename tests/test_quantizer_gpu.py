@@ -87,6 +87,20 @@ def test_edge_values_bit_exact():
         _assert_same(got, oracle.quantize_ops(keys, 4, 4, 128))
 
 
+@pytest.mark.parametrize("dtype_name", ["bf16", "fp16"])
+@pytest.mark.parametrize("which", [0, 1])
+def test_fast_paths_agree_with_exact_paths_for_every_16_bit_input_pair(dtype_name, which):
+    """Exhaustive: all 2^32 (x, y) patterns.  which 0 = angle and radius of a key pair, 1 = quantisation level."""
+    from polarquant_b200 import _lib
+    lib = _lib.load()
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    dt = _lib.PQ_BF16 if dtype_name == "bf16" else _lib.PQ_F16
+    rc = lib.pq_selftest_quantizer(dt, which, counter.data_ptr(), None)
+    assert rc == 0, lib.pq_strerror(rc)
+    torch.cuda.synchronize()
+    assert int(counter.item()) == 0
+
+
 def test_empty_and_invalid_inputs():
     import polarquant_b200 as pq
     out = pq.quantize_and_pack_nbit(torch.empty(2, 4, 0, 128, dtype=torch.bfloat16, device="cuda"), 4, 4, 128)
