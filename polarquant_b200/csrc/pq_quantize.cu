@@ -83,16 +83,16 @@ template <> __device__ __forceinline__ bool rounds_safely<__half>(float v) {
 }
 template <> __device__ __forceinline__ bool rounds_safely<float>(float) { return false; }
 
-__device__ __forceinline__ bool mid_range_bits(unsigned mag) {      // 2^-100 < |v| < 2^100: no flush, no overflow, no NaN
-  return mag > 0x0d800000u && mag < 0x71800000u;
+// 2^-100 < |v| < 2^100 and not NaN: the range in which the approximations neither flush nor overflow.
+// It is tested on RESULTS: zero, NaN, inf or denormal inputs and underflowing ratios all surface there.
+__device__ __forceinline__ bool mid_range(float v) {
+  return ((__float_as_uint(v) & 0x7fffffffu) - 0x0d800001u) < (0x71800000u - 0x0d800001u);
 }
-__device__ __forceinline__ bool mid_range(float v) { return mid_range_bits(__float_as_uint(v) & 0x7fffffffu); }
 
-__device__ __noinline__ float atan2_exact(float y, float x) { return atan2f(y, x); }
-__device__ __noinline__ float sqrt_exact(float s) { return __fsqrt_rn(s); }
-__device__ __noinline__ float div_exact(float a, float b) { return __fdiv_rn(a, b); }
 // float -> int64 -> uint8, the cast ATen performs: NaN gives 0, +inf and anything past 2^63 give 0xff
-__device__ __noinline__ unsigned cast_exact(float q) { return static_cast<unsigned>(static_cast<long long>(q)) & 0xffu; }
+__device__ __forceinline__ unsigned cast_like_aten(float q) {
+  return static_cast<unsigned>(static_cast<long long>(q)) & 0xffu;
+}
 
 // round two fp32 values to T and back with one packed conversion (full-rate pipe, unlike the scalar cvt)
 template <typename T> __device__ __forceinline__ void round2(float a, float b, float& ra, float& rb) {
@@ -101,16 +101,13 @@ template <typename T> __device__ __forceinline__ void round2(float a, float b, f
 }
 
 // atan2 by the odd polynomial atan(z) = z * P(z^2) on z = min/max in [0, 1] (relative error 2.4e-7 when
-// evaluated in fp32) and the usual octant fix-ups.  `ok` is false where the approximation is not trusted:
-// zeros, NaN/inf, magnitudes outside 2^+-100, ratios that underflow.
-__device__ __forceinline__ float atan2_approx(float y, float x, bool& ok) {
+// evaluated in fp32) and the usual octant fix-ups.
+__device__ __forceinline__ float atan2_approx(float y, float x) {
   const unsigned ix = __float_as_uint(x) & 0x7fffffffu, iy = __float_as_uint(y) & 0x7fffffffu;
-  const unsigned imx = max(ix, iy), imn = min(ix, iy);            // integer order == order of magnitudes; NaN sorts last
-  const float mx = __uint_as_float(imx), mn = __uint_as_float(imn);
+  const unsigned imx = max(ix, iy), imn = min(ix, iy);            // integer order == order of magnitudes
   float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(mx));
-  const float z = mn * r, u = z * z;
-  ok = mid_range_bits(imx) && z > 1e-30f;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__uint_as_float(imx)));
+  const float z = __uint_as_float(imn) * r, u = z * z;
   float p = -0.004780454095453024f;
   p = fmaf(p, u, 0.024557121098041534f);
   p = fmaf(p, u, -0.059904709458351135f);
@@ -125,31 +122,36 @@ __device__ __forceinline__ float atan2_approx(float y, float x, bool& ok) {
   return y < 0.0f ? -a : a;
 }
 
+// exact (library) angle and radius before rounding, out of line: taken by a fraction of a percent of the items
+__device__ __noinline__ float2 polar_exact(float x, float y, bool norm_separate) {
+  const float s = norm_separate ? __fadd_rn(__fmul_rn(x, x), __fmul_rn(y, y)) : __fmaf_rn(y, y, __fmul_rn(x, x));
+  return make_float2(atan2f(y, x), __fsqrt_rn(s));
+}
+__device__ __noinline__ float div_exact(float a, float b) { return __fdiv_rn(a, b); }
+
 // angle and radius of two pairs at once (the roundings are packed two by two)
 template <typename T, bool FAST = true>
 __device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[2], float wrap, bool norm_separate,
                                           float (&phi)[2], float (&rad)[2]) {
   constexpr bool kFast = FAST && !(Elem<T>::kDtype == PQ_F32);
   float a[2], r[2];
+  bool ok[2] = {false, false};
+  if constexpr (kFast) {
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    bool ok = false;
-    if constexpr (kFast) {
-      a[k] = atan2_approx(y[k], x[k], ok);
-      ok = ok && rounds_safely<T>(a[k]);
-    }
-    if (!ok) a[k] = atan2_exact(y[k], x[k]);
-    // for 16-bit keys the two products are exact in fp32, so both forms of the sum agree
-    const float s = norm_separate ? __fadd_rn(__fmul_rn(x[k], x[k]), __fmul_rn(y[k], y[k]))
-                                  : __fmaf_rn(y[k], y[k], __fmul_rn(x[k], x[k]));
-    ok = false;
-    if constexpr (kFast) {
+    for (int k = 0; k < 2; ++k) {
+      a[k] = atan2_approx(y[k], x[k]);
+      // for 16-bit keys the two products are exact in fp32, so both forms of the sum agree
+      const float s = __fmaf_rn(y[k], y[k], __fmul_rn(x[k], x[k]));
       float rs;
       asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(rs) : "f"(s));
       r[k] = s * rs;
-      ok = mid_range(s) && rounds_safely<T>(r[k]);
+      ok[k] = mid_range(a[k]) && rounds_safely<T>(a[k]) && mid_range(r[k]) && rounds_safely<T>(r[k]);
     }
-    if (!ok) r[k] = sqrt_exact(s);
+  }
+  if (!(ok[0] && ok[1])) {                     // one rarely taken branch for both items
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      if (!ok[k]) { const float2 e = polar_exact(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
   }
   round2<T>(a[0], a[1], a[0], a[1]);
   float w[2];
@@ -161,28 +163,33 @@ __device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[
 
 // floor(RN(RN(v - lo) / step)) clamped to [0, top], for two values.  `rstep` is the correctly rounded
 // reciprocal of `step`; the product is within 1.5 ulp of the IEEE quotient and is used when it rounds safely.
+// A quotient that is not below 256 (inf, NaN from a zero step, ...) takes the exact division and cast.
 template <typename T, bool FAST = true>
 __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)[2], const float (&step)[2],
                                           const float (&rstep)[2], unsigned top, unsigned (&lvl)[2]) {
   constexpr bool kFast = FAST && !(Elem<T>::kDtype == PQ_F32);
   float d[2], q[2];
   round2<T>(__fsub_rn(v[0], lo[0]), __fsub_rn(v[1], lo[1]), d[0], d[1]);
+  bool ok[2] = {false, false};
+  if constexpr (kFast) {
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    bool ok = false;
-    if constexpr (kFast) {
+    for (int k = 0; k < 2; ++k) {
       q[k] = d[k] * rstep[k];
-      ok = mid_range(step[k]) && rounds_safely<T>(q[k]);
+      ok[k] = q[k] < 256.0f && rounds_safely<T>(q[k]);
     }
-    if (!ok) q[k] = div_exact(d[k], step[k]);
+  }
+  if (!(ok[0] && ok[1])) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      if (!ok[k]) q[k] = div_exact(d[k], step[k]);
   }
   round2<T>(q[0], q[1], q[0], q[1]);
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
     // in [0, 256) truncation to int is the floor and equals the reference's cast chain
-    unsigned u;
-    if (q[k] >= 0.0f && q[k] < 256.0f) u = static_cast<unsigned>(__float2int_rz(q[k]));
-    else u = cast_exact(floorf(q[k]));
+    const bool small = q[k] >= 0.0f && q[k] < 256.0f;
+    unsigned u = static_cast<unsigned>(__float2int_rz(small ? q[k] : 0.0f));
+    if (!small) u = cast_like_aten(floorf(q[k]));
     lvl[k] = u < top ? u : top;
   }
 }
