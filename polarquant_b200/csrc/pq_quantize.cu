@@ -119,21 +119,34 @@ __device__ __forceinline__ float atan2_approx(float y, float x) {
   float a = p * z;
   if (iy > ix) a = 1.5707963267948966f - a;
   if (x < 0.0f) a = 3.141592653589793f - a;
-  return y < 0.0f ? -a : a;
+  return __float_as_int(y) < 0 ? -a : a;      // sign bit, so that y = -0 gives -pi (x < 0) like atan2f
 }
 
 // exact (library) angle and radius before rounding, out of line: taken by a fraction of a percent of the items
-__device__ __noinline__ float2 polar_exact(float x, float y, bool norm_separate) {
+__device__ __forceinline__ float2 polar_exact_inline(float x, float y, bool norm_separate) {
   const float s = norm_separate ? __fadd_rn(__fmul_rn(x, x), __fmul_rn(y, y)) : __fmaf_rn(y, y, __fmul_rn(x, x));
   return make_float2(atan2f(y, x), __fsqrt_rn(s));
 }
+__device__ __noinline__ float2 polar_exact(float x, float y, bool norm_separate) {
+  return polar_exact_inline(x, y, norm_separate);
+}
 __device__ __noinline__ float div_exact(float a, float b) { return __fdiv_rn(a, b); }
 
+// Which key dtypes use the approximations.  bf16 ties are 2^16 fp32 steps apart, so about one value in a thousand
+// needs the exact routine and a warp rarely diverges.  fp16 ties are 2^13 apart: with four tests per pair of items
+// half of all warps would take the slow branch (measured: 2.7 ms against 1.9 ms for the exact-only code at the 32k
+// prefill shape), so fp16 - like fp32, where nothing is rounded - stays on the exact routines.
+template <typename T> struct FastPathPays { static constexpr bool value = false; };
+template <> struct FastPathPays<__nv_bfloat16> { static constexpr bool value = true; };
+#ifdef PQ_FAST_FP16
+template <> struct FastPathPays<__half> { static constexpr bool value = true; };
+#endif
+
 // angle and radius of two pairs at once (the roundings are packed two by two)
-template <typename T, bool FAST = true>
+template <typename T, bool FAST = true, bool FORCE = false>
 __device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[2], float wrap, bool norm_separate,
                                           float (&phi)[2], float (&rad)[2]) {
-  constexpr bool kFast = FAST && !(Elem<T>::kDtype == PQ_F32);
+  constexpr bool kFast = FAST && (FORCE || FastPathPays<T>::value) && Elem<T>::kDtype != PQ_F32;
   float a[2], r[2];
   bool ok[2] = {false, false};
   if constexpr (kFast) {
@@ -148,7 +161,10 @@ __device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[
       ok[k] = mid_range(a[k]) && rounds_safely<T>(a[k]) && mid_range(r[k]) && rounds_safely<T>(r[k]);
     }
   }
-  if (!(ok[0] && ok[1])) {                     // one rarely taken branch for both items
+  if constexpr (!kFast) {                      // exact-only dtypes: the library calls inline, no call overhead
+#pragma unroll
+    for (int k = 0; k < 2; ++k) { const float2 e = polar_exact_inline(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
+  } else if (!(ok[0] && ok[1])) {              // one rarely taken branch for both items
 #pragma unroll
     for (int k = 0; k < 2; ++k)
       if (!ok[k]) { const float2 e = polar_exact(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
@@ -164,10 +180,10 @@ __device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[
 // floor(RN(RN(v - lo) / step)) clamped to [0, top], for two values.  `rstep` is the correctly rounded
 // reciprocal of `step`; the product is within 1.5 ulp of the IEEE quotient and is used when it rounds safely.
 // A quotient that is not below 256 (inf, NaN from a zero step, ...) takes the exact division and cast.
-template <typename T, bool FAST = true>
+template <typename T, bool FAST = true, bool FORCE = false>
 __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)[2], const float (&step)[2],
                                           const float (&rstep)[2], unsigned top, unsigned (&lvl)[2]) {
-  constexpr bool kFast = FAST && !(Elem<T>::kDtype == PQ_F32);
+  constexpr bool kFast = FAST && (FORCE || FastPathPays<T>::value) && Elem<T>::kDtype != PQ_F32;
   float d[2], q[2];
   round2<T>(__fsub_rn(v[0], lo[0]), __fsub_rn(v[1], lo[1]), d[0], d[1]);
   bool ok[2] = {false, false};
@@ -175,10 +191,13 @@ __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       q[k] = d[k] * rstep[k];
-      ok[k] = q[k] < 256.0f && rounds_safely<T>(q[k]);
+      // the step must be an ordinary number, or its reciprocal has lost precision (the test is loop-invariant)
+      ok[k] = mid_range(step[k]) && q[k] < 256.0f && rounds_safely<T>(q[k]);
     }
   }
-  if (!(ok[0] && ok[1])) {
+  if constexpr (!kFast) {
+    q[0] = __fdiv_rn(d[0], step[0]); q[1] = __fdiv_rn(d[1], step[1]);
+  } else if (!(ok[0] && ok[1])) {
 #pragma unroll
     for (int k = 0; k < 2; ++k)
       if (!ok[k]) q[k] = div_exact(d[k], step[k]);
@@ -370,7 +389,7 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
     if (which == 0) {
       const float xx[2] = {x, y}, yy[2] = {y, x};             // the pair and its mirror image
       float p0[2], r0[2], p1[2], r1[2];
-      polar_of2<T, true>(xx, yy, 6.283185307179586f, true, p0, r0);
+      polar_of2<T, true, true>(xx, yy, 6.283185307179586f, true, p0, r0);
       polar_of2<T, false>(xx, yy, 6.283185307179586f, true, p1, r1);
       // values compare equal or both NaN; +0 and -0 count as equal, as they do for torch.equal
       const bool same_p = (p0[0] == p1[0]) || (p0[0] != p0[0] && p1[0] != p1[0]);
@@ -379,7 +398,7 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
     } else {
       const float v[2] = {x, x}, lo[2] = {0.0f, 0.0f}, st[2] = {y, y}, rc[2] = {__frcp_rn(y), __frcp_rn(y)};
       unsigned a[2], b[2];
-      level_of2<T, true>(v, lo, st, rc, 255u, a);
+      level_of2<T, true, true>(v, lo, st, rc, 255u, a);
       level_of2<T, false>(v, lo, st, rc, 255u, b);
       bad += a[0] != b[0];
     }
