@@ -54,6 +54,18 @@ int pq_quantize(const void* keys, const int64_t strides[4], int B, int Nk, int L
                 uint8_t* codes, void* rscale, void* rmn, void* tscale, void* tmn, void* stream);
 
 /*
+ * pq_quantize writing into a preallocated cache: the outputs of (batch b, kv head h) start at
+ * b * out_strides[0] + h * out_strides[1] bytes (codes) and b * out_strides[2] + h * out_strides[3] elements
+ * (each scale tensor); within a (b, h) unit the L/G groups are contiguous as in pq_quantize.  Pass pointers to
+ * the first group to be written.  This is how an in-place cache appends a freshly quantised group without the
+ * torch.cat of the reference's decode branch (models/modeling_llama_polar.py:84-90).
+ */
+int pq_quantize_into(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G,
+                     int rbits, int tbits, int dtype, unsigned flags,
+                     uint8_t* codes, void* rscale, void* rmn, void* tscale, void* tmn,
+                     const int64_t out_strides[4], void* stream);
+
+/*
  * Self-test of the quantizer's fast paths (no reference counterpart).  The kernel replaces atan2f, sqrtf and the
  * IEEE division by cheaper approximations wherever the approximation provably rounds to the same 16-bit value,
  * and calls the exact routine otherwise.  This entry point checks that claim exhaustively on the device: for all

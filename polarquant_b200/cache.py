@@ -1,0 +1,121 @@
+"""Preallocated, in-place polar KV cache for one attention layer, and the decode step over it.
+
+The reference grows its cache with ``torch.cat`` on every step and re-materialises GQA copies of keys and values
+(``repeat_kv``) before each matmul (models/modeling_llama_polar.py:77,86-90,98-99): per generated token the whole
+value cache is copied twice.  Here all buffers are allocated once for ``max_tokens``; a step writes the new key and
+value into their slots, runs the fused attention kernel over views of the buffers, and - every ``residual_length``
+steps - quantises the full-precision window straight into the next free group of the code buffer
+(``pq_quantize_into``).  Semantics follow the reference's decode branch exactly: attention sees the residual window
+in full precision, including the current token, and only afterwards the window is quantised (:79 precedes :83).
+
+Cache layout (what the reference's 8-tuple holds, with capacity):
+    codes   (B, Nk, max_groups, G, 64) uint8        rscale/rmn/tscale/tmn (B, Nk, max_groups, 1, 64)
+    k_res   (B, Nk, residual_length, 128)           values (B, Nk, max_tokens, 128)
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib, ops
+
+
+class PolarKVCache:
+    def __init__(self, batch: int, kv_heads: int, max_tokens: int, dtype=torch.bfloat16, device="cuda",
+                 rbits: int = 4, tbits: int = 4, group_size: int = 128, residual_length: int = 128,
+                 head_dim: int = 128):
+        if residual_length % group_size:
+            raise ValueError("residual_length must be a multiple of group_size")
+        if head_dim != 128:
+            raise NotImplementedError("head_dim must be 128")
+        self.B, self.Nk, self.G, self.RL = batch, kv_heads, group_size, residual_length
+        self.rbits, self.tbits, self.dtype = rbits, tbits, dtype
+        self.max_groups = max_tokens // group_size
+        self.max_tokens = max_tokens
+        dev = torch.device(device)
+        self.codes = torch.empty((batch, kv_heads, self.max_groups, group_size, 64), dtype=torch.uint8, device=dev)
+        self.scales = [torch.empty((batch, kv_heads, self.max_groups, 1, 64), dtype=dtype, device=dev)
+                       for _ in range(4)]                     # rscale, rmn, tscale, tmn
+        self.k_res = torch.empty((batch, kv_heads, residual_length, head_dim), dtype=dtype, device=dev)
+        self.values = torch.empty((batch, kv_heads, max_tokens, head_dim), dtype=dtype, device=dev)
+        self.num_groups = 0        # quantised token groups
+        self.res_len = 0           # full-precision keys in the window
+        need = _lib.load().pq_decode_workspace_bytes(batch, kv_heads * 8, kv_heads, self.max_groups, group_size,
+                                                     residual_length, 0)
+        self.workspace = torch.empty(max(need, 1 << 20) + 256, dtype=torch.uint8, device=dev)
+
+    @property
+    def seq_len(self) -> int:
+        return self.num_groups * self.G + self.res_len
+
+    # ------------------------------------------------------------------ writes
+    def _quantize_into(self, keys: torch.Tensor, first_group: int) -> None:
+        """Quantise ``keys`` (B, Nk, n*G, 128; any strides with unit inner stride) into groups
+        [first_group, first_group + n) of the code and scale buffers."""
+        n = keys.shape[2] // self.G
+        if n == 0:
+            return
+        if first_group + n > self.max_groups:
+            raise RuntimeError("PolarKVCache is full")
+        if not ops._vec_ok(keys, 4):
+            keys = keys.contiguous()
+        lib = _lib.load()
+        dev = keys.device
+        in_strides = (ctypes.c_int64 * 4)(*keys.stride())
+        out_strides = (ctypes.c_int64 * 4)(self.codes.stride(0), self.codes.stride(1),
+                                           self.scales[0].stride(0), self.scales[0].stride(1))
+        es = self.scales[0].element_size()
+        code_ptr = self.codes.data_ptr() + first_group * self.G * 64
+        scale_ptrs = [s.data_ptr() + first_group * 64 * es for s in self.scales]
+        with torch.cuda.device(dev):
+            rc = lib.pq_quantize_into(keys.data_ptr(), in_strides, self.B, self.Nk, n * self.G, 128, self.G,
+                                      self.rbits, self.tbits, ops._DT[keys.dtype], 0, code_ptr, *scale_ptrs,
+                                      out_strides, ops._stream(dev))
+        _lib.check(rc, "pq_quantize_into")
+
+    def prefill(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
+        """Store a prompt: keys/values (B, Nk, L, 128), strided views allowed (the (B, L, Nk, hd) layout the
+        projections produce).  The first L - L % residual_length keys are quantised, the rest stay in full
+        precision, as at models/modeling_llama_polar.py:116-126."""
+        length = key_states.shape[2]
+        if length > self.max_tokens:
+            raise RuntimeError("prompt longer than the cache")
+        rest = length % self.RL
+        nq = length - rest
+        self.num_groups = 0
+        self._quantize_into(key_states[:, :, :nq], 0)
+        self.num_groups = nq // self.G
+        self.res_len = rest
+        if rest:
+            self.k_res[:, :, :rest].copy_(key_states[:, :, nq:])
+        self.values[:, :, :length].copy_(value_states)
+
+    def decode_step(self, query_states: torch.Tensor, key_new: torch.Tensor, value_new: torch.Tensor,
+                    attention_mask=None, sm_scale=None, out_dtype=None) -> torch.Tensor:
+        """Append one token per sequence and attend.  query_states (B, N, 1, 128); key_new / value_new
+        (B, Nk, 1, 128).  Returns (B, N, 1, 128).  No allocation proportional to the context, no copy of the cache."""
+        pos = self.seq_len
+        if pos + 1 > self.max_tokens:
+            raise RuntimeError("PolarKVCache is full")
+        self.k_res[:, :, self.res_len:self.res_len + 1].copy_(key_new)
+        self.values[:, :, pos:pos + 1].copy_(value_new)
+        self.res_len += 1
+        ng = self.num_groups
+        packed = (self.codes[:, :, :ng], *(s[:, :, :ng] for s in self.scales)) if ng else (None,) * 5
+        out = ops.decode_attention(query_states, self.k_res[:, :, :self.res_len], *packed,
+                                   self.values[:, :, :pos + 1], attention_mask=attention_mask, rbits=self.rbits,
+                                   tbits=self.tbits, sm_scale=sm_scale, out_dtype=out_dtype,
+                                   workspace=self.workspace)
+        if self.res_len == self.RL:                      # window full: quantise it in place (:83-92)
+            self._quantize_into(self.k_res, ng)
+            self.num_groups += self.RL // self.G
+            self.res_len = 0
+        return out
+
+    def as_reference_tuple(self):
+        """The reference's 8-tuple view of the cache (models/modeling_llama_polar.py:62,101): views, no copies."""
+        ng = self.num_groups
+        packed = (self.codes[:, :, :ng], *(s[:, :, :ng] for s in self.scales)) if ng else (None,) * 5
+        k_full = self.k_res[:, :, :self.res_len] if self.res_len else None
+        return (k_full, *packed, self.values[:, :, :self.seq_len], self.seq_len)

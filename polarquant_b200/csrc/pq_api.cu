@@ -10,7 +10,7 @@ int& last_cuda_error() {
 }
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
                     int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
-                    void* tmn, cudaStream_t stream);
+                    void* tmn, const int64_t* out_strides, cudaStream_t stream);
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
                      const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
@@ -58,7 +58,15 @@ int pq_quantize(const void* keys, const int64_t strides[4], int B, int Nk, int L
                 int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
                 void* tmn, void* stream) {
   return quantize_device(keys, strides, B, Nk, L, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale,
-                         tmn, static_cast<cudaStream_t>(stream));
+                         tmn, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int pq_quantize_into(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
+                     int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
+                     void* tmn, const int64_t out_strides[4], void* stream) {
+  if (!out_strides) return PQ_ERR_INVALID;
+  return quantize_device(keys, strides, B, Nk, L, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale,
+                         tmn, out_strides, static_cast<cudaStream_t>(stream));
 }
 
 int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream) {
@@ -141,7 +149,7 @@ int pq_quantize_host(const void* keys_host, int B, int Nk, int L, int hd, int G,
   void* d_rs = c.take(sbytes); void* d_rm = c.take(sbytes); void* d_ts = c.take(sbytes); void* d_tm = c.take(sbytes);
   PQ_CUDA_TRY(cudaMemcpyAsync(d_keys, keys_host, kbytes, cudaMemcpyHostToDevice, s));
   const int64_t st[4] = {static_cast<int64_t>(Nk) * L * hd, static_cast<int64_t>(L) * hd, hd, 1};
-  int rc = quantize_device(d_keys, st, B, Nk, L, hd, G, rbits, tbits, dtype, flags, d_codes, d_rs, d_rm, d_ts, d_tm, s);
+  int rc = quantize_device(d_keys, st, B, Nk, L, hd, G, rbits, tbits, dtype, flags, d_codes, d_rs, d_rm, d_ts, d_tm, nullptr, s);
   if (rc != PQ_OK) return rc;
   PQ_CUDA_TRY(cudaMemcpyAsync(codes_host, d_codes, cbytes, cudaMemcpyDeviceToHost, s));
   PQ_CUDA_TRY(cudaMemcpyAsync(rscale_host, d_rs, sbytes, cudaMemcpyDeviceToHost, s));

@@ -219,7 +219,8 @@ template <typename T, int NI>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, int Nk, int nb, int G,
                 int rbits, int tbits, unsigned flags, uint8_t* __restrict__ codes, T* __restrict__ rscale,
-                T* __restrict__ rmn_out, T* __restrict__ tscale, T* __restrict__ tmn_out) {
+                T* __restrict__ rmn_out, T* __restrict__ tscale, T* __restrict__ tmn_out,
+                int64_t c_sb, int64_t c_sh, int64_t s_sb, int64_t s_sh) {
   using E = Elem<T>;
   __shared__ float red[4][kQuantThreads / 32][kPairs];
   __shared__ float fin[4][kPairs];
@@ -322,7 +323,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
     rrcp[p] = __frcp_rn(rstep[p]);
   }
   if (warp == 0 && tsub == 0) {
-    const int64_t so = static_cast<int64_t>(tile) * kPairs + p0;
+    const int64_t so = b * s_sb + h * s_sh + static_cast<int64_t>(j) * kPairs + p0;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       rscale[so + p] = E::from_float(rstep[p]); rmn_out[so + p] = E::from_float(rmn[p]);
@@ -331,7 +332,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   }
 
   const unsigned ttop = (1u << tbits) - 1u, rtop = (1u << rbits) - 1u;
-  uint8_t* crow = codes + static_cast<int64_t>(tile) * G * kPairs + p0;
+  uint8_t* crow = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j) * G * kPairs + p0;
   if constexpr (NI > 0) {
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
@@ -408,7 +409,8 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
 
 template <typename T>
 int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, int G, int rbits, int tbits,
-                    unsigned flags, uint8_t* codes, void* rs, void* rm, void* ts, void* tm, cudaStream_t s) {
+                    unsigned flags, uint8_t* codes, void* rs, void* rm, void* ts, void* tm, const int64_t* os,
+                    cudaStream_t s) {
   const int nb = L / G;
   const int64_t tiles = static_cast<int64_t>(B) * Nk * nb;
   if (tiles == 0) return PQ_OK;
@@ -418,7 +420,7 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
 #define PQ_LAUNCH_Q(NI)                                                                                   \
   quantize_kernel<T, NI><<<grid, block, 0, s>>>(k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, \
                                                 codes, static_cast<T*>(rs), static_cast<T*>(rm),        \
-                                                static_cast<T*>(ts), static_cast<T*>(tm))
+                                                static_cast<T*>(ts), static_cast<T*>(tm), os[0], os[1], os[2], os[3])
   switch (G) {
     case 16: PQ_LAUNCH_Q(1); break;
     case 32: PQ_LAUNCH_Q(2); break;
@@ -443,9 +445,11 @@ int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatch
   return PQ_OK;
 }
 
+// out_strides: {codes_stride_b, codes_stride_h} in bytes and {scale_stride_b, scale_stride_h} in elements;
+// nullptr means dense outputs.
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G,
                     int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn,
-                    void* tscale, void* tmn, cudaStream_t stream) {
+                    void* tscale, void* tmn, const int64_t* out_strides, cudaStream_t stream) {
   if (!strides || B < 0 || Nk < 0 || L < 0 || G <= 0) return PQ_ERR_INVALID;
   if (rbits < 0 || tbits < 0 || rbits + tbits > 8 || (hd & 1) || L % G != 0) return PQ_ERR_INVALID;
   if (!dtype_ok(dtype)) return PQ_ERR_INVALID;
@@ -458,10 +462,16 @@ int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, i
   if (reinterpret_cast<uintptr_t>(keys) % vec || strides[0] % 4 || strides[1] % 4 || strides[2] % 4)
     return PQ_ERR_ALIGNMENT;
   if (reinterpret_cast<uintptr_t>(codes) % 4) return PQ_ERR_ALIGNMENT;
+  const int64_t nb = L / G;
+  int64_t os[4] = {nb * G * kPairs * Nk, nb * G * kPairs, nb * kPairs * Nk, nb * kPairs};
+  if (out_strides) {
+    for (int i = 0; i < 4; ++i) os[i] = out_strides[i];
+    if (os[0] % 4 || os[1] % 4 || os[1] < nb * G * kPairs || os[3] < nb * kPairs) return PQ_ERR_INVALID;
+  }
   switch (dtype) {
-    case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, stream);
-    case PQ_BF16: return launch_quantize<__nv_bfloat16>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, stream);
-    default: return launch_quantize<float>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, stream);
+    case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, stream);
+    case PQ_BF16: return launch_quantize<__nv_bfloat16>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, stream);
+    default: return launch_quantize<float>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, stream);
   }
 }
 
