@@ -389,6 +389,53 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
                           "each step, so this leg is bound by the host link, not by the kernels"}
     del staging, host, hpacked
 
+    # ---- serving-style step on the in-place cache: only the step's own inputs cross the host link ----
+    from polarquant_b200.cache import PolarKVCache
+    res_steps = max(8, min(args.steps, 100))
+    ctx0 = Nb * G + R - res_steps                      # the timed steps end at the benchmark context
+    cache = PolarKVCache(B, Nk, max_tokens=Nb * G + R + 128, dtype=torch.bfloat16, device=device, rbits=args.rbits,
+                         tbits=args.tbits, group_size=G)
+    gen = torch.Generator(device=device).manual_seed(11 + rank)
+    for b0 in range(0, B, 4):                          # prefill in slices to bound temporaries
+        kb = torch.randn(min(4, B - b0), Nk, ctx0, 128, device=device, generator=gen).to(torch.bfloat16)
+        sub = PolarKVCache.__new__(PolarKVCache)
+        sub.__dict__.update(cache.__dict__)
+        sub.B = kb.shape[0]
+        sub.codes, sub.scales = cache.codes[b0:b0 + 4], [t[b0:b0 + 4] for t in cache.scales]
+        sub.k_res, sub.values = cache.k_res[b0:b0 + 4], cache.values[b0:b0 + 4]
+        sub.prefill(kb, inp["v"][b0:b0 + 4, :, :ctx0])
+        cache.num_groups, cache.res_len = sub.num_groups, sub.res_len
+    hq = torch.randn(res_steps, B, N, 1, 128).to(torch.bfloat16).pin_memory()
+    hk = torch.randn(res_steps, B, Nk, 1, 128).to(torch.bfloat16).pin_memory()
+    hv = torch.randn(res_steps, B, Nk, 1, 128).to(torch.bfloat16).pin_memory()
+    dq, dk, dv = (torch.empty_like(t[0], device=device) for t in (hq, hk, hv))
+    hres = torch.empty(B, N, 1, 128, dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    a, b = new_event(), new_event()
+    lib.pq_event_record(a, stream)
+    for i in range(res_steps):
+        dq.copy_(hq[i], non_blocking=True); dk.copy_(hk[i], non_blocking=True); dv.copy_(hv[i], non_blocking=True)
+        o = cache.decode_step(dq, dk, dv)
+        hres.copy_(o, non_blocking=True)
+    lib.pq_event_record(b, stream)
+    torch.cuda.synchronize(device)
+    lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
+    res_ms = ms.value / res_steps
+    if world > 1:
+        t = torch.tensor([res_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res_ms = float(t.item())
+    out["e2e_resident_cache"] = {
+        "value": nbytes * world / (res_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": res_ms, "steps": res_steps,
+        "tokens_per_s_per_layer": B * world / (res_ms * 1e-3),
+        "h2d_bytes_per_step": (dq.numel() + dk.numel() + dv.numel()) * 2, "d2h_bytes_per_step": hres.numel() * 2,
+        "note": "PolarKVCache.decode_step: query / new key / new value copied from pinned host memory, appended in "
+                "place, fused attention over the resident cache (window re-quantised in place when full), output "
+                "copied back; context ends at the benchmark context"}
+    del cache
+
     # ---- quantizer at a 32k-token prefill, strided (B, L, Nk, hd) layout as the prefill hands it over ----
     if rank == 0:
         L = args.ctx
