@@ -66,6 +66,17 @@ int pq_quantize_into(const void* keys, const int64_t strides[4], int B, int Nk, 
                      const int64_t out_strides[4], void* stream);
 
 /*
+ * Append the current token to an in-place cache: for every (batch, kv head) copy the key row k_new[b, h, :] into
+ * slot res_pos of the residual window k_res (B, Nk, RL, hd) and the value row v_new[b, h, :] into slot ctx_pos of
+ * the value buffer (B, Nk, max_tokens, hd).  in_strides = {k_new stride_b, stride_h, v_new stride_b, stride_h},
+ * kres_strides / v_strides = {stride_b, stride_h, stride_token}, all in elements.  Replaces the two torch.cat
+ * calls of the reference's decode branch (models/modeling_llama_polar.py:77,98).
+ */
+int pq_cache_append(const void* k_new, const void* v_new, const int64_t in_strides[4], void* k_res,
+                    const int64_t kres_strides[3], void* values, const int64_t v_strides[3], int B, int Nk, int hd,
+                    int res_pos, int ctx_pos, int dtype, void* stream);
+
+/*
  * Self-test of the quantizer's fast paths (no reference counterpart).  The kernel replaces atan2f, sqrtf and the
  * IEEE division by cheaper approximations wherever the approximation provably rounds to the same 16-bit value,
  * and calls the exact routine otherwise.  This entry point checks that claim exhaustively on the device: for all

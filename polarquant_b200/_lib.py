@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = (
     "pq_quantize_host", "pq_quantize_host_staging_bytes", "pq_decode_attention_host",
     "pq_decode_host_staging_bytes", "pq_strerror", "pq_last_cuda_error", "pq_abi_version", "pq_decode_params_size",
     "pq_event_create", "pq_event_destroy", "pq_event_record", "pq_event_elapsed_ms",
-    "pq_decode_attention_static", "pq_decode_static_scratch_bytes", "pq_selftest_quantizer", "pq_quantize_into",
+    "pq_decode_attention_static", "pq_decode_static_scratch_bytes", "pq_selftest_quantizer", "pq_quantize_into", "pq_cache_append",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -61,6 +61,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_quantize_into.restype = _int
     lib.pq_quantize_into.argtypes = [_vp, ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _int, _int,
                                      ctypes.c_uint, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_i64), _vp]
+    lib.pq_cache_append.restype = _int
+    lib.pq_cache_append.argtypes = [_vp, _vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _vp,
+                                    ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _vp]
     lib.pq_qk_decode.restype = _int
     lib.pq_qk_decode.argtypes = [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
                                  _int, _int, _int, _int, _int, _int, _int, _int, _int, _vp]

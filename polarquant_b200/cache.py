@@ -44,6 +44,24 @@ class PolarKVCache:
         need = _lib.load().pq_decode_workspace_bytes(batch, kv_heads * 8, kv_heads, self.max_groups, group_size,
                                                      residual_length, 0)
         self.workspace = torch.empty(max(need, 1 << 20) + 256, dtype=torch.uint8, device=dev)
+        # everything that does not change from step to step is marshalled once
+        self._dev = dev
+        self._dt = ops._DT[dtype]
+        p = _lib.DecodeParams()
+        p.codes, p.codes_stride_b, p.codes_stride_h = self.codes.data_ptr(), self.codes.stride(0), self.codes.stride(1)
+        p.rscale, p.rmn, p.tscale, p.tmn = (t.data_ptr() for t in self.scales)
+        p.scale_stride_b, p.scale_stride_h = self.scales[0].stride(0), self.scales[0].stride(1)
+        p.k_res = self.k_res.data_ptr()
+        p.kres_stride_b, p.kres_stride_h, p.kres_stride_t = self.k_res.stride(0), self.k_res.stride(1), self.k_res.stride(2)
+        p.v = self.values.data_ptr()
+        p.v_stride_b, p.v_stride_h, p.v_stride_t = self.values.stride(0), self.values.stride(1), self.values.stride(2)
+        p.workspace, p.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+        p.B, p.Nk, p.G, p.hd = batch, kv_heads, group_size, head_dim
+        p.rbits, p.tbits = rbits, tbits
+        p.qk_dtype = p.v_dtype = self._dt
+        self._params = p
+        self._kres_strides = (ctypes.c_int64 * 3)(self.k_res.stride(0), self.k_res.stride(1), self.k_res.stride(2))
+        self._v_strides = (ctypes.c_int64 * 3)(self.values.stride(0), self.values.stride(1), self.values.stride(2))
 
     @property
     def seq_len(self) -> int:
@@ -94,10 +112,49 @@ class PolarKVCache:
     def decode_step(self, query_states: torch.Tensor, key_new: torch.Tensor, value_new: torch.Tensor,
                     attention_mask=None, sm_scale=None, out_dtype=None) -> torch.Tensor:
         """Append one token per sequence and attend.  query_states (B, N, 1, 128); key_new / value_new
-        (B, Nk, 1, 128).  Returns (B, N, 1, 128).  No allocation proportional to the context, no copy of the cache."""
+        (B, Nk, 1, 128), any batch/head strides.  Returns (B, N, 1, 128).  Three library calls (append, attention,
+        and - every residual_length steps - quantise); no allocation proportional to the context, no copy of the
+        cache."""
         pos = self.seq_len
         if pos + 1 > self.max_tokens:
             raise RuntimeError("PolarKVCache is full")
+        if attention_mask is not None or query_states.dtype != self.dtype or key_new.dtype != self.dtype \
+                or value_new.dtype != self.dtype or key_new.stride(-1) != 1 or value_new.stride(-1) != 1:
+            return self._decode_step_general(query_states, key_new, value_new, attention_mask, sm_scale, out_dtype)
+        lib = _lib.load()
+        dev = self._dev
+        stream = ops._stream(dev)
+        in_strides = (ctypes.c_int64 * 4)(key_new.stride(0), key_new.stride(1), value_new.stride(0),
+                                          value_new.stride(1))
+        with torch.cuda.device(dev):
+            rc = lib.pq_cache_append(key_new.data_ptr(), value_new.data_ptr(), in_strides, self.k_res.data_ptr(),
+                                     self._kres_strides, self.values.data_ptr(), self._v_strides, self.B, self.Nk,
+                                     128, self.res_len, pos, self._dt, stream)
+            _lib.check(rc, "pq_cache_append")
+            self.res_len += 1
+            bsz, nq, _, hd = query_states.shape
+            q = query_states.reshape(bsz, nq, hd)
+            if not ops._vec_ok(q, 8):
+                q = q.contiguous()
+            out_dtype = out_dtype or self.dtype
+            out = torch.empty((bsz, nq, 1, hd), dtype=out_dtype, device=dev)
+            p = self._params
+            p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+            p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+            p.N, p.Nb, p.R = nq, self.num_groups, self.res_len
+            p.out_dtype = ops._DT[out_dtype]
+            p.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
+            rc = lib.pq_decode_attention(ctypes.byref(p), stream)
+        _lib.check(rc, "pq_decode_attention")
+        if self.res_len == self.RL:                      # window full: quantise it in place (:83-92)
+            self._quantize_into(self.k_res, self.num_groups)
+            self.num_groups += self.RL // self.G
+            self.res_len = 0
+        return out
+
+    def _decode_step_general(self, query_states, key_new, value_new, attention_mask, sm_scale, out_dtype):
+        """Same step through the general tensor-level entry points (masks, dtype conversions, odd strides)."""
+        pos = self.seq_len
         self.k_res[:, :, self.res_len:self.res_len + 1].copy_(key_new)
         self.values[:, :, pos:pos + 1].copy_(value_new)
         self.res_len += 1
@@ -107,7 +164,7 @@ class PolarKVCache:
                                    self.values[:, :, :pos + 1], attention_mask=attention_mask, rbits=self.rbits,
                                    tbits=self.tbits, sm_scale=sm_scale, out_dtype=out_dtype,
                                    workspace=self.workspace)
-        if self.res_len == self.RL:                      # window full: quantise it in place (:83-92)
+        if self.res_len == self.RL:
             self._quantize_into(self.k_res, ng)
             self.num_groups += self.RL // self.G
             self.res_len = 0

@@ -11,6 +11,9 @@ int& last_cuda_error() {
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
                     int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
                     void* tmn, const int64_t* out_strides, cudaStream_t stream);
+int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_strides, void* k_res,
+                        const int64_t* kres_strides, void* values, const int64_t* v_strides, int B, int Nk, int hd,
+                        int res_pos, int ctx_pos, int dtype, cudaStream_t stream);
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
                      const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
@@ -67,6 +70,13 @@ int pq_quantize_into(const void* keys, const int64_t strides[4], int B, int Nk, 
   if (!out_strides) return PQ_ERR_INVALID;
   return quantize_device(keys, strides, B, Nk, L, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale,
                          tmn, out_strides, static_cast<cudaStream_t>(stream));
+}
+
+int pq_cache_append(const void* k_new, const void* v_new, const int64_t in_strides[4], void* k_res,
+                    const int64_t kres_strides[3], void* values, const int64_t v_strides[3], int B, int Nk, int hd,
+                    int res_pos, int ctx_pos, int dtype, void* stream) {
+  return cache_append_device(k_new, v_new, in_strides, k_res, kres_strides, values, v_strides, B, Nk, hd, res_pos,
+                             ctx_pos, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream) {

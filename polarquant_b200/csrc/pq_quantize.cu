@@ -433,7 +433,40 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
   return PQ_OK;
 }
 
+// Append one token per (batch, kv head): copy the new key row into slot `res_pos` of the residual window and the new
+// value row into slot `ctx_pos` of the value buffer.  One warp per row pair, 16-byte copies where alignment allows.
+template <typename T>
+__global__ void cache_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, int64_t n_sb, int64_t n_sh,
+                                    int64_t vn_sb, int64_t vn_sh, T* __restrict__ k_res, int64_t kr_sb, int64_t kr_sh,
+                                    int64_t kr_st, T* __restrict__ values, int64_t v_sb, int64_t v_sh, int64_t v_st,
+                                    int Nk, int res_pos, int ctx_pos) {
+  const int b = blockIdx.x / Nk, h = blockIdx.x % Nk;
+  const int c = threadIdx.x;                               // channel
+  k_res[b * kr_sb + h * kr_sh + res_pos * kr_st + c] = k_new[b * n_sb + h * n_sh + c];
+  values[b * v_sb + h * v_sh + ctx_pos * v_st + c] = v_new[b * vn_sb + h * vn_sh + c];
+}
+
 }  // namespace
+
+int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_strides, void* k_res,
+                        const int64_t* kres_strides, void* values, const int64_t* v_strides, int B, int Nk, int hd,
+                        int res_pos, int ctx_pos, int dtype, cudaStream_t stream) {
+  if (!k_new || !v_new || !k_res || !values || !in_strides || !kres_strides || !v_strides) return PQ_ERR_INVALID;
+  if (B <= 0 || Nk <= 0 || res_pos < 0 || ctx_pos < 0 || !dtype_ok(dtype)) return PQ_ERR_INVALID;
+  if (hd != kHeadDim) return PQ_ERR_UNSUPPORTED;
+  const unsigned grid = static_cast<unsigned>(B) * Nk;
+#define PQ_APPEND(T)                                                                                              \
+  cache_append_kernel<T><<<grid, kHeadDim, 0, stream>>>(                                                         \
+      static_cast<const T*>(k_new), static_cast<const T*>(v_new), in_strides[0], in_strides[1], in_strides[2],   \
+      in_strides[3], static_cast<T*>(k_res), kres_strides[0], kres_strides[1], kres_strides[2],                  \
+      static_cast<T*>(values), v_strides[0], v_strides[1], v_strides[2], Nk, res_pos, ctx_pos)
+  if (dtype == PQ_F32) PQ_APPEND(float);
+  else if (dtype == PQ_F16) PQ_APPEND(__half);
+  else PQ_APPEND(__nv_bfloat16);
+#undef PQ_APPEND
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
 
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream) {
   if (!mismatches_dev || which < 0 || which > 1) return PQ_ERR_INVALID;
