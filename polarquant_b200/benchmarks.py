@@ -3,6 +3,7 @@
     python -m polarquant_b200.benchmarks qk        # the reference's QK micro-benchmark grid
     python -m polarquant_b200.benchmarks sweep     # fused decode attention over bit widths / group sizes / shapes
     python -m polarquant_b200.benchmarks quant     # quantizer at prefill sizes
+    torchrun --nproc-per-node N -m polarquant_b200.benchmarks longctx   # 128k-context step sharded over N GPUs
 
 `qk` reproduces the grid of the reference's benchmark/benchmark_matmul.py (`test4polar`, lines 89-120: 32 heads on
 the code tensor, D = 64, fp16, random codes in [0, 250) and randn scales, batch 1/2/4/8, length 4096..131072), but
@@ -91,6 +92,86 @@ def quant_sizes():
         del base, keys
 
 
+def long_context():
+    """70B-shaped long-context decode attention over the GPUs of one node (launch with torchrun):
+    64 q / 8 kv heads, batch 8, context 131072, polar 4/4, group 128.  Two shardings of the same step:
+    `heads` - kv heads split over the ranks, no collective; `sequence` - every rank holds all heads but a slice of
+    the context, one all-gather of (output, lse) per step and a local log-sum-exp merge."""
+    import os
+    import torch.distributed as dist
+    from . import distributed as pqd
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    B, N, Nk, ctx, G, R = 8, 64, 8, 131072, 128, 128
+    Nb = (ctx - R) // G
+    g = torch.Generator(device=dev).manual_seed(1005 + rank)
+
+    def build(kv_heads, q_heads, groups, residual):
+        tokens = groups * G + residual
+        q = torch.randn(B, q_heads, 1, 128, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, kv_heads, tokens, 128, device=dev, generator=g).to(torch.bfloat16)
+        kres = torch.randn(B, kv_heads, residual, 128, device=dev, generator=g).to(torch.bfloat16) if residual else None
+        packed = []
+        for h in range(kv_heads):                      # head by head to bound temporaries
+            keys = torch.randn(B, 1, groups * G, 128, device=dev, generator=g).to(torch.bfloat16)
+            packed.append(ops.quantize_and_pack_nbit(keys, 4, 4, G))
+        packed = [torch.cat([p[i] for p in packed], dim=1) for i in range(5)]
+        nbytes = (packed[0].numel() + 4 * packed[1].numel() * 2 + v.numel() * 2 + q.numel() * 4
+                  + (kres.numel() * 2 if residual else 0))
+        return q, kres, packed, v, nbytes
+
+    def timed(fn, reps=30):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps * 1e3], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # --- kv heads over ranks ---
+    h0, h1 = pqd.shard_range(Nk, rank, world)
+    q, kres, packed, v, nbytes = build(h1 - h0, (h1 - h0) * (N // Nk), Nb, R)
+    us = timed(lambda: ops.decode_attention(q, kres, *packed, v))
+    tot = torch.tensor([float(nbytes)], device=dev)
+    if world > 1:
+        dist.all_reduce(tot)
+    if rank == 0:
+        print(json.dumps({"bench": "longctx", "sharding": "kv heads", "n_gpus": world, "us": us,
+                          "aggregate_gbs": float(tot.item()) / us / 1e3, "collective": "none"}))
+    del q, kres, packed, v
+
+    # --- sequence over ranks ---
+    g0, g1, owns = pqd.split_sequence(Nb, R, rank, world)
+    q, kres, packed, v, nbytes = build(Nk, N, g1 - g0, R if owns else 0)
+    if world > 1:
+        dist.broadcast(q, 0)                           # one query for all ranks
+    us = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v) if world > 1
+               else ops.decode_attention(q, kres, *packed, v))
+    tot = torch.tensor([float(nbytes)], device=dev)
+    if world > 1:
+        dist.all_reduce(tot)
+    if rank == 0:
+        print(json.dumps({"bench": "longctx", "sharding": "sequence", "n_gpus": world, "us": us,
+                          "aggregate_gbs": float(tot.item()) / us / 1e3,
+                          "collective": "all_gather of (B*N, 129) fp32 per rank + local merge"}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "sweep"
-    {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes}[what]()
+    {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes, "longctx": long_context}[what]()
