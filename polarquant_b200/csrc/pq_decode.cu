@@ -80,6 +80,17 @@ __device__ __forceinline__ long long range_lo(long long w, long long total, int 
   return (w * total) / nwarps;
 }
 
+// A CTA whose four warp ranges all lie inside one unit combines its four partials in shared memory and
+// emits a single one (in the slot of its first warp): four times fewer partials for the merge kernel when a
+// unit is spread over many warps.  Both kernels evaluate this predicate the same way.
+__device__ __forceinline__ bool cta_in_one_unit(long long cta, long long total_slots, int total_warps,
+                                                int slots_per_unit) {
+  const long long w_first = cta * 4, w_end = w_first + 4;
+  if (w_end > total_warps) return false;
+  const long long lo = range_lo(w_first, total_slots, total_warps), hi = range_lo(w_end, total_slots, total_warps);
+  return lo / slots_per_unit == (hi - 1) / slots_per_unit;
+}
+
 // ---- per-group constants staged in shared memory ------------------------------------
 // The four scale rows of a token group (rscale, rmn, tscale, tmn: 4 x 64 elements) are
 // copied global -> shared with cp.async one group ahead of their use, double-buffered,
@@ -457,6 +468,8 @@ decode_kernel(const DecodeArgs a) {
   long long unit = lo / a.slots_per_unit;
   int pos = static_cast<int>(lo - unit * a.slots_per_unit);
   int seg = 0;
+  // block-uniform: all four warps of such a CTA have exactly one segment, in the same unit
+  const bool combine = !QK_ONLY && cta_in_one_unit(blockIdx.x, a.total_slots, a.total_warps, a.slots_per_unit);
 
   while (lo < hi) {
     const long long unit_end = (unit + 1) * a.slots_per_unit;
@@ -671,6 +684,61 @@ decode_kernel(const DecodeArgs a) {
         st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, o);
         st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, o);
       }
+      if (combine) {
+        // stage this warp's partial in its own (now idle) value stages, then one warp-wide pass per channel
+        cp_async_wait<0>();
+        __syncwarp();
+        float* so = reinterpret_cast<float*>(warp_smem + kPairs * A * 4 + 2 * kStageBytes);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int chn = 16 * j + g, chn2 = chn + 8;
+          *reinterpret_cast<float2*>(so + chn * kHeadTile + 2 * t) = make_float2(O[j][0], O[j][1]);
+          *reinterpret_cast<float2*>(so + chn2 * kHeadTile + 2 * t) = make_float2(O[j][2], O[j][3]);
+        }
+        if (g == 0) {
+          float2* sml = reinterpret_cast<float2*>(so + kPartialFloats);
+          sml[2 * t] = make_float2(st.m0, st.l0);
+          sml[2 * t + 1] = make_float2(st.m1, st.l1);
+        }
+        __syncthreads();
+        // thread = channel: merge the four staged partials and write one
+        const int ch = threadIdx.x;
+        const long long slot = static_cast<long long>(blockIdx.x) * kWarps * a.max_seg;     // first warp, segment 0
+        float mx[kHeadTile], ls[kHeadTile], acc[kHeadTile];
+#pragma unroll
+        for (int h = 0; h < kHeadTile; ++h) { mx[h] = -INFINITY; ls[h] = 0.f; acc[h] = 0.f; }
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float2* sml = reinterpret_cast<const float2*>(smem_dyn + w * kWarpSmem + kPairs * A * 4 + 2 * kStageBytes) +
+                              kPartialFloats / 2;
+#pragma unroll
+          for (int h = 0; h < kHeadTile; ++h) mx[h] = fmaxf(mx[h], sml[h].x);
+        }
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float* sw = reinterpret_cast<const float*>(smem_dyn + w * kWarpSmem + kPairs * A * 4 + 2 * kStageBytes);
+          const float2* sml = reinterpret_cast<const float2*>(sw + kPartialFloats);
+          const float4 o0 = *reinterpret_cast<const float4*>(sw + ch * kHeadTile);
+          const float4 o1 = *reinterpret_cast<const float4*>(sw + ch * kHeadTile + 4);
+          const float ov[kHeadTile] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+          for (int h = 0; h < kHeadTile; ++h) {
+            const float2 ml = sml[h];
+            const float wgt = ml.x == -INFINITY ? 0.f : exp2_approx(ml.x - mx[h]);
+            ls[h] = fmaf(wgt, ml.y, ls[h]);
+            acc[h] = fmaf(wgt, ov[h], acc[h]);
+          }
+        }
+        float4* po = reinterpret_cast<float4*>(a.part_o + slot * kPartialFloats + ch * kHeadTile);
+        po[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        po[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        if (ch < kHeadTile) {
+          float m = -INFINITY, l = 0.f;
+#pragma unroll
+          for (int h = 0; h < kHeadTile; ++h) if (h == ch) { m = mx[h]; l = ls[h]; }
+          a.part_ml[slot * kHeadTile + ch] = make_float2(m, l);
+        }
+      } else {
       const long long slot = gw * a.max_seg + seg;
       float* po = a.part_o + slot * kPartialFloats;
 #pragma unroll
@@ -683,6 +751,7 @@ decode_kernel(const DecodeArgs a) {
       if (g == 0) {
         a.part_ml[slot * kHeadTile + 2 * t] = make_float2(st.m0, st.l0);
         a.part_ml[slot * kHeadTile + 2 * t + 1] = make_float2(st.m1, st.l1);
+      }
       }
     }
 
@@ -734,7 +803,22 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
   const long long w1 = warp_of(last, a.total_slots, a.total_warps);
   const int seg0 = static_cast<int>(unit - range_lo(w0, a.total_slots, a.total_warps) / a.slots_per_unit);
   const int n = static_cast<int>(w1 - w0 + 1);
+  // warp i of the unit holds a partial unless its CTA lies in one unit and it is not the CTA's first warp
   auto slot_of = [&](int i) { return (w0 + i) * a.max_seg + (i == 0 ? seg0 : 0); };
+  // the predicate costs 64-bit divisions: evaluate it once per CTA of the attention grid, into shared memory
+  constexpr int kMaxFlags = 1024;                      // CTAs of the attention grid a unit can span before falling back
+  __shared__ unsigned char s_single[kMaxFlags];
+  const long long cta0 = w0 >> 2;
+  const int ncta = static_cast<int>((w1 >> 2) - cta0 + 1);
+  for (int c = threadIdx.x; c < min(ncta, kMaxFlags); c += blockDim.x)
+    s_single[c] = cta_in_one_unit(cta0 + c, a.total_slots, a.total_warps, a.slots_per_unit);
+  __syncthreads();
+  auto has_partial = [&](int i) {
+    const long long w = w0 + i;
+    if ((w & 3) == 0) return true;
+    const long long c = (w >> 2) - cta0;
+    return c < kMaxFlags ? !s_single[c] : !cta_in_one_unit(w >> 2, a.total_slots, a.total_warps, a.slots_per_unit);
+  };
 
   // The first batch of partial rows is requested before anything else so that its DRAM round trip
   // overlaps the one of the (m, l) entries.
@@ -742,7 +826,8 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const int i = grp + u * kMergeGroups;
-    if (i < n) {
+    o_first[u][0] = o_first[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < n && has_partial(i)) {
       const float4* po = reinterpret_cast<const float4*>(a.part_o + slot_of(i) * kPartialFloats + ch * kHeadTile);
       o_first[u][0] = po[0]; o_first[u][1] = po[1];
     }
@@ -758,11 +843,11 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
 #pragma unroll
     for (int k = 0; k < kKeep; ++k) {
       const int i = (threadIdx.x >> 3) + k * (kThreadsM >> 3);
-      kept[k] = i < n ? a.part_ml[slot_of(i) * kHeadTile + h_mine] : make_float2(-INFINITY, 0.f);
+      kept[k] = (i < n && has_partial(i)) ? a.part_ml[slot_of(i) * kHeadTile + h_mine] : make_float2(-INFINITY, 0.f);
       m = fmaxf(m, kept[k].x);
     }
     for (int i = (threadIdx.x >> 3) + kKeep * (kThreadsM >> 3); i < n; i += kThreadsM >> 3)
-      m = fmaxf(m, a.part_ml[slot_of(i) * kHeadTile + h_mine].x);
+      if (has_partial(i)) m = fmaxf(m, a.part_ml[slot_of(i) * kHeadTile + h_mine].x);
     // lanes with equal (lane & 7) hold the same head
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
@@ -798,7 +883,8 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
     } else {
       for (int e = threadIdx.x; e < cn * kHeadTile; e += kThreadsM) {
         const int i = e >> 3;
-        const float2 ml = a.part_ml[slot_of(c0 + i) * kHeadTile + h_mine];
+        const float2 ml = has_partial(c0 + i) ? a.part_ml[slot_of(c0 + i) * kHeadTile + h_mine]
+                                              : make_float2(-INFINITY, 0.f);
         const float w = ml.x == -INFINITY ? 0.f : exp2_approx(ml.x - s_max[h_mine]);
         s_w[i][h_mine] = w;
         lsum = fmaf(w, ml.y, lsum);
@@ -810,8 +896,9 @@ merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, 
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * kMergeGroups;
+        o[u][0] = o[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c0 == 0 && i0 == grp) { o[u][0] = o_first[u][0]; o[u][1] = o_first[u][1]; }
-        else if (i < cn) {
+        else if (i < cn && has_partial(c0 + i)) {
           const float4* po = reinterpret_cast<const float4*>(a.part_o + slot_of(c0 + i) * kPartialFloats + ch * kHeadTile);
           o[u][0] = po[0]; o[u][1] = po[1];
         }
