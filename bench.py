@@ -114,8 +114,15 @@ class ClockSampler:
                         reasons.add(name)
             except Exception:
                 continue
+        powers = []
+        for r in self.rows:
+            try:
+                powers.append(float(r[2]))
+            except Exception:
+                continue
         return {"sm_mhz": statistics.median(clocks) if clocks else None,
-                "sm_max_mhz": max(maxes) if maxes else None, "samples": len(clocks), "reasons": sorted(reasons)}
+                "sm_max_mhz": max(maxes) if maxes else None, "samples": len(clocks), "reasons": sorted(reasons),
+                "power_w_median": statistics.median(powers) if powers else None}
 
 
 def make_inputs(args, device, seed):
@@ -435,6 +442,27 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
                 "place, fused attention over the resident cache (window re-quantised in place when full), output "
                 "copied back; context ends at the benchmark context"}
     del cache
+
+    # ---- context for the roofline: a plain device copy run as long as the timed region (same power regime) ----
+    if rank == 0:
+        src = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+        dst = torch.empty_like(src)
+        for _ in range(3):
+            dst.copy_(src)
+        reps = max(10, int(0.5 / (2 * src.numel() / 6.0e12)))
+        sampler2 = ClockSampler(torch.cuda.current_device())
+        sampler2.start()
+        a, b = new_event(), new_event()
+        lib.pq_event_record(a, stream)
+        for _ in range(reps):
+            dst.copy_(src)
+        lib.pq_event_record(b, stream)
+        lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
+        out["sustained_copy"] = {"gbs": 2 * src.numel() * reps / (ms.value * 1e-3) / 1e9, "seconds": ms.value / 1e3,
+                                 "clocks": sampler2.stop(),
+                                 "note": "torch copy of 1 GiB (read + write bytes) repeated for ~0.5 s: the copy "
+                                         "bandwidth in the power regime of the long timed region"}
+        del src, dst
 
     # ---- quantizer at a 32k-token prefill, strided (B, L, Nk, hd) layout as the prefill hands it over ----
     if rank == 0:
