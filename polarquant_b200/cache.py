@@ -86,7 +86,7 @@ class PolarKVCache:
         es = self.scales[0].element_size()
         code_ptr = self.codes.data_ptr() + first_group * self.G * 64
         scale_ptrs = [s.data_ptr() + first_group * 64 * es for s in self.scales]
-        with torch.cuda.device(dev):
+        with ops._on_device(dev):
             rc = lib.pq_quantize_into(keys.data_ptr(), in_strides, self.B, self.Nk, n * self.G, 128, self.G,
                                       self.rbits, self.tbits, ops._DT[keys.dtype], 0, code_ptr, *scale_ptrs,
                                       out_strides, ops._stream(dev))
@@ -126,7 +126,7 @@ class PolarKVCache:
         stream = ops._stream(dev)
         in_strides = (ctypes.c_int64 * 4)(key_new.stride(0), key_new.stride(1), value_new.stride(0),
                                           value_new.stride(1))
-        with torch.cuda.device(dev):
+        with ops._on_device(dev):
             rc = lib.pq_cache_append(key_new.data_ptr(), value_new.data_ptr(), in_strides, self.k_res.data_ptr(),
                                      self._kres_strides, self.values.data_ptr(), self._v_strides, self.B, self.Nk,
                                      128, self.res_len, pos, self._dt, stream)

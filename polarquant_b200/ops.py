@@ -41,6 +41,24 @@ def _stream(dev: torch.device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
+class _on_device:
+    """Device guard that costs nothing when the tensors' device is already current (the usual case)."""
+    __slots__ = ("dev", "guard")
+
+    def __init__(self, dev: torch.device):
+        self.dev, self.guard = dev, None
+
+    def __enter__(self):
+        if torch.cuda.current_device() != self.dev.index:
+            self.guard = torch.cuda.device(self.dev)
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+        return False
+
+
 def _vec_ok(t: torch.Tensor, elems: int) -> bool:
     """True when 4/8-element vector loads are legal on every row of ``t``."""
     if t.stride(-1) != 1:
@@ -74,7 +92,7 @@ def quantize_and_pack_nbit(key_states: torch.Tensor, rbits: int = 4, tbits: int 
     scales = [torch.empty((bsz, heads, nb, 1, hd // 2), dtype=key_states.dtype, device=dev) for _ in range(4)]
     strides = (ctypes.c_int64 * 4)(*key_states.stride())
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = lib.pq_quantize(key_states.data_ptr(), strides, bsz, heads, length, hd, group_size, rbits, tbits, dt,
                              flags, codes.data_ptr(), scales[0].data_ptr(), scales[1].data_ptr(),
                              scales[2].data_ptr(), scales[3].data_ptr(), _stream(dev))
@@ -108,7 +126,7 @@ def qk_decode(query_states: torch.Tensor, indices: torch.Tensor, rscale, rmn, ts
         scales.append(s.contiguous())
     out = torch.empty((bsz, nq, 1, nb * grp), dtype=torch.float32, device=dev)
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = lib.pq_qk_decode(q.data_ptr(), q.stride(0), q.stride(1), indices.data_ptr(), scales[0].data_ptr(),
                               scales[1].data_ptr(), scales[2].data_ptr(), scales[3].data_ptr(), out.data_ptr(),
                               bsz, nq, kvh, nb, grp, half, rbits, tbits, dt, _stream(dev))
@@ -237,7 +255,7 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     p.num_ctas = num_ctas
     p.mid_event = mid_event
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         need = lib.pq_decode_workspace_bytes(bsz, nq, kvh, nb, grp, res, num_ctas)
         ws = workspace if workspace is not None else _workspace(dev, need)
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
@@ -259,7 +277,7 @@ def merge_lse(outs: torch.Tensor, lses: torch.Tensor, out_dtype: torch.dtype = t
     out = torch.empty(outs.shape[1:], dtype=out_dtype, device=dev)
     lse = torch.empty(lses.shape[1:], dtype=torch.float32, device=dev) if return_lse else None
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = lib.pq_merge_lse(outs.data_ptr(), lses.data_ptr(), parts, rows, hd, out.data_ptr(), _DT[out_dtype],
                               lse.data_ptr() if return_lse else None, _stream(dev))
     _lib.check(rc, "pq_merge_lse")
