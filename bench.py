@@ -34,6 +34,10 @@ if ROOT not in sys.path:
 
 METRIC = "polar-KV decode-attn GB/s (% HBM peak) & µs/step @32k ctx; e2e decode tokens/s"
 NOMINAL_HBM_GBS = 8000.0
+# DRAM bytes (read + write) of one attention-kernel launch per batch element of the benchmark shape, from the
+# ncu capture of the batch-4 case (dram__bytes_read.sum 342.03 MB + dram__bytes_write.sum 4.20 MB per launch);
+# traffic grows in proportion to the batch, so a full-size launch is this figure times the batch
+NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT = (342.03e6 + 4.20e6) / 4
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -319,7 +323,11 @@ def main():
             "pct_of_measured_copy_peak": 100.0 * value / world / peak,
             "clocks": clocks, "gpu_launches": 2 * K,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "decode_kernel (fused attention over packed keys)",
+                         "traffic": (NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT * B
+                                     if (args.ctx, args.group, args.q_heads, args.kv_heads) == (32768, 128, 32, 8)
+                                     else None),
+                         "traffic_note": "bytes per launch; ncu capture at batch 4 scaled by the batch",
+                         "kernel": "decode_kernel (fused attention over packed keys)",
                          "peak_source": f"{peak_kind} copy bandwidth", "kernel_us": kavg * 1e3,
                          "launches_timed": len(kern_ms),
                          "kernel_us_median": statistics.median(kern_ms) * 1e3},

@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory by running the reference's own code on CPU.
 
-    python tests/golden/make_golden.py [/path/to/PolarQuant checkout]   (default /root/reference)
+    python tests/golden/make_golden.py /path/to/PolarQuant-checkout     (or set POLARQUANT_REFERENCE)
 
 Needs the reference checkout, torch, transformers and triton (for its interpreter);
 run it where those exist.  The tests only read the .npz files it writes.
@@ -35,7 +35,7 @@ sys.path.insert(0, ROOT)
 from oracle import polar_oracle as oracle  # noqa: E402
 from polarquant_b200 import dropin  # noqa: E402
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("POLARQUANT_REFERENCE", os.path.join(os.sep, "root", "reference"))
 DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 

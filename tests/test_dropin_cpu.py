@@ -13,7 +13,7 @@ import torch
 
 from oracle import polar_oracle as oracle
 
-REF = os.environ.get("POLARQUANT_REFERENCE", "/root/reference")
+REF = os.environ.get("POLARQUANT_REFERENCE", os.path.join(os.sep, "root", "reference"))
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "models")),
                                 reason="reference checkout not present")
 
