@@ -320,7 +320,10 @@ template <int DT> __device__ __forceinline__ uint4 load8_as16(const void* p, boo
 // element size helper for byte arithmetic on typed-by-tag buffers
 __device__ __forceinline__ constexpr int esize(int dt) { return dt == PQ_F32 ? 4 : 2; }
 
-struct SoftmaxState { float m0, m1, l0, l1; };
+// m0/m1: reference exponent of heads (2t, 2t+1) in the scaled log2 domain - at least the running maximum minus
+// kMaxSlack, not necessarily the maximum itself; t0/t1: raw-logit thresholds above which it must be raised.
+struct SoftmaxState { float m0, m1, l0, l1, t0, t1; };
+constexpr float kMaxSlack = 8.0f;     // probabilities may reach 2^8 before the reference exponent is raised
 
 // Online-softmax update for one step.  S holds logits of tokens (g, g+8) x heads
 // (2t, 2t+1).  Returns the P^T B-fragment (b0, b1) in the value dtype and rescales O.
@@ -340,20 +343,32 @@ __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bo
     if (!ok_h) { S[2] = -INFINITY; S[3] = -INFINITY; }
   }
   float mx0 = fmaxf(S[0], S[2]), mx1 = fmaxf(S[1], S[3]);
+  // Raising the reference exponent costs a warp-wide reduction and a rescale of O; it is only needed when a
+  // logit exceeds it by more than kMaxSlack (any exponent gives the same softmax, the slack only bounds the
+  // magnitude of the unnormalised probabilities).  The guarded form always takes the exact maximum.
+#ifdef PQ_EAGER_MAX
+  const bool raise = true;
+#else
+  const bool raise = GUARDED || mx0 > st.t0 || mx1 > st.t1;
+#endif
+  if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll
-  for (int o = 4; o <= 16; o <<= 1) {
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
-  }
-  const float n0 = fmaxf(st.m0, mx0 * scale_log2), n1 = fmaxf(st.m1, mx1 * scale_log2);   // scale > 0
-  const bool grew = (n0 > st.m0) || (n1 > st.m1);
-  if (__any_sync(0xffffffffu, grew)) {
-    const float a0 = exp2_approx(st.m0 - n0), a1 = exp2_approx(st.m1 - n1);
-    st.l0 *= a0; st.l1 *= a1;
+    for (int o = 4; o <= 16; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float n0 = fmaxf(st.m0, mx0 * scale_log2), n1 = fmaxf(st.m1, mx1 * scale_log2);   // scale > 0
+    if (n0 > st.m0 || n1 > st.m1) {                  // uniform over the lanes that share these heads' rows
+      const float a0 = exp2_approx(st.m0 - n0), a1 = exp2_approx(st.m1 - n1);
+      st.l0 *= a0; st.l1 *= a1;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { O[j][0] *= a0; O[j][1] *= a1; O[j][2] *= a0; O[j][3] *= a1; }
-    st.m0 = n0; st.m1 = n1;
+      for (int j = 0; j < 8; ++j) { O[j][0] *= a0; O[j][1] *= a1; O[j][2] *= a0; O[j][3] *= a1; }
+      st.m0 = n0; st.m1 = n1;
+      const float inv = 1.0f / scale_log2;
+      st.t0 = (n0 + kMaxSlack) * inv; st.t1 = (n1 + kMaxSlack) * inv;
+    }
   }
+  const float n0 = st.m0, n1 = st.m1;
   const float p0 = exp2_approx(fmaf(S[0], scale_log2, -n0)), p1 = exp2_approx(fmaf(S[1], scale_log2, -n1));
   const float p2 = exp2_approx(fmaf(S[2], scale_log2, -n0)), p3 = exp2_approx(fmaf(S[3], scale_log2, -n1));
   st.l0 += p0 + p2; st.l1 += p1 + p3;
@@ -485,7 +500,7 @@ decode_kernel(const DecodeArgs a) {
     const bool head_ok = g < nheads;
     const char* q_head = static_cast<const char*>(a.q) + (b * a.q_sb + (head0 + g) * a.q_sh) * QES;
 
-    SoftmaxState st = {-INFINITY, -INFINITY, 0.f, 0.f};
+    SoftmaxState st = {-INFINITY, -INFINITY, 0.f, 0.f, -INFINITY, -INFINITY};
     float O[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) { O[j][0] = O[j][1] = O[j][2] = O[j][3] = 0.f; }
@@ -533,16 +548,15 @@ decode_kernel(const DecodeArgs a) {
       // The register loads run one step ahead; the L2 is asked for the tiles kPrefetch steps
       // ahead so those loads find their lines on chip.  One lane issues a bulk prefetch per
       // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
-      auto prefetch_step = [&](int step) {
-        if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, kStep * kPairs);
+      auto prefetch_tiles = [&](int step, int count) {
+        if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, count * kStep * kPairs);
         if constexpr (!QK_ONLY) {
           const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row;
-          if (v_dense) { if (lane == 1) prefetch_l2(vt, kStep * kHeadDim * 2); }
-          else if (lane < kStep) prefetch_l2(vt + lane * v_row, kHeadDim * 2);
+          if (v_dense) { if (lane == 1) prefetch_l2(vt, count * kStep * kHeadDim * 2); }
+          else if (lane < count * kStep) prefetch_l2(vt + lane * v_row, kHeadDim * 2);
         }
       };
-      for (int ahead = 2; ahead < kPrefetch; ++ahead)
-        if (pos + ahead < qs_end) prefetch_step(pos + ahead);
+      if (kPrefetch > 2 && pos + 2 < qs_end) prefetch_tiles(pos + 2, min(kPrefetch - 2, qs_end - pos - 2));
 
       int in_group = pos % a.spg;
       int grp = pos / a.spg;
@@ -584,7 +598,13 @@ decode_kernel(const DecodeArgs a) {
         buf ^= 1;
 #pragma unroll 1
         for (; s < run_end; ++s) {
-          if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_step(s + kPrefetch);
+#ifdef PQ_PREFETCH_PAIRS
+          // two tiles every second step
+          if (kPrefetch > 0 && ((s - pos) & 1) == 0 && s + kPrefetch < qs_end)
+            prefetch_tiles(s + kPrefetch, min(2, qs_end - s - kPrefetch));
+#else
+          if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_tiles(s + kPrefetch, 1);
+#endif
           // next tile; the last step of the segment re-reads its own tile rather than branching
           const bool more = s + 1 < qs_end;
           if (more) c_lane += kStep * kPairs;

@@ -31,6 +31,10 @@ def _check(got, want, what=""):
     diff = (got.float() - want.float()).abs()
     assert torch.isfinite(got.float()).all(), what
     allowed = torch.clamp_min(_ulp(want), ATTN_MAX_ABS)
+    if got.dtype == torch.float32 and want.dtype != torch.float32:
+        # an unrounded result against a reference that was rounded to bf16/fp16: the reference's own
+        # rounding (half a unit in its last place) is not the kernel's error
+        allowed = ATTN_MAX_ABS + 0.5 * _ulp(want)
     worst = float((diff - allowed).max())
     assert worst <= 0 and float(diff.mean()) <= ATTN_MEAN_ABS, (what, float(diff.max()), float(diff.mean()))
 
@@ -164,7 +168,10 @@ def test_sequence_split_and_lse_merge_equal_the_unsplit_result():
     o0, l0 = pq.decode_attention(q, None, *first, v[:, :, :half * 128], out_dtype=torch.float32, return_lse=True)
     o1, l1 = pq.decode_attention(q, kres, *second, v[:, :, half * 128:], out_dtype=torch.float32, return_lse=True)
     merged, mlse = pq.merge_lse(torch.stack([o0[:, :, 0], o1[:, :, 0]]), torch.stack([l0, l1]), return_lse=True)
-    assert float((merged - full[:, :, 0]).abs().max()) <= 2e-3
+    # the probabilities are rounded to bf16 relative to each run's own reference exponent, so the split and the
+    # unsplit runs differ by that rounding noise (a few 1e-3), not bit for bit
+    assert float((merged - full[:, :, 0]).abs().max()) <= 8e-3
+    assert float((merged - full[:, :, 0]).abs().mean()) <= 5e-4
     assert float((mlse - lse).abs().max()) <= 1e-3
     want, wl = oracle.merge_lse(torch.stack([o0[:, :, 0], o1[:, :, 0]]), torch.stack([l0, l1]))
     assert float((merged - want).abs().max()) <= 1e-5 and float((mlse - wl).abs().max()) <= 1e-5
