@@ -608,7 +608,9 @@ decode_kernel(const DecodeArgs a) {
           // next tile; the last step of the segment re-reads its own tile rather than branching
           const bool more = s + 1 < qs_end;
           if (more) c_lane += kStep * kPairs;
+#ifndef PQ_CODES_INPLACE
           const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
+#endif
           if constexpr (!QK_ONLY) {
             if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
             int fill = vstage + kVStages - 1;
@@ -619,6 +621,10 @@ decode_kernel(const DecodeArgs a) {
 
           float S[4] = {0.f, 0.f, 0.f, 0.f};
           qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
+#ifdef PQ_CODES_INPLACE
+          // the code registers are free again: refill them for the next step (its lines are in L2 already)
+          cg = ldg_stream(c_lane); ch = ldg_stream(c_lane + 8 * kPairs);
+#endif
 
           if constexpr (QK_ONLY) {
             // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
@@ -640,7 +646,9 @@ decode_kernel(const DecodeArgs a) {
             __syncwarp();                   // every lane is done with the stage before it is refilled
             if (++vstage == kVStages) vstage = 0;
           }
+#ifndef PQ_CODES_INPLACE
           cg = ng; ch = nh;
+#endif
         }
         in_group = 0;
         ++grp;
