@@ -1,0 +1,78 @@
+"""Seeded random shapes through all three entry points against the oracle: odd GQA group sizes, tiny and ragged
+contexts, every supported bit split, group sizes 16..128, residual windows 0..128, strided caches, masks."""
+import random
+
+import pytest
+import torch
+
+from conftest import ATTN_MAX_ABS, ATTN_MEAN_ABS
+from oracle import polar_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+BITS = [(4, 4), (3, 3), (2, 4), (4, 3), (3, 4), (2, 2), (2, 3), (3, 2), (4, 2)]
+
+
+def _cases(n, seed):
+    rng = random.Random(seed)
+    out = []
+    for _ in range(n):
+        nk = rng.choice([1, 2, 3, 4, 8])
+        rep = rng.choice([1, 2, 3, 4, 5, 7, 8, 9, 16])
+        grp = rng.choice([16, 32, 64, 128])
+        nb = rng.choice([0, 1, 2, 3, 5, 9, 17, 40])
+        res = rng.choice([0, 1, 2, 15, 16, 17, 31, 64, 100, 127, 128])
+        if nb == 0 and res == 0:
+            res = 3
+        out.append(dict(B=rng.choice([1, 2, 3, 5]), Nk=nk, N=nk * rep, Nb=nb, G=grp, R=res, bits=rng.choice(BITS),
+                        dtype=rng.choice([torch.bfloat16, torch.float16, torch.float32]),
+                        strided=rng.random() < 0.4, mask=rng.random() < 0.3, seed=rng.randrange(1 << 30)))
+    return out
+
+
+@pytest.mark.parametrize("case", _cases(40, 777), ids=lambda c: f"B{c['B']}N{c['N']}k{c['Nk']}nb{c['Nb']}g{c['G']}r{c['R']}")
+def test_random_configuration(case):
+    import polarquant_b200 as pq
+    dev = "cuda"
+    B, N, Nk, Nb, G, R = (case[k] for k in ("B", "N", "Nk", "Nb", "G", "R"))
+    rb, tb = case["bits"]
+    dt = case["dtype"]
+    vdt = torch.bfloat16 if dt == torch.bfloat16 else torch.float16
+    g = torch.Generator(device=dev).manual_seed(case["seed"])
+    ctx = Nb * G + R
+    keys = oracle.synth_keys(B, Nk, ctx, 128, dt, seed=case["seed"] % 1000, device=dev)
+    q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+    v = (torch.randn(B, Nk, ctx, 128, device=dev, generator=g) * 0.5).to(vdt)
+
+    packed = (None,) * 5
+    if Nb:
+        kq = keys[:, :, :Nb * G]
+        if case["strided"]:
+            kq = kq.transpose(1, 2).contiguous().transpose(1, 2)          # (B, L, Nk, hd) storage
+        packed = pq.quantize_and_pack_nbit(kq, rb, tb, G)
+        want_packed = oracle.quantize_ops(kq.contiguous(), rb, tb, G)
+        for a, b in zip(packed, want_packed):                               # bit-exact on the same GPU
+            assert torch.equal(a, b)
+        if rb + tb <= 8 and 1 <= tb <= 4:
+            logits = pq.attention_decode_forward_triton_impl(q, *packed, rbits=rb, tbits=tb)
+            ref = oracle.qk_logits(q, *packed, rb, tb)
+            scale = max(1.0, float(ref.abs().max()))
+            assert float((logits - ref).abs().max()) <= 2e-3 * scale
+
+    kres = keys[:, :, Nb * G:].contiguous() if R else None
+    vv = v.transpose(1, 2).contiguous().transpose(1, 2) if case["strided"] else v
+    mask = None
+    if case["mask"] and ctx > 4:
+        mask = torch.ones(B, ctx, device=dev)
+        mask[0, : ctx // 3] = 0
+    got = pq.decode_attention(q, kres, *packed, vv, attention_mask=mask, rbits=rb, tbits=tb)
+    # the oracle's matmuls need one dtype: fp32 queries go with fp32-upcast values and no intermediate rounding
+    if dt == torch.float32:
+        want = oracle.decode_attention(q, kres, *packed, v.float(), attention_mask=mask, rbits=rb, tbits=tb,
+                                       faithful_rounding=False)
+    else:
+        want = oracle.decode_attention(q, kres, *packed, v.to(dt), attention_mask=mask, rbits=rb, tbits=tb)
+    assert got.shape == (B, N, 1, 128) and torch.isfinite(got.float()).all()
+    diff = (got.float() - want.float()).abs()
+    assert float(diff.max()) <= ATTN_MAX_ABS and float(diff.mean()) <= ATTN_MEAN_ABS, \
+        (float(diff.max()), float(diff.mean()))
