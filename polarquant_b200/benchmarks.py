@@ -20,14 +20,33 @@ import torch
 from . import ops
 
 
-def _time_us(fn, reps: int = 20, warm: int = 3) -> float:
+def _time_us(fn, reps: int = 20, warm: int = 3, graph: bool = True) -> float:
+    """Mean microseconds per call over back-to-back launches; the call is replayed from a CUDA graph when it can
+    be captured, so that small problems are not timed by the Python launcher."""
     for _ in range(warm):
         fn()
+    torch.cuda.synchronize()
+    run = fn
+    if graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            run = g.replay
+            run()
+        except Exception:
+            torch.cuda.synchronize()
+            run = fn
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(reps):
-        fn()
+        run()
     b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) / reps * 1e3
