@@ -37,7 +37,7 @@ NOMINAL_HBM_GBS = 8000.0
 # DRAM bytes (read + write) of one attention-kernel launch per batch element of the benchmark shape, from the
 # ncu capture of the batch-4 case (dram__bytes_read.sum 342.03 MB + dram__bytes_write.sum 4.20 MB per launch);
 # traffic grows in proportion to the batch, so a full-size launch is this figure times the batch
-NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT = (342.03e6 + 4.20e6) / 4
+NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT = (342.04e6 + 4.45e6) / 4
 FALLBACK_HBM_GBS = 6650.0
 
 
