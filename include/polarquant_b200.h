@@ -130,7 +130,7 @@ typedef struct pq_decode_params {
      current token.  NULL allowed when R == 0. */
   const void* k_res;
   int64_t kres_stride_b, kres_stride_h, kres_stride_t;
-  /* values (B, Nk, Nb*G + R, hd), dtype v_dtype (PQ_F16 or PQ_BF16) */
+  /* values (B, Nk, Nb*G + R, hd), dtype v_dtype (PQ_F16 or PQ_BF16); with vbits == 4 only the last R tokens */
   const void* v;
   int64_t v_stride_b, v_stride_h, v_stride_t;
   /* optional key mask (B, Nb*G + R) uint8, 1 = attend, 0 = masked; NULL = none */
@@ -149,6 +149,18 @@ typedef struct pq_decode_params {
   float sm_scale;  /* logits multiplier; 0 means 1/sqrt(hd) as at modeling_llama_polar.py:80 */
   int num_ctas;    /* 0 = choose from the device's SM count */
   void* mid_event; /* optional cudaEvent_t recorded between the attention kernel and the merge kernel */
+  /* Optional packed values (vbits == 4; 0 = none): the values of the Nb*G packed-key tokens as 4-bit codes in
+     the PQ_VALUES_TILED layout of pq_quantize_values, 64 bytes per token, tokens contiguous per (b, kvh) unit,
+     unit at b * vcodes_stride_b + kvh * vcodes_stride_h BYTES; v_scale / v_mn one element of v_dtype per token,
+     unit at b * vscale_stride_b + kvh * vscale_stride_h ELEMENTS (even).  `v` then holds only the R
+     full-precision values of the residual window, (B, Nk, R, hd).  Requires qk_dtype == v_dtype (fp16 or bf16).
+     This is the decode branch of LlamaPolarMixedGroupAttention (models/modeling_llama_polar.py:189-246). */
+  const void* v_codes;
+  int64_t vcodes_stride_b, vcodes_stride_h;
+  const void* v_scale;
+  const void* v_mn;
+  int64_t vscale_stride_b, vscale_stride_h;
+  int vbits;
 } pq_decode_params;
 
 int pq_decode_attention(const pq_decode_params* p, void* stream);
@@ -179,6 +191,36 @@ size_t pq_decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int
  */
 int pq_decode_attention_static(const pq_decode_params* p, void* stream);
 size_t pq_decode_static_scratch_bytes(void);
+
+/*
+ * Packed value cache (the reference's LlamaPolarMixedGroupAttention, models/modeling_llama_polar.py:160-292).
+ * pq_quantize_values replaces `triton_quantize_and_pack_along_last_dim(values, 128, 4)` (:242, :285; a KIVI routine
+ * the reference imports without shipping it): per token, min/max over the 128 channels, scale = (mx - mn) / 15,
+ * level = round(clamp((v - mn) / scale, 0, 15)), every step rounded to `dtype` as torch on CUDA rounds it.
+ * values (B, Nk, T, hd) with element strides[4], strides[3] == 1; codes 64 bytes per token; scale, mn one element
+ * of `dtype` per token.  out_strides NULL: outputs contiguous, codes (B, Nk, T, 16) int32, scale / mn
+ * (B, Nk, T, 1).  Otherwise unit (b, h) starts at b * out_strides[0] + h * out_strides[1] bytes (codes) and
+ * b * out_strides[2] + h * out_strides[3] elements (scale, mn), tokens contiguous within a unit: pass pointers to
+ * the first token to be written (in-place cache).  hd == 128, vbits == 4.
+ *
+ * layout PQ_VALUES_KIVI: channel c at bits 4 * (c % 8) of word c / 8 (what `cuda_bmm_fA_qB_outer` and
+ * pq_values_matmul read).  PQ_VALUES_TILED: channel c at 4-bit field c / 8 of the 64-bit slot c % 8 - the order in
+ * which pq_decode_attention consumes them.  pq_values_relayout converts `tokens` rows of 64 bytes between the two
+ * (out of place).
+ */
+#define PQ_VALUES_KIVI 0
+#define PQ_VALUES_TILED 1
+int pq_quantize_values(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
+                       int dtype, int layout, void* codes, void* scale, void* mn, const int64_t* out_strides,
+                       void* stream);
+int pq_values_relayout(const void* codes_in, void* codes_out, int64_t tokens, int to_layout, void* stream);
+/*
+ * out (BH, M, hd) = probs (BH, M, T) x dequantised values (BH, T, hd), all contiguous, `dtype` throughout, fp32
+ * accumulation; codes in the PQ_VALUES_KIVI layout.  Replaces `cuda_bmm_fA_qB_outer(128, probs, codes, scale, mn, 4)`
+ * as called at models/modeling_llama_polar.py:230-237 (the reference passes per-query-head copies: BH = B * N).
+ */
+int pq_values_matmul(const void* probs, const void* codes, const void* scale, const void* mn, void* out,
+                     int64_t BH, int M, int T, int hd, int vbits, int dtype, void* stream);
 
 /*
  * Merge P partial attention results over disjoint key ranges (sequence split

@@ -282,6 +282,157 @@ def decode_attention(query, key_residual, codes, rscale, rmn, tscale, tmn, value
     return (out, lse) if return_lse else out
 
 
+# ---------------------------------------------------------------------------------------------
+# Quantised value cache (LlamaPolarMixedGroupAttention, models/modeling_llama_polar.py:160-292)
+#
+# PARITY UNPINNED for this part: the reference calls `triton_quantize_and_pack_along_last_dim` and
+# `cuda_bmm_fA_qB_outer` from the KIVI project (github.com/jy-yuan/KIVI, `quant/new_pack.py` and
+# `quant/matmul.py`; the reference imports them as models.kivi_quant.* and vendors neither, nor pins a
+# version).  What follows restates KIVI's published algorithm as the reference's call sites use it
+# (:242, :285: group 128 along the channel axis = one group per token, 4 bits; :230-237: dequantise
+# and multiply); nothing here could be checked against an executed KIVI.
+# ---------------------------------------------------------------------------------------------
+def quantize_values(values: torch.Tensor, bits: int = 4, layout: str = "kivi", scalar_division: str = "reciprocal"):
+    """Per-token asymmetric min/max quantisation of (B, Nk, T, 128) values, every op in the tensor dtype as
+    torch executes it: ``mn, mx`` over the 128 channels; ``scale = (mx - mn) / (2^bits - 1)``;
+    ``q = round_half_even(clamp((v - mn) / scale, 0, 2^bits - 1))`` (a constant token gives 0/0 = NaN, which the
+    CUDA float-to-int cast turns into 0); 32/bits consecutive channels share an int32, channel ``c`` at bits
+    ``bits * (c % (32/bits))`` of word ``c // (32/bits)``.  Returns codes (B, Nk, T, 128*bits/32) int32 and
+    scale, mn (B, Nk, T, 1).  ``layout="tiled"`` applies ``kivi_to_tiled`` to the codes.
+
+    ``scalar_division``: KIVI only runs on CUDA, where torch divides a tensor by a Python scalar by multiplying
+    with the scalar's fp32 reciprocal - ``"reciprocal"`` states that explicitly (the default, on any device);
+    ``"true"`` leaves ``/ (2^bits - 1)`` to torch, i.e. a true division on CPU and whatever the device does on
+    CUDA (the GPU tests use it to pin "reciprocal" against torch executing there)."""
+    levels = 2 ** bits - 1
+    dt = values.dtype
+    mn = values.min(dim=-1, keepdim=True)[0]
+    mx = values.max(dim=-1, keepdim=True)[0]
+    if scalar_division == "reciprocal":
+        inv = torch.tensor(1.0, dtype=torch.float32, device=values.device) / levels
+        scale = ((mx - mn).to(torch.float32) * inv).to(dt)
+    elif scalar_division == "true":
+        scale = (mx - mn) / levels
+    else:
+        raise ValueError(scalar_division)
+    q = (values - mn) / scale
+    q = torch.nan_to_num(q.clamp(0, levels).round().to(torch.float32), nan=0.0).to(torch.int32)
+    per = 32 // bits
+    q = q.reshape(*q.shape[:-1], q.shape[-1] // per, per)
+    codes = torch.zeros(q.shape[:-1], dtype=torch.int32, device=values.device)
+    for i in range(per):          # OR of disjoint bit fields; int32 wrap-around of the top field is intended
+        codes |= q[..., i] << (bits * i)
+    if layout == "tiled":
+        codes = kivi_to_tiled(codes, bits)
+    elif layout != "kivi":
+        raise ValueError(layout)
+    return codes, scale, mn
+
+
+def unpack_values(codes: torch.Tensor, bits: int = 4, layout: str = "kivi") -> torch.Tensor:
+    """Integer levels (B, Nk, T, 128) int32 from packed codes of either layout."""
+    if layout == "tiled":
+        codes = tiled_to_kivi(codes, bits)
+    per = 32 // bits
+    shifts = torch.arange(per, dtype=torch.int32, device=codes.device) * bits
+    q = (codes[..., None] >> shifts) & (2 ** bits - 1)
+    return q.reshape(*codes.shape[:-1], codes.shape[-1] * per)
+
+
+def _tiled_perm(bits: int = 4) -> np.ndarray:
+    """Channel held by each field of a token's packed row in the tiled layout, in field order.  4 bits: the row is
+    eight 64-bit lane slots; slot g (words 2g, 2g+1) holds channels g + 8j at field j = 0..15 - what lane group
+    g of the attention kernel needs for the rows (g, g + 8) of all eight 16-channel output tiles."""
+    if bits != 4:
+        raise NotImplementedError("tiled layout is defined for 4-bit values")
+    perm = np.empty(128, dtype=np.int64)
+    for g in range(8):
+        for j in range(16):
+            perm[16 * g + j] = g + 8 * j
+    return perm
+
+
+def kivi_to_tiled(codes: torch.Tensor, bits: int = 4) -> torch.Tensor:
+    per = 32 // bits
+    q = unpack_values(codes, bits)[..., torch.from_numpy(_tiled_perm(bits)).to(codes.device)]
+    q = q.reshape(*q.shape[:-1], q.shape[-1] // per, per)
+    out = torch.zeros(q.shape[:-1], dtype=torch.int32, device=codes.device)
+    for i in range(per):
+        out |= q[..., i] << (bits * i)
+    return out
+
+
+def tiled_to_kivi(codes: torch.Tensor, bits: int = 4) -> torch.Tensor:
+    per = 32 // bits
+    shifts = torch.arange(per, dtype=torch.int32, device=codes.device) * bits
+    fields = ((codes[..., None] >> shifts) & (2 ** bits - 1)).reshape(*codes.shape[:-1], codes.shape[-1] * per)
+    q = torch.empty_like(fields)
+    q[..., torch.from_numpy(_tiled_perm(bits)).to(codes.device)] = fields
+    q = q.reshape(*q.shape[:-1], q.shape[-1] // per, per)
+    out = torch.zeros(q.shape[:-1], dtype=torch.int32, device=codes.device)
+    for i in range(per):
+        out |= q[..., i] << (bits * i)
+    return out
+
+
+def dequantize_values(codes, scale, mn, bits: int = 4, layout: str = "kivi") -> torch.Tensor:
+    """fp32 values ``level * scale + mn`` (B, Nk, T, 128), scale and mn upcast first."""
+    return unpack_values(codes, bits, layout).to(torch.float32) * scale.to(torch.float32) + mn.to(torch.float32)
+
+
+def values_matmul(probs, codes, scale, mn, bits: int = 4) -> torch.Tensor:
+    """``cuda_bmm_fA_qB_outer(128, probs, codes, scale, mn, bits)`` as the reference calls it
+    (models/modeling_llama_polar.py:230-237): probs (B, H, M, T) times the dequantised values (B, H, T, 128),
+    fp32 accumulation, result in the dtype of ``probs``."""
+    v = dequantize_values(codes, scale, mn, bits)
+    return torch.matmul(probs.to(torch.float32), v).to(probs.dtype)
+
+
+def decode_attention_mixed(query, key_residual, codes, rscale, rmn, tscale, tmn, v_codes, v_scale, v_mn,
+                           value_residual, attention_mask=None, rbits: int = 4, tbits: int = 4, vbits: int = 4,
+                           sm_scale: float | None = None, faithful_rounding: bool = True,
+                           return_lse: bool = False, layout: str = "kivi"):
+    """Decode step with packed keys AND packed values (models/modeling_llama_polar.py:189-246): logits and
+    softmax as in ``decode_attention``; ``out = RN_q(P[:, :Tq] @ dequant(V)) + RN_q(P[:, Tq:] @ V_res)`` where
+    the first ``Tq = v_codes.shape[2]`` keys have packed values and the rest full-precision ones (:229-239)."""
+    qdt = query.dtype
+    bsz, nq, _, hd = query.shape
+    kvh = (value_residual if value_residual is not None else v_codes).shape[1]
+    n_rep = nq // kvh
+    parts = []
+    if codes is not None and codes.shape[2] > 0:
+        parts.append(qk_logits(query, codes, rscale, rmn, tscale, tmn, rbits, tbits))
+    if key_residual is not None and key_residual.shape[2] > 0:
+        kr = _expand_kv(key_residual, n_rep)
+        if faithful_rounding:
+            parts.append(torch.matmul(query, kr.to(qdt).transpose(2, 3)).to(torch.float32))
+        else:
+            parts.append(torch.matmul(query.to(torch.float32), kr.to(torch.float32).transpose(2, 3)))
+    w = torch.cat(parts, dim=-1)
+    w = w / math.sqrt(hd) if sm_scale is None else w * sm_scale
+    if attention_mask is not None:
+        w = w + (1.0 - attention_mask.to(torch.float32)[:, None, None, :]) * torch.finfo(torch.float32).min
+    lse = torch.logsumexp(w, dim=-1)[:, :, 0]
+    p = torch.softmax(w, dim=-1)
+    tq = 0 if v_codes is None else v_codes.shape[2]
+    out = torch.zeros((bsz, nq, 1, hd), dtype=torch.float32)
+    if faithful_rounding:
+        p = p.to(qdt)
+    if tq:
+        vq = _expand_kv(dequantize_values(v_codes, v_scale, v_mn, vbits, layout), n_rep)
+        o = torch.matmul(p[..., :tq].to(torch.float32), vq)
+        out = out + (o.to(qdt).to(torch.float32) if faithful_rounding else o)
+    if value_residual is not None and value_residual.shape[2] > 0:
+        vr = _expand_kv(value_residual, n_rep)
+        if faithful_rounding:
+            o = torch.matmul(p[..., tq:], vr.to(qdt)).to(torch.float32)
+        else:
+            o = torch.matmul(p[..., tq:], vr.to(torch.float32))
+        out = out + o
+    out = out.to(qdt) if faithful_rounding else out
+    return (out, lse) if return_lse else out
+
+
 def merge_lse(outs: torch.Tensor, lses: torch.Tensor):
     """Merge partial attention results computed over disjoint key ranges.
 

@@ -18,6 +18,7 @@ PQ_F16, PQ_BF16, PQ_F32 = 0, 1, 2
 PQ_OK = 0
 PQ_QUANT_WRAP_DTYPE = 1
 PQ_QUANT_NORM_FMA = 2
+PQ_VALUES_KIVI, PQ_VALUES_TILED = 0, 1
 
 EXPORTED_SYMBOLS = (
     "pq_quantize", "pq_qk_decode", "pq_decode_attention", "pq_decode_workspace_bytes", "pq_merge_lse",
@@ -25,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "pq_decode_host_staging_bytes", "pq_strerror", "pq_last_cuda_error", "pq_abi_version", "pq_decode_params_size",
     "pq_event_create", "pq_event_destroy", "pq_event_record", "pq_event_elapsed_ms",
     "pq_decode_attention_static", "pq_decode_static_scratch_bytes", "pq_selftest_quantizer", "pq_quantize_into", "pq_cache_append",
+    "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -49,6 +51,9 @@ class DecodeParams(ctypes.Structure):
         ("sm_scale", _f32),
         ("num_ctas", _int),
         ("mid_event", _vp),
+        ("v_codes", _vp), ("vcodes_stride_b", _i64), ("vcodes_stride_h", _i64),
+        ("v_scale", _vp), ("v_mn", _vp), ("vscale_stride_b", _i64), ("vscale_stride_h", _i64),
+        ("vbits", _int),
     ]
 
 
@@ -64,6 +69,13 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_cache_append.restype = _int
     lib.pq_cache_append.argtypes = [_vp, _vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _vp,
                                     ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _vp]
+    lib.pq_quantize_values.restype = _int
+    lib.pq_quantize_values.argtypes = [_vp, ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _int,
+                                       _vp, _vp, _vp, ctypes.POINTER(_i64), _vp]
+    lib.pq_values_relayout.restype = _int
+    lib.pq_values_relayout.argtypes = [_vp, _vp, _i64, _int, _vp]
+    lib.pq_values_matmul.restype = _int
+    lib.pq_values_matmul.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _int, _vp]
     lib.pq_qk_decode.restype = _int
     lib.pq_qk_decode.argtypes = [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
                                  _int, _int, _int, _int, _int, _int, _int, _int, _int, _vp]
@@ -117,7 +129,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 1:
+        if lib.pq_abi_version() != 2:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

@@ -22,6 +22,12 @@ size_t decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int nu
 int decode_attention_device(const pq_decode_params* p, cudaStream_t stream);
 int decode_attention_static_device(const pq_decode_params* p, cudaStream_t stream);
 size_t decode_static_scratch_bytes();
+int quantize_values_device(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
+                           int dtype, int layout, void* codes, void* scale, void* mn, const int64_t* out_strides,
+                           cudaStream_t stream);
+int values_relayout_device(const void* codes_in, void* codes_out, int64_t tokens, int to_layout, cudaStream_t stream);
+int values_matmul_device(const void* probs, const void* codes, const void* scale, const void* mn, void* out,
+                         int64_t BH, int M, int T, int hd, int vbits, int dtype, cudaStream_t stream);
 int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out, int out_dtype,
                      float* lse_out, cudaStream_t stream);
 
@@ -40,7 +46,7 @@ using namespace pq;
 
 extern "C" {
 
-int pq_abi_version(void) { return 1; }
+int pq_abi_version(void) { return 2; }
 size_t pq_decode_params_size(void) { return sizeof(pq_decode_params); }
 int pq_last_cuda_error(void) { return last_cuda_error(); }
 
@@ -102,6 +108,21 @@ int pq_decode_attention_static(const pq_decode_params* p, void* stream) {
   return decode_attention_static_device(p, static_cast<cudaStream_t>(stream));
 }
 size_t pq_decode_static_scratch_bytes(void) { return decode_static_scratch_bytes(); }
+
+int pq_quantize_values(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
+                       int dtype, int layout, void* codes, void* scale, void* mn, const int64_t* out_strides,
+                       void* stream) {
+  return quantize_values_device(values, strides, B, Nk, T, hd, vbits, dtype, layout, codes, scale, mn, out_strides,
+                                static_cast<cudaStream_t>(stream));
+}
+int pq_values_relayout(const void* codes_in, void* codes_out, int64_t tokens, int to_layout, void* stream) {
+  return values_relayout_device(codes_in, codes_out, tokens, to_layout, static_cast<cudaStream_t>(stream));
+}
+int pq_values_matmul(const void* probs, const void* codes, const void* scale, const void* mn, void* out, int64_t BH,
+                     int M, int T, int hd, int vbits, int dtype, void* stream) {
+  return values_matmul_device(probs, codes, scale, mn, out, BH, M, T, hd, vbits, dtype,
+                              static_cast<cudaStream_t>(stream));
+}
 
 int pq_merge_lse(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out, int out_dtype,
                  float* lse_out, void* stream) {
@@ -197,6 +218,7 @@ int pq_decode_attention_host(const pq_decode_params* hp, void* staging, size_t s
                                                    hp->out_dtype, hp->mask != nullptr);
   if (!staging || staging_bytes < need) return PQ_ERR_WORKSPACE;
   if (!hp->q || !hp->v || !hp->out) return PQ_ERR_INVALID;
+  if (hp->vbits != 0) return PQ_ERR_UNSUPPORTED;        // packed values: device-resident caches only
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t qe = dtype_bytes(hp->qk_dtype), ve = dtype_bytes(hp->v_dtype), oe = dtype_bytes(hp->out_dtype);
   const size_t units = static_cast<size_t>(B) * Nk, ctx = static_cast<size_t>(Nb) * G + R;

@@ -64,6 +64,9 @@ struct DecodeArgs {
   const void *rscale, *rmn, *tscale, *tmn; int64_t s_sb, s_sh;
   const void* kres; int64_t kr_sb, kr_sh, kr_st;
   const void* v; int64_t v_sb, v_sh, v_st;
+  int v_tok0;           // token of `v` that holds the first residual value: Nb*G, or 0 with packed values
+  const void* vq_codes; int64_t vq_sb, vq_sh;            // packed values, byte strides
+  const void *vq_scale, *vq_mn; int64_t vs_sb, vs_sh;    // their per-token scale / minimum, element strides
   const uint8_t* mask; int64_t m_sb;
   float* part_o;        // [slot][128][8]
   float2* part_ml;      // [slot][8]  (running max in log2 units, running sum)
@@ -330,10 +333,10 @@ constexpr float kMaxSlack = 8.0f;     // probabilities may reach 2^8 before the 
 // The running maximum lives in the scaled log2 domain; the scale is applied inside the
 // exponent's FMA.  GUARDED adds the per-token validity / mask handling (residual window,
 // masked batches); the unguarded form is the hot loop's.
-template <int VDT, bool GUARDED>
+template <int VDT, bool GUARDED, int NT>
 __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bool ok_g, bool ok_h,
                                              bool masked_g, bool masked_h, SoftmaxState& st,
-                                             float (&O)[8][4], uint32_t& b0, uint32_t& b1) {
+                                             float (&O)[NT][4], uint32_t& b0, uint32_t& b1) {
   if constexpr (GUARDED) {
     // a finite stand-in for "+ finfo.min" keeps an all-masked row uniform, as in the reference
     const float kMasked = -1.0e30f / scale_log2;
@@ -362,7 +365,7 @@ __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bo
       const float a0 = exp2_approx(st.m0 - n0), a1 = exp2_approx(st.m1 - n1);
       st.l0 *= a0; st.l1 *= a1;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { O[j][0] *= a0; O[j][1] *= a1; O[j][2] *= a0; O[j][3] *= a1; }
+      for (int j = 0; j < NT; ++j) { O[j][0] *= a0; O[j][1] *= a1; O[j][2] *= a0; O[j][3] *= a1; }
       st.m0 = n0; st.m1 = n1;
       const float inv = 1.0f / scale_log2;
       st.t0 = (n0 + kMaxSlack) * inv; st.t1 = (n1 + kMaxSlack) * inv;
@@ -426,8 +429,8 @@ __device__ __forceinline__ uint32_t ldsm_lane_offset(int lane) {
   const int mi = lane >> 3, r = lane & 7;
   return (r + 8 * (mi >> 1)) * kVRowSmem + (mi & 1) * 16;
 }
-template <int VDT>
-__device__ __forceinline__ void pv_from_smem(float (&O)[8][4], uint32_t base, uint32_t b0, uint32_t b1) {
+template <int VDT, int NT>
+__device__ __forceinline__ void pv_from_smem(float (&O)[NT][4], uint32_t base, uint32_t b0, uint32_t b1) {
 #define PQ_PV(J)                                                                                   \
   {                                                                                                \
     uint32_t a0, a1, a2, a3;                                                                       \
@@ -440,20 +443,86 @@ __device__ __forceinline__ void pv_from_smem(float (&O)[8][4], uint32_t base, ui
 #undef PQ_PV
 }
 
+// ---- packed (4-bit) values ---------------------------------------------------------------
+// A lane's share of a 16-token value tile in the tiled layout: the 64-bit slot g of tokens 2t, 2t+1, 2t+8, 2t+9
+// (fields j = 0..15 = channels g + 8 j), straight from global memory, plus the scale and minimum pairs of those
+// tokens.  No shared memory is involved.
+struct VqTile { uint2 a, b, c, d; uint32_t s01, s89, m01, m89; };
+__device__ __forceinline__ uint2 ldg8_stream(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg4_nc(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ VqTile load_vq_tile(const char* code_lane, const char* scale_lane, const char* mn_lane) {
+  VqTile x;
+  x.a = ldg8_stream(code_lane); x.b = ldg8_stream(code_lane + 64);
+  x.c = ldg8_stream(code_lane + 8 * 64); x.d = ldg8_stream(code_lane + 9 * 64);
+  x.s01 = ldg4_nc(scale_lane); x.s89 = ldg4_nc(scale_lane + 16);
+  x.m01 = ldg4_nc(mn_lane); x.m89 = ldg4_nc(mn_lane + 16);
+  return x;
+}
+// a pair of 16-bit values of type DT as an fp16 pair
+template <int DT> __device__ __forceinline__ uint32_t as_half2(uint32_t w) {
+  if constexpr (DT == PQ_F16) return w;
+  else { const float2 f = unpack2<PQ_BF16>(w); return pack2<PQ_F16>(f.x, f.y); }
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// O^T += V^T . P^T with V = level * scale + mn.  The levels enter the tensor core as they are stored: a 4-bit
+// field at bits 0-3 (4-7) of a 16-bit lane IS the fp16 subnormal level * 2^-24 (level * 2^-20), so the A operand
+// costs one AND per register pair and the powers of two are folded into the accumulators afterwards (rows g hold
+// 2^-24, rows g + 8 hold 2^-20 times the true sum).  The scale multiplies P instead of V, and the minimum's
+// contribution sum_t mn_t p_t - the same for all channels of a head - is one more MMA into O[8] whose A rows all
+// equal the minimum pair.  b0 / b1: P^T in fp16.
+template <int VDT>
+__device__ __forceinline__ void pv_quant(float (&O)[9][4], const VqTile& x, uint32_t b0, uint32_t b1) {
+  const uint32_t m01 = as_half2<VDT>(x.m01), m89 = as_half2<VDT>(x.m89);
+  mma_16816_f16(O[8], m01, m01, m89, m89, b0, b1);
+  b0 = hmul2_u(b0, as_half2<VDT>(x.s01));
+  b1 = hmul2_u(b1, as_half2<VDT>(x.s89));
+#define PQ_PVQ(J, Z, Y)                                                                          \
+  mma_16816_f16(O[J], (Z) & 0x000f000fu, (Z) & 0x00f000f0u, (Y) & 0x000f000fu, (Y) & 0x00f000f0u, b0, b1);
+  {
+    const uint32_t zl = __byte_perm(x.a.x, x.b.x, 0x5410), zh = __byte_perm(x.a.x, x.b.x, 0x7632);
+    const uint32_t yl = __byte_perm(x.c.x, x.d.x, 0x5410), yh = __byte_perm(x.c.x, x.d.x, 0x7632);
+    PQ_PVQ(0, zl, yl) PQ_PVQ(1, zl >> 8, yl >> 8) PQ_PVQ(2, zh, yh) PQ_PVQ(3, zh >> 8, yh >> 8)
+  }
+  {
+    const uint32_t zl = __byte_perm(x.a.y, x.b.y, 0x5410), zh = __byte_perm(x.a.y, x.b.y, 0x7632);
+    const uint32_t yl = __byte_perm(x.c.y, x.d.y, 0x5410), yh = __byte_perm(x.c.y, x.d.y, 0x7632);
+    PQ_PVQ(4, zl, yl) PQ_PVQ(5, zl >> 8, yl >> 8) PQ_PVQ(6, zh, yh) PQ_PVQ(7, zh >> 8, yh >> 8)
+  }
+#undef PQ_PVQ
+}
+
 // ---------------------------------------------------------------------------------
 // fused decode attention
 // ---------------------------------------------------------------------------------
 #ifndef PQ_MIN_CTAS
 #define PQ_MIN_CTAS 3
 #endif
-template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
+// value stages a warp owns: the cp.async pipeline of full-precision values, one tile for the residual window
+// when the packed tokens' values are packed too (VQ), none for the logits-only kernel
+constexpr int v_stages(bool qk_only, int vq) { return qk_only ? 0 : (vq ? 1 : kVStages); }
+
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ>
 __global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : PQ_MIN_CTAS)
 decode_kernel(const DecodeArgs a) {
   constexpr int A = 1 << TBITS;
+  constexpr bool kVPipe = !QK_ONLY && VQ == 0;   // values of the packed tokens stream through shared memory
+  constexpr int NT = VQ ? 9 : 8;                 // accumulator tiles: 8 channel tiles (+ the minimum term)
   constexpr int QES = QDT == PQ_F32 ? 4 : 2;     // bytes per q / scale / residual-key element
   constexpr int kStageBytes = 4 * kPairs * QES;   // four scale rows of one group
   extern __shared__ __align__(256) unsigned char smem_dyn[];
-  constexpr int kWarpSmem = kPairs * A * 4 + 2 * kStageBytes + (QK_ONLY ? 0 : kVStages * kVTileSmem);
+  constexpr int kWarpSmem = kPairs * A * 4 + 2 * kStageBytes + v_stages(QK_ONLY, VQ) * kVTileSmem;
   unsigned char* warp_smem = smem_dyn + (threadIdx.x >> 5) * kWarpSmem;
   uint32_t* s_tbl_w = reinterpret_cast<uint32_t*>(warp_smem);
   char* s_sc_w = reinterpret_cast<char*>(warp_smem + kPairs * A * 4);
@@ -501,9 +570,9 @@ decode_kernel(const DecodeArgs a) {
     const char* q_head = static_cast<const char*>(a.q) + (b * a.q_sb + (head0 + g) * a.q_sh) * QES;
 
     SoftmaxState st = {-INFINITY, -INFINITY, 0.f, 0.f, -INFINITY, -INFINITY};
-    float O[8][4];
+    float O[NT][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { O[j][0] = O[j][1] = O[j][2] = O[j][3] = 0.f; }
+    for (int j = 0; j < NT; ++j) { O[j][0] = O[j][1] = O[j][2] = O[j][3] = 0.f; }
 
     const char* v_unit = static_cast<const char*>(a.v) + (b * a.v_sb + kvh * a.v_sh) * 2;
     const int64_t v_row = a.v_st * 2;                       // bytes between tokens
@@ -537,10 +606,20 @@ decode_kernel(const DecodeArgs a) {
         if (v_dense) load_v_tile_fast<true>(cp_dst + stage * kVTileSmem, v_tile, two_rows);
         else load_v_tile_fast<false>(cp_dst + stage * kVTileSmem, v_tile, two_rows);
       };
-      if constexpr (!QK_ONLY) {
+      if constexpr (kVPipe) {
         cp_async_wait<0>();               // nothing of an earlier segment may still be landing in the stages
         __syncwarp();
         fetch_tile(0);                    // committed with the first scales below
+      }
+      // packed values: this lane's slot of tokens 2t, 2t+1 (+8, +9) of the step and their scale / minimum pairs
+      const char* vq_lane = nullptr; const char* vs_lane = nullptr; const char* vm_lane = nullptr;
+      VqTile vq{};
+      if constexpr (VQ != 0) {
+        const int64_t tok0 = static_cast<int64_t>(pos) * kStep + 2 * t;
+        vq_lane = static_cast<const char*>(a.vq_codes) + b * a.vq_sb + kvh * a.vq_sh + tok0 * 64 + 8 * g;
+        vs_lane = static_cast<const char*>(a.vq_scale) + (b * a.vs_sb + kvh * a.vs_sh + tok0) * 2;
+        vm_lane = static_cast<const char*>(a.vq_mn) + (b * a.vs_sb + kvh * a.vs_sh + tok0) * 2;
+        vq = load_vq_tile(vq_lane, vs_lane, vm_lane);
       }
       const int last_tile = qs_end - 1;   // tiles past the segment are never fetched: the last one is re-read
       int next_tile = pos;
@@ -550,10 +629,15 @@ decode_kernel(const DecodeArgs a) {
       // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
       auto prefetch_tiles = [&](int step, int count) {
         if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, count * kStep * kPairs);
-        if constexpr (!QK_ONLY) {
+        if constexpr (kVPipe) {
           const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row;
           if (v_dense) { if (lane == 1) prefetch_l2(vt, count * kStep * kHeadDim * 2); }
           else if (lane < count * kStep) prefetch_l2(vt + lane * v_row, kHeadDim * 2);
+        }
+        if constexpr (VQ != 0) {
+          if (lane == 1)
+            prefetch_l2(static_cast<const char*>(a.vq_codes) + b * a.vq_sb + kvh * a.vq_sh +
+                            static_cast<int64_t>(step) * kStep * 64, count * kStep * 64);
         }
       };
       if (kPrefetch > 2 && pos + 2 < qs_end) prefetch_tiles(pos + 2, min(kPrefetch - 2, qs_end - pos - 2));
@@ -562,7 +646,7 @@ decode_kernel(const DecodeArgs a) {
       int grp = pos / a.spg;
       const int last_grp = (qs_end - 1) / a.spg;
       const uint32_t sc_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_sc_w));
-      constexpr bool kCommitScales = QK_ONLY;   // fused kernel: the scale copies join the next value-tile group
+      constexpr bool kCommitScales = !kVPipe;   // with a value pipeline the scale copies join the next value-tile group
       auto stage_group = [&](int gidx, int buf) {
         const int64_t row = static_cast<int64_t>(gidx) * kPairs * QES;
         stage_scales_async<QDT, kCommitScales>(sc_addr + buf * kStageBytes, rs_unit + row, rm_unit + row,
@@ -571,7 +655,7 @@ decode_kernel(const DecodeArgs a) {
       __syncwarp();                       // earlier readers of the staging buffers are done
       int buf = 0;
       stage_group(grp, buf);
-      if constexpr (!QK_ONLY) {
+      if constexpr (kVPipe) {
         cp_async_commit();                           // first value tile + first scales
 #pragma unroll
         for (int d = 1; d < kVStages - 1; ++d) {     // fill the pipeline: tiles pos+1 .. pos+kVStages-2
@@ -589,7 +673,7 @@ decode_kernel(const DecodeArgs a) {
         // group committed at the first step of the previous run; when that run had at least kVStages
         // steps the group is older than the kVStages - 1 groups allowed in flight and nothing needs
         // draining.  (The first run of a segment may be shorter than a token group.)
-        if (!QK_ONLY && prev_run >= kVStages) { cp_async_wait<kVStages - 1>(); __syncwarp(); }
+        if (kVPipe && prev_run >= kVStages) { cp_async_wait<kVStages - 1>(); __syncwarp(); }
         else wait_staged();
         prev_run = run_end - s;
         if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
@@ -611,12 +695,17 @@ decode_kernel(const DecodeArgs a) {
 #ifndef PQ_CODES_INPLACE
           const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
 #endif
-          if constexpr (!QK_ONLY) {
+          if constexpr (kVPipe) {
             if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
             int fill = vstage + kVStages - 1;
             if (fill >= kVStages) fill -= kVStages;
             fetch_tile(fill);
             cp_async_commit();              // also carries scale rows staged since the last commit
+          }
+          VqTile nvq{};
+          if constexpr (VQ != 0) {
+            if (more) { vq_lane += kStep * 64; vs_lane += kStep * 2; vm_lane += kStep * 2; }
+            nvq = load_vq_tile(vq_lane, vs_lane, vm_lane);
           }
 
           float S[4] = {0.f, 0.f, 0.f, 0.f};
@@ -634,17 +723,23 @@ decode_kernel(const DecodeArgs a) {
             if (2 * t + 1 < nheads) { orow[Lq] = S[1]; orow[Lq + 8] = S[3]; }
           } else {
             uint32_t b0, b1;
+            constexpr int PDT = VQ ? PQ_F16 : VDT;      // packed values are multiplied in fp16 whatever VDT is
             if (mask_row) {
               const bool mg = mask_row[s * kStep + g] == 0, mh = mask_row[s * kStep + g + 8] == 0;
-              softmax_step<VDT, true>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
+              softmax_step<PDT, true>(S, a.scale_log2, true, true, mg, mh, st, O, b0, b1);
             } else {
-              softmax_step<VDT, false>(S, a.scale_log2, true, true, false, false, st, O, b0, b1);
+              softmax_step<PDT, false>(S, a.scale_log2, true, true, false, false, st, O, b0, b1);
             }
-            cp_async_wait<kVStages - 1>();  // this step's tile has landed; the newer ones may be in flight
-            __syncwarp();
-            pv_from_smem<VDT>(O, ldsm_base + vstage * kVTileSmem, b0, b1);
-            __syncwarp();                   // every lane is done with the stage before it is refilled
-            if (++vstage == kVStages) vstage = 0;
+            if constexpr (VQ != 0) {
+              pv_quant<VDT>(O, vq, b0, b1);
+              vq = nvq;
+            } else {
+              cp_async_wait<kVStages - 1>();  // this step's tile has landed; the newer ones may be in flight
+              __syncwarp();
+              pv_from_smem<VDT>(O, ldsm_base + vstage * kVTileSmem, b0, b1);
+              __syncwarp();                   // every lane is done with the stage before it is refilled
+              if (++vstage == kVStages) vstage = 0;
+            }
           }
 #ifndef PQ_CODES_INPLACE
           cg = ng; ch = nh;
@@ -654,6 +749,15 @@ decode_kernel(const DecodeArgs a) {
         ++grp;
       }
       cp_async_wait<0>();                 // the last (redundant) prefetch of the segment
+      if constexpr (VQ != 0) {
+        // back to true scale: undo the subnormal encoding of the levels and add the minimum term
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          O[j][0] = fmaf(O[j][0], 16777216.0f, O[8][0]); O[j][1] = fmaf(O[j][1], 16777216.0f, O[8][1]);
+          O[j][2] = fmaf(O[j][2], 1048576.0f, O[8][2]);  O[j][3] = fmaf(O[j][3], 1048576.0f, O[8][3]);
+        }
+        O[8][0] = O[8][1] = O[8][2] = O[8][3] = 0.f;
+      }
     }
 
     // ------------------------------ residual steps -------------------------------
@@ -678,7 +782,7 @@ decode_kernel(const DecodeArgs a) {
           }
           cp_async_wait<0>();
           __syncwarp();
-          load_v_tile_async(vst_addr, v_unit + static_cast<int64_t>(Lq + r0) * v_row, v_row, a.R - r0, lane);
+          load_v_tile_async(vst_addr, v_unit + static_cast<int64_t>(a.v_tok0 + r0) * v_row, v_row, a.R - r0, lane);
           cp_async_commit();
           float S[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -1041,21 +1145,28 @@ size_t workspace_bytes_for(const DecodeArgs& a) {
   return slots * (kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2));
 }
 
-template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY>
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ = 0>
 int launch_decode(const DecodeArgs& a, cudaStream_t s) {
   constexpr int kStageBytes = 4 * kPairs * (QDT == PQ_F32 ? 4 : 2);
-  constexpr int kWarpSmem = kPairs * (1 << TBITS) * 4 + 2 * kStageBytes + (QK_ONLY ? 0 : kVStages * kVTileSmem);
+  constexpr int kWarpSmem = kPairs * (1 << TBITS) * 4 + 2 * kStageBytes + v_stages(QK_ONLY, VQ) * kVTileSmem;
   constexpr int kSmem = kWarps * kWarpSmem;
   if (kSmem > 48 * 1024)
-    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY>,
+    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, kSmem, s>>>(a);
+  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, kSmem, s>>>(a);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
 
 template <int RBITS, int TBITS, bool QK_ONLY>
 int dispatch_dtypes(const DecodeArgs& a, int qdt, int vdt, cudaStream_t s) {
+  if constexpr (!QK_ONLY) {
+    if (a.vq_codes) {       // packed values: one instance per 16-bit dtype
+      if (qdt == PQ_F16 && vdt == PQ_F16) return launch_decode<RBITS, TBITS, PQ_F16, PQ_F16, false, 4>(a, s);
+      if (qdt == PQ_BF16 && vdt == PQ_BF16) return launch_decode<RBITS, TBITS, PQ_BF16, PQ_BF16, false, 4>(a, s);
+      return PQ_ERR_UNSUPPORTED;
+    }
+  }
 #define PQ_CASE(Q, V) if (qdt == Q && vdt == V) return launch_decode<RBITS, TBITS, Q, V, QK_ONLY>(a, s)
   if constexpr (QK_ONLY) {
     PQ_CASE(PQ_F16, PQ_F16); PQ_CASE(PQ_BF16, PQ_F16); PQ_CASE(PQ_F32, PQ_F16);
@@ -1119,14 +1230,24 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (p->hd != kHeadDim || p->G % kStep != 0) return PQ_ERR_UNSUPPORTED;
   if (p->B == 0) return PQ_OK;
   if (p->Nb == 0 && p->R == 0) return PQ_ERR_INVALID;          // softmax over nothing
-  if (!p->q || !p->v || !p->out) return PQ_ERR_INVALID;
+  const bool packed_v = p->vbits != 0 && p->Nb > 0;
+  if (p->vbits != 0 && p->vbits != 4) return PQ_ERR_UNSUPPORTED;
+  if (!p->q || !p->out || (!p->v && !(packed_v && p->R == 0))) return PQ_ERR_INVALID;
   if (p->Nb > 0 && (!p->codes || !p->rscale || !p->rmn || !p->tscale || !p->tmn)) return PQ_ERR_INVALID;
   if (p->R > 0 && !p->k_res) return PQ_ERR_INVALID;
   const int qes = static_cast<int>(dtype_bytes(p->qk_dtype));
   auto mis = [](const void* ptr, size_t al) { return reinterpret_cast<uintptr_t>(ptr) % al != 0; };
   // 128-bit loads: pointers 16-byte aligned, strides multiples of 16 bytes
-  if (mis(p->v, 16) || (p->v_stride_b * 2) % 16 || (p->v_stride_h * 2) % 16 || (p->v_stride_t * 2) % 16)
+  if (p->v && (mis(p->v, 16) || (p->v_stride_b * 2) % 16 || (p->v_stride_h * 2) % 16 || (p->v_stride_t * 2) % 16))
     return PQ_ERR_ALIGNMENT;
+  if (packed_v) {
+    if (!p->v_codes || !p->v_scale || !p->v_mn) return PQ_ERR_INVALID;
+    if (p->qk_dtype != p->v_dtype) return PQ_ERR_UNSUPPORTED;
+    // 8-byte code loads at 8-byte offsets within 64-byte rows; 4-byte loads of (scale, scale) token pairs
+    if (mis(p->v_codes, 16) || p->vcodes_stride_b % 16 || p->vcodes_stride_h % 16 || mis(p->v_scale, 4) ||
+        mis(p->v_mn, 4) || p->vscale_stride_b % 2 || p->vscale_stride_h % 2)
+      return PQ_ERR_ALIGNMENT;
+  }
   if (mis(p->q, 16) || (p->q_stride_b * qes) % 16 || (p->q_stride_h * qes) % 16) return PQ_ERR_ALIGNMENT;
   if (p->Nb > 0) {
     if (mis(p->codes, 16) || p->codes_stride_b % 16 || p->codes_stride_h % 16) return PQ_ERR_ALIGNMENT;
@@ -1145,6 +1266,11 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   a.s_sb = p->scale_stride_b; a.s_sh = p->scale_stride_h;
   a.kres = p->k_res; a.kr_sb = p->kres_stride_b; a.kr_sh = p->kres_stride_h; a.kr_st = p->kres_stride_t;
   a.v = p->v; a.v_sb = p->v_stride_b; a.v_sh = p->v_stride_h; a.v_st = p->v_stride_t;
+  a.v_tok0 = packed_v ? 0 : p->Nb * p->G;
+  if (packed_v) {
+    a.vq_codes = p->v_codes; a.vq_sb = p->vcodes_stride_b; a.vq_sh = p->vcodes_stride_h;
+    a.vq_scale = p->v_scale; a.vq_mn = p->v_mn; a.vs_sb = p->vscale_stride_b; a.vs_sh = p->vscale_stride_h;
+  }
   a.mask = p->mask; a.m_sb = p->mask_stride_b;
   a.B = p->B; a.N = p->N; a.Nk = p->Nk; a.Nb = p->Nb; a.G = p->G; a.R = p->R;
   plan(a, PQ_MIN_CTAS, p->num_ctas);

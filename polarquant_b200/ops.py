@@ -161,7 +161,7 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
                      value_states: torch.Tensor, attention_mask=None, rbits: int = 4, tbits: int = 4,
                      sm_scale: float | None = None, out_dtype: torch.dtype | None = None,
                      return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0,
-                     mid_event=None):
+                     mid_event=None, value_codes=None, value_scale=None, value_mn=None, vbits: int = 4):
     """One fused decode-attention step over the polar cache.
 
     Computes what the reference's decode branch computes with separate ops
@@ -176,11 +176,19 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     attention_mask (B, Nb*G + R), nonzero = attend.  Returns (B, N, 1, 128) in
     ``out_dtype`` (default: the query dtype) and, with ``return_lse``, the
     natural-log log-sum-exp (B, N) fp32.
+
+    Packed values (the decode branch of LlamaPolarMixedGroupAttention,
+    models/modeling_llama_polar.py:189-246): pass ``value_codes`` (B, Nk, Nb*G, 16) int32 in the TILED layout of
+    ``quantize_values`` with ``value_scale`` / ``value_mn`` (B, Nk, Nb*G, 1); ``value_states`` then holds only
+    the R full-precision values of the residual window (or is None when R == 0).
     """
-    dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask)
+    dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask, value_codes)
     bsz, nq, qlen, hd = query_states.shape
     if qlen != 1:
         raise ValueError("decode attention takes exactly one query position")
+    packed_v = value_codes is not None and value_codes.shape[2] > 0
+    if packed_v and value_states is None:
+        value_states = torch.empty((bsz, value_codes.shape[1], 0, hd), dtype=value_scale.dtype, device=dev)
     kvh = value_states.shape[1]
     qdt = _dtype_code(query_states, "decode_attention")
     vdt = _dtype_code(value_states, "decode_attention")
@@ -193,7 +201,10 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
         grp = 128
     res = 0 if key_residual is None else key_residual.shape[2]
     ctx = nb * grp + res
-    if value_states.shape[2] != ctx:
+    if packed_v:
+        if value_codes.shape[2] != nb * grp or value_states.shape[2] != res:
+            raise ValueError("packed values must cover exactly the packed keys, value_states the residual window")
+    elif value_states.shape[2] != ctx:
         raise ValueError(f"value_states holds {value_states.shape[2]} tokens, keys hold {ctx}")
 
     p = _lib.DecodeParams()
@@ -237,6 +248,21 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
         v = v.contiguous()
     p.v, p.v_stride_b, p.v_stride_h, p.v_stride_t = v.data_ptr(), v.stride(0), v.stride(1), v.stride(2)
     keep.append(v)
+    if packed_v:
+        if value_codes.dtype != torch.int32 or value_codes.shape[-1] != 16:
+            raise ValueError("value_codes must be (B, Nk, T, 16) int32")
+        vc = value_codes
+        if _unit_strides(vc, 1) is None or vc.data_ptr() % 16 or (vc.stride(0) * 4) % 16 or (vc.stride(1) * 4) % 16:
+            vc = vc.contiguous()
+        vs, vm = (x if x.dtype == v.dtype else x.to(v.dtype) for x in (value_scale, value_mn))
+        if _unit_strides(vs, 1) is None or _unit_strides(vm, 1) is None or vs.stride()[:2] != vm.stride()[:2] \
+                or vs.stride(0) % 2 or vs.stride(1) % 2 or vs.data_ptr() % 4 or vm.data_ptr() % 4:
+            vs, vm = vs.contiguous(), vm.contiguous()
+        p.v_codes, p.vcodes_stride_b, p.vcodes_stride_h = vc.data_ptr(), vc.stride(0) * 4, vc.stride(1) * 4
+        p.v_scale, p.v_mn = vs.data_ptr(), vm.data_ptr()
+        p.vscale_stride_b, p.vscale_stride_h = vs.stride(0), vs.stride(1)
+        p.vbits = vbits
+        keep += [vc, vs, vm]
     if attention_mask is not None:
         m = (attention_mask != 0).to(torch.uint8)
         if m.shape != (bsz, ctx):
@@ -282,3 +308,75 @@ def merge_lse(outs: torch.Tensor, lses: torch.Tensor, out_dtype: torch.dtype = t
                               lse.data_ptr() if return_lse else None, _stream(dev))
     _lib.check(rc, "pq_merge_lse")
     return (out, lse) if return_lse else out
+
+
+# ------------------------------------------------------------------------------------------------
+# packed value cache
+# ------------------------------------------------------------------------------------------------
+_LAYOUTS = {"kivi": _lib.PQ_VALUES_KIVI, "tiled": _lib.PQ_VALUES_TILED}
+
+
+def quantize_values(value_states: torch.Tensor, vbits: int = 4, layout: str = "kivi"):
+    """Per-token 4-bit min/max quantisation of values (B, Nk, T, 128), strided views allowed.
+
+    What ``triton_quantize_and_pack_along_last_dim(values, 128, 4)`` returns at
+    models/modeling_llama_polar.py:242,285 (a KIVI routine): codes (B, Nk, T, 16) int32 and scale, mn
+    (B, Nk, T, 1) in the value dtype.  ``layout="kivi"`` packs channel c at bits 4*(c%8) of word c//8;
+    ``layout="tiled"`` is the order the fused attention kernel reads (see ``decode_attention``).
+    """
+    if value_states.dim() != 4:
+        raise ValueError("value_states must be (batch, kv_heads, tokens, head_dim)")
+    bsz, heads, tokens, hd = value_states.shape
+    dev = _require_cuda(value_states)
+    dt = _dtype_code(value_states, "quantize_values")
+    if not _vec_ok(value_states, 8 if dt != _lib.PQ_F32 else 4):
+        value_states = value_states.contiguous()
+    codes = torch.empty((bsz, heads, tokens, hd * vbits // 32), dtype=torch.int32, device=dev)
+    scale = torch.empty((bsz, heads, tokens, 1), dtype=value_states.dtype, device=dev)
+    mn = torch.empty_like(scale)
+    strides = (ctypes.c_int64 * 4)(*value_states.stride())
+    lib = _lib.load()
+    with _on_device(dev):
+        rc = lib.pq_quantize_values(value_states.data_ptr(), strides, bsz, heads, tokens, hd, vbits, dt,
+                                    _LAYOUTS[layout], codes.data_ptr(), scale.data_ptr(), mn.data_ptr(), None,
+                                    _stream(dev))
+    _lib.check(rc, "pq_quantize_values")
+    return codes, scale, mn
+
+
+def values_relayout(codes: torch.Tensor, to_layout: str) -> torch.Tensor:
+    """Convert packed value codes (..., T, 16) int32 between the "kivi" and "tiled" layouts (new tensor)."""
+    dev = _require_cuda(codes)
+    if codes.dtype != torch.int32 or codes.shape[-1] != 16:
+        raise ValueError("codes must be (..., 16) int32")
+    codes = codes.contiguous()
+    out = torch.empty_like(codes)
+    lib = _lib.load()
+    with _on_device(dev):
+        rc = lib.pq_values_relayout(codes.data_ptr(), out.data_ptr(), codes.numel() // 16, _LAYOUTS[to_layout],
+                                    _stream(dev))
+    _lib.check(rc, "pq_values_relayout")
+    return out
+
+
+def values_matmul(probs: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor,
+                  vbits: int = 4) -> torch.Tensor:
+    """probs (B, H, M, T) times the dequantised values (B, H, T, 128) in the "kivi" layout -> (B, H, M, 128).
+
+    What ``cuda_bmm_fA_qB_outer(128, probs, codes, scale, mn, 4)`` computes at
+    models/modeling_llama_polar.py:230-237 (H = query heads there: the caller passes repeated kv tensors)."""
+    dev = _require_cuda(probs, codes, scale, mn)
+    dt = _dtype_code(probs, "values_matmul")
+    bsz, heads, m, tokens = probs.shape
+    if codes.shape[:3] != (bsz, heads, tokens) or codes.dtype != torch.int32:
+        raise ValueError("codes must be (B, H, T, 16) int32 matching probs (B, H, M, T)")
+    probs, codes = probs.contiguous(), codes.contiguous()
+    scale = scale.to(probs.dtype).contiguous()
+    mn = mn.to(probs.dtype).contiguous()
+    out = torch.empty((bsz, heads, m, 128), dtype=probs.dtype, device=dev)
+    lib = _lib.load()
+    with _on_device(dev):
+        rc = lib.pq_values_matmul(probs.data_ptr(), codes.data_ptr(), scale.data_ptr(), mn.data_ptr(),
+                                  out.data_ptr(), bsz * heads, m, tokens, 128, vbits, dt, _stream(dev))
+    _lib.check(rc, "pq_values_matmul")
+    return out

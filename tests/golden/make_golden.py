@@ -16,6 +16,12 @@ What is executed (nothing of the reference is copied, its files are imported in 
                  models/modeling_qwen_polar.py:60-100), unmodified, with identity projections
                  and an identity rotary embedding so its inputs are the fixture's tensors; its
                  kernel call is served by the Triton kernel above through the interpreter.
+  * mixed      - the decode branch of ``LlamaPolarMixedGroupAttention.forward``
+                 (models/modeling_llama_polar.py:189-246), unmodified, the same way.  Its two KIVI routines are
+                 not part of the reference checkout; the module globals ``cuda_bmm_fA_qB_outer`` and
+                 ``triton_quantize_and_pack_along_last_dim`` are bound to the restatement in
+                 oracle/polar_oracle.py, so these fixtures pin the reference's composition (which logits meet
+                 which values, the roundings at :225, :237, :239), not KIVI's arithmetic.
 """
 from __future__ import annotations
 
@@ -39,7 +45,12 @@ REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("POLARQUANT_REFERENCE
 DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 
+ONLY = os.environ.get("GOLDEN_ONLY")      # regenerate only the fixtures whose name starts with this
+
+
 def save(name, **arrays):
+    if ONLY and not name.startswith(ONLY):
+        return
     out = {}
     for k, v in arrays.items():
         out[k] = oracle.as_numpy(v) if torch.is_tensor(v) else np.asarray(v)
@@ -181,6 +192,63 @@ def main():
         save(tag, q=q, k_res=k_res, indices=idx, rscale=rs, rmn=rm, tscale=ts, tmn=tm, v=v_all,
              mask=(mask if mask is not None else np.zeros(0, dtype=np.float32)), out=attn_out,
              meta=np.array([4, 4, G]))
+
+    def run_forward_mixed(dn, B, N, Nk, Nb, R, with_mask, seed):
+        """One decode step through LlamaPolarMixedGroupAttention: packed keys and packed values for the first
+        Nb*128 tokens, R full-precision keys / values (incl. the new token) behind them."""
+        dt = DT[dn]
+        hd, G = 128, 128
+        hidden = (N + 2 * Nk) * hd
+        cfg = LlamaConfig(hidden_size=hidden, intermediate_size=64, num_hidden_layers=1,
+                          num_attention_heads=N, num_key_value_heads=Nk, vocab_size=32, head_dim=hd)
+        attn = llama.LlamaPolarMixedGroupAttention(cfg, layer_idx=0).to(dt).eval()
+        with torch.no_grad():
+            def select(lin, start, rows):
+                w = torch.zeros(rows, hidden)
+                w[torch.arange(rows), start + torch.arange(rows)] = 1.0
+                lin.weight.copy_(w.to(dt))
+            select(attn.q_proj, 0, N * hd)
+            select(attn.k_proj, N * hd, Nk * hd)
+            select(attn.v_proj, (N + Nk) * hd, Nk * hd)
+            w = torch.zeros(hidden, N * hd)
+            w[torch.arange(N * hd), torch.arange(N * hd)] = 1.0
+            attn.o_proj.weight.copy_(w.to(dt))
+        g = torch.Generator().manual_seed(seed)
+        q = torch.randn(B, N, 1, hd, generator=g).to(dt)
+        k_new = oracle.synth_keys(B, Nk, 1, hd, dt, seed=seed + 1)
+        v_q = (torch.randn(B, Nk, Nb * G, hd, generator=g) * (1.0 + torch.rand(B, Nk, Nb * G, 1, generator=g))).to(dt)
+        v_res = torch.randn(B, Nk, R, hd, generator=g).to(dt)          # incl. the new token's value (last row)
+        keys_q = oracle.synth_keys(B, Nk, Nb * G, hd, dt, seed=seed + 2)
+        k_res_old = oracle.synth_keys(B, Nk, R - 1, hd, dt, seed=seed + 3) if R > 1 else None
+        stub = types.SimpleNamespace(rbits=4, tbits=4, group_size=G)
+        idx, rs, rm, ts, tm = llama.LlamaPolarGroupAttention.quantize_and_pack_nbit(stub, keys_q)
+        vc, vs, vm = oracle.quantize_values(v_q, 4)
+        hidden_states = torch.cat([q.transpose(1, 2).reshape(B, 1, N * hd),
+                                   k_new.transpose(1, 2).reshape(B, 1, Nk * hd),
+                                   v_res[:, :, -1:, :].transpose(1, 2).reshape(B, 1, Nk * hd)], dim=-1)
+        cos = torch.ones(B, 1, hd, dtype=dt)
+        sin = torch.zeros(B, 1, hd, dtype=dt)
+        v_res_old = v_res[:, :, :-1, :] if R > 1 else None
+        past = (k_res_old, idx, rs, rm, ts, tm, v_res_old, vc, vs, vm, Nb * G + R - 1)
+        mask = None
+        if with_mask:
+            mask = torch.ones(B, Nb * G + R, dtype=torch.float32)
+            mask[0, :37] = 0.0
+        with torch.no_grad():
+            out, new_past = attn(hidden_states, attention_mask=mask, past_key_value=past,
+                                 position_embeddings=(cos, sin))
+        attn_out = out[:, 0, : N * hd].reshape(B, N, hd)[:, :, None, :]
+        k_res = k_new if k_res_old is None else torch.cat([k_res_old, k_new], dim=2)
+        tag = f"attn_mixed_{dn}_n{N}k{Nk}_nb{Nb}_r{R}" + ("_mask" if with_mask else "")
+        save(tag, q=q, k_res=k_res, indices=idx, rscale=rs, rmn=rm, tscale=ts, tmn=tm, v_codes=vc, v_scale=vs,
+             v_mn=vm, v_res=v_res, mask=(mask if mask is not None else np.zeros(0, dtype=np.float32)),
+             out=attn_out, meta=np.array([4, 4, G, 4]))
+
+    llama.cuda_bmm_fA_qB_outer = lambda group, fA, qB, scales, zeros, bits: oracle.values_matmul(fA, qB, scales, zeros, bits)
+    llama.triton_quantize_and_pack_along_last_dim = lambda data, group, bit: oracle.quantize_values(data, bit)
+    run_forward_mixed("bf16", 2, 8, 2, 2, 37, False, 4500)
+    run_forward_mixed("fp16", 1, 4, 4, 1, 1, False, 4510)
+    run_forward_mixed("bf16", 2, 4, 2, 2, 100, True, 4520)
 
     run_forward("llama", "bf16", 2, 8, 2, 2, 37, False, 4400)
     run_forward("llama", "fp16", 1, 4, 4, 1, 1, False, 4410)

@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_mirror_and_status_strings():
     from polarquant_b200 import _lib
     lib = _lib.load()
-    assert lib.pq_abi_version() == 1
+    assert lib.pq_abi_version() == 2
     assert lib.pq_decode_params_size() == ctypes.sizeof(_lib.DecodeParams)
     for code in (0, -1, -2, -3, -4, -5):
         assert lib.pq_strerror(code)
@@ -58,6 +58,20 @@ def test_argument_validation_needs_no_gpu():
     p.tbits = 4
     p.v_dtype = _lib.PQ_F32
     assert lib.pq_decode_attention(ctypes.byref(p), None) == -2           # fp32 values are not built
+    p.v_dtype = _lib.PQ_BF16
+    p.vbits = 2
+    assert lib.pq_decode_attention(ctypes.byref(p), None) == -2           # only 4-bit packed values are built
+    # packed value cache
+    vst = (ctypes.c_int64 * 4)(128 * 64, 128 * 64, 128, 1)
+    assert lib.pq_quantize_values(None, vst, 1, 1, 64, 128, 4, _lib.PQ_BF16, 7, None, None, None, None, None) == -1
+    assert lib.pq_quantize_values(None, vst, 1, 1, 64, 128, 2, _lib.PQ_BF16, 0, None, None, None, None, None) == -2
+    assert lib.pq_quantize_values(None, vst, 1, 1, 64, 64, 4, _lib.PQ_BF16, 0, None, None, None, None, None) == -2
+    assert lib.pq_quantize_values(None, vst, 1, 1, 0, 128, 4, _lib.PQ_BF16, 0, None, None, None, None, None) == 0
+    assert lib.pq_quantize_values(None, vst, 1, 1, 64, 128, 4, _lib.PQ_BF16, 0, None, None, None, None, None) == -1
+    assert lib.pq_values_relayout(None, None, 0, 1, None) == 0
+    assert lib.pq_values_relayout(None, None, 5, 1, None) == -1
+    assert lib.pq_values_matmul(None, None, None, None, None, 0, 1, 10, 128, 4, 0, None) == 0
+    assert lib.pq_values_matmul(None, None, None, None, None, 2, 1, 10, 128, 8, 0, None) == -2
     assert lib.pq_decode_workspace_bytes(16, 32, 8, 255, 128, 128, 0) > 0
     assert lib.pq_decode_workspace_bytes(16, 32, 6, 255, 128, 128, 0) == 0
 

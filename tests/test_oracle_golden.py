@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from conftest import ATTN_MAX_ABS, ATTN_MEAN_ABS, golden_names, load_golden
+from conftest import ATTN_MAX_ABS, ATTN_MEAN_ABS, check_mixed, golden_names, load_golden
 from oracle import polar_oracle as oracle
 
 
@@ -62,7 +62,7 @@ def test_qk_logits_match_reference_kernel(name):
         assert float((got - g["logits"]).abs().max()) <= 2e-5 * max(1.0, scale), fn.__name__
 
 
-@pytest.mark.parametrize("name", golden_names("attn_"))
+@pytest.mark.parametrize("name", golden_names("attn_", exclude="attn_mixed_"))
 def test_decode_attention_matches_reference_forward(name):
     g = load_golden(name)
     rb, tb, _ = g["meta"]
@@ -76,6 +76,60 @@ def test_decode_attention_matches_reference_forward(name):
                                     g["v"], attention_mask=mask, rbits=rb, tbits=tb, faithful_rounding=False)
     diff = (exact - g["out"].float()).abs()
     assert float(diff.max()) <= ATTN_MAX_ABS and float(diff.mean()) <= ATTN_MEAN_ABS
+
+
+@pytest.mark.parametrize("name", golden_names("attn_mixed_"))
+def test_mixed_decode_attention_matches_reference_forward(name):
+    """The reference's LlamaPolarMixedGroupAttention forward (its KIVI calls served by the oracle's restatement)
+    against the oracle's own composition of packed keys + packed values + residual window."""
+    g = load_golden(name)
+    rb, tb, _, vb = g["meta"]
+    mask = g["mask"] if g["mask"].numel() else None
+    args = (g["q"], g["k_res"], g["indices"], g["rscale"], g["rmn"], g["tscale"], g["tmn"], g["v_codes"],
+            g["v_scale"], g["v_mn"], g["v_res"])
+    got = oracle.decode_attention_mixed(*args, attention_mask=mask, rbits=rb, tbits=tb, vbits=vb)
+    diff = (got.float() - g["out"].float()).abs()
+    assert float(diff.max()) <= 8e-3 and float(diff.mean()) <= 4e-4, (float(diff.max()), float(diff.mean()))
+    exact = oracle.decode_attention_mixed(*args, attention_mask=mask, rbits=rb, tbits=tb, vbits=vb,
+                                          faithful_rounding=False)
+    check_mixed(exact, g["out"], name)
+    # the tiled layout holds the same levels
+    tiled = oracle.kivi_to_tiled(g["v_codes"])
+    assert torch.equal(oracle.tiled_to_kivi(tiled), g["v_codes"])
+    again = oracle.decode_attention_mixed(*args[:7], tiled, *args[8:], attention_mask=mask, rbits=rb, tbits=tb,
+                                          vbits=vb, faithful_rounding=False, layout="tiled")
+    assert torch.equal(again, exact)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_value_quantiser_properties(dtype):
+    torch.manual_seed(7)
+    v = (torch.randn(2, 3, 50, 128) * (0.2 + 3 * torch.rand(2, 3, 50, 1))).to(dtype)
+    v[0, 0, 3] = 1.5                                    # constant token: 0 / 0 -> level 0, exact reconstruction
+    v[1, 2, 7, 5] = 40.0                                # outlier stretches one token's scale
+    codes, scale, mn = oracle.quantize_values(v)
+    assert codes.shape == (2, 3, 50, 16) and codes.dtype == torch.int32 and scale.shape == (2, 3, 50, 1)
+    levels = oracle.unpack_values(codes)
+    assert int(levels.min()) >= 0 and int(levels.max()) <= 15
+    assert torch.equal(levels[0, 0, 3], torch.zeros(128, dtype=torch.int32)) and float(scale[0, 0, 3]) == 0.0
+    back = oracle.dequantize_values(codes, scale, mn)
+    assert torch.equal(back[0, 0, 3], torch.full((128,), 1.5))
+    # every channel within (a little over, for the 16-bit roundings) half a step of its value
+    err = (back - v.float()).abs()
+    slack = 0.5 if dtype == torch.float32 else 0.65
+    assert bool((err <= slack * scale.float() + 1e-6).all())
+    # the minimum maps to level 0 and the maximum to level 15
+    am, ax = v.float().argmin(-1, keepdim=True), v.float().argmax(-1, keepdim=True)
+    nz = scale.float()[..., 0] > 0
+    assert bool((levels.gather(-1, am)[..., 0][nz] == 0).all()) and bool((levels.gather(-1, ax)[..., 0][nz] == 15).all())
+    # the two scale formulas differ only in the last place of the scale
+    _, s_true, _ = oracle.quantize_values(v, scalar_division="true")
+    assert float(((s_true.float() - scale.float()).abs() / scale.float().clamp_min(1e-30)).max()) <= 2.0 ** -7
+    # product with probabilities
+    p = torch.softmax(torch.randn(2, 3, 1, 50), -1).to(dtype)
+    ref = torch.matmul(p.float(), back)
+    got = oracle.values_matmul(p, codes, scale, mn)
+    assert float((got.float() - ref).abs().max()) <= 2e-2
 
 
 def test_merge_lse_recombines_a_split_sequence():
