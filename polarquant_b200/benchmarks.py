@@ -3,6 +3,7 @@
     python -m polarquant_b200.benchmarks qk        # the reference's QK micro-benchmark grid
     python -m polarquant_b200.benchmarks sweep     # fused decode attention over bit widths / group sizes / shapes
     python -m polarquant_b200.benchmarks quant     # quantizer at prefill sizes
+    python -m polarquant_b200.benchmarks values    # packed (4-bit) value cache: fused attention and value quantiser
     torchrun --nproc-per-node N -m polarquant_b200.benchmarks longctx   # 128k-context step sharded over N GPUs
 
 `qk` reproduces the grid of the reference's benchmark/benchmark_matmul.py (`test4polar`, lines 89-120: 32 heads on
@@ -111,6 +112,43 @@ def quant_sizes():
         del base, keys
 
 
+def packed_values():
+    """Fused decode attention with packed keys AND packed 4-bit values (the mixed class of the reference,
+    models/modeling_llama_polar.py:160-292) beside the same step with full-precision values, and the value
+    quantiser at the prefill size.  Bytes are the algorithmic ones of each variant."""
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1006)
+    shapes = [("llama3-8b B16 ctx32k", 16, 32, 8, 32768), ("qwen2.5-7b B64 ctx8k", 64, 28, 4, 8192),
+              ("70b-shaped 1 kv head/GPU B8 ctx128k", 8, 8, 1, 131072)]
+    for name, B, N, Nk, ctx in shapes:
+        G, R = 128, 128
+        Nb = (ctx - R) // G
+        q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, Nk, ctx, 128, device=dev, generator=g).to(torch.bfloat16)
+        kres = torch.randn(B, Nk, R, 128, device=dev, generator=g).to(torch.bfloat16)
+        keys = torch.randn(B, Nk, Nb * G, 128, device=dev, generator=g).to(torch.bfloat16)
+        packed = ops.quantize_and_pack_nbit(keys, 4, 4, G)
+        del keys
+        vq = v[:, :, :Nb * G]
+        us_q = _time_us(lambda: ops.quantize_values(vq, layout="tiled"), reps=10)
+        vc, vs, vm = ops.quantize_values(vq, layout="tiled")
+        v_res = v[:, :, Nb * G:].contiguous()
+        qbytes = vq.numel() * 2 + vc.numel() * 4 + 2 * vs.numel() * 2
+        print(json.dumps({"bench": "quantize_values", "shape": name, "us": us_q, "mb": qbytes / 1e6,
+                          "gbs": qbytes / us_q / 1e3}))
+        us_full = _time_us(lambda: ops.decode_attention(q, kres, *packed, v), reps=20)
+        us_pack = _time_us(lambda: ops.decode_attention(q, kres, *packed, v_res, value_codes=vc, value_scale=vs,
+                                                        value_mn=vm), reps=20)
+        kbytes = packed[0].numel() + 4 * packed[1].numel() * 2 + kres.numel() * 2 + q.numel() * 4
+        full_b = kbytes + v.numel() * 2
+        pack_b = kbytes + vc.numel() * 4 + 2 * vs.numel() * 2 + v_res.numel() * 2
+        print(json.dumps({"bench": "decode_packed_values", "shape": name, "us_full_values": us_full,
+                          "us_packed_values": us_pack, "speedup": us_full / us_pack, "mb_full": full_b / 1e6,
+                          "mb_packed": pack_b / 1e6, "gbs_full": full_b / us_full / 1e3,
+                          "gbs_packed": pack_b / us_pack / 1e3}))
+        del packed, v, vc, vs, vm
+
+
 def long_context():
     """70B-shaped long-context decode attention over the GPUs of one node (launch with torchrun):
     64 q / 8 kv heads, batch 8, context 131072, polar 4/4, group 128.  Two shardings of the same step:
@@ -214,4 +252,5 @@ def long_context():
 
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "sweep"
-    {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes, "longctx": long_context}[what]()
+    {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes, "values": packed_values,
+     "longctx": long_context}[what]()

@@ -215,9 +215,14 @@ __device__ __forceinline__ uint32_t hmul2_hi(uint32_t cs, uint32_t rr) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+#ifdef PQ_LDS_NOVOL
+#define PQ_LDS_ASM asm
+#else
+#define PQ_LDS_ASM asm volatile
+#endif
 template <int IMM> __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+  PQ_LDS_ASM("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
   return v;
 }
 
@@ -678,6 +683,11 @@ decode_kernel(const DecodeArgs a) {
         prev_run = run_end - s;
         if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
         build_angle_table<TBITS, QDT>(tbl_addr, s_sc_w + buf * kStageBytes, lane);
+        uint32_t tbl_run = tbl_addr;
+#ifdef PQ_LDS_NOVOL
+        // the gathers are plain (movable) asm: tie them to this build of the table
+        asm volatile("" : "+r"(tbl_run) :: "memory");
+#endif
         load_radius_consts<RBITS, QDT>(s_sc_w + buf * kStageBytes, t, rs2, rc2);
         buf ^= 1;
 #pragma unroll 1
@@ -709,7 +719,7 @@ decode_kernel(const DecodeArgs a) {
           }
 
           float S[4] = {0.f, 0.f, 0.f, 0.f};
-          qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_addr, lane_xor, rs2, rc2, qb);
+          qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_run, lane_xor, rs2, rc2, qb);
 #ifdef PQ_CODES_INPLACE
           // the code registers are free again: refill them for the next step (its lines are in L2 already)
           cg = ldg_stream(c_lane); ch = ldg_stream(c_lane + 8 * kPairs);
