@@ -75,6 +75,17 @@ int pq_quantize_into(const void* keys, const int64_t strides[4], int B, int Nk, 
 int pq_cache_append(const void* k_new, const void* v_new, const int64_t in_strides[4], void* k_res,
                     const int64_t kres_strides[3], void* values, const int64_t v_strides[3], int B, int Nk, int hd,
                     int res_pos, int ctx_pos, int dtype, void* stream);
+/*
+ * The same with the positions read on the device from lengths = {token groups, residual tokens} (see
+ * pq_decode_params.dyn_lengths): key slot lengths[1]; value slot lengths[1] when `values` is only the residual
+ * window (values_window != 0, packed-value caches), else lengths[0] * G + lengths[1].  Slots at or beyond res_cap /
+ * value_cap tokens are not written.  The lengths are not modified: advance lengths[1] once per step, after the
+ * attention calls of all layers that share the array.
+ */
+int pq_cache_append_dyn(const void* k_new, const void* v_new, const int64_t in_strides[4], void* k_res,
+                        const int64_t kres_strides[3], void* values, const int64_t v_strides[3], int B, int Nk,
+                        int hd, int G, const int* lengths, int values_window, int res_cap, int value_cap, int dtype,
+                        void* stream);
 
 /*
  * Self-test of the quantizer's fast paths (no reference counterpart).  The kernel replaces atan2f, sqrtf and the
@@ -161,6 +172,13 @@ typedef struct pq_decode_params {
   const void* v_mn;
   int64_t vscale_stride_b, vscale_stride_h;
   int vbits;
+  /* Optional device-side lengths, for replaying one captured CUDA graph over a growing cache: a device pointer
+     to two ints {token groups, residual tokens}.  When set, the kernels use dyn_lengths[0] and
+     dyn_lengths[1] + dyn_r_add instead of Nb and R and partition the work themselves; Nb and R then state the
+     CAPACITY of the buffers (lengths beyond them are clamped), the workspace must hold
+     pq_decode_workspace_bytes_dyn() bytes, and qk_dtype == v_dtype (fp16 or bf16). */
+  const int* dyn_lengths;
+  int dyn_r_add;
 } pq_decode_params;
 
 int pq_decode_attention(const pq_decode_params* p, void* stream);
@@ -169,6 +187,8 @@ size_t pq_decode_params_size(void);
 
 /* Scratch bytes pq_decode_attention needs for this problem on the current device. */
 size_t pq_decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int num_ctas);
+/* Scratch bytes that suffice for every length when dyn_lengths is used. */
+size_t pq_decode_workspace_bytes_dyn(int B, int N, int Nk, int num_ctas);
 
 /*
  * pq_decode_attention for callers that cannot provide scratch memory or call an allocator

@@ -415,7 +415,7 @@ def decode_attention_mixed(query, key_residual, codes, rscale, rmn, tscale, tmn,
     lse = torch.logsumexp(w, dim=-1)[:, :, 0]
     p = torch.softmax(w, dim=-1)
     tq = 0 if v_codes is None else v_codes.shape[2]
-    out = torch.zeros((bsz, nq, 1, hd), dtype=torch.float32)
+    out = torch.zeros((bsz, nq, 1, hd), dtype=torch.float32, device=query.device)
     if faithful_rounding:
         p = p.to(qdt)
     if tq:

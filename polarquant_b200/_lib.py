@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "pq_event_create", "pq_event_destroy", "pq_event_record", "pq_event_elapsed_ms",
     "pq_decode_attention_static", "pq_decode_static_scratch_bytes", "pq_selftest_quantizer", "pq_quantize_into", "pq_cache_append",
     "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
+    "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -54,6 +55,7 @@ class DecodeParams(ctypes.Structure):
         ("v_codes", _vp), ("vcodes_stride_b", _i64), ("vcodes_stride_h", _i64),
         ("v_scale", _vp), ("v_mn", _vp), ("vscale_stride_b", _i64), ("vscale_stride_h", _i64),
         ("vbits", _int),
+        ("dyn_lengths", _vp), ("dyn_r_add", _int),
     ]
 
 
@@ -76,6 +78,11 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_values_relayout.argtypes = [_vp, _vp, _i64, _int, _vp]
     lib.pq_values_matmul.restype = _int
     lib.pq_values_matmul.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _int, _vp]
+    lib.pq_cache_append_dyn.restype = _int
+    lib.pq_cache_append_dyn.argtypes = [_vp, _vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _vp,
+                                        ctypes.POINTER(_i64), _int, _int, _int, _int, _vp, _int, _int, _int, _int, _vp]
+    lib.pq_decode_workspace_bytes_dyn.restype = _sz
+    lib.pq_decode_workspace_bytes_dyn.argtypes = [_int] * 4
     lib.pq_qk_decode.restype = _int
     lib.pq_qk_decode.argtypes = [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
                                  _int, _int, _int, _int, _int, _int, _int, _int, _int, _vp]
@@ -129,7 +136,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 2:
+        if lib.pq_abi_version() != 3:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

@@ -11,6 +11,21 @@ in full precision, including the current token, and only afterwards the window i
 Cache layout (what the reference's 8-tuple holds, with capacity):
     codes   (B, Nk, max_groups, G, 64) uint8        rscale/rmn/tscale/tmn (B, Nk, max_groups, 1, 64)
     k_res   (B, Nk, residual_length, 128)           values (B, Nk, max_tokens, 128)
+
+With ``vbits=4`` the values are packed too, as in the reference's LlamaPolarMixedGroupAttention
+(models/modeling_llama_polar.py:160-292): the values of the quantised tokens live as 4-bit codes with a scale and a
+minimum per token, the values of the residual window in full precision, and both windows are quantised together
+when the window fills (:240-248):
+    v_codes (B, Nk, max_tokens, 16) int32, tiled layout     v_scale / v_mn (B, Nk, max_tokens, 1)
+    v_res   (B, Nk, residual_length, 128)
+136 bytes per token and kv head instead of 324.
+
+CUDA-graph replay.  With ``lengths`` (an int32 device tensor ``[token groups, residual tokens]``, shared by the
+caches of all layers) ``decode_step_graph`` enqueues the append and the attention with the lengths read on the
+device, and changes nothing on the host: one captured graph of the whole model step is replayed for every token.
+The owner of the tensor advances ``lengths[1]`` once per step inside the graph (after the last layer) and calls
+``after_replay()`` on every cache afterwards, which mirrors the step on the host and, every ``residual_length``
+steps, quantises the full window outside the graph.
 """
 from __future__ import annotations
 
@@ -24,11 +39,14 @@ from . import _lib, ops
 class PolarKVCache:
     def __init__(self, batch: int, kv_heads: int, max_tokens: int, dtype=torch.bfloat16, device="cuda",
                  rbits: int = 4, tbits: int = 4, group_size: int = 128, residual_length: int = 128,
-                 head_dim: int = 128):
+                 head_dim: int = 128, vbits: int = 0, lengths: torch.Tensor | None = None):
         if residual_length % group_size:
             raise ValueError("residual_length must be a multiple of group_size")
         if head_dim != 128:
             raise NotImplementedError("head_dim must be 128")
+        if vbits not in (0, 4):
+            raise NotImplementedError("values are kept in full precision (vbits=0) or packed to 4 bits")
+        self.vbits = vbits
         self.B, self.Nk, self.G, self.RL = batch, kv_heads, group_size, residual_length
         self.rbits, self.tbits, self.dtype = rbits, tbits, dtype
         self.max_groups = max_tokens // group_size
@@ -38,11 +56,24 @@ class PolarKVCache:
         self.scales = [torch.empty((batch, kv_heads, self.max_groups, 1, 64), dtype=dtype, device=dev)
                        for _ in range(4)]                     # rscale, rmn, tscale, tmn
         self.k_res = torch.empty((batch, kv_heads, residual_length, head_dim), dtype=dtype, device=dev)
-        self.values = torch.empty((batch, kv_heads, max_tokens, head_dim), dtype=dtype, device=dev)
+        if vbits:
+            cap = max(self.max_groups * group_size, group_size)      # packed tokens come in whole groups
+            self.v_codes = torch.empty((batch, kv_heads, cap, 16), dtype=torch.int32, device=dev)
+            self.v_scale = torch.empty((batch, kv_heads, cap, 1), dtype=dtype, device=dev)
+            self.v_mn = torch.empty((batch, kv_heads, cap, 1), dtype=dtype, device=dev)
+            self.values = torch.empty((batch, kv_heads, residual_length, head_dim), dtype=dtype, device=dev)
+        else:
+            self.values = torch.empty((batch, kv_heads, max_tokens, head_dim), dtype=dtype, device=dev)
         self.num_groups = 0        # quantised token groups
         self.res_len = 0           # full-precision keys in the window
         need = _lib.load().pq_decode_workspace_bytes(batch, kv_heads * 8, kv_heads, self.max_groups, group_size,
                                                      residual_length, 0)
+        self.lengths = lengths
+        if lengths is not None:
+            if lengths.dtype != torch.int32 or lengths.numel() != 2 or not lengths.is_cuda or \
+                    (dev.index is not None and lengths.device.index != dev.index):
+                raise ValueError("lengths must be an int32 tensor of two elements on the cache's device")
+            need = max(need, _lib.load().pq_decode_workspace_bytes_dyn(batch, kv_heads * 16, kv_heads, 0))
         self.workspace = torch.empty(max(need, 1 << 20) + 256, dtype=torch.uint8, device=dev)
         # everything that does not change from step to step is marshalled once
         self._dev = dev
@@ -59,6 +90,12 @@ class PolarKVCache:
         p.B, p.Nk, p.G, p.hd = batch, kv_heads, group_size, head_dim
         p.rbits, p.tbits = rbits, tbits
         p.qk_dtype = p.v_dtype = self._dt
+        if vbits:
+            p.v_codes = self.v_codes.data_ptr()
+            p.vcodes_stride_b, p.vcodes_stride_h = self.v_codes.stride(0) * 4, self.v_codes.stride(1) * 4
+            p.v_scale, p.v_mn = self.v_scale.data_ptr(), self.v_mn.data_ptr()
+            p.vscale_stride_b, p.vscale_stride_h = self.v_scale.stride(0), self.v_scale.stride(1)
+            p.vbits = vbits
         self._params = p
         self._kres_strides = (ctypes.c_int64 * 3)(self.k_res.stride(0), self.k_res.stride(1), self.k_res.stride(2))
         self._v_strides = (ctypes.c_int64 * 3)(self.values.stride(0), self.values.stride(1), self.values.stride(2))
@@ -92,6 +129,28 @@ class PolarKVCache:
                                       out_strides, ops._stream(dev))
         _lib.check(rc, "pq_quantize_into")
 
+    def _quantize_values_into(self, values: torch.Tensor, first_token: int) -> None:
+        """Pack ``values`` (B, Nk, n, 128; unit inner stride) into tokens [first_token, first_token + n) of the
+        packed value buffers (models/modeling_llama_polar.py:242,285)."""
+        n = values.shape[2]
+        if n == 0:
+            return
+        if not ops._vec_ok(values, 8):
+            values = values.contiguous()
+        lib = _lib.load()
+        in_strides = (ctypes.c_int64 * 4)(*values.stride())
+        out_strides = (ctypes.c_int64 * 4)(self.v_codes.stride(0) * 4, self.v_codes.stride(1) * 4,
+                                           self.v_scale.stride(0), self.v_scale.stride(1))
+        es = self.v_scale.element_size()
+        with ops._on_device(values.device):
+            rc = lib.pq_quantize_values(values.data_ptr(), in_strides, self.B, self.Nk, n, 128, self.vbits,
+                                        ops._DT[values.dtype], _lib.PQ_VALUES_TILED,
+                                        self.v_codes.data_ptr() + first_token * 64,
+                                        self.v_scale.data_ptr() + first_token * es,
+                                        self.v_mn.data_ptr() + first_token * es, out_strides,
+                                        ops._stream(values.device))
+        _lib.check(rc, "pq_quantize_values")
+
     def prefill(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
         """Store a prompt: keys/values (B, Nk, L, 128), strided views allowed (the (B, L, Nk, hd) layout the
         projections produce).  The first L - L % residual_length keys are quantised, the rest stay in full
@@ -107,7 +166,12 @@ class PolarKVCache:
         self.res_len = rest
         if rest:
             self.k_res[:, :, :rest].copy_(key_states[:, :, nq:])
-        self.values[:, :, :length].copy_(value_states)
+        if self.vbits:
+            self._quantize_values_into(value_states[:, :, :nq].to(self.dtype), 0)
+            if rest:
+                self.values[:, :, :rest].copy_(value_states[:, :, nq:])
+        else:
+            self.values[:, :, :length].copy_(value_states)
 
     def decode_step(self, query_states: torch.Tensor, key_new: torch.Tensor, value_new: torch.Tensor,
                     attention_mask=None, sm_scale=None, out_dtype=None) -> torch.Tensor:
@@ -129,7 +193,7 @@ class PolarKVCache:
         with ops._on_device(dev):
             rc = lib.pq_cache_append(key_new.data_ptr(), value_new.data_ptr(), in_strides, self.k_res.data_ptr(),
                                      self._kres_strides, self.values.data_ptr(), self._v_strides, self.B, self.Nk,
-                                     128, self.res_len, pos, self._dt, stream)
+                                     128, self.res_len, self.res_len if self.vbits else pos, self._dt, stream)
             _lib.check(rc, "pq_cache_append")
             self.res_len += 1
             bsz, nq, _, hd = query_states.shape
@@ -147,27 +211,88 @@ class PolarKVCache:
             rc = lib.pq_decode_attention(ctypes.byref(p), stream)
         _lib.check(rc, "pq_decode_attention")
         if self.res_len == self.RL:                      # window full: quantise it in place (:83-92)
-            self._quantize_into(self.k_res, self.num_groups)
-            self.num_groups += self.RL // self.G
-            self.res_len = 0
+            self._requantize_window()
         return out
+
+    # ------------------------------------------------------------------ CUDA-graph replay
+    def decode_step_graph(self, query_states: torch.Tensor, key_new: torch.Tensor, value_new: torch.Tensor,
+                          out: torch.Tensor | None = None) -> torch.Tensor:
+        """``decode_step`` with every length read on the device from ``self.lengths``: safe to capture in a CUDA
+        graph and to replay as the cache grows.  Tensors must already have the cache dtype and unit inner
+        strides; their addresses are what a captured graph will reuse.  Host state is not touched - call
+        ``after_replay()`` once per executed step."""
+        if self.lengths is None:
+            raise RuntimeError("this cache was built without a device-side lengths tensor")
+        lib = _lib.load()
+        dev = self._dev
+        stream = ops._stream(dev)
+        in_strides = (ctypes.c_int64 * 4)(key_new.stride(0), key_new.stride(1), value_new.stride(0),
+                                          value_new.stride(1))
+        bsz, nq, _, hd = query_states.shape
+        q = query_states.reshape(bsz, nq, hd)
+        if not ops._vec_ok(q, 8) or query_states.dtype != self.dtype or key_new.dtype != self.dtype \
+                or value_new.dtype != self.dtype or key_new.stride(-1) != 1 or value_new.stride(-1) != 1:
+            raise ValueError("decode_step_graph needs cache-dtype tensors with unit inner stride and aligned rows")
+        if out is None:
+            out = torch.empty((bsz, nq, 1, hd), dtype=self.dtype, device=dev)
+        with ops._on_device(dev):
+            rc = lib.pq_cache_append_dyn(key_new.data_ptr(), value_new.data_ptr(), in_strides, self.k_res.data_ptr(),
+                                         self._kres_strides, self.values.data_ptr(), self._v_strides, self.B,
+                                         self.Nk, 128, self.G, self.lengths.data_ptr(), 1 if self.vbits else 0,
+                                         self.RL, self.values.shape[2], self._dt, stream)
+            _lib.check(rc, "pq_cache_append_dyn")
+            p = _lib.DecodeParams()
+            ctypes.memmove(ctypes.byref(p), ctypes.byref(self._params), ctypes.sizeof(p))
+            p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+            p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+            p.N, p.Nb, p.R = nq, self.max_groups, self.RL             # capacities; the lengths come from the device
+            p.out_dtype = self._dt
+            p.dyn_lengths, p.dyn_r_add = self.lengths.data_ptr(), 1   # the appended token is not counted yet
+            rc = lib.pq_decode_attention(ctypes.byref(p), stream)
+        _lib.check(rc, "pq_decode_attention")
+        return out
+
+    def after_replay(self) -> bool:
+        """Mirror one executed ``decode_step_graph`` on the host; quantise the window when it has filled (outside
+        the graph).  Returns True when it did, i.e. when the caller must store the new lengths
+        (``num_groups``, 0) into the shared tensor (``sync_lengths`` does that)."""
+        self.res_len += 1
+        if self.res_len == self.RL:
+            self._requantize_window()
+            return True
+        return False
+
+    def sync_lengths(self) -> None:
+        """Write this cache's host-side lengths into the device tensor (after prefill, after a re-quantisation)."""
+        self.lengths.copy_(torch.tensor([self.num_groups, self.res_len], dtype=torch.int32), non_blocking=False)
+
+    def _requantize_window(self) -> None:
+        if self.vbits:                                   # values of the window first: they sit at the same tokens
+            self._quantize_values_into(self.values, self.num_groups * self.G)
+        self._quantize_into(self.k_res, self.num_groups)
+        self.num_groups += self.RL // self.G
+        self.res_len = 0
 
     def _decode_step_general(self, query_states, key_new, value_new, attention_mask, sm_scale, out_dtype):
         """Same step through the general tensor-level entry points (masks, dtype conversions, odd strides)."""
         pos = self.seq_len
         self.k_res[:, :, self.res_len:self.res_len + 1].copy_(key_new)
-        self.values[:, :, pos:pos + 1].copy_(value_new)
+        vpos = self.res_len if self.vbits else pos
+        self.values[:, :, vpos:vpos + 1].copy_(value_new)
         self.res_len += 1
         ng = self.num_groups
         packed = (self.codes[:, :, :ng], *(s[:, :, :ng] for s in self.scales)) if ng else (None,) * 5
+        kw = {}
+        if self.vbits and ng:
+            nq = ng * self.G
+            kw = dict(value_codes=self.v_codes[:, :, :nq], value_scale=self.v_scale[:, :, :nq],
+                      value_mn=self.v_mn[:, :, :nq], vbits=self.vbits)
         out = ops.decode_attention(query_states, self.k_res[:, :, :self.res_len], *packed,
-                                   self.values[:, :, :pos + 1], attention_mask=attention_mask, rbits=self.rbits,
+                                   self.values[:, :, :vpos + 1], attention_mask=attention_mask, rbits=self.rbits,
                                    tbits=self.tbits, sm_scale=sm_scale, out_dtype=out_dtype,
-                                   workspace=self.workspace)
+                                   workspace=self.workspace, **kw)
         if self.res_len == self.RL:
-            self._quantize_into(self.k_res, ng)
-            self.num_groups += self.RL // self.G
-            self.res_len = 0
+            self._requantize_window()
         return out
 
     def as_reference_tuple(self):
@@ -175,4 +300,13 @@ class PolarKVCache:
         ng = self.num_groups
         packed = (self.codes[:, :, :ng], *(s[:, :, :ng] for s in self.scales)) if ng else (None,) * 5
         k_full = self.k_res[:, :, :self.res_len] if self.res_len else None
+        if self.vbits:
+            # the mixed class's 11-tuple (models/modeling_llama_polar.py:190,246); its value codes are in the
+            # kivi layout, so this one member is a converted copy
+            nq = ng * self.G
+            v_full = self.values[:, :, :self.res_len] if self.res_len else None
+            if not nq:
+                return (k_full, *packed, v_full, None, None, None, self.seq_len)
+            v_quant = ops.values_relayout(self.v_codes[:, :, :nq], "kivi")
+            return (k_full, *packed, v_full, v_quant, self.v_scale[:, :, :nq], self.v_mn[:, :, :nq], self.seq_len)
         return (k_full, *packed, self.values[:, :, :self.seq_len], self.seq_len)

@@ -13,7 +13,9 @@ int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, i
                     void* tmn, const int64_t* out_strides, cudaStream_t stream);
 int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_strides, void* k_res,
                         const int64_t* kres_strides, void* values, const int64_t* v_strides, int B, int Nk, int hd,
-                        int res_pos, int ctx_pos, int dtype, cudaStream_t stream);
+                        int res_pos, int ctx_pos, int dtype, const int* lengths, int G, int values_window,
+                        int res_cap, int value_cap, cudaStream_t stream);
+size_t decode_workspace_bytes_dyn(int B, int N, int Nk, int num_ctas);
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
                      const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
@@ -46,7 +48,7 @@ using namespace pq;
 
 extern "C" {
 
-int pq_abi_version(void) { return 2; }
+int pq_abi_version(void) { return 3; }
 size_t pq_decode_params_size(void) { return sizeof(pq_decode_params); }
 int pq_last_cuda_error(void) { return last_cuda_error(); }
 
@@ -82,7 +84,16 @@ int pq_cache_append(const void* k_new, const void* v_new, const int64_t in_strid
                     const int64_t kres_strides[3], void* values, const int64_t v_strides[3], int B, int Nk, int hd,
                     int res_pos, int ctx_pos, int dtype, void* stream) {
   return cache_append_device(k_new, v_new, in_strides, k_res, kres_strides, values, v_strides, B, Nk, hd, res_pos,
-                             ctx_pos, dtype, static_cast<cudaStream_t>(stream));
+                             ctx_pos, dtype, nullptr, 0, 0, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+int pq_cache_append_dyn(const void* k_new, const void* v_new, const int64_t in_strides[4], void* k_res,
+                        const int64_t kres_strides[3], void* values, const int64_t v_strides[3], int B, int Nk,
+                        int hd, int G, const int* lengths, int values_window, int res_cap, int value_cap, int dtype,
+                        void* stream) {
+  if (!lengths) return PQ_ERR_INVALID;
+  return cache_append_device(k_new, v_new, in_strides, k_res, kres_strides, values, v_strides, B, Nk, hd, 0, 0,
+                             dtype, lengths, G, values_window, res_cap, value_cap, static_cast<cudaStream_t>(stream));
 }
 
 int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream) {
@@ -98,6 +109,9 @@ int pq_qk_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const ui
 
 size_t pq_decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int num_ctas) {
   return decode_workspace_bytes(B, N, Nk, Nb, G, R, num_ctas);
+}
+size_t pq_decode_workspace_bytes_dyn(int B, int N, int Nk, int num_ctas) {
+  return decode_workspace_bytes_dyn(B, N, Nk, num_ctas);
 }
 
 int pq_decode_attention(const pq_decode_params* p, void* stream) {
@@ -218,7 +232,7 @@ int pq_decode_attention_host(const pq_decode_params* hp, void* staging, size_t s
                                                    hp->out_dtype, hp->mask != nullptr);
   if (!staging || staging_bytes < need) return PQ_ERR_WORKSPACE;
   if (!hp->q || !hp->v || !hp->out) return PQ_ERR_INVALID;
-  if (hp->vbits != 0) return PQ_ERR_UNSUPPORTED;        // packed values: device-resident caches only
+  if (hp->vbits != 0 || hp->dyn_lengths) return PQ_ERR_UNSUPPORTED;   // packed values, device-side lengths: resident caches only
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t qe = dtype_bytes(hp->qk_dtype), ve = dtype_bytes(hp->v_dtype), oe = dtype_bytes(hp->out_dtype);
   const size_t units = static_cast<size_t>(B) * Nk, ctx = static_cast<size_t>(Nb) * G + R;

@@ -77,7 +77,45 @@ struct DecodeArgs {
   int nq, nr, slots_per_unit;   // quantised steps, residual steps, nq + 2*nr
   long long total_slots; int total_warps; int max_seg;
   float scale_log2;     // sm_scale * log2(e)
+  // Lengths read on the device (CUDA-graph replay of a growing cache): dyn[0] = token groups, dyn[1] + dyn_r_add =
+  // residual tokens.  The kernels then redo the partition themselves from these and from the launch's CTA count.
+  const int* dyn; int dyn_r_add;
+  long long plan_ctas; int plan_forced;
 };
+
+constexpr int kMinSlotsPerWarp = 16;   // below this a partial costs more than the work it covers
+
+// The partition of the flat step space over warps, from the problem's dimensions and the CTAs available.  Host
+// and device evaluate the same integer arithmetic, so a kernel that reads its lengths on the device arrives at
+// the plan the host would have made.
+__host__ __device__ inline void plan_core(DecodeArgs& a, long long ctas, bool forced) {
+  a.nrep = a.N / a.Nk;
+  a.head_tiles = (a.nrep + kHeadTile - 1) / kHeadTile;
+  a.spg = a.G / kStep;
+  a.nq = a.Nb * a.spg;
+  a.nr = (a.R + kStep - 1) / kStep;
+  a.slots_per_unit = a.nq + 2 * a.nr;
+  const long long units = static_cast<long long>(a.B) * a.Nk * a.head_tiles;
+  a.total_slots = units * a.slots_per_unit;
+  const long long useful = (a.total_slots + static_cast<long long>(kMinSlotsPerWarp) * kWarps - 1) /
+                           (static_cast<long long>(kMinSlotsPerWarp) * kWarps);
+  if (!forced && ctas > useful) ctas = useful;
+  if (ctas < 1) ctas = 1;
+  long long warps = ctas * kWarps;
+  if (warps > a.total_slots) warps = a.total_slots > 0 ? a.total_slots : 1;   // every warp range is non-empty
+  a.total_warps = static_cast<int>(warps);
+  const long long per_warp = (a.total_slots + a.total_warps - 1) / a.total_warps;
+  a.max_seg = static_cast<int>((per_warp + a.slots_per_unit - 1) / (a.slots_per_unit > 0 ? a.slots_per_unit : 1)) + 1;
+}
+__device__ __forceinline__ void plan_on_device(DecodeArgs& a) {
+  // the host's Nb / R are the capacities of the buffers: lengths beyond them are clamped, never followed
+  a.Nb = min(max(a.dyn[0], 0), a.Nb);
+  a.R = min(max(a.dyn[1] + a.dyn_r_add, 0), a.R);
+  if (!a.vq_codes) a.v_tok0 = a.Nb * a.G;
+  plan_core(a, a.plan_ctas, a.plan_forced != 0);
+}
+// partial slots no plan over the given CTAs can exceed: total_warps * max_seg <= units + 3 * warps
+__host__ __device__ inline long long slot_bound(long long units, long long ctas) { return units + 3 * ctas * kWarps; }
 
 __device__ __forceinline__ long long range_lo(long long w, long long total, int nwarps) {
   return (w * total) / nwarps;
@@ -518,9 +556,13 @@ __device__ __forceinline__ void pv_quant(float (&O)[9][4], const VqTile& x, uint
 // when the packed tokens' values are packed too (VQ), none for the logits-only kernel
 constexpr int v_stages(bool qk_only, int vq) { return qk_only ? 0 : (vq ? 1 : kVStages); }
 
-template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ>
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ, bool DYN>
 __global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : PQ_MIN_CTAS)
-decode_kernel(const DecodeArgs a) {
+decode_kernel(const DecodeArgs a_in) {
+  // with device-side lengths the plan is recomputed here; otherwise `a` is the parameter itself
+  DecodeArgs a_dyn;
+  if constexpr (DYN) { a_dyn = a_in; plan_on_device(a_dyn); }
+  const DecodeArgs& a = DYN ? a_dyn : a_in;
   constexpr int A = 1 << TBITS;
   constexpr bool kVPipe = !QK_ONLY && VQ == 0;   // values of the packed tokens stream through shared memory
   constexpr int NT = VQ ? 9 : 8;                 // accumulator tiles: 8 channel tiles (+ the minimum term)
@@ -920,8 +962,10 @@ static_assert(kMergeGroups == kHeadTile, "each thread group finishes one head");
 
 template <int ODT>
 __global__ void __launch_bounds__(kMergeCh * kMergeGroups)
-merge_partials_kernel(const DecodeArgs a, void* __restrict__ out, int64_t o_sb, int64_t o_sh,
+merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_sb, int64_t o_sh,
                       float* __restrict__ lse) {
+  DecodeArgs a = a_in;
+  if (a.dyn) plan_on_device(a);
   constexpr int kThreadsM = kMergeCh * kMergeGroups;
   __shared__ float s_w[kMergeChunk][kHeadTile];                // weight of partial i for head h
   __shared__ float s_red[kThreadsM / 32][kHeadTile];
@@ -1127,27 +1171,10 @@ int sm_count() {
   return cached;
 }
 
-constexpr int kMinSlotsPerWarp = 16;   // below this a partial costs more than the work it covers
-
 void plan(DecodeArgs& a, int ctas_per_sm, int num_ctas) {
-  a.nrep = a.N / a.Nk;
-  a.head_tiles = (a.nrep + kHeadTile - 1) / kHeadTile;
-  a.spg = a.G / kStep;
-  a.nq = a.Nb * a.spg;
-  a.nr = (a.R + kStep - 1) / kStep;
-  a.slots_per_unit = a.nq + 2 * a.nr;
-  const long long units = static_cast<long long>(a.B) * a.Nk * a.head_tiles;
-  a.total_slots = units * a.slots_per_unit;
-  long long ctas = num_ctas > 0 ? num_ctas : static_cast<long long>(sm_count()) * ctas_per_sm;
-  const long long useful = (a.total_slots + static_cast<long long>(kMinSlotsPerWarp) * kWarps - 1) /
-                           (static_cast<long long>(kMinSlotsPerWarp) * kWarps);
-  if (num_ctas <= 0 && ctas > useful) ctas = useful;
-  if (ctas < 1) ctas = 1;
-  long long warps = ctas * kWarps;
-  if (warps > a.total_slots) warps = a.total_slots > 0 ? a.total_slots : 1;   // every warp range is non-empty
-  a.total_warps = static_cast<int>(warps);
-  const long long per_warp = (a.total_slots + a.total_warps - 1) / a.total_warps;
-  a.max_seg = static_cast<int>((per_warp + a.slots_per_unit - 1) / (a.slots_per_unit > 0 ? a.slots_per_unit : 1)) + 1;
+  a.plan_ctas = num_ctas > 0 ? num_ctas : static_cast<long long>(sm_count()) * ctas_per_sm;
+  a.plan_forced = num_ctas > 0;
+  plan_core(a, a.plan_ctas, a.plan_forced != 0);
 }
 
 size_t workspace_bytes_for(const DecodeArgs& a) {
@@ -1155,15 +1182,17 @@ size_t workspace_bytes_for(const DecodeArgs& a) {
   return slots * (kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2));
 }
 
-template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ = 0>
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ = 0, bool DYN = false>
 int launch_decode(const DecodeArgs& a, cudaStream_t s) {
   constexpr int kStageBytes = 4 * kPairs * (QDT == PQ_F32 ? 4 : 2);
   constexpr int kWarpSmem = kPairs * (1 << TBITS) * 4 + 2 * kStageBytes + v_stages(QK_ONLY, VQ) * kVTileSmem;
   constexpr int kSmem = kWarps * kWarpSmem;
   if (kSmem > 48 * 1024)
-    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ>,
+    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ, DYN>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ><<<(a.total_warps + kWarps - 1) / kWarps, kThreads, kSmem, s>>>(a);
+  // device-side lengths: always the full grid, the kernel retires the warps its own plan does not use
+  const unsigned grid = DYN ? static_cast<unsigned>(a.plan_ctas) : (a.total_warps + kWarps - 1) / kWarps;
+  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ, DYN><<<grid, kThreads, kSmem, s>>>(a);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
@@ -1171,6 +1200,15 @@ int launch_decode(const DecodeArgs& a, cudaStream_t s) {
 template <int RBITS, int TBITS, bool QK_ONLY>
 int dispatch_dtypes(const DecodeArgs& a, int qdt, int vdt, cudaStream_t s) {
   if constexpr (!QK_ONLY) {
+    if (a.dyn) {            // device-side lengths: one instance per 16-bit dtype, with and without packed values
+      if (qdt == PQ_F16 && vdt == PQ_F16)
+        return a.vq_codes ? launch_decode<RBITS, TBITS, PQ_F16, PQ_F16, false, 4, true>(a, s)
+                          : launch_decode<RBITS, TBITS, PQ_F16, PQ_F16, false, 0, true>(a, s);
+      if (qdt == PQ_BF16 && vdt == PQ_BF16)
+        return a.vq_codes ? launch_decode<RBITS, TBITS, PQ_BF16, PQ_BF16, false, 4, true>(a, s)
+                          : launch_decode<RBITS, TBITS, PQ_BF16, PQ_BF16, false, 0, true>(a, s);
+      return PQ_ERR_UNSUPPORTED;
+    }
     if (a.vq_codes) {       // packed values: one instance per 16-bit dtype
       if (qdt == PQ_F16 && vdt == PQ_F16) return launch_decode<RBITS, TBITS, PQ_F16, PQ_F16, false, 4>(a, s);
       if (qdt == PQ_BF16 && vdt == PQ_BF16) return launch_decode<RBITS, TBITS, PQ_BF16, PQ_BF16, false, 4>(a, s);
@@ -1230,6 +1268,16 @@ size_t decode_workspace_bytes(int B, int N, int Nk, int Nb, int G, int R, int nu
   return workspace_bytes_for(a);
 }
 
+// scratch that suffices for every (Nb, R) a growing cache passes through with device-side lengths
+size_t decode_workspace_bytes_dyn(int B, int N, int Nk, int num_ctas) {
+  if (B <= 0 || N <= 0 || Nk <= 0 || N % Nk != 0) return 0;
+  DecodeArgs a{};
+  a.B = B; a.N = N; a.Nk = Nk; a.Nb = 0; a.G = kStep; a.R = 1;
+  plan(a, PQ_MIN_CTAS, num_ctas);
+  const long long units = static_cast<long long>(B) * Nk * a.head_tiles;
+  return static_cast<size_t>(slot_bound(units, a.plan_ctas)) * (kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2));
+}
+
 int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (!p) return PQ_ERR_INVALID;
   if (p->B < 0 || p->N <= 0 || p->Nk <= 0 || p->Nb < 0 || p->G <= 0 || p->R < 0 || p->N % p->Nk != 0)
@@ -1284,17 +1332,24 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   a.mask = p->mask; a.m_sb = p->mask_stride_b;
   a.B = p->B; a.N = p->N; a.Nk = p->Nk; a.Nb = p->Nb; a.G = p->G; a.R = p->R;
   plan(a, PQ_MIN_CTAS, p->num_ctas);
-  const size_t need = workspace_bytes_for(a);
+  size_t need = workspace_bytes_for(a);
+  size_t slots = static_cast<size_t>(a.total_warps) * a.max_seg;
+  if (p->dyn_lengths) {
+    if (mis(p->dyn_lengths, 4)) return PQ_ERR_ALIGNMENT;
+    if (p->qk_dtype != p->v_dtype || p->qk_dtype == PQ_F32) return PQ_ERR_UNSUPPORTED;
+    a.dyn = p->dyn_lengths; a.dyn_r_add = p->dyn_r_add;
+    slots = static_cast<size_t>(slot_bound(static_cast<long long>(a.B) * a.Nk * a.head_tiles, a.plan_ctas));
+    need = slots * (kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2));
+  }
   if (!p->workspace || p->workspace_bytes < need) return PQ_ERR_WORKSPACE;
   if (mis(p->workspace, 256)) return PQ_ERR_ALIGNMENT;
-  const size_t slots = static_cast<size_t>(a.total_warps) * a.max_seg;
   a.part_o = static_cast<float*>(p->workspace);
   a.part_ml = reinterpret_cast<float2*>(a.part_o + slots * kPartialFloats);
   const float sm = p->sm_scale != 0.f ? p->sm_scale : 0.08838834764831845f;   // 1/sqrt(128)
   a.scale_log2 = sm * 1.4426950408889634f;
 
   // a kernel instance exists per (rbits, tbits); without packed keys any instance serves
-  const int rb = p->Nb > 0 ? p->rbits : 4, tb = p->Nb > 0 ? p->tbits : 4;
+  const int rb = (p->Nb > 0 || p->dyn_lengths) ? p->rbits : 4, tb = (p->Nb > 0 || p->dyn_lengths) ? p->tbits : 4;
   int rc = dispatch_bits<false>(a, rb, tb, p->qk_dtype, p->v_dtype, stream);
   if (rc != PQ_OK) return rc;
   if (p->mid_event) PQ_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(p->mid_event), stream));

@@ -439,7 +439,13 @@ template <typename T>
 __global__ void cache_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, int64_t n_sb, int64_t n_sh,
                                     int64_t vn_sb, int64_t vn_sh, T* __restrict__ k_res, int64_t kr_sb, int64_t kr_sh,
                                     int64_t kr_st, T* __restrict__ values, int64_t v_sb, int64_t v_sh, int64_t v_st,
-                                    int Nk, int res_pos, int ctx_pos) {
+                                    int Nk, int res_pos, int ctx_pos, const int* __restrict__ lengths, int G,
+                                    int values_window, int res_cap, int value_cap) {
+  if (lengths) {                                           // positions kept on the device
+    res_pos = lengths[1];
+    ctx_pos = values_window ? res_pos : lengths[0] * G + res_pos;
+    if (res_pos < 0 || res_pos >= res_cap || ctx_pos < 0 || ctx_pos >= value_cap) return;
+  }
   const int b = blockIdx.x / Nk, h = blockIdx.x % Nk;
   const int c = threadIdx.x;                               // channel
   k_res[b * kr_sb + h * kr_sh + res_pos * kr_st + c] = k_new[b * n_sb + h * n_sh + c];
@@ -450,16 +456,19 @@ __global__ void cache_append_kernel(const T* __restrict__ k_new, const T* __rest
 
 int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_strides, void* k_res,
                         const int64_t* kres_strides, void* values, const int64_t* v_strides, int B, int Nk, int hd,
-                        int res_pos, int ctx_pos, int dtype, cudaStream_t stream) {
+                        int res_pos, int ctx_pos, int dtype, const int* lengths, int G, int values_window,
+                        int res_cap, int value_cap, cudaStream_t stream) {
   if (!k_new || !v_new || !k_res || !values || !in_strides || !kres_strides || !v_strides) return PQ_ERR_INVALID;
   if (B <= 0 || Nk <= 0 || res_pos < 0 || ctx_pos < 0 || !dtype_ok(dtype)) return PQ_ERR_INVALID;
+  if (lengths && (G <= 0 || res_cap <= 0 || value_cap <= 0)) return PQ_ERR_INVALID;
   if (hd != kHeadDim) return PQ_ERR_UNSUPPORTED;
   const unsigned grid = static_cast<unsigned>(B) * Nk;
 #define PQ_APPEND(T)                                                                                              \
   cache_append_kernel<T><<<grid, kHeadDim, 0, stream>>>(                                                         \
       static_cast<const T*>(k_new), static_cast<const T*>(v_new), in_strides[0], in_strides[1], in_strides[2],   \
       in_strides[3], static_cast<T*>(k_res), kres_strides[0], kres_strides[1], kres_strides[2],                  \
-      static_cast<T*>(values), v_strides[0], v_strides[1], v_strides[2], Nk, res_pos, ctx_pos)
+      static_cast<T*>(values), v_strides[0], v_strides[1], v_strides[2], Nk, res_pos, ctx_pos, lengths, G,       \
+      values_window, res_cap, value_cap)
   if (dtype == PQ_F32) PQ_APPEND(float);
   else if (dtype == PQ_F16) PQ_APPEND(__half);
   else PQ_APPEND(__nv_bfloat16);

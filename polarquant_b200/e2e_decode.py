@@ -62,6 +62,8 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--prefill-chunk", type=int, default=2, help="sequences prefilled at a time")
+    ap.add_argument("--vbits", type=int, default=0, choices=(0, 4),
+                    help="4: pack the values to 4 bits as well (the reference's mixed key/value class)")
     args = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -85,7 +87,8 @@ def main():
     prompts = torch.randint(0, vocab, (args.batch, args.prompt), generator=g2)[lo:hi].to(dev)
 
     max_tokens = ((args.prompt + args.new_tokens + 127) // 128 + 1) * 128
-    caches = [PolarKVCache(B, kvh, max_tokens, dtype=torch.bfloat16, device=dev) for _ in range(args.layers)]
+    caches = [PolarKVCache(B, kvh, max_tokens, dtype=torch.bfloat16, device=dev, vbits=args.vbits)
+              for _ in range(args.layers)]
 
     def split_qkv(x, L):
         q, k, v = x.split([heads * hd, kvh * hd, kvh * hd], dim=-1)
@@ -120,6 +123,9 @@ def main():
                 sub.B = x.shape[0]
                 sub.codes, sub.scales = caches[li].codes[sl], [t[sl] for t in caches[li].scales]
                 sub.k_res, sub.values = caches[li].k_res[sl], caches[li].values[sl]
+                if args.vbits:
+                    sub.v_codes, sub.v_scale, sub.v_mn = (t[sl] for t in (caches[li].v_codes, caches[li].v_scale,
+                                                                           caches[li].v_mn))
                 sub.prefill(k, v)
                 caches[li].num_groups, caches[li].res_len = sub.num_groups, sub.res_len
             last_hidden[sl] = x[:, -1]
@@ -159,7 +165,9 @@ def main():
             "bench": "e2e_decode", "model": f"Llama-3.1-8B-shaped, {args.layers} layers, random init, bf16",
             "n_gpus": world, "global_batch": args.batch, "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
             "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": decode_s / steps * 1e3,
-            "prefill_s": prefill_s, "keys": "polar 4/4, group 128, residual 128", "values": "bf16",
+            "prefill_s": prefill_s, "keys": "polar 4/4, group 128, residual 128",
+            "values": "4-bit per-token min/max, residual 128 in bf16" if args.vbits else "bf16",
+            "cache_bytes_per_token_per_kv_head": 136 if args.vbits else 324,
             "note": "eager torch around PolarKVCache.decode_step; the step is host-launch bound at this batch"}))
     if world > 1:
         dist.barrier()

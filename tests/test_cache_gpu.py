@@ -62,3 +62,116 @@ def test_cache_refuses_to_overflow():
     q = torch.randn(1, 4, 1, 128, device="cuda").to(torch.bfloat16)
     with pytest.raises(RuntimeError):
         cache.decode_step(q, k[:, :, :1], k[:, :, :1])
+
+
+@pytest.mark.parametrize("prompt,steps", [(300, 140), (128, 130), (7, 260)])
+def test_in_place_cache_with_packed_values_tracks_the_mixed_reference_state(prompt, steps):
+    """vbits=4: the cache of LlamaPolarMixedGroupAttention (models/modeling_llama_polar.py:189-246) - values of
+    the quantised tokens packed, those of the residual window in full precision, both re-quantised together."""
+    import polarquant_b200 as pq
+    from conftest import check_mixed
+    from polarquant_b200.cache import PolarKVCache
+    dev, dt = "cuda", torch.bfloat16
+    B, N, Nk = 2, 8, 2
+    g = torch.Generator(device=dev).manual_seed(400 + prompt)
+    k_blnh = oracle.synth_keys(B, prompt, Nk, 128, dt, seed=401, device=dev)
+    v_blnh = torch.randn(B, prompt, Nk, 128, device=dev, generator=g).to(dt)
+    keys, vals = k_blnh.transpose(1, 2), v_blnh.transpose(1, 2)
+    cache = PolarKVCache(B, Nk, max_tokens=prompt + steps + 128, dtype=dt, vbits=4)
+    cache.prefill(keys, vals)
+
+    nq = prompt - prompt % 128
+    ref = list(oracle.quantize_ops(keys[:, :, :nq].contiguous(), 4, 4, 128)) if nq else None
+    vref = list(oracle.quantize_values(vals[:, :, :nq].contiguous())) if nq else None
+    kres, vres = keys[:, :, nq:].contiguous(), vals[:, :, nq:].contiguous()
+    for step in range(steps):
+        q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+        k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=3000 + step, device=dev)
+        v_new = torch.randn(B, Nk, 1, 128, device=dev, generator=g).to(dt)
+        got = cache.decode_step(q, k_new, v_new)
+        kres = torch.cat([kres, k_new], dim=2)
+        vres = torch.cat([vres, v_new], dim=2)
+        if step % 16 == 0 or kres.shape[2] % 128 in (0, 1):
+            want = oracle.decode_attention_mixed(q, kres, *(ref or (None,) * 5), *(vref or (None,) * 3), vres)
+            check_mixed(got, want, f"step {step}")
+        if kres.shape[2] % 128 == 0:
+            fresh, vfresh = oracle.quantize_ops(kres, 4, 4, 128), oracle.quantize_values(vres)
+            ref = [torch.cat([a, b], dim=2) for a, b in zip(ref, fresh)] if ref else list(fresh)
+            vref = [torch.cat([a, b], dim=2) for a, b in zip(vref, vfresh)] if vref else list(vfresh)
+            kres, vres = kres[:, :, :0], vres[:, :, :0]
+        assert cache.seq_len == prompt + step + 1
+    tup = cache.as_reference_tuple()
+    assert len(tup) == 11 and tup[10] == prompt + steps
+    if ref:
+        for a, b in zip(tup[1:6], ref):
+            assert torch.equal(a, b)
+        for a, b in zip(tup[7:10], vref):            # value codes (kivi layout), scales and minima, bit for bit
+            assert torch.equal(a, b)
+    if vres.shape[2]:
+        assert torch.equal(tup[6], vres)
+    else:
+        assert tup[6] is None
+    # the general (masked) path over the same cache state agrees with the lean path's kernels
+    q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+    k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=9, device=dev)
+    mask = torch.ones(B, cache.seq_len + 1, device=dev)
+    a = cache.decode_step(q, k_new, k_new, attention_mask=mask)
+    assert torch.isfinite(a.float()).all()
+
+
+@pytest.mark.parametrize("vbits", [0, 4])
+def test_one_captured_graph_replays_over_the_growing_cache(vbits):
+    """Device-side lengths: the append + attention of a step are captured once in a CUDA graph and replayed for
+    every token; results equal the eager cache's bit for bit, across a re-quantisation of the window."""
+    from polarquant_b200.cache import PolarKVCache
+    dev, dt = "cuda", torch.bfloat16
+    B, N, Nk, prompt, steps = 2, 8, 2, 300, 100
+    g = torch.Generator(device=dev).manual_seed(77)
+    keys = oracle.synth_keys(B, Nk, prompt, 128, dt, seed=78, device=dev)
+    vals = torch.randn(B, Nk, prompt, 128, device=dev, generator=g).to(dt)
+    lengths = torch.zeros(2, dtype=torch.int32, device=dev)
+    eager = PolarKVCache(B, Nk, max_tokens=prompt + steps + 128, dtype=dt, vbits=vbits)
+    graph = PolarKVCache(B, Nk, max_tokens=prompt + steps + 128, dtype=dt, vbits=vbits, lengths=lengths)
+    eager.prefill(keys, vals)
+    graph.prefill(keys, vals)
+    graph.sync_lengths()
+    # static buffers the captured graph reads and writes
+    q_buf = torch.empty(B, N, 1, 128, device=dev, dtype=dt)
+    k_buf = torch.empty(B, Nk, 1, 128, device=dev, dtype=dt)
+    v_buf = torch.empty(B, Nk, 1, 128, device=dev, dtype=dt)
+    out_buf = torch.empty(B, N, 1, 128, device=dev, dtype=dt)
+
+    def step_fn():
+        graph.decode_step_graph(q_buf, k_buf, v_buf, out=out_buf)
+        lengths[1:2].add_(1)
+
+    q_buf.normal_(); k_buf.normal_(); v_buf.normal_()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        # warm-up outside capture, on a throw-away copy of the state: undo its effect on the lengths afterwards
+        step_fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph.sync_lengths()                               # the warm-up step is discarded (its slot is overwritten)
+    cg = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(cg):
+        step_fn()
+    graph.sync_lengths()                               # capture does not execute, but keep the state explicit
+    crossed = False
+    for step in range(steps):
+        q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+        k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=5000 + step, device=dev)
+        v_new = torch.randn(B, Nk, 1, 128, device=dev, generator=g).to(dt)
+        want = eager.decode_step(q, k_new, v_new)
+        q_buf.copy_(q); k_buf.copy_(k_new); v_buf.copy_(v_new)
+        cg.replay()
+        assert torch.equal(out_buf, want), step
+        if graph.after_replay():
+            graph.sync_lengths()
+            crossed = True
+        assert graph.seq_len == eager.seq_len
+        assert lengths.tolist() == [graph.num_groups, graph.res_len], step
+    assert crossed
+    for a, b in zip(graph.as_reference_tuple(), eager.as_reference_tuple()):
+        assert (a is None and b is None) or (isinstance(a, int) and a == b) or torch.equal(a, b)
