@@ -62,6 +62,8 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--prefill-chunk", type=int, default=2, help="sequences prefilled at a time")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every decode step from Python instead of replaying one captured CUDA graph")
     ap.add_argument("--vbits", type=int, default=0, choices=(0, 4),
                     help="4: pack the values to 4 bits as well (the reference's mixed key/value class)")
     args = ap.parse_args()
@@ -87,7 +89,10 @@ def main():
     prompts = torch.randint(0, vocab, (args.batch, args.prompt), generator=g2)[lo:hi].to(dev)
 
     max_tokens = ((args.prompt + args.new_tokens + 127) // 128 + 1) * 128
-    caches = [PolarKVCache(B, kvh, max_tokens, dtype=torch.bfloat16, device=dev, vbits=args.vbits)
+    use_graph = not args.no_graph
+    # all layers hold the same number of tokens: one device-side lengths pair serves every cache
+    lengths = torch.zeros(2, dtype=torch.int32, device=dev) if use_graph else None
+    caches = [PolarKVCache(B, kvh, max_tokens, dtype=torch.bfloat16, device=dev, vbits=args.vbits, lengths=lengths)
               for _ in range(args.layers)]
 
     def split_qkv(x, L):
@@ -139,19 +144,60 @@ def main():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        t0 = time.perf_counter()
-        for step in range(args.new_tokens - 1):
-            pos = args.prompt + step
-            cos1, sin1 = rope_tables(torch.tensor([pos], device=dev), hd, theta, dev)
-            x = embed[tok][:, None, :]
+        def model_step(tok_in, cos1, sin1, attend):
+            x = embed[tok_in][:, None, :]
             for li, layer in enumerate(layers):
                 h = rms_norm(x, layer.n1)
                 q, k, v = split_qkv(F.linear(h, layer.qkv), 1)
                 q, k = apply_rope(q, cos1, sin1), apply_rope(k, cos1, sin1)
-                att = caches[li].decode_step(q, k, v)                       # (B, heads, 1, hd)
+                att = attend(caches[li], q, k, v)                           # (B, heads, 1, hd)
                 x = x + F.linear(att.transpose(1, 2).reshape(B, 1, heads * hd), layer.o)
                 x = x + mlp(layer, rms_norm(x, layer.n2))
-            tok = F.linear(rms_norm(x[:, 0], final_norm), lm_head).argmax(-1)
+            return F.linear(rms_norm(x[:, 0], final_norm), lm_head).argmax(-1)
+
+        graph = None
+        if use_graph:
+            # The whole model step - 32 x (projections, RoPE, cache append, fused attention, MLP), the LM head, the
+            # argmax and the advance of position and lengths - is captured once and replayed per token.  The cache
+            # kernels read their lengths on the device; the window is re-quantised outside the graph.
+            caches[0].sync_lengths()
+            tok_buf = tok.clone()
+            pos_dev = torch.full((1,), args.prompt, device=dev, dtype=torch.int64)
+
+            def graph_step():
+                cos1, sin1 = rope_tables(pos_dev, hd, theta, dev)
+                nxt = model_step(tok_buf, cos1, sin1, lambda c, q, k, v: c.decode_step_graph(q, k.contiguous(), v))
+                tok_buf.copy_(nxt)
+                lengths[1:2].add_(1)
+                pos_dev.add_(1)
+
+            # warm-up on a side stream, then restore what it changed: token, position, lengths (the slot it wrote
+            # is overwritten by the first real step)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph_step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            tok_buf.copy_(tok); pos_dev.fill_(args.prompt); caches[0].sync_lengths()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_step()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        t0 = time.perf_counter()
+        for step in range(args.new_tokens - 1):
+            if graph is not None:
+                graph.replay()
+                generated.append(tok_buf.clone())
+                full = [c.after_replay() for c in caches]
+                if full[0]:
+                    caches[0].sync_lengths()
+                continue
+            pos = args.prompt + step
+            cos1, sin1 = rope_tables(torch.tensor([pos], device=dev), hd, theta, dev)
+            tok = model_step(tok, cos1, sin1, lambda c, q, k, v: c.decode_step(q, k, v))
             generated.append(tok)
         torch.cuda.synchronize()
         decode_s = time.perf_counter() - t0
@@ -168,7 +214,10 @@ def main():
             "prefill_s": prefill_s, "keys": "polar 4/4, group 128, residual 128",
             "values": "4-bit per-token min/max, residual 128 in bf16" if args.vbits else "bf16",
             "cache_bytes_per_token_per_kv_head": 136 if args.vbits else 324,
-            "note": "eager torch around PolarKVCache.decode_step; the step is host-launch bound at this batch"}))
+            "cuda_graph": use_graph,
+            "note": ("one captured CUDA graph of the whole model step, replayed per token; cache lengths on the device"
+                     if use_graph else
+                     "eager torch around PolarKVCache.decode_step; the step is host-launch bound at this batch")}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
