@@ -494,6 +494,40 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
         out["quantizer"] = {"workload": f"{L}-token prefill, batch {B}, {Nk} kv heads, bf16, strided (B, L, Nk, hd)",
                             "us": q_ms * 1e3, "algorithmic_mb": q_bytes / 1e6,
                             "gbs": q_bytes / (q_ms * 1e-3) / 1e9, "frac_of_peak": q_bytes / (q_ms * 1e-3) / 1e9 / peak}
+        del base, keys
+
+    # ---- the same step with the values packed to 4 bits as well (the reference's mixed key/value class) ----
+    if rank == 0:
+        Lq = Nb * G
+        vq = inp["v"][:, :, :Lq]
+        for _ in range(2):
+            vc, vs, vm = pq.quantize_values(vq, layout="tiled")
+        a, b = new_event(), new_event()
+        lib.pq_event_record(a, stream)
+        for _ in range(5):
+            pq.quantize_values(vq, layout="tiled")
+        lib.pq_event_record(b, stream)
+        lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
+        vq_ms = ms.value / 5
+        v_res = inp["v"][:, :, Lq:].contiguous()
+        kw = dict(rbits=args.rbits, tbits=args.tbits, value_codes=vc, value_scale=vs, value_mn=vm)
+        for _ in range(3):
+            pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], v_res, **kw)
+        reps = 50
+        lib.pq_event_record(a, stream)
+        for _ in range(reps):
+            pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], v_res, **kw)
+        lib.pq_event_record(b, stream)
+        lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
+        p_ms = ms.value / reps
+        p_bytes = nbytes - vq.numel() * 2 + vc.numel() * 4 + 2 * vs.numel() * 2
+        vq_bytes = vq.numel() * 2 + vc.numel() * 4 + 2 * vs.numel() * 2
+        out["packed_values"] = {"us_per_step": p_ms * 1e3, "algorithmic_mb": p_bytes / 1e6,
+                                "gbs": p_bytes / (p_ms * 1e-3) / 1e9,
+                                "bytes_per_token_per_kv_head": 64 + 4 + 64 + 4,
+                                "value_quantizer_us": vq_ms * 1e3, "value_quantizer_gbs": vq_bytes / (vq_ms * 1e-3) / 1e9,
+                                "note": "4-bit per-token values fused into the P.V loop: 2.4x less cache, same step "
+                                        "time - the step is bound by instruction issue, not by bytes"}
     return out
 
 
