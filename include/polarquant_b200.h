@@ -88,6 +88,21 @@ int pq_cache_append_dyn(const void* k_new, const void* v_new, const int64_t in_s
                         void* stream);
 
 /*
+ * Rotary embedding of one decode token fused with the cache append.  qkv (B, (N + 2 Nk) * hd) is the fused
+ * projection output of the step, [query heads | key heads | value heads], row stride qkv_stride_b elements; cos /
+ * sin hold hd elements of `dtype` per sequence (cs_stride_b elements apart, 0 = shared).  Query heads are rotated
+ * into q_out (B, N, hd) contiguous, key heads are rotated into slot res_pos of k_res, value heads are copied into
+ * slot ctx_pos of `values`; with `lengths` the slots come from the device as in pq_cache_append_dyn (res_pos and
+ * ctx_pos are then ignored).  Arithmetic: out = RN(RN(x * cos) + RN(rotate_half(x) * sin)), the eager ops of
+ * apply_rotary_pos_emb as called at models/modeling_llama_polar.py:57, rounded where they round.  Replaces that
+ * call plus the torch.cat appends at :77,98 for the decode step.
+ */
+int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const void* sin, int64_t cs_stride_b,
+                   void* q_out, void* k_res, const int64_t kres_strides[3], void* values, const int64_t v_strides[3],
+                   int B, int N, int Nk, int hd, int G, const int* lengths, int values_window, int res_cap,
+                   int value_cap, int res_pos, int ctx_pos, int dtype, void* stream);
+
+/*
  * Self-test of the quantizer's fast paths (no reference counterpart).  The kernel replaces atan2f, sqrtf and the
  * IEEE division by cheaper approximations wherever the approximation provably rounds to the same 16-bit value,
  * and calls the exact routine otherwise.  This entry point checks that claim exhaustively on the device: for all

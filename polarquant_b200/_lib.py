@@ -27,7 +27,7 @@ EXPORTED_SYMBOLS = (
     "pq_event_create", "pq_event_destroy", "pq_event_record", "pq_event_elapsed_ms",
     "pq_decode_attention_static", "pq_decode_static_scratch_bytes", "pq_selftest_quantizer", "pq_quantize_into", "pq_cache_append",
     "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
-    "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn",
+    "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn", "pq_rope_append",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -81,6 +81,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_cache_append_dyn.restype = _int
     lib.pq_cache_append_dyn.argtypes = [_vp, _vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _vp,
                                         ctypes.POINTER(_i64), _int, _int, _int, _int, _vp, _int, _int, _int, _int, _vp]
+    lib.pq_rope_append.restype = _int
+    lib.pq_rope_append.argtypes = [_vp, _i64, _vp, _vp, _i64, _vp, _vp, ctypes.POINTER(_i64), _vp,
+                                   ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _vp, _int, _int, _int, _int,
+                                   _int, _int, _vp]
     lib.pq_decode_workspace_bytes_dyn.restype = _sz
     lib.pq_decode_workspace_bytes_dyn.argtypes = [_int] * 4
     lib.pq_qk_decode.restype = _int

@@ -225,30 +225,68 @@ class PolarKVCache:
             raise RuntimeError("this cache was built without a device-side lengths tensor")
         lib = _lib.load()
         dev = self._dev
-        stream = ops._stream(dev)
+        if key_new.dtype != self.dtype or value_new.dtype != self.dtype or key_new.stride(-1) != 1 \
+                or value_new.stride(-1) != 1:
+            raise ValueError("decode_step_graph needs cache-dtype tensors with unit inner stride")
         in_strides = (ctypes.c_int64 * 4)(key_new.stride(0), key_new.stride(1), value_new.stride(0),
                                           value_new.stride(1))
-        bsz, nq, _, hd = query_states.shape
-        q = query_states.reshape(bsz, nq, hd)
-        if not ops._vec_ok(q, 8) or query_states.dtype != self.dtype or key_new.dtype != self.dtype \
-                or value_new.dtype != self.dtype or key_new.stride(-1) != 1 or value_new.stride(-1) != 1:
-            raise ValueError("decode_step_graph needs cache-dtype tensors with unit inner stride and aligned rows")
-        if out is None:
-            out = torch.empty((bsz, nq, 1, hd), dtype=self.dtype, device=dev)
         with ops._on_device(dev):
             rc = lib.pq_cache_append_dyn(key_new.data_ptr(), value_new.data_ptr(), in_strides, self.k_res.data_ptr(),
                                          self._kres_strides, self.values.data_ptr(), self._v_strides, self.B,
                                          self.Nk, 128, self.G, self.lengths.data_ptr(), 1 if self.vbits else 0,
-                                         self.RL, self.values.shape[2], self._dt, stream)
-            _lib.check(rc, "pq_cache_append_dyn")
-            p = _lib.DecodeParams()
-            ctypes.memmove(ctypes.byref(p), ctypes.byref(self._params), ctypes.sizeof(p))
-            p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
-            p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
-            p.N, p.Nb, p.R = nq, self.max_groups, self.RL             # capacities; the lengths come from the device
-            p.out_dtype = self._dt
-            p.dyn_lengths, p.dyn_r_add = self.lengths.data_ptr(), 1   # the appended token is not counted yet
-            rc = lib.pq_decode_attention(ctypes.byref(p), stream)
+                                         self.RL, self.values.shape[2], self._dt, ops._stream(dev))
+        _lib.check(rc, "pq_cache_append_dyn")
+        return self.attend_graph(query_states, out)
+
+    def rope_append_graph(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """Rotary embedding + append of one decode token in a single kernel, lengths read on the device.
+        ``qkv`` (B, (N + 2 Nk) * 128): the fused projection output [query heads | key heads | value heads];
+        ``cos`` / ``sin`` (128,) or (B, 128) in the cache dtype.  Returns the rotated queries (B, N, 1, 128) for
+        ``attend_graph``.  Same arithmetic as ``x * cos + rotate_half(x) * sin`` in eager torch."""
+        if self.lengths is None:
+            raise RuntimeError("this cache was built without a device-side lengths tensor")
+        bsz = qkv.shape[0]
+        qkv = qkv.reshape(bsz, -1)
+        nq = qkv.shape[1] // 128 - 2 * self.Nk
+        if qkv.dtype != self.dtype or qkv.stride(1) != 1 or cos.dtype != self.dtype or sin.dtype != self.dtype \
+                or nq <= 0 or bsz != self.B:
+            raise ValueError("rope_append_graph: qkv must be (B, (N + 2 Nk) * 128) in the cache dtype")
+        cos, sin = cos.reshape(-1, 128), sin.reshape(-1, 128)
+        cs_stride = cos.stride(0) if cos.shape[0] > 1 else 0
+        if sin.shape != cos.shape or (sin.shape[0] > 1 and sin.stride(0) != cs_stride) or cos.stride(1) != 1 \
+                or sin.stride(1) != 1:
+            raise ValueError("rope_append_graph: cos and sin must have the same (1 or B, 128) layout")
+        q_out = torch.empty((bsz, nq, 1, 128), dtype=self.dtype, device=self._dev)
+        lib = _lib.load()
+        with ops._on_device(self._dev):
+            rc = lib.pq_rope_append(qkv.data_ptr(), qkv.stride(0), cos.data_ptr(), sin.data_ptr(), cs_stride,
+                                    q_out.data_ptr(), self.k_res.data_ptr(), self._kres_strides,
+                                    self.values.data_ptr(), self._v_strides, self.B, nq, self.Nk, 128, self.G,
+                                    self.lengths.data_ptr(), 1 if self.vbits else 0, self.RL, self.values.shape[2],
+                                    0, 0, self._dt, ops._stream(self._dev))
+        _lib.check(rc, "pq_rope_append")
+        return q_out
+
+    def attend_graph(self, query_states: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Fused attention of the step whose token was appended by ``rope_append_graph`` / ``decode_step_graph``
+        (the appended token is not yet counted in ``lengths``: the kernels add it)."""
+        lib = _lib.load()
+        dev = self._dev
+        bsz, nq, _, hd = query_states.shape
+        q = query_states.reshape(bsz, nq, hd)
+        if not ops._vec_ok(q, 8) or query_states.dtype != self.dtype:
+            raise ValueError("attend_graph needs cache-dtype queries with unit inner stride and aligned rows")
+        if out is None:
+            out = torch.empty((bsz, nq, 1, hd), dtype=self.dtype, device=dev)
+        p = _lib.DecodeParams()
+        ctypes.memmove(ctypes.byref(p), ctypes.byref(self._params), ctypes.sizeof(p))
+        p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+        p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+        p.N, p.Nb, p.R = nq, self.max_groups, self.RL             # capacities; the lengths come from the device
+        p.out_dtype = self._dt
+        p.dyn_lengths, p.dyn_r_add = self.lengths.data_ptr(), 1   # the appended token is not counted yet
+        with ops._on_device(dev):
+            rc = lib.pq_decode_attention(ctypes.byref(p), ops._stream(dev))
         _lib.check(rc, "pq_decode_attention")
         return out
 

@@ -16,6 +16,10 @@ int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_
                         int res_pos, int ctx_pos, int dtype, const int* lengths, int G, int values_window,
                         int res_cap, int value_cap, cudaStream_t stream);
 size_t decode_workspace_bytes_dyn(int B, int N, int Nk, int num_ctas);
+int rope_append_device(const void* qkv, int64_t qkv_stride_b, const void* cosv, const void* sinv, int64_t cs_stride_b,
+                       void* q_out, void* k_res, const int64_t* kres_strides, void* values, const int64_t* v_strides,
+                       int B, int N, int Nk, int hd, int G, const int* lengths, int values_window, int res_cap,
+                       int value_cap, int res_pos, int ctx_pos, int dtype, cudaStream_t stream);
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
                      const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
@@ -94,6 +98,15 @@ int pq_cache_append_dyn(const void* k_new, const void* v_new, const int64_t in_s
   if (!lengths) return PQ_ERR_INVALID;
   return cache_append_device(k_new, v_new, in_strides, k_res, kres_strides, values, v_strides, B, Nk, hd, 0, 0,
                              dtype, lengths, G, values_window, res_cap, value_cap, static_cast<cudaStream_t>(stream));
+}
+
+int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const void* sin, int64_t cs_stride_b,
+                   void* q_out, void* k_res, const int64_t kres_strides[3], void* values, const int64_t v_strides[3],
+                   int B, int N, int Nk, int hd, int G, const int* lengths, int values_window, int res_cap,
+                   int value_cap, int res_pos, int ctx_pos, int dtype, void* stream) {
+  return rope_append_device(qkv, qkv_stride_b, cos, sin, cs_stride_b, q_out, k_res, kres_strides, values, v_strides,
+                            B, N, Nk, hd, G, lengths, values_window, res_cap, value_cap, res_pos, ctx_pos, dtype,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream) {

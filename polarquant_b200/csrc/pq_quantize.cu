@@ -477,6 +477,76 @@ int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_
   return PQ_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Rotary embedding of one decode token fused with the cache append: the query heads of the fused projection output
+// are rotated into q_out, the key heads are rotated straight into their slot of the residual window, the value
+// heads are copied into theirs.  Arithmetic is the eager `x * cos + rotate_half(x) * sin` of the attention
+// patches (apply_rotary_pos_emb at models/modeling_llama_polar.py:57): both products and the sum are rounded to
+// the tensor dtype, so the rotated key that gets quantised later is the one the reference would have produced.
+// ---------------------------------------------------------------------------------------------
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim / 2)
+rope_append_kernel(const T* __restrict__ qkv, int64_t qkv_sb, const T* __restrict__ cosv, const T* __restrict__ sinv,
+                   int64_t cs_sb, T* __restrict__ q_out, T* __restrict__ k_res, int64_t kr_sb, int64_t kr_sh,
+                   int64_t kr_st, T* __restrict__ values, int64_t v_sb, int64_t v_sh, int64_t v_st, int N, int Nk,
+                   int res_pos, int ctx_pos, const int* __restrict__ lengths, int G, int values_window, int res_cap,
+                   int value_cap) {
+  constexpr int H = kHeadDim / 2;
+  if (lengths) {
+    res_pos = lengths[1];
+    ctx_pos = values_window ? res_pos : lengths[0] * G + res_pos;
+  }
+  const bool slot_ok = res_pos >= 0 && res_pos < res_cap && ctx_pos >= 0 && ctx_pos < value_cap;
+  const int b = blockIdx.x, j = blockIdx.y, d = threadIdx.x;
+  const T* x = qkv + b * qkv_sb + static_cast<int64_t>(j) * kHeadDim;
+  if (j >= N + Nk) {                                        // value head: copy
+    if (!slot_ok) return;
+    T* dst = values + b * v_sb + (j - N - Nk) * v_sh + ctx_pos * v_st;
+    dst[d] = x[d]; dst[d + H] = x[d + H];
+    return;
+  }
+  const T* c = cosv + b * cs_sb;
+  const T* s = sinv + b * cs_sb;
+  const float lo = Elem<T>::to_float(x[d]), hi = Elem<T>::to_float(x[d + H]);
+  const float o_lo = Elem<T>::round(__fadd_rn(Elem<T>::round(__fmul_rn(lo, Elem<T>::to_float(c[d]))),
+                                              Elem<T>::round(__fmul_rn(-hi, Elem<T>::to_float(s[d])))));
+  const float o_hi = Elem<T>::round(__fadd_rn(Elem<T>::round(__fmul_rn(hi, Elem<T>::to_float(c[d + H]))),
+                                              Elem<T>::round(__fmul_rn(lo, Elem<T>::to_float(s[d + H])))));
+  T* dst;
+  if (j < N) dst = q_out + (static_cast<int64_t>(b) * N + j) * kHeadDim;
+  else {
+    if (!slot_ok) return;
+    dst = k_res + b * kr_sb + (j - N) * kr_sh + res_pos * kr_st;
+  }
+  dst[d] = Elem<T>::from_float(o_lo);
+  dst[d + H] = Elem<T>::from_float(o_hi);
+}
+}  // namespace
+
+int rope_append_device(const void* qkv, int64_t qkv_stride_b, const void* cosv, const void* sinv, int64_t cs_stride_b,
+                       void* q_out, void* k_res, const int64_t* kres_strides, void* values, const int64_t* v_strides,
+                       int B, int N, int Nk, int hd, int G, const int* lengths, int values_window, int res_cap,
+                       int value_cap, int res_pos, int ctx_pos, int dtype, cudaStream_t stream) {
+  if (!qkv || !cosv || !sinv || !q_out || !k_res || !values || !kres_strides || !v_strides) return PQ_ERR_INVALID;
+  if (B <= 0 || N <= 0 || Nk <= 0 || G <= 0 || res_cap <= 0 || value_cap <= 0 || !dtype_ok(dtype)) return PQ_ERR_INVALID;
+  if (!lengths && (res_pos < 0 || ctx_pos < 0 || res_pos >= res_cap || ctx_pos >= value_cap)) return PQ_ERR_INVALID;
+  if (hd != kHeadDim) return PQ_ERR_UNSUPPORTED;
+  const dim3 grid(static_cast<unsigned>(B), static_cast<unsigned>(N + 2 * Nk));
+#define PQ_ROPE(T)                                                                                                \
+  rope_append_kernel<T><<<grid, kHeadDim / 2, 0, stream>>>(                                                      \
+      static_cast<const T*>(qkv), qkv_stride_b, static_cast<const T*>(cosv), static_cast<const T*>(sinv),        \
+      cs_stride_b, static_cast<T*>(q_out), static_cast<T*>(k_res), kres_strides[0], kres_strides[1],             \
+      kres_strides[2], static_cast<T*>(values), v_strides[0], v_strides[1], v_strides[2], N, Nk, res_pos,        \
+      ctx_pos, lengths, G, values_window, res_cap, value_cap)
+  if (dtype == PQ_F32) PQ_ROPE(float);
+  else if (dtype == PQ_F16) PQ_ROPE(__half);
+  else PQ_ROPE(__nv_bfloat16);
+#undef PQ_ROPE
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream) {
   if (!mismatches_dev || which < 0 || which > 1) return PQ_ERR_INVALID;
   if (dtype != PQ_F16 && dtype != PQ_BF16) return PQ_ERR_INVALID;

@@ -144,13 +144,18 @@ def main():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        def model_step(tok_in, cos1, sin1, attend):
+        def model_step(tok_in, cos1, sin1, attend, fused_rope=False):
             x = embed[tok_in][:, None, :]
             for li, layer in enumerate(layers):
                 h = rms_norm(x, layer.n1)
-                q, k, v = split_qkv(F.linear(h, layer.qkv), 1)
-                q, k = apply_rope(q, cos1, sin1), apply_rope(k, cos1, sin1)
-                att = attend(caches[li], q, k, v)                           # (B, heads, 1, hd)
+                if fused_rope:
+                    # one kernel: rotate q and k, append k and v (positions from the device-side lengths)
+                    q = caches[li].rope_append_graph(F.linear(h, layer.qkv), cos1, sin1)
+                    att = caches[li].attend_graph(q)
+                else:
+                    q, k, v = split_qkv(F.linear(h, layer.qkv), 1)
+                    q, k = apply_rope(q, cos1, sin1), apply_rope(k, cos1, sin1)
+                    att = attend(caches[li], q, k, v)                       # (B, heads, 1, hd)
                 x = x + F.linear(att.transpose(1, 2).reshape(B, 1, heads * hd), layer.o)
                 x = x + mlp(layer, rms_norm(x, layer.n2))
             return F.linear(rms_norm(x[:, 0], final_norm), lm_head).argmax(-1)
@@ -166,7 +171,7 @@ def main():
 
             def graph_step():
                 cos1, sin1 = rope_tables(pos_dev, hd, theta, dev)
-                nxt = model_step(tok_buf, cos1, sin1, lambda c, q, k, v: c.decode_step_graph(q, k.contiguous(), v))
+                nxt = model_step(tok_buf, cos1, sin1, None, fused_rope=True)
                 tok_buf.copy_(nxt)
                 lengths[1:2].add_(1)
                 pos_dev.add_(1)

@@ -175,3 +175,43 @@ def test_one_captured_graph_replays_over_the_growing_cache(vbits):
     assert crossed
     for a, b in zip(graph.as_reference_tuple(), eager.as_reference_tuple()):
         assert (a is None and b is None) or (isinstance(a, int) and a == b) or torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("vbits", [0, 4])
+def test_fused_rope_append_equals_the_eager_ops(dt, vbits):
+    """pq_rope_append: rotate-half RoPE of the step's query and key heads + append of key and value, in one kernel,
+    bit-identical to `x * cos + rotate_half(x) * sin` followed by the plain append."""
+    from polarquant_b200.cache import PolarKVCache
+    dev = "cuda"
+    B, N, Nk, prompt = 3, 8, 2, 200
+    g = torch.Generator(device=dev).manual_seed(5)
+    keys = oracle.synth_keys(B, Nk, prompt, 128, dt, seed=6, device=dev)
+    vals = torch.randn(B, Nk, prompt, 128, device=dev, generator=g).to(dt)
+    lengths = torch.zeros(2, dtype=torch.int32, device=dev)
+    a = PolarKVCache(B, Nk, max_tokens=512, dtype=dt, vbits=vbits, lengths=lengths)
+    b = PolarKVCache(B, Nk, max_tokens=512, dtype=dt, vbits=vbits, lengths=lengths)
+    a.prefill(keys, vals); b.prefill(keys, vals); a.sync_lengths()
+    for step in range(3):
+        qkv = (torch.randn(B, 1, (N + 2 * Nk) * 128, device=dev, generator=g) * 2).to(dt)
+        ang = torch.rand(128, device=dev, generator=g) * 6.28
+        cos, sin = ang.cos().to(dt), ang.sin().to(dt)
+
+        def rope(x):
+            rot = torch.cat([-x[..., 64:], x[..., :64]], dim=-1)
+            return x * cos + rot * sin
+
+        q, k, v = qkv.split([N * 128, Nk * 128, Nk * 128], dim=-1)
+        q = q.view(B, 1, N, 128).transpose(1, 2)
+        k = k.view(B, 1, Nk, 128).transpose(1, 2)
+        v = v.view(B, 1, Nk, 128).transpose(1, 2)
+        want = a.decode_step_graph(rope(q).contiguous(), rope(k).contiguous(), v)
+        q_rot = b.rope_append_graph(qkv, cos, sin)
+        assert torch.equal(q_rot, rope(q))
+        got = b.attend_graph(q_rot)
+        assert torch.equal(got, want), step
+        assert torch.equal(a.k_res[:, :, :a.res_len + 1], b.k_res[:, :, :a.res_len + 1])
+        lengths[1:2].add_(1)
+        a.after_replay(); b.after_replay()
+    ta, tb = a.as_reference_tuple(), b.as_reference_tuple()
+    assert torch.equal(ta[0], tb[0]) and torch.equal(ta[6], tb[6])
