@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--q-heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, quantizer and CPU legs (profiler runs)")
+    ap.add_argument("--packed-values", action="store_true",
+                    help="time the step with the values packed to 4 bits as well (the reference's mixed class) "
+                         "instead of the headline configuration; implies --no-extras")
     return ap.parse_args()
 
 
@@ -224,7 +227,8 @@ def run_reference_arm(args, rank):
 def workload_config(args):
     return {"workload": f"Llama-3.1-8B-shaped GQA decode attention: batch {args.batch} per GPU, {args.q_heads} q / "
                         f"{args.kv_heads} kv heads, head_dim 128, ctx {args.ctx}, polar {args.rbits}/{args.tbits}, "
-                        f"group {args.group}, residual 128, bf16",
+                        f"group {args.group}, residual 128, bf16"
+                        + (", values packed to 4 bits per token" if getattr(args, "packed_values", False) else ""),
             "l2": "inputs of one step (1.36 GB at the default size) exceed the 126 MB L2; no flush needed",
             "sharding": "batch per GPU, no collective in the step"}
 
@@ -263,7 +267,19 @@ def main():
         assert lib.pq_event_create(ctypes.byref(e)) == 0
         return e
 
+    if args.packed_values:
+        args.no_extras = True
+        Lq = Nb * G
+        vc, vs, vm = pq.quantize_values(inp["v"][:, :, :Lq], layout="tiled")
+        v_res = inp["v"][:, :, Lq:].contiguous()
+        nbytes = nbytes - Lq * B * Nk * 256 + vc.numel() * 4 + 2 * vs.numel() * 2
+        inp["v"] = None
+
     def step(mid=None):
+        if args.packed_values:
+            return pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], v_res, rbits=args.rbits,
+                                       tbits=args.tbits, workspace=ws, mid_event=mid, value_codes=vc, value_scale=vs,
+                                       value_mn=vm)
         return pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"], rbits=args.rbits,
                                    tbits=args.tbits, workspace=ws, mid_event=mid)
 
@@ -328,7 +344,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT * B
                                      if (args.ctx, args.group, args.q_heads, args.kv_heads) == (32768, 128, 32, 8)
-                                     else None),
+                                     and not args.packed_values else None),
                          "traffic_note": "bytes per launch; ncu capture at batch 4 scaled by the batch",
                          "kernel": "decode_kernel (fused attention over packed keys)",
                          "peak_source": f"{peak_kind} copy bandwidth", "kernel_us": kavg * 1e3,

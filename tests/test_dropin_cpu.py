@@ -117,3 +117,53 @@ def test_benchmark_script_binds_to_our_entry(patched):
     bm = dropin.load_benchmark_matmul(REF, entry_module=rec)
     assert bm.attention_decode_forward_triton_impl.__self__ is rec
     assert callable(bm.test4polar) and bm.N == 32 and bm.D == 64
+
+
+def test_mixed_class_reaches_the_value_cache_entry_points(patched, monkeypatch):
+    """LlamaPolarMixedGroupAttention (models/modeling_llama_polar.py:160-292), unmodified: its two KIVI names
+    resolve to the overlay, which forwards the value-cache calls to `ops.quantize_values` / `ops.values_matmul`
+    (served here by the oracle) and refuses everything else KIVI offers."""
+    llama, _, rec, _ = patched
+    from polarquant_b200 import ops
+    from transformers import LlamaConfig
+    calls = []
+
+    def fake_quantize_values(v, vbits=4, layout="kivi"):
+        calls.append(("pack", tuple(v.shape), v.dtype, vbits, layout))
+        return oracle.quantize_values(v.contiguous(), vbits)
+
+    def fake_values_matmul(p, codes, scale, mn, vbits=4):
+        calls.append(("matmul", tuple(p.shape), tuple(codes.shape), codes.dtype, tuple(scale.shape), vbits))
+        return oracle.values_matmul(p, codes, scale, mn, vbits)
+
+    monkeypatch.setattr(ops, "quantize_values", fake_quantize_values)
+    monkeypatch.setattr(ops, "values_matmul", fake_values_matmul)
+    assert llama.cuda_bmm_fA_qB_outer.__module__ == "models.kivi_quant.matmul"
+    with pytest.raises(NotImplementedError):                      # a KIVI key-cache call: not part of the polar path
+        llama.cuda_bmm_fA_qB_outer(32, torch.zeros(1, 1, 1, 64), torch.zeros(1, 1, 64, 8, dtype=torch.int32),
+                                   torch.zeros(1, 1, 64, 4), torch.zeros(1, 1, 64, 4), 2)
+    with pytest.raises(NotImplementedError):
+        llama.triton_quantize_and_pack_along_last_dim(torch.zeros(1, 1, 128, 64), 32, 2)
+
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=256, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=100, head_dim=128)
+    torch.manual_seed(0)
+    attn = llama.LlamaPolarMixedGroupAttention(cfg, layer_idx=0).to(torch.bfloat16).eval()
+    B, L = 2, 300
+    hidden = torch.randn(B, L, 512).to(torch.bfloat16)
+    cos, sin = torch.ones(B, L, 128, dtype=torch.bfloat16), torch.zeros(B, L, 128, dtype=torch.bfloat16)
+    with torch.no_grad():
+        out, past = attn(hidden, attention_mask=None, past_key_value=None, position_embeddings=(cos, sin))
+        assert len(past) == 11 and past[7].shape == (B, 2, 256, 16) and past[6].shape == (B, 2, 44, 128)
+        for _ in range(2):
+            step = torch.randn(B, 1, 512).to(torch.bfloat16)
+            out, past = attn(step, attention_mask=None, past_key_value=past,
+                             position_embeddings=(cos[:, :1], sin[:, :1]))
+    assert out.shape == (B, 1, 512) and torch.isfinite(out.float()).all()
+    # prefill packs the 256 quantised tokens' values, one group of 128 channels per token, 4 bits
+    assert calls[0] == ("pack", (B, 2, 256, 128), torch.bfloat16, 4, "kivi")
+    # decode multiplies the probabilities of the packed tokens with per-query-head copies of the codes
+    kind, pshape, cshape, cdtype, sshape, bits = calls[1]
+    assert kind == "matmul" and pshape == (B, 4, 1, 256) and cshape == (B, 4, 256, 16) and cdtype == torch.int32
+    assert sshape == (B, 4, 256, 1) and bits == 4
+    assert [c[0] for c in calls] == ["pack", "matmul", "matmul"]
