@@ -35,6 +35,20 @@ __device__ __forceinline__ float min_nan(float a, float b) {
   return r;
 }
 
+// NaN-propagating max / min of two packed 16-bit pairs of type DT (exact: the operands are already values of DT)
+template <int DT> __device__ __forceinline__ uint32_t max2_nan(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if constexpr (DT == PQ_BF16) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <int DT> __device__ __forceinline__ uint32_t min2_nan(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if constexpr (DT == PQ_BF16) asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // four consecutive elements starting at p
 template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
 template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
@@ -175,7 +189,10 @@ __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)
 // NI > 0: the thread keeps phi and r of its NI tokens x 4 pairs in registers
 // (G == 16 * NI).  NI == 0: any G; phi and r are recomputed in the second pass.
 template <typename T, int NI>
-__global__ void __launch_bounds__(kQuantThreads)
+#ifndef PQ_QUANT_MIN_CTAS
+#define PQ_QUANT_MIN_CTAS 3
+#endif
+__global__ void __launch_bounds__(kQuantThreads, sizeof(T) == 2 ? PQ_QUANT_MIN_CTAS : 2)
 quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, int Nk, int nb, int G,
                 int rbits, int tbits, unsigned flags, uint8_t* __restrict__ codes, T* __restrict__ rscale,
                 T* __restrict__ rmn_out, T* __restrict__ tscale, T* __restrict__ tmn_out,
@@ -197,13 +214,48 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   const bool norm_sep = (flags & PQ_QUANT_NORM_FMA) == 0;
 
   constexpr int NR = NI > 0 ? NI : 1;
-  float phi[NR][4], rad[NR][4];
+  // 16-bit keys: angle and radius are values of T already, so the NI tokens a thread keeps between the two passes
+  // are held (and min/max-reduced) as packed pairs - half the registers, half the min/max instructions
+  constexpr bool kPacked = NI > 0 && E::kDtype != PQ_F32;
+  constexpr int DT16 = E::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
+  float phi[kPacked ? 1 : NR][4], rad[kPacked ? 1 : NR][4];
+  uint32_t phi_w[kPacked ? NR : 1][2], rad_w[kPacked ? NR : 1][2];
   float tmx[4], tmn[4], rmx[4], rmn[4];
 #pragma unroll
   for (int p = 0; p < 4; ++p) { tmx[p] = -INFINITY; tmn[p] = INFINITY; rmx[p] = -INFINITY; rmn[p] = INFINITY; }
 
   const int tok0 = 2 * warp + tsub;
-  if constexpr (NI > 0) {
+  if constexpr (kPacked) {
+    uint32_t tmx_w[2], tmn_w[2], rmx_w[2], rmn_w[2];
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const T* row = base + static_cast<int64_t>(tok0 + 16 * i) * sl;
+      float x[4], y[4];
+      load4<T>(row + p0, x);
+      load4<T>(row + p0 + kPairs, y);
+#pragma unroll
+      for (int p = 0; p < 4; p += 2) {
+        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
+        float ph[2], rd[2];
+        polar_of2<T>(xx, yy, wrap, norm_sep, ph, rd);
+        const uint32_t pw = pack2<DT16>(ph[0], ph[1]), rw = pack2<DT16>(rd[0], rd[1]);   // exact: already rounded
+        phi_w[i][p >> 1] = pw; rad_w[i][p >> 1] = rw;
+        if (i == 0) { tmx_w[p >> 1] = tmn_w[p >> 1] = pw; rmx_w[p >> 1] = rmn_w[p >> 1] = rw; }
+        else {
+          tmx_w[p >> 1] = max2_nan<DT16>(tmx_w[p >> 1], pw); tmn_w[p >> 1] = min2_nan<DT16>(tmn_w[p >> 1], pw);
+          rmx_w[p >> 1] = max2_nan<DT16>(rmx_w[p >> 1], rw); rmn_w[p >> 1] = min2_nan<DT16>(rmn_w[p >> 1], rw);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      float2 f;
+      f = unpack2<DT16>(tmx_w[k]); tmx[2 * k] = f.x; tmx[2 * k + 1] = f.y;
+      f = unpack2<DT16>(tmn_w[k]); tmn[2 * k] = f.x; tmn[2 * k + 1] = f.y;
+      f = unpack2<DT16>(rmx_w[k]); rmx[2 * k] = f.x; rmx[2 * k + 1] = f.y;
+      f = unpack2<DT16>(rmn_w[k]); rmn[2 * k] = f.x; rmn[2 * k + 1] = f.y;
+    }
+  } else if constexpr (NI > 0) {
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
       const T* row = base + static_cast<int64_t>(tok0 + 16 * i) * sl;
@@ -298,7 +350,13 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
       uint32_t word = 0;
 #pragma unroll
       for (int p = 0; p < 4; p += 2) {
-        const float pv[2] = {phi[i][p], phi[i][p + 1]}, rv[2] = {rad[i][p], rad[i][p + 1]};
+        float pv[2], rv[2];
+        if constexpr (kPacked) {
+          const float2 pf = unpack2<DT16>(phi_w[i][p >> 1]), rf = unpack2<DT16>(rad_w[i][p >> 1]);
+          pv[0] = pf.x; pv[1] = pf.y; rv[0] = rf.x; rv[1] = rf.y;
+        } else {
+          pv[0] = phi[i][p]; pv[1] = phi[i][p + 1]; rv[0] = rad[i][p]; rv[1] = rad[i][p + 1];
+        }
         const float tl[2] = {tmn[p], tmn[p + 1]}, ts[2] = {tstep[p], tstep[p + 1]}, tr[2] = {trcp[p], trcp[p + 1]};
         const float rl[2] = {rmn[p], rmn[p + 1]}, rs[2] = {rstep[p], rstep[p + 1]}, rr[2] = {rrcp[p], rrcp[p + 1]};
         unsigned th[2], rh[2];
