@@ -427,8 +427,9 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
     from polarquant_b200.cache import PolarKVCache
     res_steps = max(8, min(args.steps, 100))
     ctx0 = Nb * G + R - res_steps                      # the timed steps end at the benchmark context
+    lengths = torch.zeros(2, dtype=torch.int32, device=device)
     cache = PolarKVCache(B, Nk, max_tokens=Nb * G + R + 128, dtype=torch.bfloat16, device=device, rbits=args.rbits,
-                         tbits=args.tbits, group_size=G)
+                         tbits=args.tbits, group_size=G, lengths=lengths)
     gen = torch.Generator(device=device).manual_seed(11 + rank)
     for b0 in range(0, B, 4):                          # prefill in slices to bound temporaries
         kb = torch.randn(min(4, B - b0), Nk, ctx0, 128, device=device, generator=gen).to(torch.bfloat16)
@@ -439,20 +440,48 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
         sub.k_res, sub.values = cache.k_res[b0:b0 + 4], cache.values[b0:b0 + 4]
         sub.prefill(kb, inp["v"][b0:b0 + 4, :, :ctx0])
         cache.num_groups, cache.res_len = sub.num_groups, sub.res_len
-    hq = torch.randn(res_steps, B, N, 1, 128).to(torch.bfloat16).pin_memory()
-    hk = torch.randn(res_steps, B, Nk, 1, 128).to(torch.bfloat16).pin_memory()
-    hv = torch.randn(res_steps, B, Nk, 1, 128).to(torch.bfloat16).pin_memory()
-    dq, dk, dv = (torch.empty_like(t[0], device=device) for t in (hq, hk, hv))
+    cache.sync_lengths()
+    hq = torch.randn(B, N, 1, 128).to(torch.bfloat16).pin_memory()
+    hk = torch.randn(B, Nk, 1, 128).to(torch.bfloat16).pin_memory()
+    hv = torch.randn(B, Nk, 1, 128).to(torch.bfloat16).pin_memory()
+    dq, dk, dv = (torch.empty_like(t, device=device) for t in (hq, hk, hv))
+    dout = torch.empty(B, N, 1, 128, dtype=torch.bfloat16, device=device)
     hres = torch.empty(B, N, 1, 128, dtype=torch.bfloat16).pin_memory()
+
+    def resident_step():
+        # host -> device copies of the step's inputs, append + fused attention with the lengths read on the
+        # device, advance of the lengths, device -> host copy of the result
+        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
+        cache.decode_step_graph(dq, dk, dv, out=dout)
+        lengths[1:2].add_(1)
+        hres.copy_(dout, non_blocking=True)
+
+    # one captured graph replayed per step (what a serving loop does); eager launches if capture is refused
+    replay, graphed = resident_step, False
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            resident_step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        cache.sync_lengths()                           # the warm-up step is discarded
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            resident_step()
+        replay, graphed = cg.replay, True
+    except Exception:
+        torch.cuda.synchronize(device)
+        cache.sync_lengths()
     torch.cuda.synchronize(device)
     if world > 1:
         dist.barrier()
     a, b = new_event(), new_event()
     lib.pq_event_record(a, stream)
     for i in range(res_steps):
-        dq.copy_(hq[i], non_blocking=True); dk.copy_(hk[i], non_blocking=True); dv.copy_(hv[i], non_blocking=True)
-        o = cache.decode_step(dq, dk, dv)
-        hres.copy_(o, non_blocking=True)
+        replay()
+        if cache.after_replay():                       # window full: re-quantised in place, outside the graph
+            cache.sync_lengths()
     lib.pq_event_record(b, stream)
     torch.cuda.synchronize(device)
     lib.pq_event_elapsed_ms(a, b, ctypes.byref(ms))
@@ -465,9 +494,11 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
         "value": nbytes * world / (res_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": res_ms, "steps": res_steps,
         "tokens_per_s_per_layer": B * world / (res_ms * 1e-3),
         "h2d_bytes_per_step": (dq.numel() + dk.numel() + dv.numel()) * 2, "d2h_bytes_per_step": hres.numel() * 2,
-        "note": "PolarKVCache.decode_step: query / new key / new value copied from pinned host memory, appended in "
-                "place, fused attention over the resident cache (window re-quantised in place when full), output "
-                "copied back; context ends at the benchmark context"}
+        "cuda_graph": graphed,
+        "note": "PolarKVCache.decode_step_graph: query / new key / new value copied from pinned host memory, appended "
+                "in place, fused attention over the resident cache with the lengths read on the device (window "
+                "re-quantised in place when full), output copied back - one captured graph replayed per step; "
+                "context ends at the benchmark context"}
     del cache
 
     # ---- the same step repeated for about half a second: the power-capped regime ----

@@ -31,7 +31,7 @@ struct ValArgs {
   uint32_t* codes; int64_t c_sb, c_sh;          // byte strides; 64 bytes per token, tokens contiguous
   void* scale; void* mn; int64_t s_sb, s_sh;    // element strides; one element per token, tokens contiguous
   int Nk, T;
-  long long total;                              // B * Nk * T
+  int unit0;                                    // first (b * Nk + h) unit of this launch (grid.y counts from it)
   float inv_levels;
 };
 
@@ -84,16 +84,18 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
   const int sub = threadIdx.x & 15;
   const int lane = threadIdx.x & 31;
 #pragma unroll
+  // grid (token blocks, units): no per-thread division
+  const int unit = a.unit0 + blockIdx.y;
+  const int h = unit % a.Nk;
+  const int64_t b = unit / a.Nk;
+  const T* unit_in = static_cast<const T*>(a.v) + b * a.sb + h * a.sh + 8 * sub;
+#pragma unroll
   for (int it = 0; it < kValIters; ++it) {
-    const long long tok = (static_cast<long long>(blockIdx.x) * kValIters + it) * kTokPerIter + (threadIdx.x >> 4);
-    const bool ok = tok < a.total;
-    const long long tk = ok ? tok : 0;
-    const int t = static_cast<int>(tk % a.T);
-    const long long bh = tk / a.T;
-    const int h = static_cast<int>(bh % a.Nk);
-    const long long b = bh / a.Nk;
+    const int tok = (blockIdx.x * kValIters + it) * kTokPerIter + (threadIdx.x >> 4);
+    const bool ok = tok < a.T;
+    const int t = ok ? tok : 0;
     float v[8];
-    load8<T>(static_cast<const T*>(a.v) + b * a.sb + h * a.sh + static_cast<int64_t>(t) * a.st + 8 * sub, ok, v);
+    load8<T>(unit_in + static_cast<int64_t>(t) * a.st, ok, v);
     float mn = v[0], mx = v[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) { mn = min_nan(mn, v[i]); mx = max_nan(mx, v[i]); }
@@ -194,13 +196,16 @@ __global__ void __launch_bounds__(kMatThreads) values_matmul_kernel(const T* pro
 }
 
 template <typename T>
-int launch_quantize_values(const ValArgs& a, bool tiled, cudaStream_t s) {
-  const long long per_cta = static_cast<long long>(kTokPerIter) * kValIters;
-  const long long ctas = (a.total + per_cta - 1) / per_cta;
-  if (ctas > 0x7fffffffLL) return PQ_ERR_UNSUPPORTED;
-  if (tiled) quantize_values_kernel<T, true><<<static_cast<unsigned>(ctas), kValThreads, 0, s>>>(a);
-  else quantize_values_kernel<T, false><<<static_cast<unsigned>(ctas), kValThreads, 0, s>>>(a);
-  PQ_CUDA_TRY(cudaGetLastError());
+int launch_quantize_values(ValArgs a, long long units, bool tiled, cudaStream_t s) {
+  const int per_cta = kTokPerIter * kValIters;
+  const unsigned gx = static_cast<unsigned>((a.T + per_cta - 1) / per_cta);
+  for (long long u0 = 0; u0 < units; u0 += 65535) {          // grid.y is limited to 65535 units per launch
+    const unsigned gy = static_cast<unsigned>(units - u0 < 65535 ? units - u0 : 65535);
+    a.unit0 = static_cast<int>(u0);
+    if (tiled) quantize_values_kernel<T, true><<<dim3(gx, gy), kValThreads, 0, s>>>(a);
+    else quantize_values_kernel<T, false><<<dim3(gx, gy), kValThreads, 0, s>>>(a);
+    PQ_CUDA_TRY(cudaGetLastError());
+  }
   return PQ_OK;
 }
 
@@ -229,13 +234,14 @@ int quantize_values_device(const void* values, const int64_t strides[4], int B, 
     if (a.c_sb % 16 || a.c_sh % 16) return PQ_ERR_ALIGNMENT;
   }
   a.Nk = Nk; a.T = T;
-  a.total = static_cast<long long>(B) * Nk * T;
   a.inv_levels = 1.0f / 15.0f;
+  const long long units = static_cast<long long>(B) * Nk;
+  if (units > 0x7fffffffLL) return PQ_ERR_UNSUPPORTED;
   const bool tiled = layout == PQ_VALUES_TILED;
   switch (dtype) {
-    case PQ_F16: return launch_quantize_values<__half>(a, tiled, stream);
-    case PQ_BF16: return launch_quantize_values<__nv_bfloat16>(a, tiled, stream);
-    default: return launch_quantize_values<float>(a, tiled, stream);
+    case PQ_F16: return launch_quantize_values<__half>(a, units, tiled, stream);
+    case PQ_BF16: return launch_quantize_values<__nv_bfloat16>(a, units, tiled, stream);
+    default: return launch_quantize_values<float>(a, units, tiled, stream);
   }
 }
 
