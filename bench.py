@@ -178,13 +178,13 @@ def cpu_sample(args, seed=1002):
         algorithmic_bytes(1, N, Nk, Nb, G, R)
 
 
-def time_cpu(args, budget_s=20.0, max_reps=10):
+def time_cpu(args, limit_s=20.0, max_reps=10):
     import torch
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     sample, nbytes = cpu_sample(args)
     oracle_cpu_step(sample, args)                        # warm-up
-    times, t_end = [], time.perf_counter() + budget_s
+    times, t_end = [], time.perf_counter() + limit_s
     while len(times) < max_reps and (time.perf_counter() < t_end or len(times) < 2):
         t0 = time.perf_counter()
         oracle_cpu_step(sample, args)
