@@ -175,3 +175,49 @@ def test_packed_values_reproducible_and_masked():
     with pytest.raises(NotImplementedError):
         pq.decode_attention(q.half(), kres.half(), quant[0], *(t.half() for t in quant[1:]), v_res,
                             value_codes=vc, value_scale=vs, value_mn=vm)
+
+
+def test_full_size_step_with_packed_values():
+    """The benchmark shape (batch 16, 32 q / 8 kv heads, context 32768): the packed-value kernel against the
+    full-precision-value kernel fed with the dequantised values, reproducibility, and the sequence split + merge."""
+    import math
+    import polarquant_b200 as pq
+    B, N, Nk, Nb, grp, R = 16, 32, 8, 255, 128, 128
+    dev, dt = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(1002)
+    scale = torch.exp(torch.empty(Nk, 128, device=dev).uniform_(math.log(0.5), math.log(8.0), generator=g))
+    q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+    v = torch.randn(B, Nk, Nb * grp + R, 128, device=dev, generator=g).to(dt)
+    kres = (torch.randn(B, Nk, R, 128, device=dev, generator=g) * scale[None, :, None]).to(dt)
+    quant = [[] for _ in range(5)]
+    for b in range(B):
+        kb = (torch.randn(1, Nk, Nb * grp, 128, device=dev, generator=g) * scale[None, :, None]).to(dt)
+        for lst, t in zip(quant, pq.quantize_and_pack_nbit(kb, 4, 4, grp)):
+            lst.append(t)
+    quant = [torch.cat(lst, dim=0) for lst in quant]
+    tq = Nb * grp
+    vc, vs, vm = pq.quantize_values(v[:, :, :tq], layout="tiled")
+    kivi = pq.values_relayout(vc, "kivi")
+    assert torch.equal(pq.values_relayout(kivi, "tiled"), vc)
+    v_res = v[:, :, tq:].contiguous()
+    kw = dict(value_codes=vc, value_scale=vs, value_mn=vm)
+    got = pq.decode_attention(q, kres, *quant, v_res, out_dtype=torch.float32, **kw)
+    assert torch.equal(got, pq.decode_attention(q, kres, *quant, v_res, out_dtype=torch.float32, **kw))
+    # the same attention over the dequantised values (batch slices bound the fp32 temporaries)
+    for b in range(0, B, 4):
+        sl = slice(b, b + 4)
+        v_hat = oracle.dequantize_values(kivi[sl], vs[sl], vm[sl])
+        v_hat = torch.cat([v_hat.to(dt), v_res[sl]], dim=2)
+        want = pq.decode_attention(q[sl], kres[sl], *[t[sl] for t in quant], v_hat, out_dtype=torch.float32)
+        diff = (got[sl] - want).abs()
+        assert float(diff.max()) <= ATTN_MAX_ABS and float(diff.mean()) <= ATTN_MEAN_ABS, (b, float(diff.max()))
+    # split after 128 groups: two calls with log-sum-exp, merged
+    h = 128
+    o0, l0 = pq.decode_attention(q, None, *[t[:, :, :h] for t in quant], None, out_dtype=torch.float32,
+                                 return_lse=True, value_codes=vc[:, :, :h * grp], value_scale=vs[:, :, :h * grp],
+                                 value_mn=vm[:, :, :h * grp])
+    o1, l1 = pq.decode_attention(q, kres, *[t[:, :, h:] for t in quant], v_res, out_dtype=torch.float32,
+                                 return_lse=True, value_codes=vc[:, :, h * grp:], value_scale=vs[:, :, h * grp:],
+                                 value_mn=vm[:, :, h * grp:])
+    merged = pq.merge_lse(torch.stack([o0[:, :, 0], o1[:, :, 0]]), torch.stack([l0, l1]))
+    assert float((merged - got[:, :, 0]).abs().max()) <= 8e-3
