@@ -164,6 +164,8 @@ class PolarKVCache:
         self._quantize_into(key_states[:, :, :nq], 0)
         self.num_groups = nq // self.G
         self.res_len = rest
+        if self.lengths is not None:
+            self.sync_lengths()
         if rest:
             self.k_res[:, :, :rest].copy_(key_states[:, :, nq:])
         if self.vbits:
@@ -212,6 +214,10 @@ class PolarKVCache:
         _lib.check(rc, "pq_decode_attention")
         if self.res_len == self.RL:                      # window full: quantise it in place (:83-92)
             self._requantize_window()
+            if self.lengths is not None:
+                self.sync_lengths()
+        elif self.lengths is not None:                   # host-driven step on a cache that also has device lengths
+            self.lengths[1:2].add_(1)
         return out
 
     # ------------------------------------------------------------------ CUDA-graph replay
@@ -331,6 +337,10 @@ class PolarKVCache:
                                    workspace=self.workspace, **kw)
         if self.res_len == self.RL:
             self._requantize_window()
+            if self.lengths is not None:
+                self.sync_lengths()
+        elif self.lengths is not None:
+            self.lengths[1:2].add_(1)
         return out
 
     def as_reference_tuple(self):

@@ -112,7 +112,9 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
     constexpr bool kFast = Elem<T>::kDtype != PQ_F32;
     const float rcp = __frcp_rn(scale);
     const bool scale_ok = mid_range(scale);
-    uint32_t word = 0;
+    // levels are assembled with FMAs (level * 16^k summed exactly in fp32, four levels per accumulator): the
+    // multiply-add pipe has room, the integer/logic pipe is the one this kernel saturates
+    float acc_lo = 0.0f, acc_hi = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
       float d0, d1, q0, q1;
@@ -129,12 +131,17 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
         q0 = __fdiv_rn(d0, scale); q1 = __fdiv_rn(d1, scale);
       }
       round2<T>(q0, q1, q0, q1);
-      // fmaxf / fminf return the other operand for NaN: a NaN quotient becomes level 0, as the cast does in torch
-      const float r0 = __fadd_rn(fminf(fmaxf(q0, 0.0f), 15.0f), 12582912.0f);
-      const float r1 = __fadd_rn(fminf(fmaxf(q1, 0.0f), 15.0f), 12582912.0f);
-      word |= (__float_as_uint(r0) & 0xfu) << (4 * i);
-      word |= (__float_as_uint(r1) & 0xfu) << (4 * i + 4);
+      // fmaxf / fminf return the other operand for NaN: a NaN quotient becomes level 0, as the cast does in torch;
+      // adding and subtracting 1.5 * 2^23 rounds half to even
+      const float r0 = __fsub_rn(__fadd_rn(fminf(fmaxf(q0, 0.0f), 15.0f), 12582912.0f), 12582912.0f);
+      const float r1 = __fsub_rn(__fadd_rn(fminf(fmaxf(q1, 0.0f), 15.0f), 12582912.0f), 12582912.0f);
+      const float w0 = static_cast<float>(1u << (4 * (i & 3))), w1 = static_cast<float>(1u << (4 * (i & 3) + 4));
+      if (i < 4) { acc_lo = __fmaf_rn(r0, w0, acc_lo); acc_lo = __fmaf_rn(r1, w1, acc_lo); }
+      else { acc_hi = __fmaf_rn(r0, w0, acc_hi); acc_hi = __fmaf_rn(r1, w1, acc_hi); }
     }
+    // both sums are integers below 2^16: after adding 2^23 they sit in the low mantissa bits
+    uint32_t word = __byte_perm(__float_as_uint(__fadd_rn(acc_lo, 8388608.0f)),
+                                __float_as_uint(__fadd_rn(acc_hi, 8388608.0f)), 0x5410);
     if constexpr (TILED) word = to_tiled_word(word, lane);
     if (ok) {
       char* row = reinterpret_cast<char*>(a.codes) + b * a.c_sb + h * a.c_sh + static_cast<int64_t>(t) * 64;

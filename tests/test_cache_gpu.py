@@ -115,8 +115,13 @@ def test_in_place_cache_with_packed_values_tracks_the_mixed_reference_state(prom
     q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
     k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=9, device=dev)
     mask = torch.ones(B, cache.seq_len + 1, device=dev)
+    mask[0, :150] = 0                                   # left padding of the first sequence
+    kres = torch.cat([kres, k_new], dim=2)
+    vres = torch.cat([vres, k_new], dim=2)
     a = cache.decode_step(q, k_new, k_new, attention_mask=mask)
-    assert torch.isfinite(a.float()).all()
+    want = oracle.decode_attention_mixed(q, kres, *(ref or (None,) * 5), *(vref or (None,) * 3), vres,
+                                         attention_mask=mask)
+    check_mixed(a, want, "masked step through the general path")
 
 
 @pytest.mark.parametrize("vbits", [0, 4])

@@ -26,7 +26,7 @@ def test_shard_range_is_balanced_and_covers_everything():
         shard_range(4, 2, 2)
 
 
-def _worker(rank, world, port, nb, result_queue):
+def _worker(rank, world, port, nb, result_queue, mixed=False):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -51,24 +51,37 @@ def _worker(rank, world, port, nb, result_queue):
         my_v = torch.cat(my_v, dim=2)
 
         def attend(q_, kres_, packed_, v_, **kw):
+            if kw:                                           # packed values travel as keyword arguments
+                return oracle.decode_attention_mixed(q_, kres_, *packed_, kw["value_codes"], kw["value_scale"],
+                                                     kw["value_mn"], v_, faithful_rounding=False, return_lse=True)
             return oracle.decode_attention(q_, kres_, *packed_, v_, faithful_rounding=False, return_lse=True)
 
         def merge(outs, lses, out_dtype):
             return oracle.merge_lse(outs, lses)[0].to(out_dtype)
 
+        kw = {}
+        if mixed and nb:
+            # values of the packed tokens are packed too; only the residual window's owner holds full-precision ones
+            vc, vs, vm = oracle.quantize_values(v[:, :, :nb * G].contiguous())
+            want = oracle.decode_attention_mixed(q, kres, *packed, vc, vs, vm, v[:, :, nb * G:],
+                                                 faithful_rounding=False)
+            my_v = v[:, :, nb * G:] if owns_res else None
+            if g1 > g0:
+                kw = dict(value_codes=vc[:, :, g0 * G:g1 * G], value_scale=vs[:, :, g0 * G:g1 * G],
+                          value_mn=vm[:, :, g0 * G:g1 * G])
         got = pqd.sequence_parallel_decode(q, kres if owns_res else None, my_packed, my_v, out_dtype=torch.float32,
-                                           attend=attend, merge=merge)
+                                           attend=attend, merge=merge, **kw)
         result_queue.put((rank, float((got - want).abs().max()), tuple(got.shape)))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,nb", [(2, 6), (3, 2), (2, 0)])
-def test_sequence_split_over_gloo_matches_the_unsplit_result(world, nb):
+@pytest.mark.parametrize("world,nb,mixed", [(2, 6, False), (3, 2, False), (2, 0, False), (2, 6, True)])
+def test_sequence_split_over_gloo_matches_the_unsplit_result(world, nb, mixed):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() % 2000) + world * 7 + nb
-    procs = [ctx.Process(target=_worker, args=(r, world, port, nb, q)) for r in range(world)]
+    port = 29500 + (os.getpid() % 2000) + world * 7 + nb + (50 if mixed else 0)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, nb, q, mixed)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
