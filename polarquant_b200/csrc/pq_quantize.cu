@@ -151,7 +151,7 @@ __device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[
 }
 
 // floor(RN(RN(v - lo) / step)) clamped to [0, top], for two values.  `rstep` is the correctly rounded
-// reciprocal of `step`; the product is within 1.5 ulp of the IEEE quotient and is used when it rounds safely.
+// reciprocal of `step` (guarded_rcp); the product is within 1.5 ulp of the IEEE quotient and is used when it rounds safely.
 // A quotient that is not below 256 (inf, NaN from a zero step, ...) takes the exact division and cast.
 template <typename T, bool FAST = true, bool FORCE = false>
 __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)[2], const float (&step)[2],
@@ -164,8 +164,8 @@ __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       q[k] = d[k] * rstep[k];
-      // the step must be an ordinary number, or its reciprocal has lost precision (the test is loop-invariant)
-      ok[k] = mid_range(step[k]) && q[k] < 256.0f && rounds_safely<T>(q[k]);
+      // rstep is guarded_rcp(step): NaN unless the step is an ordinary number, and NaN fails the comparison
+      ok[k] = q[k] < 256.0f && rounds_safely<T>(q[k]);
     }
   }
   if constexpr (!kFast) {
@@ -330,8 +330,8 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
     // dividing by a power of two equals multiplying by its exact reciprocal
     tstep[p] = E::round(__fmul_rn(E::round(__fsub_rn(tmx[p], tmn[p])), inv_t));
     rstep[p] = E::round(__fmul_rn(E::round(__fsub_rn(rmx[p], rmn[p])), inv_r));
-    trcp[p] = __frcp_rn(tstep[p]);
-    rrcp[p] = __frcp_rn(rstep[p]);
+    trcp[p] = guarded_rcp(tstep[p]);
+    rrcp[p] = guarded_rcp(rstep[p]);
   }
   if (warp == 0 && tsub == 0) {
     const int64_t so = b * s_sb + h * s_sh + static_cast<int64_t>(j) * kPairs + p0;
@@ -414,7 +414,7 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
       const bool same_r = (r0[0] == r1[0]) || (r0[0] != r0[0] && r1[0] != r1[0]);
       bad += !(same_p && same_r);
     } else {
-      const float v[2] = {x, x}, lo[2] = {0.0f, 0.0f}, st[2] = {y, y}, rc[2] = {__frcp_rn(y), __frcp_rn(y)};
+      const float v[2] = {x, x}, lo[2] = {0.0f, 0.0f}, st[2] = {y, y}, rc[2] = {guarded_rcp(y), guarded_rcp(y)};
       unsigned a[2], b[2];
       level_of2<T, true, true>(v, lo, st, rc, 255u, a);
       level_of2<T, false>(v, lo, st, rc, 255u, b);

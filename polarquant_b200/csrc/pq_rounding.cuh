@@ -47,6 +47,13 @@ template <typename T> __device__ __forceinline__ void round2(float a, float b, f
   else { const float2 f = unpack2<Elem<T>::kDtype>(pack2<Elem<T>::kDtype>(a, b)); ra = f.x; rb = f.y; }
 }
 
+// Reciprocal for the multiply-instead-of-divide fast path: correctly rounded for an ordinary divisor, NaN otherwise
+// (zero, denormal, huge, NaN), so that every product with it fails the "quotient < 256" test and takes the exact
+// division - the divisor's validity costs nothing per element.
+__device__ __forceinline__ float guarded_rcp(float step) {
+  return mid_range(step) ? __frcp_rn(step) : __int_as_float(0x7fc00000);
+}
+
 // exact IEEE quotient, out of line: taken by a fraction of a percent of the items
 __device__ __noinline__ float div_exact(float a, float b) { return __fdiv_rn(a, b); }
 

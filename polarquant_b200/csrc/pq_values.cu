@@ -110,8 +110,7 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
     // the IEEE division otherwise and for fp32.  Roundings are packed conversions, the final round-half-even and the
     // conversion to an integer are one addition of 1.5 * 2^23: nothing per element runs on the quarter-rate pipe.
     constexpr bool kFast = Elem<T>::kDtype != PQ_F32;
-    const float rcp = __frcp_rn(scale);
-    const bool scale_ok = mid_range(scale);
+    const float rcp = guarded_rcp(scale);
     // levels are assembled with FMAs (level * 16^k summed exactly in fp32, four levels per accumulator): the
     // multiply-add pipe has room, the integer/logic pipe is the one this kernel saturates
     float acc_lo = 0.0f, acc_hi = 0.0f;
@@ -121,8 +120,8 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
       round2<T>(__fsub_rn(v[i], mn), __fsub_rn(v[i + 1], mn), d0, d1);
       if constexpr (kFast) {
         q0 = d0 * rcp; q1 = d1 * rcp;
-        const bool ok0 = scale_ok && q0 < 256.0f && rounds_safely<T>(q0);
-        const bool ok1 = scale_ok && q1 < 256.0f && rounds_safely<T>(q1);
+        const bool ok0 = q0 < 256.0f && rounds_safely<T>(q0);
+        const bool ok1 = q1 < 256.0f && rounds_safely<T>(q1);
         if (!(ok0 && ok1)) {
           if (!ok0) q0 = div_exact(d0, scale);
           if (!ok1) q1 = div_exact(d1, scale);
