@@ -167,3 +167,28 @@ def test_mixed_class_reaches_the_value_cache_entry_points(patched, monkeypatch):
     assert kind == "matmul" and pshape == (B, 4, 1, 256) and cshape == (B, 4, 256, 16) and cdtype == torch.int32
     assert sshape == (B, 4, 256, 1) and bits == 4
     assert [c[0] for c in calls] == ["pack", "matmul", "matmul"]
+
+
+def test_snapkv_class_runs_on_the_same_two_entry_points(patched):
+    """LlamaSnapKVAttention (models/modeling_llama_polar.py:295-443), unmodified: its prompt-side token selection is
+    plain torch; what reaches this package is the quantizer call on the selected keys (1024 + 128 of them) and the
+    same decode entry point as the base class."""
+    llama, _, rec, quant_calls = patched
+    from transformers import LlamaConfig
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=256, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=100, head_dim=128)
+    torch.manual_seed(0)
+    attn = llama.LlamaSnapKVAttention(cfg, layer_idx=0).to(torch.bfloat16).eval()
+    L = 1300                                              # longer than max_capacity_prompt = 1024 + 128
+    hidden = torch.randn(1, L, 512).to(torch.bfloat16)
+    cos, sin = torch.ones(1, L, 128, dtype=torch.bfloat16), torch.zeros(1, L, 128, dtype=torch.bfloat16)
+    n_calls = len(rec.calls)
+    with torch.no_grad():
+        out, past = attn(hidden, attention_mask=None, past_key_value=None, position_embeddings=(cos, sin))
+        # 1152 keys survive the selection: all of them are whole groups, nothing stays in full precision
+        assert past[0] is None and past[1].shape == (1, 2, 9, 128, 64) and past[6].shape == (1, 2, 1152, 128)
+        step = torch.randn(1, 1, 512).to(torch.bfloat16)
+        out, past = attn(step, attention_mask=None, past_key_value=past, position_embeddings=(cos[:, :1], sin[:, :1]))
+    assert quant_calls[-1][0] == (1, 2, 1152, 128)
+    assert len(rec.calls) == n_calls + 1 and rec.calls[-1]["idx"][0] == (1, 2, 9, 128, 64)
+    assert out.shape == (1, 1, 512) and torch.isfinite(out.float()).all()
