@@ -83,7 +83,6 @@ template <typename T, bool TILED>
 __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValArgs a) {
   const int sub = threadIdx.x & 15;
   const int lane = threadIdx.x & 31;
-#pragma unroll
   // grid (token blocks, units): no per-thread division
   const int unit = a.unit0 + blockIdx.y;
   const int h = unit % a.Nk;
