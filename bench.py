@@ -433,13 +433,7 @@ def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):
     gen = torch.Generator(device=device).manual_seed(11 + rank)
     for b0 in range(0, B, 4):                          # prefill in slices to bound temporaries
         kb = torch.randn(min(4, B - b0), Nk, ctx0, 128, device=device, generator=gen).to(torch.bfloat16)
-        sub = PolarKVCache.__new__(PolarKVCache)
-        sub.__dict__.update(cache.__dict__)
-        sub.B = kb.shape[0]
-        sub.codes, sub.scales = cache.codes[b0:b0 + 4], [t[b0:b0 + 4] for t in cache.scales]
-        sub.k_res, sub.values = cache.k_res[b0:b0 + 4], cache.values[b0:b0 + 4]
-        sub.prefill(kb, inp["v"][b0:b0 + 4, :, :ctx0])
-        cache.num_groups, cache.res_len = sub.num_groups, sub.res_len
+        cache.prefill(kb, inp["v"][b0:b0 + 4, :, :ctx0], batch_start=b0)
     cache.sync_lengths()
     hq = torch.randn(B, N, 1, 128).to(torch.bfloat16).pin_memory()
     hk = torch.randn(B, Nk, 1, 128).to(torch.bfloat16).pin_memory()

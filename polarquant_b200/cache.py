@@ -105,9 +105,9 @@ class PolarKVCache:
         return self.num_groups * self.G + self.res_len
 
     # ------------------------------------------------------------------ writes
-    def _quantize_into(self, keys: torch.Tensor, first_group: int) -> None:
-        """Quantise ``keys`` (B, Nk, n*G, 128; any strides with unit inner stride) into groups
-        [first_group, first_group + n) of the code and scale buffers."""
+    def _quantize_into(self, keys: torch.Tensor, first_group: int, batch_start: int = 0) -> None:
+        """Quantise ``keys`` (b, Nk, n*G, 128; any strides with unit inner stride) into groups
+        [first_group, first_group + n) of the code and scale buffers of sequences [batch_start, batch_start + b)."""
         n = keys.shape[2] // self.G
         if n == 0:
             return
@@ -121,17 +121,17 @@ class PolarKVCache:
         out_strides = (ctypes.c_int64 * 4)(self.codes.stride(0), self.codes.stride(1),
                                            self.scales[0].stride(0), self.scales[0].stride(1))
         es = self.scales[0].element_size()
-        code_ptr = self.codes.data_ptr() + first_group * self.G * 64
-        scale_ptrs = [s.data_ptr() + first_group * 64 * es for s in self.scales]
+        code_ptr = self.codes.data_ptr() + first_group * self.G * 64 + batch_start * self.codes.stride(0)
+        scale_ptrs = [s.data_ptr() + (first_group * 64 + batch_start * s.stride(0)) * es for s in self.scales]
         with ops._on_device(dev):
-            rc = lib.pq_quantize_into(keys.data_ptr(), in_strides, self.B, self.Nk, n * self.G, 128, self.G,
+            rc = lib.pq_quantize_into(keys.data_ptr(), in_strides, keys.shape[0], self.Nk, n * self.G, 128, self.G,
                                       self.rbits, self.tbits, ops._DT[keys.dtype], 0, code_ptr, *scale_ptrs,
                                       out_strides, ops._stream(dev))
         _lib.check(rc, "pq_quantize_into")
 
-    def _quantize_values_into(self, values: torch.Tensor, first_token: int) -> None:
-        """Pack ``values`` (B, Nk, n, 128; unit inner stride) into tokens [first_token, first_token + n) of the
-        packed value buffers (models/modeling_llama_polar.py:242,285)."""
+    def _quantize_values_into(self, values: torch.Tensor, first_token: int, batch_start: int = 0) -> None:
+        """Pack ``values`` (b, Nk, n, 128; unit inner stride) into tokens [first_token, first_token + n) of the
+        packed value buffers of sequences [batch_start, batch_start + b) (models/modeling_llama_polar.py:242,285)."""
         n = values.shape[2]
         if n == 0:
             return
@@ -143,37 +143,42 @@ class PolarKVCache:
                                            self.v_scale.stride(0), self.v_scale.stride(1))
         es = self.v_scale.element_size()
         with ops._on_device(values.device):
-            rc = lib.pq_quantize_values(values.data_ptr(), in_strides, self.B, self.Nk, n, 128, self.vbits,
+            cb, sb = batch_start * self.v_codes.stride(0) * 4, batch_start * self.v_scale.stride(0) * es
+            rc = lib.pq_quantize_values(values.data_ptr(), in_strides, values.shape[0], self.Nk, n, 128, self.vbits,
                                         ops._DT[values.dtype], _lib.PQ_VALUES_TILED,
-                                        self.v_codes.data_ptr() + first_token * 64,
-                                        self.v_scale.data_ptr() + first_token * es,
-                                        self.v_mn.data_ptr() + first_token * es, out_strides,
+                                        self.v_codes.data_ptr() + first_token * 64 + cb,
+                                        self.v_scale.data_ptr() + first_token * es + sb,
+                                        self.v_mn.data_ptr() + first_token * es + sb, out_strides,
                                         ops._stream(values.device))
         _lib.check(rc, "pq_quantize_values")
 
-    def prefill(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
-        """Store a prompt: keys/values (B, Nk, L, 128), strided views allowed (the (B, L, Nk, hd) layout the
+    def prefill(self, key_states: torch.Tensor, value_states: torch.Tensor, batch_start: int = 0) -> None:
+        """Store a prompt: keys/values (b, Nk, L, 128), strided views allowed (the (B, L, Nk, hd) layout the
         projections produce).  The first L - L % residual_length keys are quantised, the rest stay in full
-        precision, as at models/modeling_llama_polar.py:116-126."""
-        length = key_states.shape[2]
+        precision, as at models/modeling_llama_polar.py:116-126.  ``batch_start`` places a chunk of b <= B
+        sequences (chunked prefill); every chunk must have the same length L, which becomes the cache's."""
+        bsz, _, length, _ = key_states.shape
         if length > self.max_tokens:
             raise RuntimeError("prompt longer than the cache")
+        if batch_start < 0 or batch_start + bsz > self.B:
+            raise ValueError("batch chunk does not fit the cache")
+        sl = slice(batch_start, batch_start + bsz)
         rest = length % self.RL
         nq = length - rest
         self.num_groups = 0
-        self._quantize_into(key_states[:, :, :nq], 0)
+        self._quantize_into(key_states[:, :, :nq], 0, batch_start)
         self.num_groups = nq // self.G
         self.res_len = rest
         if self.lengths is not None:
             self.sync_lengths()
         if rest:
-            self.k_res[:, :, :rest].copy_(key_states[:, :, nq:])
+            self.k_res[sl, :, :rest].copy_(key_states[:, :, nq:])
         if self.vbits:
-            self._quantize_values_into(value_states[:, :, :nq].to(self.dtype), 0)
+            self._quantize_values_into(value_states[:, :, :nq].to(self.dtype), 0, batch_start)
             if rest:
-                self.values[:, :, :rest].copy_(value_states[:, :, nq:])
+                self.values[sl, :, :rest].copy_(value_states[:, :, nq:])
         else:
-            self.values[:, :, :length].copy_(value_states)
+            self.values[sl, :, :length].copy_(value_states)
 
     def decode_step(self, query_states: torch.Tensor, key_new: torch.Tensor, value_new: torch.Tensor,
                     attention_mask=None, sm_scale=None, out_dtype=None) -> torch.Tensor:

@@ -123,16 +123,7 @@ def main():
                 x = x + F.linear(att.transpose(1, 2).reshape(x.shape[0], args.prompt, heads * hd), layer.o)
                 x = x + mlp(layer, rms_norm(x, layer.n2))
                 # store this chunk's keys / values in the layer's cache (strided (B, L, Nk, hd) views, read in place)
-                sub = PolarKVCache.__new__(PolarKVCache)
-                sub.__dict__.update(caches[li].__dict__)
-                sub.B = x.shape[0]
-                sub.codes, sub.scales = caches[li].codes[sl], [t[sl] for t in caches[li].scales]
-                sub.k_res, sub.values = caches[li].k_res[sl], caches[li].values[sl]
-                if args.vbits:
-                    sub.v_codes, sub.v_scale, sub.v_mn = (t[sl] for t in (caches[li].v_codes, caches[li].v_scale,
-                                                                           caches[li].v_mn))
-                sub.prefill(k, v)
-                caches[li].num_groups, caches[li].res_len = sub.num_groups, sub.res_len
+                caches[li].prefill(k, v, batch_start=c0)
             last_hidden[sl] = x[:, -1]
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0

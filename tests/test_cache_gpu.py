@@ -220,3 +220,24 @@ def test_fused_rope_append_equals_the_eager_ops(dt, vbits):
         a.after_replay(); b.after_replay()
     ta, tb = a.as_reference_tuple(), b.as_reference_tuple()
     assert torch.equal(ta[0], tb[0]) and torch.equal(ta[6], tb[6])
+
+
+@pytest.mark.parametrize("vbits", [0, 4])
+def test_chunked_prefill_fills_the_same_cache(vbits):
+    from polarquant_b200.cache import PolarKVCache
+    dev, dt = "cuda", torch.bfloat16
+    B, Nk, L = 5, 2, 300
+    g = torch.Generator(device=dev).manual_seed(3)
+    k_blnh = oracle.synth_keys(B, L, Nk, 128, dt, seed=4, device=dev)
+    v_blnh = torch.randn(B, L, Nk, 128, device=dev, generator=g).to(dt)
+    keys, vals = k_blnh.transpose(1, 2), v_blnh.transpose(1, 2)
+    whole = PolarKVCache(B, Nk, max_tokens=512, dtype=dt, vbits=vbits)
+    parts = PolarKVCache(B, Nk, max_tokens=512, dtype=dt, vbits=vbits)
+    whole.prefill(keys, vals)
+    for b0 in range(0, B, 2):
+        parts.prefill(keys[b0:b0 + 2], vals[b0:b0 + 2], batch_start=b0)
+    assert (parts.num_groups, parts.res_len) == (whole.num_groups, whole.res_len) == (2, 44)
+    for a, b in zip(whole.as_reference_tuple(), parts.as_reference_tuple()):
+        assert (isinstance(a, int) and a == b) or torch.equal(a, b)
+    with pytest.raises(ValueError):
+        parts.prefill(keys[:2], vals[:2], batch_start=4)
