@@ -88,6 +88,25 @@ int pq_cache_append_dyn(const void* k_new, const void* v_new, const int64_t in_s
                         void* stream);
 
 /*
+ * Re-quantisation of a full residual window with everything decided on the device, so that it can sit inside a
+ * replayed CUDA graph: same arguments as pq_quantize_into / pq_quantize_values (L = T = the window length, pass the
+ * BASE pointers of the cache buffers, out_strides required), plus lengths = {token groups, residual tokens}.  The
+ * kernels do nothing unless lengths[1] + r_add equals the window length, and then write groups lengths[0]..
+ * (tokens lengths[0] * G ..) of every (b, h) unit; max_groups / max_tokens bound what a unit can hold (beyond that
+ * nothing is written).  pq_lengths_advance is the matching bookkeeping step: residual + 1, or - when that fills the
+ * window - groups += full / G and residual = 0.  Replaces the `% self.residual_length == 0` branches of the
+ * reference's decode step (models/modeling_llama_polar.py:83-92, 240-248) for a device-driven loop.
+ */
+int pq_quantize_into_dyn(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
+                         int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
+                         void* tmn, const int64_t out_strides[4], int max_groups, const int* lengths, int r_add,
+                         void* stream);
+int pq_quantize_values_dyn(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
+                           int dtype, int layout, void* codes, void* scale, void* mn, const int64_t out_strides[4],
+                           int G, int max_tokens, const int* lengths, int r_add, void* stream);
+int pq_lengths_advance(int* lengths, int full, int G, void* stream);
+
+/*
  * Rotary embedding of one decode token fused with the cache append.  qkv (B, (N + 2 Nk) * hd) is the fused
  * projection output of the step, [query heads | key heads | value heads], row stride qkv_stride_b elements; cos /
  * sin hold hd elements of `dtype` per sequence (cs_stride_b elements apart, 0 = shared).  Query heads are rotated

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "pq_decode_attention_static", "pq_decode_static_scratch_bytes", "pq_selftest_quantizer", "pq_quantize_into", "pq_cache_append",
     "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
     "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn", "pq_rope_append",
+    "pq_quantize_into_dyn", "pq_quantize_values_dyn", "pq_lengths_advance",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -81,6 +82,15 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_cache_append_dyn.restype = _int
     lib.pq_cache_append_dyn.argtypes = [_vp, _vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _vp,
                                         ctypes.POINTER(_i64), _int, _int, _int, _int, _vp, _int, _int, _int, _int, _vp]
+    lib.pq_quantize_into_dyn.restype = _int
+    lib.pq_quantize_into_dyn.argtypes = [_vp, ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _int, _int,
+                                         ctypes.c_uint, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_i64), _int, _vp,
+                                         _int, _vp]
+    lib.pq_quantize_values_dyn.restype = _int
+    lib.pq_quantize_values_dyn.argtypes = [_vp, ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _int,
+                                           _vp, _vp, _vp, ctypes.POINTER(_i64), _int, _int, _vp, _int, _vp]
+    lib.pq_lengths_advance.restype = _int
+    lib.pq_lengths_advance.argtypes = [_vp, _int, _int, _vp]
     lib.pq_rope_append.restype = _int
     lib.pq_rope_append.argtypes = [_vp, _i64, _vp, _vp, _i64, _vp, _vp, ctypes.POINTER(_i64), _vp,
                                    ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _vp, _int, _int, _int, _int,
@@ -140,7 +150,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 3:
+        if lib.pq_abi_version() != 4:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

@@ -25,7 +25,10 @@ caches of all layers) ``decode_step_graph`` enqueues the append and the attentio
 device, and changes nothing on the host: one captured graph of the whole model step is replayed for every token.
 The owner of the tensor advances ``lengths[1]`` once per step inside the graph (after the last layer) and calls
 ``after_replay()`` on every cache afterwards, which mirrors the step on the host and, every ``residual_length``
-steps, quantises the full window outside the graph.
+steps, quantises the full window outside the graph.  Fully device-driven variant: ``requantize_graph()`` after each
+layer's attention and one ``advance_graph()`` at the end of the captured step make the window's re-quantisation part
+of the graph too (a no-op launch except on the step that fills the window); the host then only counts
+(``after_replay(device_requantized=True)``).
 """
 from __future__ import annotations
 
@@ -301,13 +304,53 @@ class PolarKVCache:
         _lib.check(rc, "pq_decode_attention")
         return out
 
-    def after_replay(self) -> bool:
-        """Mirror one executed ``decode_step_graph`` on the host; quantise the window when it has filled (outside
-        the graph).  Returns True when it did, i.e. when the caller must store the new lengths
-        (``num_groups``, 0) into the shared tensor (``sync_lengths`` does that)."""
+    def requantize_graph(self) -> None:
+        """Inside the captured step, after ``attend_graph``: quantise the residual window into the next groups IF this
+        step has filled it - decided on the device (``lengths[1] + 1 == residual_length``), a no-op launch otherwise.
+        With it and ``advance_graph`` a replayed graph needs nothing from the host between tokens."""
+        if self.lengths is None:
+            raise RuntimeError("this cache was built without a device-side lengths tensor")
+        lib = _lib.load()
+        dev = self._dev
+        stream = ops._stream(dev)
+        lp = self.lengths.data_ptr()
+        with ops._on_device(dev):
+            if self.vbits:
+                vin = (ctypes.c_int64 * 4)(*self.values.stride())
+                vout = (ctypes.c_int64 * 4)(self.v_codes.stride(0) * 4, self.v_codes.stride(1) * 4,
+                                            self.v_scale.stride(0), self.v_scale.stride(1))
+                rc = lib.pq_quantize_values_dyn(self.values.data_ptr(), vin, self.B, self.Nk, self.RL, 128,
+                                                self.vbits, self._dt, _lib.PQ_VALUES_TILED, self.v_codes.data_ptr(),
+                                                self.v_scale.data_ptr(), self.v_mn.data_ptr(), vout, self.G,
+                                                self.v_codes.shape[2], lp, 1, stream)
+                _lib.check(rc, "pq_quantize_values_dyn")
+            kin = (ctypes.c_int64 * 4)(*self.k_res.stride())
+            kout = (ctypes.c_int64 * 4)(self.codes.stride(0), self.codes.stride(1),
+                                        self.scales[0].stride(0), self.scales[0].stride(1))
+            rc = lib.pq_quantize_into_dyn(self.k_res.data_ptr(), kin, self.B, self.Nk, self.RL, 128, self.G,
+                                          self.rbits, self.tbits, self._dt, 0, self.codes.data_ptr(),
+                                          *(t.data_ptr() for t in self.scales), kout, self.max_groups, lp, 1, stream)
+            _lib.check(rc, "pq_quantize_into_dyn")
+
+    def advance_graph(self) -> None:
+        """Once per captured step, after the last layer: residual + 1, or - when that fills the window - the new
+        groups are counted and the residual starts over.  One call for all caches that share ``lengths``."""
+        with ops._on_device(self._dev):
+            rc = _lib.load().pq_lengths_advance(self.lengths.data_ptr(), self.RL, self.G, ops._stream(self._dev))
+        _lib.check(rc, "pq_lengths_advance")
+
+    def after_replay(self, device_requantized: bool = False) -> bool:
+        """Mirror one executed graph step on the host.  Returns True when the step filled the window.  Without
+        ``device_requantized`` the window is quantised here, outside the graph, and the caller must then store the
+        new lengths into the shared tensor (``sync_lengths``); with it the graph already did both
+        (``requantize_graph`` + ``advance_graph``) and only the host's counters move."""
         self.res_len += 1
         if self.res_len == self.RL:
-            self._requantize_window()
+            if device_requantized:
+                self.num_groups += self.RL // self.G
+                self.res_len = 0
+            else:
+                self._requantize_window()
             return True
         return False
 

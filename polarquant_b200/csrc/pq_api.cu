@@ -10,7 +10,9 @@ int& last_cuda_error() {
 }
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
                     int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
-                    void* tmn, const int64_t* out_strides, cudaStream_t stream);
+                    void* tmn, const int64_t* out_strides, cudaStream_t stream, const int* gate_lengths = nullptr,
+                    int gate_r_add = 0, int gate_full = 0, int gate_max_groups = 0);
+int lengths_advance_device(int* lengths, int full, int G, cudaStream_t stream);
 int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_strides, void* k_res,
                         const int64_t* kres_strides, void* values, const int64_t* v_strides, int B, int Nk, int hd,
                         int res_pos, int ctx_pos, int dtype, const int* lengths, int G, int values_window,
@@ -30,7 +32,8 @@ int decode_attention_static_device(const pq_decode_params* p, cudaStream_t strea
 size_t decode_static_scratch_bytes();
 int quantize_values_device(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
                            int dtype, int layout, void* codes, void* scale, void* mn, const int64_t* out_strides,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const int* gate_lengths = nullptr, int gate_r_add = 0,
+                           int gate_full = 0, int gate_G = 0, int gate_max_tokens = 0);
 int values_relayout_device(const void* codes_in, void* codes_out, int64_t tokens, int to_layout, cudaStream_t stream);
 int values_matmul_device(const void* probs, const void* codes, const void* scale, const void* mn, void* out,
                          int64_t BH, int M, int T, int hd, int vbits, int dtype, cudaStream_t stream);
@@ -52,7 +55,7 @@ using namespace pq;
 
 extern "C" {
 
-int pq_abi_version(void) { return 3; }
+int pq_abi_version(void) { return 4; }
 size_t pq_decode_params_size(void) { return sizeof(pq_decode_params); }
 int pq_last_cuda_error(void) { return last_cuda_error(); }
 
@@ -82,6 +85,27 @@ int pq_quantize_into(const void* keys, const int64_t strides[4], int B, int Nk, 
   if (!out_strides) return PQ_ERR_INVALID;
   return quantize_device(keys, strides, B, Nk, L, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale,
                          tmn, out_strides, static_cast<cudaStream_t>(stream));
+}
+
+int pq_quantize_into_dyn(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
+                         int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
+                         void* tmn, const int64_t out_strides[4], int max_groups, const int* lengths, int r_add,
+                         void* stream) {
+  if (!out_strides || !lengths) return PQ_ERR_INVALID;
+  return quantize_device(keys, strides, B, Nk, L, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale,
+                         tmn, out_strides, static_cast<cudaStream_t>(stream), lengths, r_add, L, max_groups);
+}
+
+int pq_quantize_values_dyn(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
+                           int dtype, int layout, void* codes, void* scale, void* mn, const int64_t out_strides[4],
+                           int G, int max_tokens, const int* lengths, int r_add, void* stream) {
+  if (!out_strides || !lengths) return PQ_ERR_INVALID;
+  return quantize_values_device(values, strides, B, Nk, T, hd, vbits, dtype, layout, codes, scale, mn, out_strides,
+                                static_cast<cudaStream_t>(stream), lengths, r_add, T, G, max_tokens);
+}
+
+int pq_lengths_advance(int* lengths, int full, int G, void* stream) {
+  return lengths_advance_device(lengths, full, G, static_cast<cudaStream_t>(stream));
 }
 
 int pq_cache_append(const void* k_new, const void* v_new, const int64_t in_strides[4], void* k_res,

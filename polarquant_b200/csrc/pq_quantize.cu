@@ -186,6 +186,9 @@ __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)
   }
 }
 
+// lengths = {token groups, residual tokens} on the device; the kernel runs only when lengths[1] + r_add == full
+struct WindowGate { const int* lengths; int r_add, full, max_groups; };
+
 // NI > 0: the thread keeps phi and r of its NI tokens x 4 pairs in registers
 // (G == 16 * NI).  NI == 0: any G; phi and r are recomputed in the second pass.
 template <typename T, int NI>
@@ -196,8 +199,15 @@ __global__ void __launch_bounds__(kQuantThreads, sizeof(T) == 2 ? PQ_QUANT_MIN_C
 quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, int Nk, int nb, int G,
                 int rbits, int tbits, unsigned flags, uint8_t* __restrict__ codes, T* __restrict__ rscale,
                 T* __restrict__ rmn_out, T* __restrict__ tscale, T* __restrict__ tmn_out,
-                int64_t c_sb, int64_t c_sh, int64_t s_sb, int64_t s_sh) {
+                int64_t c_sb, int64_t c_sh, int64_t s_sb, int64_t s_sh, const WindowGate gate) {
   using E = Elem<T>;
+  // Device-side gate (re-quantisation of a cache window inside a replayed CUDA graph): run only on the step that
+  // fills the window, and write behind the groups the cache already holds.
+  int group_off = 0;
+  if (gate.lengths) {
+    group_off = gate.lengths[0];
+    if (gate.lengths[1] + gate.r_add != gate.full || group_off < 0 || group_off + nb > gate.max_groups) return;
+  }
   __shared__ float red[4][kQuantThreads / 32][kPairs];
   __shared__ float fin[4][kPairs];
 
@@ -334,7 +344,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
     rrcp[p] = guarded_rcp(rstep[p]);
   }
   if (warp == 0 && tsub == 0) {
-    const int64_t so = b * s_sb + h * s_sh + static_cast<int64_t>(j) * kPairs + p0;
+    const int64_t so = b * s_sb + h * s_sh + static_cast<int64_t>(j + group_off) * kPairs + p0;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       rscale[so + p] = E::from_float(rstep[p]); rmn_out[so + p] = E::from_float(rmn[p]);
@@ -343,7 +353,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   }
 
   const unsigned ttop = (1u << tbits) - 1u, rtop = (1u << rbits) - 1u;
-  uint8_t* crow = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j) * G * kPairs + p0;
+  uint8_t* crow = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * kPairs + p0;
   if constexpr (NI > 0) {
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
@@ -427,7 +437,7 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
 template <typename T>
 int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, int G, int rbits, int tbits,
                     unsigned flags, uint8_t* codes, void* rs, void* rm, void* ts, void* tm, const int64_t* os,
-                    cudaStream_t s) {
+                    const WindowGate& gate, cudaStream_t s) {
   const int nb = L / G;
   const int64_t tiles = static_cast<int64_t>(B) * Nk * nb;
   if (tiles == 0) return PQ_OK;
@@ -437,7 +447,7 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
 #define PQ_LAUNCH_Q(NI)                                                                                   \
   quantize_kernel<T, NI><<<grid, block, 0, s>>>(k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, \
                                                 codes, static_cast<T*>(rs), static_cast<T*>(rm),        \
-                                                static_cast<T*>(ts), static_cast<T*>(tm), os[0], os[1], os[2], os[3])
+                                                static_cast<T*>(ts), static_cast<T*>(tm), os[0], os[1], os[2], os[3], gate)
   switch (G) {
     case 16: PQ_LAUNCH_Q(1); break;
     case 32: PQ_LAUNCH_Q(2); break;
@@ -564,6 +574,22 @@ int rope_append_device(const void* qkv, int64_t qkv_stride_b, const void* cosv, 
   return PQ_OK;
 }
 
+// One step of a growing cache, on the device: lengths = {token groups, residual tokens}.  The window that has just
+// become full (residual + 1 == full) turns into full / G new groups, otherwise the residual count goes up by one.
+namespace {
+__global__ void lengths_advance_kernel(int* lengths, int full, int G) {
+  const int r = lengths[1] + 1;
+  if (r >= full) { lengths[0] += full / G; lengths[1] = 0; }
+  else lengths[1] = r;
+}
+}  // namespace
+int lengths_advance_device(int* lengths, int full, int G, cudaStream_t stream) {
+  if (!lengths || full <= 0 || G <= 0 || full % G != 0) return PQ_ERR_INVALID;
+  lengths_advance_kernel<<<1, 1, 0, stream>>>(lengths, full, G);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream) {
   if (!mismatches_dev || which < 0 || which > 1) return PQ_ERR_INVALID;
   if (dtype != PQ_F16 && dtype != PQ_BF16) return PQ_ERR_INVALID;
@@ -578,8 +604,11 @@ int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatch
 // nullptr means dense outputs.
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G,
                     int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn,
-                    void* tscale, void* tmn, const int64_t* out_strides, cudaStream_t stream) {
+                    void* tscale, void* tmn, const int64_t* out_strides, cudaStream_t stream,
+                    const int* gate_lengths, int gate_r_add, int gate_full, int gate_max_groups) {
   if (!strides || B < 0 || Nk < 0 || L < 0 || G <= 0) return PQ_ERR_INVALID;
+  const WindowGate gate{gate_lengths, gate_r_add, gate_full, gate_max_groups};
+  if (gate_lengths && (!out_strides || gate_full <= 0 || gate_max_groups <= 0)) return PQ_ERR_INVALID;
   if (rbits < 0 || tbits < 0 || rbits + tbits > 8 || (hd & 1) || L % G != 0) return PQ_ERR_INVALID;
   if (!dtype_ok(dtype)) return PQ_ERR_INVALID;
   if (hd != kHeadDim) return PQ_ERR_UNSUPPORTED;
@@ -595,12 +624,13 @@ int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, i
   int64_t os[4] = {nb * G * kPairs * Nk, nb * G * kPairs, nb * kPairs * Nk, nb * kPairs};
   if (out_strides) {
     for (int i = 0; i < 4; ++i) os[i] = out_strides[i];
-    if (os[0] % 4 || os[1] % 4 || os[1] < nb * G * kPairs || os[3] < nb * kPairs) return PQ_ERR_INVALID;
+    const int64_t span = gate_lengths ? gate_max_groups : nb;      // groups a (b, h) unit must be able to hold
+    if (os[0] % 4 || os[1] % 4 || os[1] < span * G * kPairs || os[3] < span * kPairs) return PQ_ERR_INVALID;
   }
   switch (dtype) {
-    case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, stream);
-    case PQ_BF16: return launch_quantize<__nv_bfloat16>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, stream);
-    default: return launch_quantize<float>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, stream);
+    case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
+    case PQ_BF16: return launch_quantize<__nv_bfloat16>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
+    default: return launch_quantize<float>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
   }
 }
 

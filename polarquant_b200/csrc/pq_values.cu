@@ -33,6 +33,9 @@ struct ValArgs {
   int Nk, T;
   int unit0;                                    // first (b * Nk + h) unit of this launch (grid.y counts from it)
   float inv_levels;
+  // device-side gate, as in the key quantizer: run only when lengths[1] + r_add == full, write behind the
+  // lengths[0] * G tokens the cache already holds
+  const int* gate_lengths; int gate_r_add, gate_full, gate_G, gate_max_tokens;
 };
 
 __device__ __forceinline__ float max_nan(float a, float b) {
@@ -83,6 +86,11 @@ template <typename T, bool TILED>
 __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValArgs a) {
   const int sub = threadIdx.x & 15;
   const int lane = threadIdx.x & 31;
+  int tok_off = 0;
+  if (a.gate_lengths) {
+    tok_off = a.gate_lengths[0] * a.gate_G;
+    if (a.gate_lengths[1] + a.gate_r_add != a.gate_full || tok_off < 0 || tok_off + a.T > a.gate_max_tokens) return;
+  }
   // grid (token blocks, units): no per-thread division
   const int unit = a.unit0 + blockIdx.y;
   const int h = unit % a.Nk;
@@ -142,10 +150,10 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
                                 __float_as_uint(__fadd_rn(acc_hi, 8388608.0f)), 0x5410);
     if constexpr (TILED) word = to_tiled_word(word, lane);
     if (ok) {
-      char* row = reinterpret_cast<char*>(a.codes) + b * a.c_sb + h * a.c_sh + static_cast<int64_t>(t) * 64;
+      char* row = reinterpret_cast<char*>(a.codes) + b * a.c_sb + h * a.c_sh + static_cast<int64_t>(t + tok_off) * 64;
       reinterpret_cast<uint32_t*>(row)[word_index(sub, TILED)] = word;
       if (sub == 0) {
-        const int64_t at = b * a.s_sb + h * a.s_sh + t;
+        const int64_t at = b * a.s_sb + h * a.s_sh + t + tok_off;
         static_cast<T*>(a.scale)[at] = Elem<T>::from_float(scale);
         static_cast<T*>(a.mn)[at] = Elem<T>::from_float(mn);
       }
@@ -218,7 +226,9 @@ int launch_quantize_values(ValArgs a, long long units, bool tiled, cudaStream_t 
 
 int quantize_values_device(const void* values, const int64_t strides[4], int B, int Nk, int T, int hd, int vbits,
                            int dtype, int layout, void* codes, void* scale, void* mn, const int64_t* out_strides,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const int* gate_lengths, int gate_r_add, int gate_full, int gate_G,
+                           int gate_max_tokens) {
+  if (gate_lengths && (!out_strides || gate_full <= 0 || gate_G <= 0 || gate_max_tokens < T)) return PQ_ERR_INVALID;
   if (B < 0 || Nk <= 0 || T < 0 || !dtype_ok(dtype) || !strides) return PQ_ERR_INVALID;
   if (layout != PQ_VALUES_KIVI && layout != PQ_VALUES_TILED) return PQ_ERR_INVALID;
   if (hd != kHeadDim || vbits != 4) return PQ_ERR_UNSUPPORTED;
@@ -239,6 +249,8 @@ int quantize_values_device(const void* values, const int64_t strides[4], int B, 
     if (a.c_sb % 16 || a.c_sh % 16) return PQ_ERR_ALIGNMENT;
   }
   a.Nk = Nk; a.T = T;
+  a.gate_lengths = gate_lengths; a.gate_r_add = gate_r_add; a.gate_full = gate_full; a.gate_G = gate_G;
+  a.gate_max_tokens = gate_max_tokens;
   a.inv_levels = 1.0f / 15.0f;
   const long long units = static_cast<long long>(B) * Nk;
   if (units > 0x7fffffffLL) return PQ_ERR_UNSUPPORTED;

@@ -143,6 +143,7 @@ def main():
                     # one kernel: rotate q and k, append k and v (positions from the device-side lengths)
                     q = caches[li].rope_append_graph(F.linear(h, layer.qkv), cos1, sin1)
                     att = caches[li].attend_graph(q)
+                    caches[li].requantize_graph()         # does something only on the step that fills the window
                 else:
                     q, k, v = split_qkv(F.linear(h, layer.qkv), 1)
                     q, k = apply_rope(q, cos1, sin1), apply_rope(k, cos1, sin1)
@@ -155,7 +156,8 @@ def main():
         if use_graph:
             # The whole model step - 32 x (projections, RoPE, cache append, fused attention, MLP), the LM head, the
             # argmax and the advance of position and lengths - is captured once and replayed per token.  The cache
-            # kernels read their lengths on the device; the window is re-quantised outside the graph.
+            # kernels read their lengths on the device, the window's re-quantisation included: nothing runs on the
+            # host between tokens but the replay itself.
             caches[0].sync_lengths()
             tok_buf = tok.clone()
             pos_dev = torch.full((1,), args.prompt, device=dev, dtype=torch.int64)
@@ -164,7 +166,7 @@ def main():
                 cos1, sin1 = rope_tables(pos_dev, hd, theta, dev)
                 nxt = model_step(tok_buf, cos1, sin1, None, fused_rope=True)
                 tok_buf.copy_(nxt)
-                lengths[1:2].add_(1)
+                caches[0].advance_graph()                 # one lengths pair for all layers
                 pos_dev.add_(1)
 
             # warm-up on a side stream, then restore what it changed: token, position, lengths (the slot it wrote
@@ -187,9 +189,8 @@ def main():
             if graph is not None:
                 graph.replay()
                 generated.append(tok_buf.clone())
-                full = [c.after_replay() for c in caches]
-                if full[0]:
-                    caches[0].sync_lengths()
+                for c in caches:                          # host counters only: the graph did the rest
+                    c.after_replay(device_requantized=True)
                 continue
             pos = args.prompt + step
             cos1, sin1 = rope_tables(torch.tensor([pos], device=dev), hd, theta, dev)

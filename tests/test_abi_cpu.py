@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_mirror_and_status_strings():
     from polarquant_b200 import _lib
     lib = _lib.load()
-    assert lib.pq_abi_version() == 3
+    assert lib.pq_abi_version() == 4
     assert lib.pq_decode_params_size() == ctypes.sizeof(_lib.DecodeParams)
     for code in (0, -1, -2, -3, -4, -5):
         assert lib.pq_strerror(code)
@@ -68,6 +68,9 @@ def test_argument_validation_needs_no_gpu():
     assert lib.pq_quantize_values(None, vst, 1, 1, 64, 64, 4, _lib.PQ_BF16, 0, None, None, None, None, None) == -2
     assert lib.pq_quantize_values(None, vst, 1, 1, 0, 128, 4, _lib.PQ_BF16, 0, None, None, None, None, None) == 0
     assert lib.pq_quantize_values(None, vst, 1, 1, 64, 128, 4, _lib.PQ_BF16, 0, None, None, None, None, None) == -1
+    assert lib.pq_lengths_advance(None, 128, 128, None) == -1
+    assert lib.pq_quantize_values_dyn(None, vst, 1, 1, 64, 128, 4, _lib.PQ_BF16, 0, None, None, None, None, 128, 256,
+                                      None, 1, None) == -1
     assert lib.pq_values_relayout(None, None, 0, 1, None) == 0
     assert lib.pq_values_relayout(None, None, 5, 1, None) == -1
     assert lib.pq_values_matmul(None, None, None, None, None, 0, 1, 10, 128, 4, 0, None) == 0

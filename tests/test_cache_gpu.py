@@ -241,3 +241,58 @@ def test_chunked_prefill_fills_the_same_cache(vbits):
         assert (isinstance(a, int) and a == b) or torch.equal(a, b)
     with pytest.raises(ValueError):
         parts.prefill(keys[:2], vals[:2], batch_start=4)
+
+
+@pytest.mark.parametrize("vbits", [0, 4])
+def test_device_driven_requantisation_inside_the_graph(vbits):
+    """requantize_graph + advance_graph: the captured step also re-quantises the window when it fills and keeps the
+    lengths, so 230 replays (crossing the window boundary twice) need nothing from the host; outputs and the final
+    cache equal the eager cache's bit for bit."""
+    from polarquant_b200.cache import PolarKVCache
+    dev, dt = "cuda", torch.bfloat16
+    B, N, Nk, prompt, steps = 2, 8, 2, 300, 230         # residual 44: the window fills at steps 83 and 211
+    g = torch.Generator(device=dev).manual_seed(78)
+    keys = oracle.synth_keys(B, Nk, prompt, 128, dt, seed=79, device=dev)
+    vals = torch.randn(B, Nk, prompt, 128, device=dev, generator=g).to(dt)
+    lengths = torch.zeros(2, dtype=torch.int32, device=dev)
+    eager = PolarKVCache(B, Nk, max_tokens=prompt + steps + 128, dtype=dt, vbits=vbits)
+    graph = PolarKVCache(B, Nk, max_tokens=prompt + steps + 128, dtype=dt, vbits=vbits, lengths=lengths)
+    eager.prefill(keys, vals)
+    graph.prefill(keys, vals)
+    q_buf = torch.empty(B, N, 1, 128, device=dev, dtype=dt)
+    k_buf = torch.empty(B, Nk, 1, 128, device=dev, dtype=dt)
+    v_buf = torch.empty(B, Nk, 1, 128, device=dev, dtype=dt)
+    out_buf = torch.empty(B, N, 1, 128, device=dev, dtype=dt)
+
+    def step_fn():
+        graph.decode_step_graph(q_buf, k_buf, v_buf, out=out_buf)
+        graph.requantize_graph()
+        graph.advance_graph()
+
+    q_buf.normal_(); k_buf.normal_(); v_buf.normal_()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step_fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph.sync_lengths()                               # discard the warm-up step
+    cg = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(cg):
+        step_fn()
+    graph.sync_lengths()
+    crossed = 0
+    for step in range(steps):
+        q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+        k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=7000 + step, device=dev)
+        v_new = torch.randn(B, Nk, 1, 128, device=dev, generator=g).to(dt)
+        want = eager.decode_step(q, k_new, v_new)
+        q_buf.copy_(q); k_buf.copy_(k_new); v_buf.copy_(v_new)
+        cg.replay()
+        assert torch.equal(out_buf, want), step
+        crossed += graph.after_replay(device_requantized=True)
+        if step % 37 == 0 or step == steps - 1:
+            assert lengths.tolist() == [graph.num_groups, graph.res_len] == [eager.num_groups, eager.res_len], step
+    assert crossed == 2
+    for a, b in zip(graph.as_reference_tuple(), eager.as_reference_tuple()):
+        assert (a is None and b is None) or (isinstance(a, int) and a == b) or torch.equal(a, b)
