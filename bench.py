@@ -357,7 +357,7 @@ def main():
         if rank == 0:
             result.update(extras)
     if rank == 0:
-        if not args.no_extras:
+        if not args.no_extras and world == 1:          # the CPU baseline is a single-GPU-run figure
             result["cpu_baseline"] = time_cpu(args)
         print(json.dumps(result))
     if world > 1:
