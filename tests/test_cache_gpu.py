@@ -243,13 +243,14 @@ def test_chunked_prefill_fills_the_same_cache(vbits):
         parts.prefill(keys[:2], vals[:2], batch_start=4)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("vbits", [0, 4])
-def test_device_driven_requantisation_inside_the_graph(vbits):
+def test_device_driven_requantisation_inside_the_graph(vbits, dt):
     """requantize_graph + advance_graph: the captured step also re-quantises the window when it fills and keeps the
     lengths, so 230 replays (crossing the window boundary twice) need nothing from the host; outputs and the final
     cache equal the eager cache's bit for bit."""
     from polarquant_b200.cache import PolarKVCache
-    dev, dt = "cuda", torch.bfloat16
+    dev = "cuda"
     B, N, Nk, prompt, steps = 2, 8, 2, 300, 230         # residual 44: the window fills at steps 83 and 211
     g = torch.Generator(device=dev).manual_seed(78)
     keys = oracle.synth_keys(B, Nk, prompt, 128, dt, seed=79, device=dev)
