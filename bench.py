@@ -10,11 +10,20 @@ the CUDA quantizer; queries and values randn); the inputs of one step (1.36 GB) 
 
 It prints ONE JSON line.  `value` is algorithmic GB/s with the cache resident in HBM; `e2e` is the same metric
 through the host-buffer C entry point with every input copied from pinned host memory and the output copied
-back inside the timed region; `roofline` is the attention kernel alone (CUDA events around it on its stream);
-`cpu_baseline` is the CPU oracle (a port of the reference's eager path) on a bounded sample; `sustained` repeats
-the step for half a second (power-capped clocks), `packed_values` is the step with 4-bit values.
+back inside the timed region; `roofline` is the attention kernel alone, timed in a loop of its own (20 warm-up
+and 60 sampled launches, CUDA events around the kernel on its stream) whatever --steps says; `cpu_baseline` is
+the reference's decode branch on the host cores on a bounded sample, measured BEFORE any GPU work starts;
+`sustained` repeats the step for half a second (power-capped clocks); `packed_values` is the step with 4-bit
+values; `reference_gpu` times the reference's own Triton kernel and its whole unmodified decode branch on the same
+GPU, beside this library's entry points on the same tensors; `e2e_tokens` is greedy decode of a random-init
+Llama-3.1-8B-shaped model (tokens/s).
 With N > 1 (launched by torch.distributed.run) every rank holds its own batch of 16 sequences (weak scaling,
-the path shards by batch / kv head without any collective) and the time is the max over ranks.
+the path shards by batch / kv head without any collective) and the time is the max over ranks; `longctx` then
+adds the 131072-token step of the 70B-shaped layer sharded by kv head and by sequence (the one place the path
+has an exchange: an NCCL all-gather of partial results), after a seeded correctness check of that exchange
+(`seqsplit_check`).
+
+--impl reference runs the reference's own decode branch on host cores (rank 0 only) on the same configuration.
 """
 from __future__ import annotations
 
@@ -59,6 +68,9 @@ def parse_args():
     ap.add_argument("--q-heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, quantizer and CPU legs (profiler runs)")
+    ap.add_argument("--e2e-new-tokens", type=int, default=64,
+                    help="generated tokens of the end-to-end greedy-decode leg (batch 32, 8192-token prompts); "
+                         "0 or 1 skips it")
     ap.add_argument("--packed-values", action="store_true",
                     help="time the step with the values packed to 4 bits as well (the reference's mixed class) "
                          "instead of the headline configuration; implies --no-extras")
@@ -156,13 +168,6 @@ def make_inputs(args, device, seed):
     return dict(q=q, kres=kres, packed=packed, v=v, B=B, N=N, Nk=Nk, Nb=Nb, G=G, R=R)
 
 
-def oracle_cpu_step(sample, args):
-    """The reference's eager decode path (dequantise -> matmul -> softmax -> P.V) on host cores."""
-    from oracle import polar_oracle as oracle
-    return oracle.decode_attention(sample["q"], sample["kres"], *sample["packed"], sample["v"],
-                                   rbits=args.rbits, tbits=args.tbits)
-
-
 def cpu_sample(args, seed=1002):
     """One batch element of the benchmark configuration, built on the CPU with the oracle's quantizer."""
     import torch
@@ -178,48 +183,88 @@ def cpu_sample(args, seed=1002):
         algorithmic_bytes(1, N, Nk, Nb, G, R)
 
 
+def cpu_step_fn(sample, args):
+    """The decode step on host cores as a callable, and what it is.
+
+    With the reference's files installed (oracle/_ref, see oracle/install_ref.py): the reference's own, unmodified
+    ``LlamaPolarGroupAttention.forward`` decode branch (models/modeling_llama_polar.py:61-101) - its concatenations,
+    residual-key matmul, scaling, softmax, repeat_kv and P.V as written - with the one piece that cannot run on a
+    CPU, the Triton kernel behind ``attention_decode_forward_triton_impl``, served by the reference's own
+    dequantise-then-matmul formula (models/kernel4group.py:151-155).  kind = "reference".
+    Without them: the oracle's restatement of the same branch.  kind = "port".
+    """
+    from oracle import polar_oracle as oracle
+    from oracle import ref_harness
+    root = ref_harness.ref_root()
+    if root is None or (args.rbits, args.tbits, args.group) != (4, 4, 128):   # the class hard-codes 4/4, group 128
+        def port():
+            return oracle.decode_attention(sample["q"], sample["kres"], *sample["packed"], sample["v"],
+                                           rbits=args.rbits, tbits=args.tbits)
+        return port, "port", "oracle restatement of the reference's eager decode branch, torch CPU ops"
+    from polarquant_b200 import dropin
+    llama, _ = dropin.load_polar_patches(root, entry_module=ref_harness.dequantise_entry_module(),
+                                         quantize_fn=lambda k, rbits, tbits, group_size:
+                                         oracle.quantize_ops(k, rbits, tbits, group_size))
+    q, kres, v = sample["q"], sample["kres"], sample["v"]
+    attn = ref_harness.identity_attention(llama, "llama", q.shape[1], kres.shape[1], q.dtype)
+    tokens = v.shape[2]
+    past = (kres[:, :, :-1].contiguous(), *sample["packed"], v[:, :, :-1].contiguous(), tokens - 1)
+    k_new, v_new = kres[:, :, -1:].contiguous(), v[:, :, -1:].contiguous()
+
+    def ref():
+        return ref_harness.decode_step(attn, q, k_new, v_new, past)[0]
+    return ref, "reference", ("the reference's unmodified LlamaPolarGroupAttention.forward decode branch "
+                              "(identity projections), its Triton logits call served by its dequantise-then-matmul "
+                              "formula, torch CPU ops")
+
+
 def time_cpu(args, limit_s=20.0, max_reps=10):
+    """cpu_baseline of the JSON line: run before any GPU work of this process, mean of the timed runs."""
     import torch
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     sample, nbytes = cpu_sample(args)
-    oracle_cpu_step(sample, args)                        # warm-up
+    fn, kind, what = cpu_step_fn(sample, args)
+    fn()                                                 # warm-up
     times, t_end = [], time.perf_counter() + limit_s
     while len(times) < max_reps and (time.perf_counter() < t_end or len(times) < 2):
         t0 = time.perf_counter()
-        oracle_cpu_step(sample, args)
+        fn()
         times.append(time.perf_counter() - t0)
-    best = min(times)
-    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+    mean = sum(times) / len(times)
+    return {"value": nbytes / mean / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
             "sample": f"1 of {args.batch} batch elements of the workload ({nbytes / 1e6:.1f} MB per step), "
-                      f"best of {len(times)} runs, torch CPU eager ops, {cores} threads",
-            "ms_per_sample_step": best * 1e3}
+                      f"mean of {len(times)} runs after 1 warm-up, measured before the GPU legs start; {what}, "
+                      f"{cores} threads",
+            "ms_per_sample_step": mean * 1e3, "ms_best": min(times) * 1e3}
 
 
 def run_reference_arm(args, rank):
-    """--impl reference: the reference's own eager path for this step, timed on host cores (CPU oracle port)."""
+    """--impl reference: the reference's decode branch for this step on host cores; exactly --steps timed steps
+    after --warmup untimed ones, each step one batch element of the workload."""
     if rank != 0:
         return
     import torch
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     sample, nbytes = cpu_sample(args)
-    for _ in range(min(args.warmup, 2)):
-        oracle_cpu_step(sample, args)
-    steps = max(1, min(args.steps, 10))
+    fn, kind, what = cpu_step_fn(sample, args)
+    for _ in range(args.warmup):
+        fn()
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
-        oracle_cpu_step(sample, args)
+        fn()
     dt = (time.perf_counter() - t0) / steps
     val = nbytes / dt / 1e9
     sample_txt = (f"each step = 1 of {args.batch} batch elements of the workload ({nbytes / 1e6:.1f} MB), "
-                  f"{steps} timed steps, torch CPU eager ops, {cores} threads")
+                  f"{steps} timed steps after {args.warmup} warm-ups; {what}, {cores} threads")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args),
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample_txt},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample_txt},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -241,6 +286,10 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
+
+    # The CPU baseline runs first, before this process touches the GPU: no clock samplers, no pinned buffers, no
+    # busy-waiting CUDA threads compete with it for the host cores.  It is the figure to quote.
+    cpu_base = time_cpu(args) if (rank == 0 and world == 1 and not args.no_extras) else None
 
     import torch
     import torch.distributed as dist
@@ -291,42 +340,55 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()                   # started before the warm-up so the GPU is not left idle before the timed steps
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     K = args.steps
-    ev_a = {i: new_event() for i in range(K) if i % 4 == 0}
-    ev_m = {i: new_event() for i in range(K) if i % 4 in (0, 3)}
-    ev_end = new_event()
+    ev_start, ev_end = new_event(), new_event()
     barrier()
-    # The attention kernel alone is timed on every fourth step (an event between it and the merge kernel);
-    # on the other steps the merge launch overlaps the attention kernel's tail as in normal use.
-    # The step before a timed one also launches its merge plainly, so the start event of the timed kernel
-    # sits behind a fully serialised merge.
-    sampled = [i for i in range(K) if i % 4 == 0]
-    for i in range(K):
-        if i in sampled:
-            lib.pq_event_record(ev_a[i], stream)
-            step(ev_m[i])
-        elif (i + 1) % 4 == 0:
-            step(ev_m[i])
-        else:
-            step()
+    # The first launches behind a host-side barrier (an NCCL collective plus a device synchronise) start on an idle
+    # GPU and run up to 2x slower than the steady state: a few untimed steps bring the pipeline back before the
+    # start event is recorded.
+    for _ in range(5):
+        step()
+    lib.pq_event_record(ev_start, stream)
+    for _ in range(K):
+        step()                            # attention kernel + merge kernel (launched programmatically behind it)
     lib.pq_event_record(ev_end, stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = ctypes.c_float()
-    lib.pq_event_elapsed_ms(ev_a[0], ev_end, ctypes.byref(ms))
-    total_ms = ms.value
-    kern_ms = []
-    for i in sampled:
-        lib.pq_event_elapsed_ms(ev_a[i], ev_m[i], ctypes.byref(ms))
-        kern_ms.append(ms.value)
+    lib.pq_event_elapsed_ms(ev_start, ev_end, ctypes.byref(ms))
+    my_ms = ms.value
+    total_ms = my_ms
+    per_rank = [my_ms / K]
     if world > 1:
-        t = torch.tensor([total_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+        t = torch.tensor([my_ms], device=device)
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        per_rank = [float(x.item()) / K for x in gathered]
+        total_ms = max(per_rank) * K
     ms_per_step = total_ms / K
     value = nbytes * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline: the attention kernel alone, in a fixed loop of its own (independent of --steps) ----
+    # An event sits between the kernel and its merge, so in this loop the merge is a plain launch and the next
+    # kernel's start event lies behind a fully serialised merge.
+    ROOF_WARM, ROOF_N = 20, 60
+    for _ in range(ROOF_WARM):
+        step()
+    ev_a = [new_event() for _ in range(ROOF_N)]
+    ev_m = [new_event() for _ in range(ROOF_N)]
+    for i in range(ROOF_N):
+        lib.pq_event_record(ev_a[i], stream)
+        step(ev_m[i])
+    torch.cuda.synchronize(device)
+    kern_ms = []
+    for i in range(ROOF_N):
+        lib.pq_event_elapsed_ms(ev_a[i], ev_m[i], ctypes.byref(ms))
+        kern_ms.append(ms.value)
+    for e in ev_a + ev_m:
+        lib.pq_event_destroy(e)
 
     result = None
     if rank == 0:
@@ -335,11 +397,12 @@ def main():
         achieved = nbytes / (kavg * 1e-3) / 1e9
         result = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": K,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
             "us_per_step": ms_per_step * 1e3, "algorithmic_mb_per_step_per_gpu": nbytes / 1e6,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_HBM_GBS,
             "pct_of_measured_copy_peak": 100.0 * value / world / peak,
+            "ms_per_step_per_rank": per_rank,
             "clocks": clocks, "gpu_launches": 2 * K,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT * B
@@ -348,21 +411,199 @@ def main():
                          "traffic_note": "bytes per launch; ncu capture at batch 4 scaled by the batch",
                          "kernel": "decode_kernel (fused attention over packed keys)",
                          "peak_source": f"{peak_kind} copy bandwidth", "kernel_us": kavg * 1e3,
-                         "launches_timed": len(kern_ms),
-                         "kernel_us_median": statistics.median(kern_ms) * 1e3},
+                         "launches_timed": len(kern_ms), "warmup_launches": ROOF_WARM,
+                         "kernel_us_median": statistics.median(kern_ms) * 1e3,
+                         "kernel_us_best": min(kern_ms) * 1e3},
         }
+        if cpu_base is not None:
+            result["cpu_baseline"] = cpu_base
 
     if not args.no_extras:
         extras = run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event)
         if rank == 0:
             result.update(extras)
+        del inp, ws
+        torch.cuda.empty_cache()
+        more = run_wider_legs(args, device, rank, world)
+        if rank == 0:
+            result.update(more)
     if rank == 0:
-        if not args.no_extras and world == 1:          # the CPU baseline is a single-GPU-run figure
-            result["cpu_baseline"] = time_cpu(args)
         print(json.dumps(result))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_wider_legs(args, device, rank, world):
+    """Legs beyond the headline step: the long-context sharded step (N > 1), the reference's own GPU code on the
+    same box (N = 1), and end-to-end greedy decode tokens/s."""
+    import torch
+    import torch.distributed as dist
+    from polarquant_b200 import benchmarks, e2e_decode
+    out = {}
+    peak, _ = measured_peak()
+    if world > 1:
+        # correctness of the one exchange of the path first, then its timing
+        err = benchmarks.sequence_split_check(device, rank, world)
+        out["seqsplit_check"] = "ok" if err <= 8e-3 else f"FAILED: max |diff| {err:.3e} against single-GPU attention"
+        out["seqsplit_max_abs_err"] = err
+        legs = benchmarks.long_context_legs(device, rank, world)
+        for k in ("heads", "sequence"):
+            legs[k]["pct_of_aggregate_measured_peak"] = 100.0 * legs[k]["aggregate_gbs"] / (world * peak)
+            legs[k]["pct_of_aggregate_nominal_8TBs"] = 100.0 * legs[k]["aggregate_gbs"] / (world * NOMINAL_HBM_GBS)
+        out["longctx"] = legs
+        torch.cuda.empty_cache()
+    elif rank == 0:
+        try:
+            out["reference_gpu"] = reference_gpu_legs(args, device)
+        except Exception as e:                           # context figures must not take the bench line down
+            out["reference_gpu"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+    # ---- end-to-end greedy decode, batch 32 sharded over the replicas ----
+    ns = argparse.Namespace(batch=32, prompt=8192, new_tokens=args.e2e_new_tokens, layers=32, prefill_chunk=2,
+                            no_graph=False, vbits=0)
+    if args.e2e_new_tokens > 1:
+        rec = e2e_decode.run(ns, rank, world, device)
+        floor_ms = rec["bytes_per_step_per_gpu"] / (peak * 1e9) * 1e3
+        out["e2e_tokens"] = {
+            "tokens_per_s": rec["decode_tokens_per_s"], "ms_per_step": rec["ms_per_decode_step"],
+            "global_batch": 32, "prompt_tokens": 8192, "new_tokens": args.e2e_new_tokens, "n_gpus": world,
+            "prefill_s": rec["prefill_s"], "cuda_graph": rec["cuda_graph"],
+            "bytes_floor_ms_per_step": floor_ms,
+            "model": "random-init Llama-3.1-8B shape (32 layers, hidden 4096, 32 q / 8 kv heads, rope theta 5e5, "
+                     "bf16 weights ~N(0, 0.02)); torch ops around PolarKVCache, whole step replayed from one CUDA graph",
+            "note": "every replica streams all weights each step, so with the total batch fixed the floor per step "
+                    "only falls from (weights + cache)/peak at 1 GPU to (weights + cache/N)/peak at N"}
+        torch.cuda.empty_cache()
+        if world == 1 and rank == 0:
+            try:
+                out["e2e_tokens"]["reference_patch_path"] = reference_model_tokens(args, device)
+            except Exception as e:
+                out["e2e_tokens"]["reference_patch_path"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+            torch.cuda.empty_cache()
+    return out
+
+
+def _cuda_time_us(fn, reps, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps * 1e3
+
+
+def reference_gpu_legs(args, device):
+    """The reference's own GPU code on this GPU, for context: its Triton kernel through its own wrapper
+    (models/kernel4group.py:83-109) beside pq_qk_decode on the same tensors, and its whole unmodified decode branch
+    (models/modeling_llama_polar.py:61-101: Triton logits + eager concatenations, softmax, repeat_kv, P.V) beside
+    the fused kernel.  Needs the reference's files (oracle/_ref)."""
+    import torch
+    import polarquant_b200 as pq
+    from oracle import ref_harness
+    from polarquant_b200 import dropin
+    if ref_harness.ref_root() is None:
+        return {"unavailable": "reference files not installed (python oracle/install_ref.py needs the checkout)"}
+    refk = ref_harness.load_reference_kernel_module()
+    out = {}
+    g = torch.Generator(device=device).manual_seed(2)
+
+    def qk_pair(tag, B, N, Nk, L, G, dt):
+        q = torch.randn(B, N, 1, 128, device=device, generator=g).to(dt)
+        idx = torch.randint(0, 250, (B, Nk, L // G, G, 64), device=device, generator=g, dtype=torch.uint8)
+        sc = [torch.randn(B, Nk, L // G, 1, 64, device=device, generator=g).to(dt) for _ in range(4)]
+        ours = _cuda_time_us(lambda: pq.attention_decode_forward_triton_impl(q, idx, *sc, rbits=4, tbits=4), 20)
+        rec = {"shape": f"batch {B}, {N} q / {Nk} code heads, {L} keys, group {G}, {str(dt).split('.')[-1]}",
+               "ours_qk_us": ours}
+        try:
+            a = refk.attention_decode_forward_triton_impl(q, idx, *sc, rbits=4, tbits=4)     # JIT
+            b = pq.attention_decode_forward_triton_impl(q, idx, *sc, rbits=4, tbits=4)
+            rec["max_abs_diff_vs_triton"] = float((a - b).abs().max())
+            rec["logit_scale"] = float(a.abs().max())
+            rec["triton_qk_us"] = _cuda_time_us(
+                lambda: refk.attention_decode_forward_triton_impl(q, idx, *sc, rbits=4, tbits=4), 10)
+            rec["speedup"] = rec["triton_qk_us"] / ours
+        except Exception as e:
+            rec["triton_error"] = f"{type(e).__name__}: {e}"[:300]
+        out[tag] = rec
+
+    # the reference's own micro-benchmark point (benchmark/benchmark_matmul.py:89-99: 32 heads on the codes, fp16,
+    # group 32, random codes / scales) and the headline configuration's packed part
+    qk_pair("qk_benchmark_matmul_b8_l131072", 8, 32, 32, 131072, 32, torch.float16)
+    qk_pair("qk_headline_shape", args.batch, args.q_heads, args.kv_heads, args.ctx - 128, args.group, torch.bfloat16)
+
+    # whole decode branch at the headline configuration, reference code unmodified (identity projections)
+    inp = make_inputs(args, device, seed=1002)
+    llama, _ = dropin.load_polar_patches(ref_harness.ref_root(), entry_module=refk)
+    dt = torch.bfloat16
+    attn = ref_harness.identity_attention(llama, "llama", args.q_heads, args.kv_heads, dt, device=device)
+    past = (inp["kres"][:, :, :-1].contiguous(), *inp["packed"], inp["v"][:, :, :-1].contiguous(), args.ctx - 1)
+    k_new, v_new = inp["kres"][:, :, -1:].contiguous(), inp["v"][:, :, -1:].contiguous()
+    rec = {"shape": "headline configuration, one decode step"}
+    rec["ours_decode_us"] = _cuda_time_us(
+        lambda: pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"]), 20)
+    try:
+        ref_out, _ = ref_harness.decode_step(attn, inp["q"], k_new, v_new, past)
+        ours = pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"])
+        d = (ours.float() - ref_out.float()).abs()
+        rec["max_abs_diff"], rec["mean_abs_diff"] = float(d.max()), float(d.mean())
+        rec["reference_decode_us"] = _cuda_time_us(
+            lambda: ref_harness.decode_step(attn, inp["q"], k_new, v_new, past), 5, warm=2)
+        rec["speedup"] = rec["reference_decode_us"] / rec["ours_decode_us"]
+        rec["note"] = ("reference: its Triton logits kernel + eager torch ops (concatenation of the value cache, "
+                       "repeat_kv copies, softmax over (B, N, ctx) fp32 logits); includes three selection-matrix "
+                       "projections of one token, a few tens of microseconds")
+    except Exception as e:
+        rec["reference_error"] = f"{type(e).__name__}: {e}"[:300]
+    out["decode_branch"] = rec
+    return out
+
+
+def reference_model_tokens(args, device):
+    """The unchanged reference path for the end-to-end figure: its LlamaPolarForCausalLM (random init, the
+    Llama-3.1-8B architecture) driven by its own greedy ``generate`` (models/modeling_llama_polar.py:524-562,
+    622-666), bound to the CUDA kernels through the module boundary only - torch.cat cache growth, repeat_kv
+    copies and eager softmax stay as the reference wrote them."""
+    import torch
+    from oracle import ref_harness
+    from polarquant_b200 import dropin
+    from transformers import LlamaConfig
+    if ref_harness.ref_root() is None:
+        return {"unavailable": "reference files not installed"}
+    llama, _ = dropin.load_polar_patches(ref_harness.ref_root())
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                      num_key_value_heads=8, vocab_size=128256, rope_theta=500000.0, max_position_embeddings=131072,
+                      initializer_range=0.02)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(device):
+            torch.manual_seed(1004)
+            model = llama.LlamaPolarForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(old)
+    batch, prompt, new = 8, 8192, 17
+    ids = torch.randint(0, 128256, (batch, prompt), device=device)
+    gen_cfg = argparse.Namespace(eos_token_id=[-1], top_k=0, top_p=1.0, temperature=1.0)
+    # prefill + 1 token, then prefill + `new` tokens: the difference is the decode time of new - 1 steps
+    times = []
+    for n in (1, new):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        llama.generate(model, ids, None, gen_cfg, do_sample=False, max_new_tokens=n)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    step_s = (times[1] - times[0]) / (new - 1)
+    del model
+    return {"tokens_per_s": batch / step_s, "ms_per_step": step_s * 1e3, "batch": batch, "prompt_tokens": prompt,
+            "new_tokens": new, "prefill_plus_first_token_s": times[0],
+            "note": "reference LlamaPolarForCausalLM + generate, unmodified, on the CUDA quantizer and logits entry; "
+                    "batch 8 (its decode step re-materialises the value cache per layer)"}
 
 
 def run_extras(args, inp, device, lib, stream, rank, world, nbytes, new_event):

@@ -140,6 +140,14 @@ int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_d
  * inner stride; codes (B, Nk, Nb, G, D) and the four scale tensors (B, Nk, Nb, D)
  * contiguous; out (B, N, Nb*G) fp32 contiguous.  Query head kvh*(N/Nk)+h reads
  * kv head kvh.  D == 64, G % 16 == 0, 1 <= tbits <= 4.
+ *
+ * Limits narrower than the reference's (which only asserts rbits + tbits <= 8,
+ * models/modeling_llama_polar.py:138): bit splits with tbits > 4 (or rbits > 4) are accepted
+ * by pq_quantize but refused here with PQ_ERR_UNSUPPORTED - the angle table of 64 x 2^tbits
+ * entries per warp is built for at most 16 levels.  The dequantised keys are formed in fp16,
+ * so every reconstructed |key channel| (at most the group's largest radius, rmn + rscale * 2^rbits)
+ * must stay below 65504; bf16 keys beyond that would give inf / NaN logits, not an error.
+ * pq_key_range_check tests a cache's radius scales against this bound on the device.
  */
 int pq_qk_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                  const uint8_t* codes, const void* rscale, const void* rmn,
@@ -148,12 +156,24 @@ int pq_qk_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                  void* stream);
 
 /*
+ * Range check for the fp16 dequantisation of the decode kernels (no reference counterpart: the reference
+ * dequantises in fp32 inside its Triton kernel, models/kernel4group.py:67-75).  rscale / rmn: `count` elements of
+ * `dtype` each (any of the (B, Nk, Nb, 1, 64) tensors, contiguous).  Sets *flag_dev (device memory, 4 bytes,
+ * zeroed by the caller) to 1 when some largest reconstructible radius |rmn| + |rscale| * 2^rbits is not finite or
+ * reaches 65504; leaves it untouched otherwise.  Costs one pass over the scales (1/32 of the code bytes at G = 128).
+ */
+int pq_key_range_check(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype,
+                       unsigned* flag_dev, void* stream);
+
+/*
  * Fused decode attention over the polar cache: lookup-table QK over the packed
  * keys + QK over the full-precision residual keys + scale + optional mask +
  * online softmax + P.V, split over the sequence with a log-sum-exp merge.
  * Replaces the decode branch of the patched attention forward
  * (models/modeling_llama_polar.py:61-101, models/modeling_qwen_polar.py:60-100),
  * i.e. the composition of the call at :66-75 with the eager ops at :77-99.
+ * The limits stated at pq_qk_decode (tbits and rbits at most 4, reconstructed keys below
+ * 65504 in magnitude) hold here too.
  */
 typedef struct pq_decode_params {
   /* query (B, N, hd), dtype qk_dtype */
@@ -236,8 +256,17 @@ size_t pq_decode_workspace_bytes_dyn(int B, int N, int Nk, int num_ctas);
  * work is enqueued.  The call itself performs no cudaMalloc / cudaFree and calls no
  * allocating library routine.
  *
+ * With dyn_lengths set the array must hold the bound over every length,
+ * B * Nk * ceil(N / Nk / 8) + 12 * num_ctas partial slots of 4160 bytes (4032 slots fit).  The default grid of a
+ * 148-SM GPU (444 CTAs, 5328 slots) does not fit, so with num_ctas == 0 this entry point runs the largest grid
+ * that does - (4032 - units) / 12 CTAs, e.g. 325 for batch 16 x 8 kv heads - and an explicit num_ctas beyond
+ * that, or a problem with more than 4020 units, is refused with PQ_ERR_SCRATCH_LIMIT.
+ *
  * The first call on each device looks up the array's device address (with that device
- * current) and caches it; make that first call outside any CUDA stream capture.
+ * current) and caches it for the life of the process; make that first call outside any
+ * CUDA stream capture.  The cache is keyed by device ordinal: after the host destroys the
+ * device's context (cudaDeviceReset) the address is stale and this entry point must not be
+ * called again in that process.
  * All calls on a device share the one array, and it keeps whatever the previous call left
  * in it.  Nothing in it has to start at zero: every slot a call reads was written earlier
  * by the same call.  Two calls whose kernels overlap in time on the same GPU (different

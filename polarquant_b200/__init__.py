@@ -11,12 +11,13 @@
 All compute goes through ``polarquant_b200/csrc/libpolarquant_b200.so``; there is no CPU path.
 """
 from .kernel4group import attention_decode_forward_triton_impl
-from .ops import (decode_attention, merge_lse, qk_decode, quantize_and_pack_nbit, quantize_values, values_matmul,
-                  values_relayout)
+from .ops import (decode_attention, key_range_check, merge_lse, qk_decode, quantize_and_pack_nbit, quantize_values,
+                  values_matmul, values_relayout)
 
 __all__ = [
     "attention_decode_forward_triton_impl",
     "decode_attention",
+    "key_range_check",
     "merge_lse",
     "qk_decode",
     "quantize_and_pack_nbit",

@@ -149,20 +149,38 @@ def packed_values():
         del packed, v, vc, vs, vm
 
 
-def long_context():
-    """70B-shaped long-context decode attention over the GPUs of one node (launch with torchrun):
-    64 q / 8 kv heads, batch 8, context 131072, polar 4/4, group 128.  Two shardings of the same step:
-    `heads` - kv heads split over the ranks, no collective; `sequence` - every rank holds all heads but a slice of
-    the context, one all-gather of (output, lse) per step and a local log-sum-exp merge."""
-    import os
+def sequence_split_check(dev, rank: int, world: int) -> float:
+    """Correctness of the one exchange the path has: a small seeded problem (every rank builds the same tensors),
+    attended over all keys on this GPU and, split along the sequence, over the ranks with one NCCL all-gather of
+    (output, log-sum-exp) and the CUDA merge.  Returns the largest absolute difference, maximised over ranks."""
     import torch.distributed as dist
     from . import distributed as pqd
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    B, N, Nk, Nb, G, R = 2, 16, 4, 4 * max(world, 2) + 1, 128, 45
+    g = torch.Generator(device=dev).manual_seed(2105)
+    keys = (torch.randn(B, Nk, Nb * G + R, 128, device=dev, generator=g) * 3.0).to(torch.bfloat16)
+    q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Nk, Nb * G + R, 128, device=dev, generator=g).to(torch.bfloat16)
+    packed = ops.quantize_and_pack_nbit(keys[:, :, :Nb * G].contiguous(), 4, 4, G)
+    kres = keys[:, :, Nb * G:].contiguous()
+    full = ops.decode_attention(q, kres, *packed, v, out_dtype=torch.float32)
+    g0, g1, owns = pqd.split_sequence(Nb, R, rank, world)
+    mine = [t[:, :, g0:g1].contiguous() for t in packed] if g1 > g0 else None
+    my_v = torch.cat([v[:, :, g0 * G:g1 * G]] + ([v[:, :, Nb * G:]] if owns else []), dim=2).contiguous()
+    got = pqd.sequence_parallel_decode(q, kres if owns else None, mine, my_v, out_dtype=torch.float32)
+    err = (got - full).abs().max().reshape(1)
     if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    return float(err.item())
+
+
+def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
+    """70B-shaped long-context decode attention over the GPUs of one node: 64 q / 8 kv heads, batch 8, context
+    131072, polar 4/4, group 128, bf16.  Two shardings of the same step, each replayed from a CUDA graph and timed
+    with CUDA events (max over ranks): `heads` - kv heads split over the ranks, no collective; `sequence` - every
+    rank holds all heads but a slice of the context, one all-gather of (output, lse) per step and a local
+    log-sum-exp merge.  With ``world > 1`` the default process group (NCCL) must be initialised."""
+    import torch.distributed as dist
+    from . import distributed as pqd
     B, N, Nk, ctx, G, R = 8, 64, 8, 131072, 128, 128
     Nb = (ctx - R) // G
     g = torch.Generator(device=dev).manual_seed(1005 + rank)
@@ -181,12 +199,12 @@ def long_context():
                   + (kres.numel() * 2 if residual else 0))
         return q, kres, packed, v, nbytes
 
-    def timed(fn, reps=30):
+    def timed(fn):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
-        # replay the step from a CUDA graph so the figure is the GPU's, not the Python launcher's
-        try:
+        graphed = True
+        try:                                           # replay from a CUDA graph: the GPU's time, not the launcher's
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -196,16 +214,16 @@ def long_context():
             with torch.cuda.graph(graph):
                 fn()
             run = graph.replay
-            timed.graph = True
         except Exception:                              # capture not possible: time the eager calls
             torch.cuda.synchronize()
-            run = fn
-            timed.graph = False
-        for _ in range(3):
+            run, graphed = fn, False
+        for _ in range(5):
             run()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
+        for _ in range(5):                             # the first launches behind a barrier run cold
+            run()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(reps):
@@ -215,19 +233,22 @@ def long_context():
         t = torch.tensor([a.elapsed_time(b) / reps * 1e3], device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return float(t.item()), graphed
 
+    def total(nbytes):
+        tot = torch.tensor([float(nbytes)], device=dev)
+        if world > 1:
+            dist.all_reduce(tot)
+        return float(tot.item())
+
+    out = {"shape": f"batch {B}, {N} q / {Nk} kv heads, ctx {ctx}, polar 4/4, group {G}, bf16", "n_gpus": world}
     # --- kv heads over ranks ---
     h0, h1 = pqd.shard_range(Nk, rank, world)
     q, kres, packed, v, nbytes = build(h1 - h0, (h1 - h0) * (N // Nk), Nb, R)
-    us = timed(lambda: ops.decode_attention(q, kres, *packed, v))
-    tot = torch.tensor([float(nbytes)], device=dev)
-    if world > 1:
-        dist.all_reduce(tot)
-    if rank == 0:
-        print(json.dumps({"bench": "longctx", "sharding": "kv heads", "n_gpus": world, "us": us,
-                          "aggregate_gbs": float(tot.item()) / us / 1e3, "collective": "none",
-                          "cuda_graph": getattr(timed, "graph", None)}))
+    us, graphed = timed(lambda: ops.decode_attention(q, kres, *packed, v))
+    agg = total(nbytes)
+    out["heads"] = {"us": us, "aggregate_gbs": agg / us / 1e3, "aggregate_mb": agg / 1e6, "collective": "none",
+                    "cuda_graph": graphed}
     del q, kres, packed, v
 
     # --- sequence over ranks ---
@@ -235,16 +256,36 @@ def long_context():
     q, kres, packed, v, nbytes = build(Nk, N, g1 - g0, R if owns else 0)
     if world > 1:
         dist.broadcast(q, 0)                           # one query for all ranks
-    us = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v) if world > 1
-               else ops.decode_attention(q, kres, *packed, v))
-    tot = torch.tensor([float(nbytes)], device=dev)
+    us, graphed = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v) if world > 1
+                        else ops.decode_attention(q, kres, *packed, v))
+    agg = total(nbytes)
+    out["sequence"] = {"us": us, "aggregate_gbs": agg / us / 1e3, "aggregate_mb": agg / 1e6,
+                       "collective": "all_gather of (B*N, 129) fp32 per rank + local merge", "cuda_graph": graphed}
     if world > 1:
-        dist.all_reduce(tot)
+        # the parts of the sequence-split step: local attention alone, and the exchange + merge alone
+        us_local, _ = timed(lambda: pqd.local_partial(q, kres, packed, v))
+        o, l = pqd.local_partial(q, kres, packed, v)
+        us_xchg, _ = timed(lambda: pqd.merge_across_ranks(o, l, out_dtype=torch.bfloat16))
+        out["sequence"].update(local_attention_us=us_local, exchange_and_merge_us=us_xchg)
+    del q, kres, packed, v
+    return out
+
+
+def long_context():
+    """CLI form of `long_context_legs` (launch with torchrun for more than one GPU)."""
+    import os
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    res = long_context_legs(dev, rank, world)
+    if world > 1:
+        res["seqsplit_max_abs_err"] = sequence_split_check(dev, rank, world)
     if rank == 0:
-        print(json.dumps({"bench": "longctx", "sharding": "sequence", "n_gpus": world, "us": us,
-                          "aggregate_gbs": float(tot.item()) / us / 1e3,
-                          "collective": "all_gather of (B*N, 129) fp32 per rank + local merge",
-                          "cuda_graph": getattr(timed, "graph", None)}))
+        print(json.dumps({"bench": "longctx", **res}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

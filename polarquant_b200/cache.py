@@ -42,7 +42,8 @@ from . import _lib, ops
 class PolarKVCache:
     def __init__(self, batch: int, kv_heads: int, max_tokens: int, dtype=torch.bfloat16, device="cuda",
                  rbits: int = 4, tbits: int = 4, group_size: int = 128, residual_length: int = 128,
-                 head_dim: int = 128, vbits: int = 0, lengths: torch.Tensor | None = None):
+                 head_dim: int = 128, vbits: int = 0, lengths: torch.Tensor | None = None,
+                 num_q_heads: int | None = None):
         if residual_length % group_size:
             raise ValueError("residual_length must be a multiple of group_size")
         if head_dim != 128:
@@ -69,17 +70,18 @@ class PolarKVCache:
             self.values = torch.empty((batch, kv_heads, max_tokens, head_dim), dtype=dtype, device=dev)
         self.num_groups = 0        # quantised token groups
         self.res_len = 0           # full-precision keys in the window
-        need = _lib.load().pq_decode_workspace_bytes(batch, kv_heads * 8, kv_heads, self.max_groups, group_size,
-                                                     residual_length, 0)
         self.lengths = lengths
         if lengths is not None:
             if lengths.dtype != torch.int32 or lengths.numel() != 2 or not lengths.is_cuda or \
                     (dev.index is not None and lengths.device.index != dev.index):
                 raise ValueError("lengths must be an int32 tensor of two elements on the cache's device")
-            need = max(need, _lib.load().pq_decode_workspace_bytes_dyn(batch, kv_heads * 16, kv_heads, 0))
-        self.workspace = torch.empty(max(need, 1 << 20) + 256, dtype=torch.uint8, device=dev)
-        # everything that does not change from step to step is marshalled once
+        # The scratch of the attention call grows with the number of 8-head tiles per kv head.  It is sized for
+        # ``num_q_heads`` (default: a GQA ratio of 8) and regrown by ``_ensure_workspace`` when a call brings more.
         self._dev = dev
+        self._ws_heads = 0
+        self.workspace = None
+        self._ensure_workspace(num_q_heads if num_q_heads else kv_heads * 8)
+        # everything that does not change from step to step is marshalled once
         self._dt = ops._DT[dtype]
         p = _lib.DecodeParams()
         p.codes, p.codes_stride_b, p.codes_stride_h = self.codes.data_ptr(), self.codes.stride(0), self.codes.stride(1)
@@ -102,6 +104,26 @@ class PolarKVCache:
         self._params = p
         self._kres_strides = (ctypes.c_int64 * 3)(self.k_res.stride(0), self.k_res.stride(1), self.k_res.stride(2))
         self._v_strides = (ctypes.c_int64 * 3)(self.values.stride(0), self.values.stride(1), self.values.stride(2))
+
+    def _ensure_workspace(self, num_q_heads: int) -> None:
+        """Make the scratch buffer large enough for attention calls with ``num_q_heads`` query heads.  Growing
+        allocates, so it must happen outside CUDA-graph capture: construct the cache with ``num_q_heads`` (or run
+        one eager step first) when the GQA ratio exceeds 8."""
+        if num_q_heads <= self._ws_heads:
+            return
+        if num_q_heads % self.Nk:
+            raise ValueError("query heads must be a multiple of the cache's kv heads")
+        lib = _lib.load()
+        need = lib.pq_decode_workspace_bytes(self.B, num_q_heads, self.Nk, self.max_groups, self.G, self.RL, 0)
+        if self.lengths is not None:
+            need = max(need, lib.pq_decode_workspace_bytes_dyn(self.B, num_q_heads, self.Nk, 0))
+        if self.workspace is not None and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"PolarKVCache scratch was sized for {self._ws_heads} query heads; pass "
+                               f"num_q_heads={num_q_heads} to the constructor before capturing a CUDA graph")
+        self.workspace = torch.empty(max(need, 1 << 20) + 256, dtype=torch.uint8, device=self._dev)
+        self._ws_heads = num_q_heads
+        if getattr(self, "_params", None) is not None:
+            self._params.workspace, self._params.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
 
     @property
     def seq_len(self) -> int:
@@ -207,6 +229,7 @@ class PolarKVCache:
             _lib.check(rc, "pq_cache_append")
             self.res_len += 1
             bsz, nq, _, hd = query_states.shape
+            self._ensure_workspace(nq)
             q = query_states.reshape(bsz, nq, hd)
             if not ops._vec_ok(q, 8):
                 q = q.contiguous()
@@ -292,6 +315,7 @@ class PolarKVCache:
             raise ValueError("attend_graph needs cache-dtype queries with unit inner stride and aligned rows")
         if out is None:
             out = torch.empty((bsz, nq, 1, hd), dtype=self.dtype, device=dev)
+        self._ensure_workspace(nq)
         p = _lib.DecodeParams()
         ctypes.memmove(ctypes.byref(p), ctypes.byref(self._params), ctypes.sizeof(p))
         p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
@@ -379,6 +403,7 @@ class PolarKVCache:
             nq = ng * self.G
             kw = dict(value_codes=self.v_codes[:, :, :nq], value_scale=self.v_scale[:, :, :nq],
                       value_mn=self.v_mn[:, :, :nq], vbits=self.vbits)
+        self._ensure_workspace(query_states.shape[1])
         out = ops.decode_attention(query_states, self.k_res[:, :, :self.res_len], *packed,
                                    self.values[:, :, :vpos + 1], attention_mask=attention_mask, rbits=self.rbits,
                                    tbits=self.tbits, sm_scale=sm_scale, out_dtype=out_dtype,

@@ -23,6 +23,8 @@ int rope_append_device(const void* qkv, int64_t qkv_stride_b, const void* cosv, 
                        int B, int N, int Nk, int hd, int G, const int* lengths, int values_window, int res_cap,
                        int value_cap, int res_pos, int ctx_pos, int dtype, cudaStream_t stream);
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
+int key_range_check_device(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype,
+                           unsigned* flag_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
                      const void* rmn, const void* tscale, const void* tmn, float* out, int B, int N, int Nk,
                      int Nb, int G, int D, int rbits, int tbits, int dtype, cudaStream_t stream);
@@ -131,6 +133,11 @@ int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const
   return rope_append_device(qkv, qkv_stride_b, cos, sin, cs_stride_b, q_out, k_res, kres_strides, values, v_strides,
                             B, N, Nk, hd, G, lengths, values_window, res_cap, value_cap, res_pos, ctx_pos, dtype,
                             static_cast<cudaStream_t>(stream));
+}
+
+int pq_key_range_check(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype, unsigned* flag_dev,
+                       void* stream) {
+  return key_range_check_device(rscale, rmn, count, rbits, dtype, flag_dev, static_cast<cudaStream_t>(stream));
 }
 
 int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream) {

@@ -105,7 +105,8 @@ __host__ __device__ inline void plan_core(DecodeArgs& a, long long ctas, bool fo
   if (warps > a.total_slots) warps = a.total_slots > 0 ? a.total_slots : 1;   // every warp range is non-empty
   a.total_warps = static_cast<int>(warps);
   const long long per_warp = (a.total_slots + a.total_warps - 1) / a.total_warps;
-  a.max_seg = static_cast<int>((per_warp + a.slots_per_unit - 1) / (a.slots_per_unit > 0 ? a.slots_per_unit : 1)) + 1;
+  // an empty problem (device-side lengths of an empty cache) has no slots and no partials
+  a.max_seg = a.slots_per_unit > 0 ? static_cast<int>((per_warp + a.slots_per_unit - 1) / a.slots_per_unit) + 1 : 0;
 }
 __device__ __forceinline__ void plan_on_device(DecodeArgs& a) {
   // the host's Nb / R are the capacities of the buffers: lengths beyond them are clamped, never followed
@@ -984,6 +985,19 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
   const int head0 = kvh * a.nrep + ht * kHeadTile;
   const int nheads = min(kHeadTile, a.nrep - ht * kHeadTile);
 
+  if (a.slots_per_unit == 0) {
+    // Device-side lengths that describe an empty cache: there are no keys to attend over and the attention
+    // kernel wrote no partial.  The result is defined - zeros, log-sum-exp = -inf - rather than a division by zero.
+    const int hh = grp;
+    if (hh < nheads) {
+      const int64_t off = b * o_sb + (head0 + hh) * o_sh + ch;
+      if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = 0.f;
+      else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(0.f);
+      else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(0.f);
+      if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + hh] = -INFINITY;
+    }
+    return;
+  }
   const long long first = unit * a.slots_per_unit, last = first + a.slots_per_unit - 1;
   const long long w0 = warp_of(first, a.total_slots, a.total_warps);
   const long long w1 = warp_of(last, a.total_slots, a.total_warps);
@@ -1336,6 +1350,7 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   size_t slots = static_cast<size_t>(a.total_warps) * a.max_seg;
   if (p->dyn_lengths) {
     if (mis(p->dyn_lengths, 4)) return PQ_ERR_ALIGNMENT;
+    if (p->dyn_r_add < 0) return PQ_ERR_INVALID;
     if (p->qk_dtype != p->v_dtype || p->qk_dtype == PQ_F32) return PQ_ERR_UNSUPPORTED;
     a.dyn = p->dyn_lengths; a.dyn_r_add = p->dyn_r_add;
     slots = static_cast<size_t>(slot_bound(static_cast<long long>(a.B) * a.Nk * a.head_tiles, a.plan_ctas));
@@ -1424,8 +1439,29 @@ int decode_attention_static_device(const pq_decode_params* p, cudaStream_t strea
   if (!p) return PQ_ERR_INVALID;
   // the size check needs only the dimensions and comes first, so an oversized problem is
   // refused before anything touches the device
-  const size_t need = decode_workspace_bytes(p->B, p->N, p->Nk, p->Nb, p->G, p->R, p->num_ctas);
-  if (need > kStaticScratchBytes) return PQ_ERR_SCRATCH_LIMIT;
+  pq_decode_params q = *p;
+  if (p->dyn_lengths) {
+    // Device-side lengths: the scratch must hold the bound over every length, units + 12 partial slots per CTA.
+    // With num_ctas == 0 the grid is shrunk, if need be, to the largest one whose bound fits the array
+    // (fewer, longer warp ranges: the same result up to the order of the merge); an explicit num_ctas is
+    // taken as given and refused when its bound does not fit.
+    if (p->B <= 0 || p->N <= 0 || p->Nk <= 0 || p->N % p->Nk != 0) return p->B == 0 ? PQ_OK : PQ_ERR_INVALID;
+    constexpr long long kSlotBytes = kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2);
+    const long long cap_slots = static_cast<long long>(kStaticScratchBytes) / kSlotBytes;
+    const int nrep = p->N / p->Nk;
+    const long long units = static_cast<long long>(p->B) * p->Nk * ((nrep + kHeadTile - 1) / kHeadTile);
+    const long long fit = (cap_slots - units) / (3 * kWarps);            // largest CTA count with slot_bound <= cap
+    if (fit < 1) return PQ_ERR_SCRATCH_LIMIT;
+    if (p->num_ctas > 0) {
+      if (p->num_ctas > fit) return PQ_ERR_SCRATCH_LIMIT;
+    } else {
+      const long long dflt = static_cast<long long>(sm_count()) * PQ_MIN_CTAS;
+      if (dflt > fit) q.num_ctas = static_cast<int>(fit);
+    }
+  } else {
+    const size_t need = decode_workspace_bytes(p->B, p->N, p->Nk, p->Nb, p->G, p->R, p->num_ctas);
+    if (need > kStaticScratchBytes) return PQ_ERR_SCRATCH_LIMIT;
+  }
   int dev = -1;
   PQ_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PQ_ERR_UNSUPPORTED;
@@ -1435,13 +1471,14 @@ int decode_attention_static_device(const pq_decode_params* p, cudaStream_t strea
     addr = g_scratch_addr[dev];
     if (!addr) {
       // first call on this device: resolve the device address of the array (no allocation;
-      // it may load the library's device code, so make this call before any stream capture)
+      // it may load the library's device code, so make this call before any stream capture).
+      // The address is cached per device ordinal for the life of the process: a host that
+      // destroys the device's context (cudaDeviceReset) must not call this entry point afterwards.
       PQ_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
       if (!addr) return PQ_ERR_CUDA;
       g_scratch_addr[dev] = addr;
     }
   }
-  pq_decode_params q = *p;
   q.workspace = addr;
   q.workspace_bytes = kStaticScratchBytes;
   return decode_attention_device(&q, stream);

@@ -590,6 +590,40 @@ int lengths_advance_device(int* lengths, int full, int G, cudaStream_t stream) {
   return PQ_OK;
 }
 
+// Largest radius a group can reconstruct, |rmn| + |rscale| * 2^rbits, against the fp16 range of the decode kernels'
+// dequantisation.  One pass over the two radius scale tensors; sets *flag when a value is not finite or too large.
+namespace {
+template <typename T>
+__global__ void key_range_check_kernel(const T* __restrict__ rscale, const T* __restrict__ rmn, int64_t count,
+                                       float levels, unsigned* __restrict__ flag) {
+  bool bad = false;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float top = fabsf(Elem<T>::to_float(rmn[i])) + fabsf(Elem<T>::to_float(rscale[i])) * levels;
+    bad |= !(top < 65504.0f);                  // also true for NaN
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) *flag = 1u;
+}
+}  // namespace
+
+int key_range_check_device(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype,
+                           unsigned* flag_dev, cudaStream_t stream) {
+  if (count < 0 || rbits < 0 || rbits > 8 || !dtype_ok(dtype)) return PQ_ERR_INVALID;
+  if (count == 0) return PQ_OK;
+  if (!rscale || !rmn || !flag_dev) return PQ_ERR_INVALID;
+  const int64_t want = (count + 255) / 256;
+  const unsigned grid = static_cast<unsigned>(want < 148 * 8 ? want : 148 * 8);
+  const float levels = static_cast<float>(1 << rbits);
+  if (dtype == PQ_F32)
+    key_range_check_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(rscale), static_cast<const float*>(rmn), count, levels, flag_dev);
+  else if (dtype == PQ_F16)
+    key_range_check_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(rscale), static_cast<const __half*>(rmn), count, levels, flag_dev);
+  else
+    key_range_check_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(rscale), static_cast<const __nv_bfloat16*>(rmn), count, levels, flag_dev);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream) {
   if (!mismatches_dev || which < 0 || which > 1) return PQ_ERR_INVALID;
   if (dtype != PQ_F16 && dtype != PQ_BF16) return PQ_ERR_INVALID;

@@ -76,6 +76,19 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    result = run(args, rank, world, dev)
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run(args, rank: int, world: int, dev: torch.device) -> dict:
+    """The measurement itself; ``args`` carries batch, prompt, new_tokens, layers, prefill_chunk, no_graph, vbits.
+    With ``world > 1`` the default process group must be initialised.  Returns the result record (every rank)."""
+    if world > 1:
+        import torch.distributed as dist
     hidden, heads, kvh, inter, vocab, theta = 4096, 32, 8, 14336, 128256, 500000.0
     hd = hidden // heads
     lo, hi = (rank * args.batch) // world, ((rank + 1) * args.batch) // world
@@ -202,22 +215,24 @@ def main():
         t = torch.tensor([decode_s, prefill_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         decode_s, prefill_s = float(t[0]), float(t[1])
-    if rank == 0:
-        steps = args.new_tokens - 1
-        print(json.dumps({
-            "bench": "e2e_decode", "model": f"Llama-3.1-8B-shaped, {args.layers} layers, random init, bf16",
-            "n_gpus": world, "global_batch": args.batch, "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
-            "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": decode_s / steps * 1e3,
-            "prefill_s": prefill_s, "keys": "polar 4/4, group 128, residual 128",
-            "values": "4-bit per-token min/max, residual 128 in bf16" if args.vbits else "bf16",
-            "cache_bytes_per_token_per_kv_head": 136 if args.vbits else 324,
-            "cuda_graph": use_graph,
-            "note": ("one captured CUDA graph of the whole model step, replayed per token; cache lengths on the device"
-                     if use_graph else
-                     "eager torch around PolarKVCache.decode_step; the step is host-launch bound at this batch")}))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    steps = args.new_tokens - 1
+    weight_bytes = sum(t.numel() * 2 for layer in layers for t in (layer.qkv, layer.o, layer.gate_up, layer.down)) \
+        + lm_head.numel() * 2
+    cache_bytes = args.layers * B * kvh * (args.prompt + args.new_tokens // 2) * (136 if args.vbits else 324)
+    del layers, caches, embed, lm_head, graph
+    torch.cuda.empty_cache()
+    return {
+        "bench": "e2e_decode", "model": f"Llama-3.1-8B-shaped, {args.layers} layers, random init, bf16",
+        "n_gpus": world, "global_batch": args.batch, "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
+        "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": decode_s / steps * 1e3,
+        "prefill_s": prefill_s, "keys": "polar 4/4, group 128, residual 128",
+        "values": "4-bit per-token min/max, residual 128 in bf16" if args.vbits else "bf16",
+        "cache_bytes_per_token_per_kv_head": 136 if args.vbits else 324,
+        "bytes_per_step_per_gpu": weight_bytes + cache_bytes,
+        "cuda_graph": use_graph,
+        "note": ("one captured CUDA graph of the whole model step, replayed per token; cache lengths on the device"
+                 if use_graph else
+                 "eager torch around PolarKVCache.decode_step; the step is host-launch bound at this batch")}
 
 
 if __name__ == "__main__":

@@ -134,6 +134,27 @@ def qk_decode(query_states: torch.Tensor, indices: torch.Tensor, rscale, rmn, ts
     return out
 
 
+def key_range_check(rscale: torch.Tensor, rmn: torch.Tensor, rbits: int = 4) -> torch.Tensor:
+    """Device-side check that the packed keys stay inside the fp16 range of the decode kernels' dequantisation.
+
+    The kernels form the dequantised key in fp16 (the reference's Triton kernel works in fp32,
+    models/kernel4group.py:67-75), so the largest radius a group can reconstruct, |rmn| + |rscale| * 2^rbits, must
+    stay below 65504.  Returns a one-element int32 CUDA tensor: 1 when some group breaks that bound or holds a
+    non-finite scale, else 0.  Nothing synchronises; read the tensor when convenient.
+    """
+    dev = _require_cuda(rscale, rmn)
+    if rscale.dtype != rmn.dtype or rscale.numel() != rmn.numel():
+        raise ValueError("rscale and rmn must have the same dtype and size")
+    rscale, rmn = rscale.contiguous(), rmn.contiguous()
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    with _on_device(dev):
+        rc = lib.pq_key_range_check(rscale.data_ptr(), rmn.data_ptr(), rscale.numel(), rbits,
+                                    _dtype_code(rscale, "key_range_check"), flag.data_ptr(), _stream(dev))
+    _lib.check(rc, "pq_key_range_check")
+    return flag
+
+
 _workspaces: dict = {}
 
 

@@ -54,6 +54,34 @@ def test_in_place_cache_tracks_the_growing_cache(prompt, steps, grp):
     assert torch.equal(tup[6], v_all)
 
 
+def test_cache_serves_a_gqa_ratio_of_sixteen():
+    """The scratch of the attention call grows with the 8-head tiles per kv head: a cache built with the default
+    sizing (ratio 8) must regrow for 16 query heads per kv head, one built with num_q_heads must already fit, and
+    a long context must not run out of partial slots either way."""
+    import polarquant_b200 as pq
+    from polarquant_b200.cache import PolarKVCache
+    dev, dt = "cuda", torch.bfloat16
+    B, N, Nk, prompt = 1, 128, 8, 32768 - 128
+    g = torch.Generator(device=dev).manual_seed(77)
+    keys = oracle.synth_keys(B, Nk, prompt, 128, dt, seed=78, device=dev)
+    vals = torch.randn(B, Nk, prompt, 128, device=dev, generator=g).to(dt)
+    q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(dt)
+    k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=79, device=dev)
+    v_new = torch.randn(B, Nk, 1, 128, device=dev, generator=g).to(dt)
+    outs = []
+    for nq in (None, N):
+        cache = PolarKVCache(B, Nk, max_tokens=prompt + 256, dtype=dt, num_q_heads=nq)
+        cache.prefill(keys, vals)
+        outs.append(cache.decode_step(q, k_new, v_new))
+        lib_need = pq._lib.load().pq_decode_workspace_bytes(B, N, Nk, cache.max_groups, 128, 128, 0)
+        assert cache.workspace.numel() >= lib_need
+    assert torch.equal(outs[0], outs[1])
+    packed = pq.quantize_and_pack_nbit(keys, 4, 4, 128)
+    want = oracle.decode_attention(q, k_new, *packed, torch.cat([vals, v_new], dim=2))
+    diff = (outs[0].float() - want.float()).abs()
+    assert float(diff.max()) <= ATTN_MAX_ABS and float(diff.mean()) <= ATTN_MEAN_ABS
+
+
 def test_cache_refuses_to_overflow():
     from polarquant_b200.cache import PolarKVCache
     cache = PolarKVCache(1, 1, max_tokens=128)

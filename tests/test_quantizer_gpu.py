@@ -146,3 +146,20 @@ def test_host_buffer_entry_point_matches_device_entry_point():
     assert rc == 0, lib.pq_strerror(rc)
     torch.cuda.synchronize()
     _assert_same([codes, *sc], [t.cpu() for t in want])
+
+
+def test_key_range_check_flags_scales_beyond_the_fp16_range():
+    """The decode kernels dequantise in fp16; pq_key_range_check tells a caller when a cache's radii cannot be
+    represented there (bf16 keys can reach 3e38)."""
+    import polarquant_b200 as pq
+    keys = oracle.synth_keys(1, 2, 256, 128, torch.bfloat16, seed=91, device="cuda")
+    _, rs, rm, _, _ = pq.quantize_and_pack_nbit(keys, 4, 4, 128)
+    assert int(pq.key_range_check(rs, rm, 4)) == 0
+    big = keys.clone()
+    big[0, 1, 200, 5] = 7.0e4                       # one channel beyond 65504
+    _, rs, rm, _, _ = pq.quantize_and_pack_nbit(big, 4, 4, 128)
+    assert int(pq.key_range_check(rs, rm, 4)) == 1
+    nan = keys.clone()
+    nan[0, 0, 3, 70] = float("nan")
+    _, rs, rm, _, _ = pq.quantize_and_pack_nbit(nan, 4, 4, 128)
+    assert int(pq.key_range_check(rs, rm, 4)) == 1
