@@ -38,6 +38,8 @@ typedef enum {
                                   instead of float32(2*pi) (what torch does on CUDA, the default) */
 #define PQ_QUANT_NORM_FMA 2u /* fp32 keys only: radius^2 = fma(y, y, RN(x*x)) instead of RN(x*x) + RN(y*y), the \
                                  form torch evaluates on both CPU and CUDA (for 16-bit keys the two coincide) */
+#define PQ_QUANT_PACK6 4u /* write the codes in the 48-byte-per-token PQ_KEYS_PACKED6 container (see pq_keys_repack) \
+                             instead of one byte per pair; needs rbits + tbits == 6 and G % 16 == 0 */
 
 /*
  * Polar key quantizer.  Replaces the method quantize_and_pack_nbit
@@ -156,6 +158,27 @@ int pq_qk_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                  void* stream);
 
 /*
+ * Sub-byte key codes (an opt-in second format; the reference keeps one byte per pair,
+ * models/modeling_llama_polar.py:155, and names real packing as future work, models/kernel4group.py:1-3).
+ * For the bit splits whose code has 6 bits (3/3 and 2/4) PQ_KEYS_PACKED6 stores 48 bytes per token instead of 64.
+ * The format is tiled per step of 16 consecutive tokens (768 bytes), in the order a warp of the decode kernel
+ * consumes it: bytes [0, 512) hold, for lane l = 4 g + t (g = 0..7, t = 0..3), the words A0, A1 of token g and A0,
+ * A1 of token g + 8; bytes [512, 768) hold, per lane, the word H of token g and of token g + 8.  With c[p] the code
+ * of pair 16 t + p of the token: nibble 2 i of A_k is c[8 k + i] & 15 and nibble 2 i + 1 is c[8 k + 4 + i] & 15
+ * (i = 0..3, k = 0..1); bits 2 j, 2 j + 1 of H are c[4 W + E] >> 4 and bits 16 + 2 j, 17 + 2 j are
+ * c[4 W + E + 2] >> 4 for j = 2 W + E (W = 0..3, E = 0..1).  Token counts are multiples of 16.
+ *
+ * pq_quantize / pq_quantize_into[_dyn] write it directly when PQ_QUANT_PACK6 is set in `flags` (the codes buffer
+ * then takes 48 bytes per token, out_strides[0..1] in bytes of that format); pq_keys_repack converts `steps`
+ * 16-token blocks between the two containers (to_format = PQ_KEYS_PACKED6 or PQ_KEYS_BYTE, out of place; code
+ * bits above the sixth are dropped when packing).  Packing is lossless for 6-bit codes: unpack(pack(c)) == c, and
+ * pq_decode_attention gives bit-identical results on either container.
+ */
+#define PQ_KEYS_BYTE 0
+#define PQ_KEYS_PACKED6 1
+int pq_keys_repack(const uint8_t* codes_in, uint8_t* codes_out, int64_t steps, int to_format, void* stream);
+
+/*
  * Range check for the fp16 dequantisation of the decode kernels (no reference counterpart: the reference
  * dequantises in fp32 inside its Triton kernel, models/kernel4group.py:67-75).  rscale / rmn: `count` elements of
  * `dtype` each (any of the (B, Nk, Nb, 1, 64) tensors, contiguous).  Sets *flag_dev (device memory, 4 bytes,
@@ -233,6 +256,10 @@ typedef struct pq_decode_params {
      pq_decode_workspace_bytes_dyn() bytes, and qk_dtype == v_dtype (fp16 or bf16). */
   const int* dyn_lengths;
   int dyn_r_add;
+  /* Layout of `codes`: PQ_KEYS_BYTE (0, the reference's container: one byte per pair, 64 bytes per token) or
+     PQ_KEYS_PACKED6 (48 bytes per token, see pq_keys_repack; rbits + tbits must be 6: 3/3 or 2/4; 16-bit caches
+     with qk_dtype == v_dtype).  A unit then holds Nb * G * 48 contiguous bytes. */
+  int key_format;
 } pq_decode_params;
 
 int pq_decode_attention(const pq_decode_params* p, void* stream);

@@ -26,6 +26,8 @@ algorithm of the reference project (ericshwu/PolarQuant):
                           (models/modeling_llama_polar.py:77-99, Qwen copy at
                           models/modeling_qwen_polar.py:76-98) composed with the
                           fp32 logits above.
+* ``pack_keys6`` / ``unpack_keys6`` - the 48-byte-per-token key container of this
+                          library (no reference counterpart), restated from its definition.
 * ``merge_lse``         - log-sum-exp merge of partial attention results; it has
                           no counterpart in the reference (the reference never
                           splits the sequence) and is defined by softmax algebra.
@@ -445,6 +447,70 @@ def merge_lse(outs: torch.Tensor, lses: torch.Tensor):
     w = torch.exp(lses - total[None])
     w = torch.where(torch.isfinite(w), w, torch.zeros_like(w))
     return (w[..., None] * outs.to(torch.float32)).sum(dim=0), total
+
+
+# ----------------------------------------------------------------------------
+# 6-bit packed key container (an opt-in format of this library; the reference keeps
+# one byte per pair, models/modeling_llama_polar.py:155, and lists real packing as
+# future work, models/kernel4group.py:1-3).  The layout is a definition, restated
+# here field by field from the C header so that the kernels can be checked against
+# an independent statement of it.
+# ----------------------------------------------------------------------------
+def pack_keys6(codes: torch.Tensor) -> torch.Tensor:
+    """codes (..., T, 64) uint8 with T % 16 == 0 and values < 64 -> (..., T/16, 768) uint8.
+
+    Per step of 16 tokens: lane l = 4 g + t owns pairs 16 t .. 16 t + 15 of tokens g and g + 8.  Bytes
+    16 l .. 16 l + 15 hold the little-endian words A0, A1 of token g then of token g + 8; bytes 512 + 8 l .. hold
+    the words H of token g and g + 8.  With c[p] the code of pair 16 t + p: nibble 2 i of A_k is c[8 k + i] & 15,
+    nibble 2 i + 1 is c[8 k + 4 + i] & 15; bits 2 j, 2 j + 1 of H are c[4 W + E] >> 4 and bits 16 + 2 j, 17 + 2 j are
+    c[4 W + E + 2] >> 4, j = 2 W + E."""
+    c = codes.detach().cpu().numpy().astype(np.uint32)
+    lead, T = c.shape[:-2], c.shape[-2]
+    assert c.shape[-1] == 64 and T % 16 == 0
+    c = c.reshape(-1, T // 16, 2, 8, 4, 16)                       # (unit, step, half, g, t, p)
+    lo, hi = c & 15, (c >> 4) & 3
+    A = np.zeros(c.shape[:-1] + (2,), dtype=np.uint32)            # (..., k)
+    for k in range(2):
+        for i in range(4):
+            A[..., k] |= lo[..., 8 * k + i] << (4 * (2 * i)) | lo[..., 8 * k + 4 + i] << (4 * (2 * i + 1))
+    H = np.zeros(c.shape[:-1], dtype=np.uint32)
+    for W in range(4):
+        for E in range(2):
+            j = 2 * W + E
+            H |= hi[..., 4 * W + E] << (2 * j) | hi[..., 4 * W + E + 2] << (16 + 2 * j)
+    n = c.shape[0]
+    tile = np.zeros((n, T // 16, 768), dtype=np.uint8)
+    # words of lane l: [A0(g), A1(g), A0(g+8), A1(g+8)] at 16 l; [H(g), H(g+8)] at 512 + 8 l
+    a_words = np.stack([A[:, :, 0, :, :, 0], A[:, :, 0, :, :, 1], A[:, :, 1, :, :, 0], A[:, :, 1, :, :, 1]], axis=-1)
+    h_words = np.stack([H[:, :, 0], H[:, :, 1]], axis=-1)         # (unit, step, g, t, 2)
+    tile[:, :, :512] = np.ascontiguousarray(a_words.reshape(n, T // 16, 32, 4)).astype("<u4").view(np.uint8) \
+        .reshape(n, T // 16, 512)
+    tile[:, :, 512:] = np.ascontiguousarray(h_words.reshape(n, T // 16, 32, 2)).astype("<u4").view(np.uint8) \
+        .reshape(n, T // 16, 256)
+    return torch.from_numpy(tile.reshape(*lead, T // 16, 768))
+
+
+def unpack_keys6(tiles: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``pack_keys6``: (..., S, 768) uint8 -> (..., 16 S, 64) uint8."""
+    t = tiles.detach().cpu().numpy()
+    lead, S = t.shape[:-2], t.shape[-2]
+    assert t.shape[-1] == 768
+    t = t.reshape(-1, S, 768)
+    n = t.shape[0]
+    a = np.ascontiguousarray(t[:, :, :512]).view("<u4").reshape(n, S, 8, 4, 2, 2).astype(np.uint32)  # g, t, half, k
+    h = np.ascontiguousarray(t[:, :, 512:]).view("<u4").reshape(n, S, 8, 4, 2).astype(np.uint32)     # g, t, half
+    out = np.zeros((n, S, 2, 8, 4, 16), dtype=np.uint32)                                             # half, g, t, p
+    for half in range(2):
+        for k in range(2):
+            for i in range(4):
+                out[:, :, half, :, :, 8 * k + i] |= (a[:, :, :, :, half, k] >> (4 * (2 * i))) & 15
+                out[:, :, half, :, :, 8 * k + 4 + i] |= (a[:, :, :, :, half, k] >> (4 * (2 * i + 1))) & 15
+        for W in range(4):
+            for E in range(2):
+                j = 2 * W + E
+                out[:, :, half, :, :, 4 * W + E] |= ((h[:, :, :, :, half] >> (2 * j)) & 3) << 4
+                out[:, :, half, :, :, 4 * W + E + 2] |= ((h[:, :, :, :, half] >> (16 + 2 * j)) & 3) << 4
+    return torch.from_numpy(out.astype(np.uint8).reshape(*lead, S * 16, 64))
 
 
 # ----------------------------------------------------------------------------

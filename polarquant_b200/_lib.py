@@ -19,6 +19,8 @@ PQ_OK = 0
 PQ_QUANT_WRAP_DTYPE = 1
 PQ_QUANT_NORM_FMA = 2
 PQ_VALUES_KIVI, PQ_VALUES_TILED = 0, 1
+PQ_KEYS_BYTE, PQ_KEYS_PACKED6 = 0, 1
+PQ_QUANT_PACK6 = 4
 
 EXPORTED_SYMBOLS = (
     "pq_quantize", "pq_qk_decode", "pq_decode_attention", "pq_decode_workspace_bytes", "pq_merge_lse",
@@ -29,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
     "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn", "pq_rope_append",
     "pq_quantize_into_dyn", "pq_quantize_values_dyn", "pq_lengths_advance", "pq_key_range_check",
+    "pq_keys_repack",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -57,6 +60,7 @@ class DecodeParams(ctypes.Structure):
         ("v_scale", _vp), ("v_mn", _vp), ("vscale_stride_b", _i64), ("vscale_stride_h", _i64),
         ("vbits", _int),
         ("dyn_lengths", _vp), ("dyn_r_add", _int),
+        ("key_format", _int),
     ]
 
 
@@ -64,6 +68,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_quantize.restype = _int
     lib.pq_quantize.argtypes = [_vp, ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _int, _int,
                                 ctypes.c_uint, _vp, _vp, _vp, _vp, _vp, _vp]
+    lib.pq_keys_repack.restype = _int
+    lib.pq_keys_repack.argtypes = [_vp, _vp, _i64, _int, _vp]
     lib.pq_key_range_check.restype = _int
     lib.pq_key_range_check.argtypes = [_vp, _vp, _i64, _int, _int, _vp, _vp]
     lib.pq_selftest_quantizer.restype = _int
@@ -152,7 +158,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 4:
+        if lib.pq_abi_version() != 5:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

@@ -23,6 +23,8 @@ int rope_append_device(const void* qkv, int64_t qkv_stride_b, const void* cosv, 
                        int B, int N, int Nk, int hd, int G, const int* lengths, int values_window, int res_cap,
                        int value_cap, int res_pos, int ctx_pos, int dtype, cudaStream_t stream);
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream);
+int keys_repack_device(const uint8_t* codes_in, uint8_t* codes_out, int64_t steps, int to_format,
+                       cudaStream_t stream);
 int key_range_check_device(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype,
                            unsigned* flag_dev, cudaStream_t stream);
 int qk_decode_device(const void* q, int64_t q_sb, int64_t q_sh, const uint8_t* codes, const void* rscale,
@@ -57,7 +59,7 @@ using namespace pq;
 
 extern "C" {
 
-int pq_abi_version(void) { return 4; }
+int pq_abi_version(void) { return 5; }
 size_t pq_decode_params_size(void) { return sizeof(pq_decode_params); }
 int pq_last_cuda_error(void) { return last_cuda_error(); }
 
@@ -133,6 +135,10 @@ int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const
   return rope_append_device(qkv, qkv_stride_b, cos, sin, cs_stride_b, q_out, k_res, kres_strides, values, v_strides,
                             B, N, Nk, hd, G, lengths, values_window, res_cap, value_cap, res_pos, ctx_pos, dtype,
                             static_cast<cudaStream_t>(stream));
+}
+
+int pq_keys_repack(const uint8_t* codes_in, uint8_t* codes_out, int64_t steps, int to_format, void* stream) {
+  return keys_repack_device(codes_in, codes_out, steps, to_format, static_cast<cudaStream_t>(stream));
 }
 
 int pq_key_range_check(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype, unsigned* flag_dev,

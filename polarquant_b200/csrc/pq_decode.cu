@@ -61,6 +61,7 @@ constexpr int kPrefetch = PQ_PREFETCH_STEPS;   // steps between the L2 prefetch 
 struct DecodeArgs {
   const void* q; int64_t q_sb, q_sh;
   const uint8_t* codes; int64_t c_sb, c_sh;
+  int key_format;       // PQ_KEYS_BYTE: one byte per pair; PQ_KEYS_PACKED6: 48 bytes per token, tiled per 16-token step
   const void *rscale, *rmn, *tscale, *tmn; int64_t s_sb, s_sh;
   const void* kres; int64_t kr_sb, kr_sh, kr_st;
   const void* v; int64_t v_sb, v_sh, v_st;
@@ -270,17 +271,12 @@ template <int IMM> __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr
 //   * gather address = byte permute splicing ((theta ^ x) << 2) | (t << (TBITS + 2)) from the
 //     prepared code word into the low byte of the 256-byte aligned table address; the row
 //     block offset (4W + E) << (TBITS + 4) rides in the load's immediate field;
-//   * radius = HFMA2 on the two code bytes at once; the multiply selects the half it needs.
-template <int RBITS, int TBITS, int W, int E>
-__device__ __forceinline__ void qk_kstep(float (&S)[4], uint32_t cgw, uint32_t chw, uint32_t og, uint32_t oh,
+//   * radius = HFMA2 on the two codes at once (hg / hh: the half pair 2^RBITS + rho of pairs
+//     4W + E and 4W + E + 2 of the two tokens); the multiply selects the half it needs.
+template <int TBITS, int W, int E>
+__device__ __forceinline__ void qk_kstep(float (&S)[4], uint32_t hg, uint32_t hh, uint32_t og, uint32_t oh,
                                          uint32_t tbl_addr, uint32_t rs, uint32_t rc, uint32_t qb0, uint32_t qb1) {
-  constexpr int MSH = 10 - RBITS;                                // mantissa shift of rho
-  constexpr uint32_t RM = (((1u << RBITS) - 1u) << MSH) * 0x00010001u;
-  constexpr uint32_t MAGIC = (static_cast<uint32_t>(15 + RBITS) << 10) * 0x00010001u;
-  constexpr int SR = 8 * E + TBITS + RBITS - 10;
   constexpr int ROW_A = (4 * W + E) << (TBITS + 4), ROW_B = (4 * W + E + 2) << (TBITS + 4);
-  const uint32_t hg = ((SR >= 0 ? cgw >> (SR >= 0 ? SR : 0) : cgw << (SR < 0 ? -SR : 0)) & RM) | MAGIC;
-  const uint32_t hh = ((SR >= 0 ? chw >> (SR >= 0 ? SR : 0) : chw << (SR < 0 ? -SR : 0)) & RM) | MAGIC;
   const uint32_t rg = hfma2_u(hg, rs, rc);
   const uint32_t rh = hfma2_u(hh, rs, rc);
   const uint32_t csAg = lds_u32_imm<ROW_A>(__byte_perm(og, tbl_addr, 0x7650 | E));
@@ -288,6 +284,19 @@ __device__ __forceinline__ void qk_kstep(float (&S)[4], uint32_t cgw, uint32_t c
   const uint32_t csAh = lds_u32_imm<ROW_A>(__byte_perm(oh, tbl_addr, 0x7650 | E));
   const uint32_t csBh = lds_u32_imm<ROW_B>(__byte_perm(oh, tbl_addr, 0x7650 | (E + 2)));
   mma_16816_f16(S, hmul2_lo(csAg, rg), hmul2_lo(csAh, rh), hmul2_hi(csBg, rg), hmul2_hi(csBh, rh), qb0, qb1);
+}
+
+// shift right by SR bits (left when SR is negative), SR a compile-time constant
+template <int SR> __device__ __forceinline__ uint32_t shift_by(uint32_t x) {
+  if constexpr (SR >= 0) return x >> SR; else return x << (-SR);
+}
+
+// Byte container: radius code of byte E (and E + 2) of a code word -> mantissa of the half 2^RBITS.
+template <int RBITS, int TBITS, int E> __device__ __forceinline__ uint32_t radius_half_bytes(uint32_t cw) {
+  constexpr int MSH = 10 - RBITS;                                // mantissa shift of rho
+  constexpr uint32_t RM = (((1u << RBITS) - 1u) << MSH) * 0x00010001u;
+  constexpr uint32_t MAGIC = (static_cast<uint32_t>(15 + RBITS) << 10) * 0x00010001u;
+  return (shift_by<8 * E + TBITS + RBITS - 10>(cw) & RM) | MAGIC;
 }
 
 // S^T (16 tokens x 8 heads) += K^ (16 tokens x 128 pair-channels) . q^T for one step.
@@ -305,15 +314,70 @@ __device__ __forceinline__ void qk_step_quant(float (&S)[4], const uint4& cg4, c
   {                                                                                                            \
     const uint32_t og = (((CG) << 2) & TM4) ^ lane_xor[W];                                                     \
     const uint32_t oh = (((CH) << 2) & TM4) ^ lane_xor[W];                                                     \
-    qk_kstep<RBITS, TBITS, W, 0>(S, CG, CH, og, oh, tbl_addr, rs2[W][0], rc2[W][0], qb[2 * W][0], qb[2 * W][1]); \
-    qk_kstep<RBITS, TBITS, W, 1>(S2, CG,     CH, og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0],       \
-                                 qb[2 * W + 1][1]);                                                            \
+    qk_kstep<TBITS, W, 0>(S, radius_half_bytes<RBITS, TBITS, 0>(CG), radius_half_bytes<RBITS, TBITS, 0>(CH),  \
+                          og, oh, tbl_addr, rs2[W][0], rc2[W][0], qb[2 * W][0], qb[2 * W][1]);                 \
+    qk_kstep<TBITS, W, 1>(S2, radius_half_bytes<RBITS, TBITS, 1>(CG), radius_half_bytes<RBITS, TBITS, 1>(CH), \
+                          og, oh, tbl_addr, rs2[W][1], rc2[W][1], qb[2 * W + 1][0], qb[2 * W + 1][1]);         \
   }
   PQ_WORD(0, cg4.x, ch4.x)
   PQ_WORD(1, cg4.y, ch4.y)
   PQ_WORD(2, cg4.z, ch4.z)
   PQ_WORD(3, cg4.w, ch4.w)
 #undef PQ_WORD
+#pragma unroll
+  for (int i = 0; i < 4; ++i) S[i] += S2[i];
+}
+
+// ---- 6-bit packed keys (PQ_KEYS_PACKED6) -----------------------------------------------------
+// 48 bytes per token instead of 64, for the bit splits whose code has 6 bits (3/3 and 2/4).  The format is tiled
+// per 16-token step (768 bytes) in the order the warp consumes it, so that a lane's share of a step is one 16-byte
+// and one 8-byte load and the unpacking costs what the byte container costs:
+//   bytes [0, 512):   lane l = 4 g + t holds words A0, A1 of token g, then A0, A1 of token g + 8;
+//   bytes [512, 768): lane l holds word H of token g, then H of token g + 8.
+// With c[p] the code of pair 16 t + p (p = 0..15) of a token:
+//   A_k (k = 0, 1): nibble 2 i = c[8 k + i] & 15, nibble 2 i + 1 = c[8 k + 4 + i] & 15   (i = 0..3), so the even
+//                   nibbles of A_k are the low code bits of code word 2 k and the odd ones of code word 2 k + 1;
+//   H: bits 2 j .. 2 j + 1 = c[4 W + E] >> 4 and bits 16 + 2 j .. = c[4 W + E + 2] >> 4 with j = 2 W + E
+//                   (W = 0..3, E = 0..1): the two codes one HFMA2 handles sit 16 bits apart.
+// The low nibble holds the angle code (and, for 3/3, the lowest radius bit); H holds the upper two radius bits.
+constexpr int kPackedStepBytes = 768;
+template <int RBITS, int TBITS, int W, int E>
+__device__ __forceinline__ uint32_t radius_half_packed(uint32_t aw, uint32_t hw) {
+  static_assert((RBITS == 2 && TBITS == 4) || (RBITS == 3 && TBITS == 3), "6-bit codes: 2/4 or 3/3");
+  constexpr uint32_t MAGIC = (static_cast<uint32_t>(15 + RBITS) << 10) * 0x00010001u;
+  constexpr uint32_t HI = (3u << 8) * 0x00010001u;               // the two upper radius bits at mantissa bits 8..9
+  const uint32_t top = (shift_by<2 * (2 * W + E) - 8>(hw) & HI) | MAGIC;
+  if constexpr (RBITS == 2) return top;
+  else {
+    // lowest radius bit: bit 3 of nibble 2 E + (W & 1) of the A word, to mantissa bit 7
+    constexpr uint32_t LO = (1u << 7) * 0x00010001u;
+    return (shift_by<8 * E + 4 * (W & 1) + 3 - 7>(aw) & LO) | top;
+  }
+}
+template <int RBITS, int TBITS>
+__device__ __forceinline__ void qk_step_packed6(float (&S)[4], const uint4& ca, const uint2& chh,
+                                                uint32_t tbl_addr, const uint32_t (&lane_xor)[4],
+                                                const uint32_t (&rs2)[4][2], const uint32_t (&rc2)[4][2],
+                                                const uint32_t (&qb)[8][2]) {
+  constexpr uint32_t TM4 = (((1u << TBITS) - 1u) << 2) * 0x01010101u;
+  float S2[4] = {0.f, 0.f, 0.f, 0.f};
+  // AG / AH: the A word of tokens g / g + 8 that holds code word W (A_{W / 2}); even W reads its even nibbles
+#define PQ_WORD6(W, AG, AH)                                                                                          \
+  {                                                                                                                  \
+    const uint32_t og = (shift_by<((W) & 1) ? 2 : -2>(AG) & TM4) ^ lane_xor[W];                                      \
+    const uint32_t oh = (shift_by<((W) & 1) ? 2 : -2>(AH) & TM4) ^ lane_xor[W];                                      \
+    qk_kstep<TBITS, W, 0>(S, radius_half_packed<RBITS, TBITS, W, 0>(AG, chh.x),                                      \
+                          radius_half_packed<RBITS, TBITS, W, 0>(AH, chh.y), og, oh, tbl_addr, rs2[W][0], rc2[W][0], \
+                          qb[2 * W][0], qb[2 * W][1]);                                                               \
+    qk_kstep<TBITS, W, 1>(S2, radius_half_packed<RBITS, TBITS, W, 1>(AG, chh.x),                                     \
+                          radius_half_packed<RBITS, TBITS, W, 1>(AH, chh.y), og, oh, tbl_addr, rs2[W][1], rc2[W][1], \
+                          qb[2 * W + 1][0], qb[2 * W + 1][1]);                                                       \
+  }
+  PQ_WORD6(0, ca.x, ca.z)
+  PQ_WORD6(1, ca.x, ca.z)
+  PQ_WORD6(2, ca.y, ca.w)
+  PQ_WORD6(3, ca.y, ca.w)
+#undef PQ_WORD6
 #pragma unroll
   for (int i = 0; i < 4; ++i) S[i] += S2[i];
 }
@@ -557,7 +621,7 @@ __device__ __forceinline__ void pv_quant(float (&O)[9][4], const VqTile& x, uint
 // when the packed tokens' values are packed too (VQ), none for the logits-only kernel
 constexpr int v_stages(bool qk_only, int vq) { return qk_only ? 0 : (vq ? 1 : kVStages); }
 
-template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ, bool DYN>
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ, bool DYN, int KF = PQ_KEYS_BYTE>
 __global__ void __launch_bounds__(kThreads, QK_ONLY ? 4 : PQ_MIN_CTAS)
 decode_kernel(const DecodeArgs a_in) {
   // with device-side lengths the plan is recomputed here; otherwise `a` is the parameter itself
@@ -639,9 +703,21 @@ decode_kernel(const DecodeArgs a_in) {
       const char* tm_unit = static_cast<const char*>(a.tmn) + (b * a.s_sb + kvh * a.s_sh) * QES;
       uint32_t rs2[4][2], rc2[4][2];
 
-      // lane's code bytes: token row * 64 + 16 t
-      const uint8_t* c_lane = c_unit + static_cast<int64_t>(pos) * kStep * kPairs + g * kPairs + 16 * t;
-      uint4 cg = ldg_stream(c_lane), ch = ldg_stream(c_lane + 8 * kPairs);
+      // lane's code bytes: token row * 64 + 16 t (byte container); with packed keys its 16-byte and 8-byte
+      // chunks of the step's 768-byte tile (cg: A words of tokens g and g + 8, ch.x / ch.y: their H words)
+      constexpr int kCodeStep = KF == PQ_KEYS_PACKED6 ? kPackedStepBytes : kStep * kPairs;   // code bytes per step
+      const uint8_t* c_lane = KF == PQ_KEYS_PACKED6
+                                  ? c_unit + static_cast<int64_t>(pos) * kCodeStep + 16 * lane
+                                  : c_unit + static_cast<int64_t>(pos) * kCodeStep + g * kPairs + 16 * t;
+      auto load_second = [&](const uint8_t* cl) {
+        if constexpr (KF == PQ_KEYS_PACKED6) {
+          const uint2 h = ldg8_stream(cl + 512 - 8 * lane);      // 512 + 8 * lane from the tile's start
+          return make_uint4(h.x, h.y, 0u, 0u);
+        } else {
+          return ldg_stream(cl + 8 * kPairs);
+        }
+      };
+      uint4 cg = ldg_stream(c_lane), ch = load_second(c_lane);
       // value tiles go global -> shared (cp.async) one step ahead, two stages per warp
       // this lane's fixed part of the copy addresses: row lane / 16 (+ 2 per copy), 16-byte column lane % 16
       const char* v_tile = v_unit + static_cast<int64_t>(pos) * kStep * v_row + (lane >> 4) * v_row + (lane & 15) * 16;
@@ -676,7 +752,7 @@ decode_kernel(const DecodeArgs a_in) {
       // ahead so those loads find their lines on chip.  One lane issues a bulk prefetch per
       // tile (codes: 1 KB contiguous; values: 4 KB when token rows are dense, else row by row).
       auto prefetch_tiles = [&](int step, int count) {
-        if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kStep * kPairs, count * kStep * kPairs);
+        if (lane == 0) prefetch_l2(c_unit + static_cast<int64_t>(step) * kCodeStep, count * kCodeStep);
         if constexpr (kVPipe) {
           const char* vt = v_unit + static_cast<int64_t>(step) * kStep * v_row;
           if (v_dense) { if (lane == 1) prefetch_l2(vt, count * kStep * kHeadDim * 2); }
@@ -744,9 +820,9 @@ decode_kernel(const DecodeArgs a_in) {
 #endif
           // next tile; the last step of the segment re-reads its own tile rather than branching
           const bool more = s + 1 < qs_end;
-          if (more) c_lane += kStep * kPairs;
+          if (more) c_lane += kCodeStep;
 #ifndef PQ_CODES_INPLACE
-          const uint4 ng = ldg_stream(c_lane), nh = ldg_stream(c_lane + 8 * kPairs);
+          const uint4 ng = ldg_stream(c_lane), nh = load_second(c_lane);
 #endif
           if constexpr (kVPipe) {
             if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
@@ -762,10 +838,13 @@ decode_kernel(const DecodeArgs a_in) {
           }
 
           float S[4] = {0.f, 0.f, 0.f, 0.f};
-          qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_run, lane_xor, rs2, rc2, qb);
+          if constexpr (KF == PQ_KEYS_PACKED6)
+            qk_step_packed6<RBITS, TBITS>(S, cg, make_uint2(ch.x, ch.y), tbl_run, lane_xor, rs2, rc2, qb);
+          else
+            qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_run, lane_xor, rs2, rc2, qb);
 #ifdef PQ_CODES_INPLACE
           // the code registers are free again: refill them for the next step (its lines are in L2 already)
-          cg = ldg_stream(c_lane); ch = ldg_stream(c_lane + 8 * kPairs);
+          cg = ldg_stream(c_lane); ch = load_second(c_lane);
 #endif
 
           if constexpr (QK_ONLY) {
@@ -1196,24 +1275,44 @@ size_t workspace_bytes_for(const DecodeArgs& a) {
   return slots * (kPartialFloats * sizeof(float) + kHeadTile * sizeof(float2));
 }
 
-template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ = 0, bool DYN = false>
+template <int RBITS, int TBITS, int QDT, int VDT, bool QK_ONLY, int VQ = 0, bool DYN = false, int KF = PQ_KEYS_BYTE>
 int launch_decode(const DecodeArgs& a, cudaStream_t s) {
   constexpr int kStageBytes = 4 * kPairs * (QDT == PQ_F32 ? 4 : 2);
   constexpr int kWarpSmem = kPairs * (1 << TBITS) * 4 + 2 * kStageBytes + v_stages(QK_ONLY, VQ) * kVTileSmem;
   constexpr int kSmem = kWarps * kWarpSmem;
   if (kSmem > 48 * 1024)
-    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ, DYN>,
+    PQ_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ, DYN, KF>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   // device-side lengths: always the full grid, the kernel retires the warps its own plan does not use
   const unsigned grid = DYN ? static_cast<unsigned>(a.plan_ctas) : (a.total_warps + kWarps - 1) / kWarps;
-  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ, DYN><<<grid, kThreads, kSmem, s>>>(a);
+  decode_kernel<RBITS, TBITS, QDT, VDT, QK_ONLY, VQ, DYN, KF><<<grid, kThreads, kSmem, s>>>(a);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
+}
+
+// 6-bit packed keys: the two 6-bit splits, 16-bit caches (query, keys and values of one dtype), every variant of
+// the fused kernel (full-precision or packed values, host- or device-side lengths)
+template <int RBITS, int TBITS>
+int dispatch_packed6(const DecodeArgs& a, int qdt, int vdt, cudaStream_t s) {
+  if constexpr ((RBITS == 2 && TBITS == 4) || (RBITS == 3 && TBITS == 3)) {
+#define PQ_P6(DT)                                                                                              \
+  if (qdt == DT && vdt == DT) {                                                                                \
+    if (a.dyn) return a.vq_codes ? launch_decode<RBITS, TBITS, DT, DT, false, 4, true, PQ_KEYS_PACKED6>(a, s)  \
+                                 : launch_decode<RBITS, TBITS, DT, DT, false, 0, true, PQ_KEYS_PACKED6>(a, s); \
+    return a.vq_codes ? launch_decode<RBITS, TBITS, DT, DT, false, 4, false, PQ_KEYS_PACKED6>(a, s)            \
+                      : launch_decode<RBITS, TBITS, DT, DT, false, 0, false, PQ_KEYS_PACKED6>(a, s);           \
+  }
+    PQ_P6(PQ_F16)
+    PQ_P6(PQ_BF16)
+#undef PQ_P6
+  }
+  return PQ_ERR_UNSUPPORTED;
 }
 
 template <int RBITS, int TBITS, bool QK_ONLY>
 int dispatch_dtypes(const DecodeArgs& a, int qdt, int vdt, cudaStream_t s) {
   if constexpr (!QK_ONLY) {
+    if (a.key_format == PQ_KEYS_PACKED6) return dispatch_packed6<RBITS, TBITS>(a, qdt, vdt, s);
     if (a.dyn) {            // device-side lengths: one instance per 16-bit dtype, with and without packed values
       if (qdt == PQ_F16 && vdt == PQ_F16)
         return a.vq_codes ? launch_decode<RBITS, TBITS, PQ_F16, PQ_F16, false, 4, true>(a, s)
@@ -1300,6 +1399,8 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (!dtype_ok(p->qk_dtype) || !dtype_ok(p->out_dtype)) return PQ_ERR_INVALID;
   if (p->v_dtype != PQ_F16 && p->v_dtype != PQ_BF16) return PQ_ERR_UNSUPPORTED;
   if (p->hd != kHeadDim || p->G % kStep != 0) return PQ_ERR_UNSUPPORTED;
+  if (p->key_format != PQ_KEYS_BYTE && p->key_format != PQ_KEYS_PACKED6) return PQ_ERR_INVALID;
+  if (p->key_format == PQ_KEYS_PACKED6 && p->rbits + p->tbits != 6) return PQ_ERR_INVALID;
   if (p->B == 0) return PQ_OK;
   if (p->Nb == 0 && p->R == 0) return PQ_ERR_INVALID;          // softmax over nothing
   const bool packed_v = p->vbits != 0 && p->Nb > 0;
@@ -1334,6 +1435,7 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   DecodeArgs a{};
   a.q = p->q; a.q_sb = p->q_stride_b; a.q_sh = p->q_stride_h;
   a.codes = p->codes; a.c_sb = p->codes_stride_b; a.c_sh = p->codes_stride_h;
+  a.key_format = p->key_format;
   a.rscale = p->rscale; a.rmn = p->rmn; a.tscale = p->tscale; a.tmn = p->tmn;
   a.s_sb = p->scale_stride_b; a.s_sh = p->scale_stride_h;
   a.kres = p->k_res; a.kr_sb = p->kres_stride_b; a.kr_sh = p->kres_stride_h; a.kr_st = p->kres_stride_t;

@@ -186,6 +186,49 @@ __device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)
   }
 }
 
+// ---- 6-bit packed container (PQ_KEYS_PACKED6; layout stated in include/polarquant_b200.h at pq_keys_repack) ----
+constexpr int kPackedStepBytes = 768;      // 16 tokens x 48 bytes
+// upper two code bits of the four code bytes of word W, at their places in the H word
+__device__ __forceinline__ uint32_t h_part(uint32_t word, int W) {
+  const uint32_t hb = (word >> 4) & 0x03030303u;
+  return ((hb & 0x3u) | ((hb >> 6) & 0xcu) | (hb & 0x30000u) | ((hb >> 6) & 0xc0000u)) << (4 * W);
+}
+// the four code bytes of word W back from A_{W / 2} and H
+__device__ __forceinline__ uint32_t unpack_word(uint32_t a, uint32_t h, int W) {
+  const uint32_t h4 = h >> (4 * W);
+  const uint32_t hs = (h4 & 0x3u) | ((h4 & 0xcu) << 6) | (h4 & 0x30000u) | ((h4 & 0xc0000u) << 6);
+  return ((a >> (4 * (W & 1))) & 0x0f0f0f0fu) | (hs << 4);
+}
+
+// One warp per 16-token step: lane l = 4 g + t owns pairs 16 t .. 16 t + 15 of tokens g and g + 8 in both containers.
+__global__ void keys_repack_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t steps,
+                                   int to_packed) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  for (int64_t s = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); s < steps;
+       s += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+    const uint8_t* bytes = (to_packed ? in : out) + s * 16 * kPairs + g * kPairs + 16 * t;
+    const uint8_t* tile = (to_packed ? out : in) + s * kPackedStepBytes;
+    if (to_packed) {
+      const uint4 lo = *reinterpret_cast<const uint4*>(bytes), hi = *reinterpret_cast<const uint4*>(bytes + 8 * kPairs);
+      uint4 a; uint2 h;
+      a.x = (lo.x & 0x0f0f0f0fu) | ((lo.y & 0x0f0f0f0fu) << 4); a.y = (lo.z & 0x0f0f0f0fu) | ((lo.w & 0x0f0f0f0fu) << 4);
+      a.z = (hi.x & 0x0f0f0f0fu) | ((hi.y & 0x0f0f0f0fu) << 4); a.w = (hi.z & 0x0f0f0f0fu) | ((hi.w & 0x0f0f0f0fu) << 4);
+      h.x = h_part(lo.x, 0) | h_part(lo.y, 1) | h_part(lo.z, 2) | h_part(lo.w, 3);
+      h.y = h_part(hi.x, 0) | h_part(hi.y, 1) | h_part(hi.z, 2) | h_part(hi.w, 3);
+      *reinterpret_cast<uint4*>(const_cast<uint8_t*>(tile) + 16 * lane) = a;
+      *reinterpret_cast<uint2*>(const_cast<uint8_t*>(tile) + 512 + 8 * lane) = h;
+    } else {
+      const uint4 a = *reinterpret_cast<const uint4*>(tile + 16 * lane);
+      const uint2 h = *reinterpret_cast<const uint2*>(tile + 512 + 8 * lane);
+      uint4 lo, hi;
+      lo.x = unpack_word(a.x, h.x, 0); lo.y = unpack_word(a.x, h.x, 1); lo.z = unpack_word(a.y, h.x, 2); lo.w = unpack_word(a.y, h.x, 3);
+      hi.x = unpack_word(a.z, h.y, 0); hi.y = unpack_word(a.z, h.y, 1); hi.z = unpack_word(a.w, h.y, 2); hi.w = unpack_word(a.w, h.y, 3);
+      *reinterpret_cast<uint4*>(const_cast<uint8_t*>(bytes)) = lo;
+      *reinterpret_cast<uint4*>(const_cast<uint8_t*>(bytes) + 8 * kPairs) = hi;
+    }
+  }
+}
+
 // lengths = {token groups, residual tokens} on the device; the kernel runs only when lengths[1] + r_add == full
 struct WindowGate { const int* lengths; int r_add, full, max_groups; };
 
@@ -353,7 +396,26 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   }
 
   const unsigned ttop = (1u << tbits) - 1u, rtop = (1u << rbits) - 1u;
+  const bool pack6 = (flags & PQ_QUANT_PACK6) != 0;
   uint8_t* crow = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * kPairs + p0;
+  uint8_t* ctile = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * 48;   // packed container
+  // Store the four codes (one per byte of `word`) of this thread's pairs for token `tok` of the group.  In the packed
+  // container the 16 lanes that share a token assemble their words with shuffles: the lane of code word W = lane % 4
+  // of pair block t = (lane / 4) % 4 contributes the nibbles of its codes to A_{W / 2} and their upper bits to H.
+  auto emit = [&](int tok, uint32_t word) {
+    if (!pack6) { *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok) * kPairs) = word; return; }
+    const int W = lane & 3, t = (lane >> 2) & 3;
+    uint32_t a = (word & 0x0f0f0f0fu) << (4 * (W & 1));
+    a |= __shfl_xor_sync(0xffffffffu, a, 1);
+    uint32_t hw = h_part(word, W);
+    hw |= __shfl_xor_sync(0xffffffffu, hw, 1);
+    hw |= __shfl_xor_sync(0xffffffffu, hw, 2);
+    const int r = tok & 15, l = 4 * (r & 7) + t, hi = r >> 3;
+    uint8_t* tile = ctile + static_cast<int64_t>(tok >> 4) * kPackedStepBytes;
+    if (W == 0) *reinterpret_cast<uint32_t*>(tile + 16 * l + 8 * hi) = a;
+    else if (W == 2) *reinterpret_cast<uint32_t*>(tile + 16 * l + 8 * hi + 4) = a;
+    else if (W == 1) *reinterpret_cast<uint32_t*>(tile + 512 + 8 * l + 4 * hi) = hw;
+  };
   if constexpr (NI > 0) {
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
@@ -375,7 +437,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
         word |= (((rh[0] << tbits) + th[0]) & 0xffu) << (8 * p);
         word |= (((rh[1] << tbits) + th[1]) & 0xffu) << (8 * p + 8);
       }
-      *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok0 + 16 * i) * kPairs) = word;
+      emit(tok0 + 16 * i, word);
     }
   } else {
     for (int tok = tok0; tok < G; tok += 16) {
@@ -397,7 +459,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
         word |= (((rh[0] << tbits) + th[0]) & 0xffu) << (8 * p);
         word |= (((rh[1] << tbits) + th[1]) & 0xffu) << (8 * p + 8);
       }
-      *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok) * kPairs) = word;
+      emit(tok, word);
     }
   }
 }
@@ -606,6 +668,19 @@ __global__ void key_range_check_kernel(const T* __restrict__ rscale, const T* __
 }
 }  // namespace
 
+int keys_repack_device(const uint8_t* codes_in, uint8_t* codes_out, int64_t steps, int to_format,
+                       cudaStream_t stream) {
+  if (steps < 0 || (to_format != PQ_KEYS_BYTE && to_format != PQ_KEYS_PACKED6)) return PQ_ERR_INVALID;
+  if (steps == 0) return PQ_OK;
+  if (!codes_in || !codes_out) return PQ_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(codes_in) % 16 || reinterpret_cast<uintptr_t>(codes_out) % 16) return PQ_ERR_ALIGNMENT;
+  const int64_t want = (steps + 7) / 8;
+  const unsigned grid = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
+  keys_repack_kernel<<<grid, 256, 0, stream>>>(codes_in, codes_out, steps, to_format == PQ_KEYS_PACKED6);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
 int key_range_check_device(const void* rscale, const void* rmn, int64_t count, int rbits, int dtype,
                            unsigned* flag_dev, cudaStream_t stream) {
   if (count < 0 || rbits < 0 || rbits > 8 || !dtype_ok(dtype)) return PQ_ERR_INVALID;
@@ -655,11 +730,14 @@ int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, i
     return PQ_ERR_ALIGNMENT;
   if (reinterpret_cast<uintptr_t>(codes) % 4) return PQ_ERR_ALIGNMENT;
   const int64_t nb = L / G;
-  int64_t os[4] = {nb * G * kPairs * Nk, nb * G * kPairs, nb * kPairs * Nk, nb * kPairs};
+  const bool pack6 = (flags & PQ_QUANT_PACK6) != 0;
+  if (pack6 && (rbits + tbits != 6 || G % 16 != 0)) return PQ_ERR_INVALID;
+  const int64_t tok_bytes = pack6 ? 48 : kPairs;                   // code bytes per token
+  int64_t os[4] = {nb * G * tok_bytes * Nk, nb * G * tok_bytes, nb * kPairs * Nk, nb * kPairs};
   if (out_strides) {
     for (int i = 0; i < 4; ++i) os[i] = out_strides[i];
     const int64_t span = gate_lengths ? gate_max_groups : nb;      // groups a (b, h) unit must be able to hold
-    if (os[0] % 4 || os[1] % 4 || os[1] < span * G * kPairs || os[3] < span * kPairs) return PQ_ERR_INVALID;
+    if (os[0] % 4 || os[1] % 4 || os[1] < span * G * tok_bytes || os[3] < span * kPairs) return PQ_ERR_INVALID;
   }
   switch (dtype) {
     case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);

@@ -70,13 +70,17 @@ def _vec_ok(t: torch.Tensor, elems: int) -> bool:
 
 
 def quantize_and_pack_nbit(key_states: torch.Tensor, rbits: int = 4, tbits: int = 4, group_size: int = 128,
-                           flags: int = 0):
+                           flags: int = 0, key_format: str = "byte"):
     """Polar-quantise keys (B, Nk, L, 128); same contract as the reference method.
 
     Reference: ``quantize_and_pack_nbit`` at models/modeling_llama_polar.py:135-157.
     Returns ``(indices, rscale, rmn, tscale, tmn)`` with shapes (B, Nk, L/G, G, 64)
     uint8 and four (B, Nk, L/G, 1, 64) tensors in the key dtype.  Strided inputs
     (the (B, L, Nk, hd) layout the prefill hands over) are read in place.
+
+    ``key_format="packed6"`` (bit splits 3/3 and 2/4 only) writes the codes in the 48-byte-per-token container
+    instead: ``indices`` is then (B, Nk, L/G, G/16, 768) uint8, one 768-byte tile per 16 tokens (layout:
+    ``pq_keys_repack`` in the C header); scales are unchanged.  ``decode_attention(key_format="packed6")`` reads it.
     """
     if key_states.dim() != 4:
         raise ValueError("key_states must be (batch, kv_heads, length, head_dim)")
@@ -88,7 +92,15 @@ def quantize_and_pack_nbit(key_states: torch.Tensor, rbits: int = 4, tbits: int 
     if not _vec_ok(key_states, 4):
         key_states = key_states.contiguous()
     nb = length // group_size
-    codes = torch.empty((bsz, heads, nb, group_size, hd // 2), dtype=torch.uint8, device=dev)
+    if key_format == "packed6":
+        if rbits + tbits != 6 or group_size % 16:
+            raise ValueError("the packed container holds 6-bit codes (rbits + tbits == 6) of groups of 16 k tokens")
+        flags |= _lib.PQ_QUANT_PACK6
+        codes = torch.empty((bsz, heads, nb, group_size // 16, 768), dtype=torch.uint8, device=dev)
+    elif key_format == "byte":
+        codes = torch.empty((bsz, heads, nb, group_size, hd // 2), dtype=torch.uint8, device=dev)
+    else:
+        raise ValueError("key_format must be 'byte' or 'packed6'")
     scales = [torch.empty((bsz, heads, nb, 1, hd // 2), dtype=key_states.dtype, device=dev) for _ in range(4)]
     strides = (ctypes.c_int64 * 4)(*key_states.stride())
     lib = _lib.load()
@@ -131,6 +143,35 @@ def qk_decode(query_states: torch.Tensor, indices: torch.Tensor, rscale, rmn, ts
                               scales[1].data_ptr(), scales[2].data_ptr(), scales[3].data_ptr(), out.data_ptr(),
                               bsz, nq, kvh, nb, grp, half, rbits, tbits, dt, _stream(dev))
     _lib.check(rc, "pq_qk_decode")
+    return out
+
+
+_KEY_FORMATS = {"byte": _lib.PQ_KEYS_BYTE, "packed6": _lib.PQ_KEYS_PACKED6}
+
+
+def keys_repack(indices: torch.Tensor, to_format: str) -> torch.Tensor:
+    """Convert key codes between the byte container (..., G, 64) and the 6-bit packed container
+    (..., G/16, 768); returns a new tensor.  Lossless for 6-bit codes (bit splits 3/3 and 2/4)."""
+    dev = _require_cuda(indices)
+    if indices.dtype != torch.uint8:
+        raise ValueError("indices must be uint8")
+    indices = indices.contiguous()
+    if to_format == "packed6":
+        if indices.shape[-1] != 64 or indices.shape[-2] % 16:
+            raise ValueError("byte container: (..., G, 64) with G a multiple of 16")
+        steps = indices.numel() // (16 * 64)
+        out = torch.empty((*indices.shape[:-2], indices.shape[-2] // 16, 768), dtype=torch.uint8, device=dev)
+    elif to_format == "byte":
+        if indices.shape[-1] != 768:
+            raise ValueError("packed container: (..., G/16, 768)")
+        steps = indices.numel() // 768
+        out = torch.empty((*indices.shape[:-2], indices.shape[-2] * 16, 64), dtype=torch.uint8, device=dev)
+    else:
+        raise ValueError("to_format must be 'byte' or 'packed6'")
+    lib = _lib.load()
+    with _on_device(dev):
+        rc = lib.pq_keys_repack(indices.data_ptr(), out.data_ptr(), steps, _KEY_FORMATS[to_format], _stream(dev))
+    _lib.check(rc, "pq_keys_repack")
     return out
 
 
@@ -182,7 +223,8 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
                      value_states: torch.Tensor, attention_mask=None, rbits: int = 4, tbits: int = 4,
                      sm_scale: float | None = None, out_dtype: torch.dtype | None = None,
                      return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0,
-                     mid_event=None, value_codes=None, value_scale=None, value_mn=None, vbits: int = 4):
+                     mid_event=None, value_codes=None, value_scale=None, value_mn=None, vbits: int = 4,
+                     key_format: str = "byte"):
     """One fused decode-attention step over the polar cache.
 
     Computes what the reference's decode branch computes with separate ops
@@ -202,6 +244,10 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     models/modeling_llama_polar.py:189-246): pass ``value_codes`` (B, Nk, Nb*G, 16) int32 in the TILED layout of
     ``quantize_values`` with ``value_scale`` / ``value_mn`` (B, Nk, Nb*G, 1); ``value_states`` then holds only
     the R full-precision values of the residual window (or is None when R == 0).
+
+    ``key_format="packed6"``: ``indices`` is the 48-byte-per-token container (B, Nk, Nb, G/16, 768) written by
+    ``quantize_and_pack_nbit(key_format="packed6")`` or ``keys_repack`` (bit splits 3/3 and 2/4, fp16/bf16 caches);
+    the result is bit-identical to the byte container's.
     """
     dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask, value_codes)
     bsz, nq, qlen, hd = query_states.shape
@@ -217,6 +263,10 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     nb = grp = 0
     if indices is not None and indices.shape[2] > 0:
         _, _, nb, grp, _ = indices.shape
+        if key_format == "packed6":
+            if indices.shape[-1] != 768:
+                raise ValueError("packed keys must be (B, Nk, Nb, G/16, 768) uint8")
+            grp *= 16
     else:
         indices = None
         grp = 128
@@ -297,6 +347,7 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     p.lse = lse.data_ptr() if return_lse else None
     p.B, p.N, p.Nk, p.Nb, p.G, p.R, p.hd = bsz, nq, kvh, nb, grp, res, hd
     p.rbits, p.tbits = rbits, tbits
+    p.key_format = _KEY_FORMATS[key_format]
     p.qk_dtype, p.v_dtype, p.out_dtype = qdt, vdt, _DT[out_dtype]
     p.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
     p.num_ctas = num_ctas

@@ -150,3 +150,19 @@ def test_merge_lse_recombines_a_split_sequence():
     merged, mlse = oracle.merge_lse(torch.stack([o0[:, :, 0], o1[:, :, 0]]), torch.stack([l0, l1]))
     assert float((merged - full[:, :, 0]).abs().max()) < 1e-5
     assert float((mlse - lse).abs().max()) < 1e-5
+
+
+def test_packed_key_container_round_trips_in_the_oracle():
+    """pack_keys6 / unpack_keys6 restate the 48-byte-per-token layout; they must invert each other and place
+    individual codes where the definition says."""
+    import numpy as np
+    g = torch.Generator().manual_seed(17)
+    c = torch.randint(0, 64, (3, 48, 64), generator=g, dtype=torch.uint8)
+    p = oracle.pack_keys6(c)
+    assert p.shape == (3, 3, 768) and torch.equal(oracle.unpack_keys6(p), c)
+    tile = p[1, 2].numpy()                                     # unit 1, tokens 32..47
+    lane = 4 * 5 + 2                                           # token row g = 5, pair block t = 2
+    a1 = int(np.frombuffer(tile[16 * lane + 4: 16 * lane + 8].tobytes(), dtype="<u4")[0])     # A1 of token 32 + 5
+    assert (a1 >> 8) & 15 == int(c[1, 37, 32 + 8 + 1]) & 15    # nibble 2: code p = 9 (k = 1, i = 1)
+    h_hi = int(np.frombuffer(tile[512 + 8 * lane + 4: 512 + 8 * lane + 8].tobytes(), dtype="<u4")[0])   # token 45
+    assert (h_hi >> (16 + 2 * 5)) & 3 == int(c[1, 45, 32 + 4 * 2 + 1 + 2]) >> 4                # W = 2, E = 1 partner
