@@ -131,10 +131,15 @@ def test_llama_patch_prefill_and_decode_on_the_cuda_kernels(clean_models_namespa
 
 def test_qwen_patch_prefill_and_decode_on_the_cuda_kernels(clean_models_namespace):
     """7 query heads per kv head; the Qwen patch hands the kernel codes and scales repeated per query head
-    (models/modeling_qwen_polar.py:64-76)."""
+    (models/modeling_qwen_polar.py:64-76).  Two kv heads, not one: with a single kv head ``repeat_kv_quant``
+    returns a stride-0 view instead of a copy, and the reference's Triton wrapper, which does raw pointer
+    arithmetic on what it assumes to be contiguous tensors (models/kernel4group.py:40-53), then reads memory that
+    is not the tensor's.  This library's entry point honours the strides (covered with one kv head by
+    test_decode_branch_of_the_reference_forward_matches_the_fused_kernel); the yardstick needs a case where the
+    reference itself is well defined."""
     from transformers import Qwen2Config
-    cfg = Qwen2Config(hidden_size=7 * 128, intermediate_size=512, num_hidden_layers=2, num_attention_heads=7,
-                      num_key_value_heads=1, vocab_size=128)
+    cfg = Qwen2Config(hidden_size=14 * 128, intermediate_size=512, num_hidden_layers=2, num_attention_heads=14,
+                      num_key_value_heads=2, vocab_size=128)
     compare_runs(lambda qwen: qwen.Qwen2PolarForCausalLM(cfg), lambda pair: pair[1])
 
 
