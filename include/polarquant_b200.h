@@ -128,8 +128,10 @@ int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const
  * IEEE division by cheaper approximations wherever the approximation provably rounds to the same 16-bit value,
  * and calls the exact routine otherwise.  This entry point checks that claim exhaustively on the device: for all
  * 2^32 pairs of 16-bit patterns of `dtype` (PQ_F16 or PQ_BF16) it compares the fast-path result with the
- * exact-only result - which = 0: angle and radius of the key pair (x, y); which = 1: quantisation level of value
- * x with step y - and writes the number of disagreeing pairs to *mismatches_dev (device memory, 8 bytes).
+ * exact-only result - which = 0: angle and radius of the key pair (x, y), its mirror image and both with the first
+ * channel negated; which = 1: quantisation level of the rounded difference x with step y; which = 2: the packed
+ * 16-bit subtraction x - y against the fp32 subtraction rounded to `dtype` - and writes the number of disagreeing
+ * cases to *mismatches_dev (device memory, 8 bytes).
  */
 int pq_selftest_quantizer(int dtype, int which, unsigned long long* mismatches_dev, void* stream);
 

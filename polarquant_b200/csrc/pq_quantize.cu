@@ -115,75 +115,144 @@ template <> struct FastPathPays<__nv_bfloat16> { static constexpr bool value = t
 template <> struct FastPathPays<__half> { static constexpr bool value = true; };
 #endif
 
-// angle and radius of two pairs at once (the roundings are packed two by two)
+// Angle and radius of the four pairs a thread holds of one token, each rounded to T where torch rounds:
+//   phi = RN(atan2f(y, x)); if (phi < 0) phi = RN(phi + wrap);   rad = RN(sqrtf(x^2 + y^2)).
+// Fast form (16-bit T): polynomial arctangent and rsqrt-based root, accepted when polar_safe says the approximation
+// rounds like the exact value; one branch per token covers the rare items that need the library routines.
 template <typename T, bool FAST = true, bool FORCE = false>
-__device__ __forceinline__ void polar_of2(const float (&x)[2], const float (&y)[2], float wrap, bool norm_separate,
-                                          float (&phi)[2], float (&rad)[2]) {
+__device__ __forceinline__ void polar_of4(const float (&x)[4], const float (&y)[4], float wrap, bool norm_separate,
+                                          float (&phi)[4], float (&rad)[4]) {
   constexpr bool kFast = FAST && (FORCE || FastPathPays<T>::value) && Elem<T>::kDtype != PQ_F32;
-  float a[2], r[2];
-  bool ok[2] = {false, false};
+  float a[4], r[4];
   if constexpr (kFast) {
+    bool all_ok = true;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < 4; ++k) {
       a[k] = atan2_approx(y[k], x[k]);
       // for 16-bit keys the two products are exact in fp32, so both forms of the sum agree
       const float s = __fmaf_rn(y[k], y[k], __fmul_rn(x[k], x[k]));
       float rs;
       asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(rs) : "f"(s));
       r[k] = s * rs;
-      ok[k] = mid_range(a[k]) && rounds_safely<T>(a[k]) && mid_range(r[k]) && rounds_safely<T>(r[k]);
+      all_ok = all_ok & polar_safe<T>(a[k], r[k]);       // bitwise: no short-circuit branches in the hot path
     }
-  }
-  if constexpr (!kFast) {                      // exact-only dtypes: the library calls inline, no call overhead
+    if (!all_ok) {                             // rarely taken: redo the unsafe items with the library routines
 #pragma unroll
-    for (int k = 0; k < 2; ++k) { const float2 e = polar_exact_inline(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
-  } else if (!(ok[0] && ok[1])) {              // one rarely taken branch for both items
+      for (int k = 0; k < 4; ++k)
+        if (!polar_safe<T>(a[k], r[k])) { const float2 e = polar_exact(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
+    }
+  } else {                                     // exact-only dtypes: the library calls inline, no call overhead
 #pragma unroll
-    for (int k = 0; k < 2; ++k)
-      if (!ok[k]) { const float2 e = polar_exact(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
+    for (int k = 0; k < 4; ++k) { const float2 e = polar_exact_inline(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
   }
-  round2<T>(a[0], a[1], a[0], a[1]);
-  float w[2];
-  round2<T>(__fadd_rn(a[0], wrap), __fadd_rn(a[1], wrap), w[0], w[1]);
-  phi[0] = a[0] < 0.0f ? w[0] : a[0];
-  phi[1] = a[1] < 0.0f ? w[1] : a[1];
-  round2<T>(r[0], r[1], rad[0], rad[1]);
+#pragma unroll
+  for (int k = 0; k < 4; k += 2) {
+    round2<T>(a[k], a[k + 1], a[k], a[k + 1]);
+    float w[2];
+    round2<T>(__fadd_rn(a[k], wrap), __fadd_rn(a[k + 1], wrap), w[0], w[1]);
+    phi[k] = a[k] < 0.0f ? w[0] : a[k];
+    phi[k + 1] = a[k + 1] < 0.0f ? w[1] : a[k + 1];
+    round2<T>(r[k], r[k + 1], rad[k], rad[k + 1]);
+  }
 }
 
-// floor(RN(RN(v - lo) / step)) clamped to [0, top], for two values.  `rstep` is the correctly rounded
-// reciprocal of `step` (guarded_rcp); the product is within 1.5 ulp of the IEEE quotient and is used when it rounds safely.
-// A quotient that is not below 256 (inf, NaN from a zero step, ...) takes the exact division and cast.
+// The same for 16-bit T with the results as packed pairs (pairs 0-1 and 2-3), which is how the kernel keeps them
+// between its two passes: one conversion rounds the angle, the wrap is added in fp32 to the rounded value and the
+// selected value is packed (packing an already rounded value is exact), the radius is packed once.
 template <typename T, bool FAST = true, bool FORCE = false>
-__device__ __forceinline__ void level_of2(const float (&v)[2], const float (&lo)[2], const float (&step)[2],
-                                          const float (&rstep)[2], unsigned top, unsigned (&lvl)[2]) {
-  constexpr bool kFast = FAST && (FORCE || FastPathPays<T>::value) && Elem<T>::kDtype != PQ_F32;
-  float d[2], q[2];
-  round2<T>(__fsub_rn(v[0], lo[0]), __fsub_rn(v[1], lo[1]), d[0], d[1]);
-  bool ok[2] = {false, false};
+__device__ __forceinline__ void polar_of4_packed(const float (&x)[4], const float (&y)[4], float wrap, bool norm_separate,
+                                                 uint32_t (&phi_w)[2], uint32_t (&rad_w)[2]) {
+  constexpr bool kFast = FAST && (FORCE || FastPathPays<T>::value);
+  constexpr int DT16 = Elem<T>::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
+  float a[4], r[4];
   if constexpr (kFast) {
+    bool all_ok = true;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      q[k] = d[k] * rstep[k];
-      // rstep is guarded_rcp(step): NaN unless the step is an ordinary number, and NaN fails the comparison
-      ok[k] = q[k] < 256.0f && rounds_safely<T>(q[k]);
+    for (int k = 0; k < 4; ++k) {
+      a[k] = atan2_approx(y[k], x[k]);
+      const float s = __fmaf_rn(y[k], y[k], __fmul_rn(x[k], x[k]));
+      float rs;
+      asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(rs) : "f"(s));
+      r[k] = s * rs;
+      all_ok = all_ok & polar_safe<T>(a[k], r[k]);
     }
-  }
-  if constexpr (!kFast) {
-    q[0] = __fdiv_rn(d[0], step[0]); q[1] = __fdiv_rn(d[1], step[1]);
-  } else if (!(ok[0] && ok[1])) {
+    if (!all_ok) {
 #pragma unroll
-    for (int k = 0; k < 2; ++k)
-      if (!ok[k]) q[k] = div_exact(d[k], step[k]);
+      for (int k = 0; k < 4; ++k)
+        if (!polar_safe<T>(a[k], r[k])) { const float2 e = polar_exact(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 e = polar_exact_inline(x[k], y[k], norm_separate); a[k] = e.x; r[k] = e.y; }
   }
-  round2<T>(q[0], q[1], q[0], q[1]);
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
-    // in [0, 256) truncation to int is the floor and equals the reference's cast chain
-    const bool small = q[k] >= 0.0f && q[k] < 256.0f;
-    unsigned u = static_cast<unsigned>(__float2int_rz(small ? q[k] : 0.0f));
-    if (!small) u = cast_like_aten(floorf(q[k]));
-    lvl[k] = u < top ? u : top;
+    const float2 ar = unpack2<DT16>(pack2<DT16>(a[2 * k], a[2 * k + 1]));
+    const float p0 = ar.x < 0.0f ? __fadd_rn(ar.x, wrap) : ar.x, p1 = ar.y < 0.0f ? __fadd_rn(ar.y, wrap) : ar.y;
+    phi_w[k] = pack2<DT16>(p0, p1);
+    rad_w[k] = pack2<DT16>(r[2 * k], r[2 * k + 1]);
   }
+}
+
+// Quantisation level of d = RN(v - lo) (already rounded to T): min(u8(floor(RN(d / step))), top), the reference's
+// chain floor -> uint8 cast -> clamp.  `exact` is the reference arithmetic verbatim.
+template <typename T> __device__ __forceinline__ unsigned level_exact(float d, float step, unsigned top) {
+  const float q = Elem<T>::round(__fdiv_rn(d, step));
+  // in [0, 256) truncation to int is the floor and equals the reference's cast chain
+  const bool small = q >= 0.0f && q < 256.0f;
+  unsigned u = static_cast<unsigned>(__float2int_rz(small ? q : 0.0f));
+  if (!small) u = cast_like_aten(floorf(q));
+  return u < top ? u : top;
+}
+__device__ __noinline__ unsigned level_exact_bf16(float d, float step, unsigned top) { return level_exact<__nv_bfloat16>(d, step, top); }
+__device__ __noinline__ unsigned level_exact_f16(float d, float step, unsigned top) { return level_exact<__half>(d, step, top); }
+template <typename T> __device__ __forceinline__ unsigned level_exact_call(float d, float step, unsigned top) {
+  if constexpr (Elem<T>::kDtype == PQ_BF16) return level_exact_bf16(d, step, top);
+  else if constexpr (Elem<T>::kDtype == PQ_F16) return level_exact_f16(d, step, top);
+  else return level_exact<T>(d, step, top);
+}
+
+// Code bytes (rho << tbits) + theta of four pairs from the rounded differences dt = RN(phi - tmn), dr = RN(rad - rmn).
+// Fast form: the quotient by div_refined (correctly rounded, no tie test), accepted while 0 <= q < 255 - which also
+// screens NaN, negative and degenerate steps (their reciprocal is NaN) - then RN to T, clamp and floor in floating
+// point (a quotient below 255 cannot round up to 256, where the reference's uint8 cast wraps to 0).
+template <typename T, bool FAST = true>
+__device__ __forceinline__ uint32_t codes_of4(const float (&dt)[4], const float (&dr)[4], const float (&tstep)[4],
+                                              const float (&trcp)[4], const float (&rstep)[4], const float (&rrcp)[4],
+                                              unsigned ttop, unsigned rtop, int tbits) {
+  constexpr bool kFast = FAST && Elem<T>::kDtype != PQ_F32;
+  uint32_t word = 0;
+  if constexpr (kFast) {
+    float qt[4], qr[4];
+    bool all_ok = true;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      qt[k] = div_refined(dt[k], tstep[k], trcp[k]);
+      qr[k] = div_refined(dr[k], rstep[k], rrcp[k]);
+      all_ok = all_ok & (__float_as_uint(qt[k]) < 0x437f0000u) & (__float_as_uint(qr[k]) < 0x437f0000u);   // [0, 255)
+    }
+    if (all_ok) {
+      const float tf = static_cast<float>(ttop), rf = static_cast<float>(rtop);
+#pragma unroll
+      for (int k = 0; k < 4; k += 2) {
+        round2<T>(qt[k], qt[k + 1], qt[k], qt[k + 1]);
+        round2<T>(qr[k], qr[k + 1], qr[k], qr[k + 1]);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t th = floor_bits(fminf(qt[k], tf)), rh = floor_bits(fminf(qr[k], rf));
+        word |= (((rh << tbits) + th) & 0xffu) << (8 * k);
+      }
+      return word;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const unsigned th = kFast ? level_exact_call<T>(dt[k], tstep[k], ttop) : level_exact<T>(dt[k], tstep[k], ttop);
+    const unsigned rh = kFast ? level_exact_call<T>(dr[k], rstep[k], rtop) : level_exact<T>(dr[k], rstep[k], rtop);
+    word |= (((rh << tbits) + th) & 0xffu) << (8 * k);
+  }
+  return word;
 }
 
 // ---- 6-bit packed container (PQ_KEYS_PACKED6; layout stated in include/polarquant_b200.h at pq_keys_repack) ----
@@ -231,6 +300,168 @@ __global__ void keys_repack_kernel(const uint8_t* __restrict__ in, uint8_t* __re
 
 // lengths = {token groups, residual tokens} on the device; the kernel runs only when lengths[1] + r_add == full
 struct WindowGate { const int* lengths; int r_add, full, max_groups; };
+
+// 16-bit keys, G a multiple of 16 up to kMaxSmemGroup: angle and radius of the group wait in shared memory between
+// the two passes (16 bytes per thread and token, conflict-free), so the token loops stay rolled - a small code
+// footprint that the instruction cache holds - and a thread needs 64 registers (four CTAs per SM).
+// A CTA of eight warps covers 128 tokens: one group of 128, or 128 / G groups side by side for G = 16, 32, 64
+// (`wpg` warps per group), so that the fixed cost per CTA - two barriers, the min/max reduction, the reciprocals of
+// the steps - is spread over the same number of pairs whatever the group size.  Other multiples of 16 take one
+// group per CTA.
+constexpr int kMaxSmemGroup = 128;
+#ifndef PQ_QUANT16_MIN_CTAS
+#define PQ_QUANT16_MIN_CTAS 4
+#endif
+template <typename T, int WPG>
+__global__ void __launch_bounds__(kQuantThreads, PQ_QUANT16_MIN_CTAS)
+quantize_kernel16(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, int Nk, int nb, int G,
+                  int rbits, int tbits, unsigned flags, uint8_t* __restrict__ codes, T* __restrict__ rscale,
+                  T* __restrict__ rmn_out, T* __restrict__ tscale, T* __restrict__ tmn_out,
+                  int64_t c_sb, int64_t c_sh, int64_t s_sb, int64_t s_sh, const WindowGate gate, int total_groups) {
+  constexpr int wpg = WPG;                                 // warps per group
+  using E = Elem<T>;
+  constexpr int DT16 = E::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
+  int group_off = 0;
+  if (gate.lengths) {
+    group_off = gate.lengths[0];
+    if (gate.lengths[1] + gate.r_add != gate.full || group_off < 0 || group_off + nb > gate.max_groups) return;
+  }
+  extern __shared__ uint4 s_polar[];                       // [G / 16][kQuantThreads]: phi pairs 0-1, 2-3, rad pairs 0-1, 2-3
+  __shared__ float red[4][kQuantThreads / 32][kPairs];
+  constexpr int gpc = (kQuantThreads / 32) / wpg;          // groups per CTA
+  __shared__ float fin[gpc][4][kPairs];                    // per group of the CTA
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gsub = warp / wpg, wsub = warp % wpg;          // this warp's group within the CTA, its place in it
+  const int tile = blockIdx.x * gpc + gsub;                // (b * Nk + h) * nb + j; the host keeps it below 2^31
+  const bool live = tile < total_groups;                   // the last CTA may hold fewer groups
+  const int tl = live ? tile : 0;
+  const int j = tl % nb;
+  const int bh = tl / nb;
+  const int h = bh % Nk, b = bh / Nk;
+  const int tsub = lane >> 4;
+  const int p0 = (lane & 15) * 4;             // first of this thread's four pairs
+  const int tok_step = 2 * wpg;               // tokens the group's warps cover per iteration
+  const int ni = live ? G / tok_step : 0;
+  const int tok0 = 2 * wsub + tsub;
+  const T* row = keys + b * sb + h * sh + (static_cast<int64_t>(j) * G + tok0) * sl + p0;
+  const int64_t row_step = tok_step * sl;
+
+  const float wrap = (flags & PQ_QUANT_WRAP_DTYPE) ? E::round(6.283185307179586f) : 6.283185307179586f;
+  const bool norm_sep = (flags & PQ_QUANT_NORM_FMA) == 0;
+
+  // identities of the NaN-propagating max / min: -inf and +inf as packed pairs
+  constexpr uint32_t kNegInf2 = DT16 == PQ_BF16 ? 0xff80ff80u : 0xfc00fc00u, kPosInf2 = DT16 == PQ_BF16 ? 0x7f807f80u : 0x7c007c00u;
+  uint32_t tmx_w[2] = {kNegInf2, kNegInf2}, tmn_w[2] = {kPosInf2, kPosInf2};
+  uint32_t rmx_w[2] = {kNegInf2, kNegInf2}, rmn_w[2] = {kPosInf2, kPosInf2};
+#pragma unroll 2
+  for (int i = 0; i < ni; ++i) {
+    float x[4], y[4];
+    load4<T>(row, x);
+    load4<T>(row + kPairs, y);
+    row += row_step;
+    uint32_t pw[2], rw[2];
+    polar_of4_packed<T>(x, y, wrap, norm_sep, pw, rw);
+    s_polar[i * kQuantThreads + threadIdx.x] = make_uint4(pw[0], pw[1], rw[0], rw[1]);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      tmx_w[k] = max2_nan<DT16>(tmx_w[k], pw[k]); tmn_w[k] = min2_nan<DT16>(tmn_w[k], pw[k]);
+      rmx_w[k] = max2_nan<DT16>(rmx_w[k], rw[k]); rmn_w[k] = min2_nan<DT16>(rmn_w[k], rw[k]);
+    }
+  }
+  float tmx[4], tmn[4], rmx[4], rmn[4];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    float2 f;
+    f = unpack2<DT16>(tmx_w[k]); tmx[2 * k] = f.x; tmx[2 * k + 1] = f.y;
+    f = unpack2<DT16>(tmn_w[k]); tmn[2 * k] = f.x; tmn[2 * k + 1] = f.y;
+    f = unpack2<DT16>(rmx_w[k]); rmx[2 * k] = f.x; rmx[2 * k + 1] = f.y;
+    f = unpack2<DT16>(rmn_w[k]); rmn[2 * k] = f.x; rmn[2 * k + 1] = f.y;
+  }
+  // combine the two token halves of the warp, then the eight warps
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    tmx[p] = max_nan(tmx[p], __shfl_xor_sync(0xffffffffu, tmx[p], 16));
+    tmn[p] = min_nan(tmn[p], __shfl_xor_sync(0xffffffffu, tmn[p], 16));
+    rmx[p] = max_nan(rmx[p], __shfl_xor_sync(0xffffffffu, rmx[p], 16));
+    rmn[p] = min_nan(rmn[p], __shfl_xor_sync(0xffffffffu, rmn[p], 16));
+  }
+  if (tsub == 0) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      red[0][warp][p0 + p] = tmx[p]; red[1][warp][p0 + p] = tmn[p];
+      red[2][warp][p0 + p] = rmx[p]; red[3][warp][p0 + p] = rmn[p];
+    }
+  }
+  __syncthreads();
+  {
+    const int stat = threadIdx.x >> 6, pair = threadIdx.x & 63;
+#pragma unroll
+    for (int gq = 0; gq < gpc; ++gq) {
+      float v = red[stat][gq * wpg][pair];
+#pragma unroll
+      for (int w = 1; w < wpg; ++w)
+        v = (stat & 1) ? min_nan(v, red[stat][gq * wpg + w][pair]) : max_nan(v, red[stat][gq * wpg + w][pair]);
+      fin[gq][stat][pair] = v;
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+
+  float tstep[4], rstep[4], trcp[4], rrcp[4];
+  const float inv_t = 1.0f / static_cast<float>(1 << tbits), inv_r = 1.0f / static_cast<float>(1 << rbits);
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    tmx[p] = fin[gsub][0][p0 + p]; tmn[p] = fin[gsub][1][p0 + p];
+    rmx[p] = fin[gsub][2][p0 + p]; rmn[p] = fin[gsub][3][p0 + p];
+    // dividing by a power of two equals multiplying by its exact reciprocal
+    tstep[p] = E::round(__fmul_rn(E::round(__fsub_rn(tmx[p], tmn[p])), inv_t));
+    rstep[p] = E::round(__fmul_rn(E::round(__fsub_rn(rmx[p], rmn[p])), inv_r));
+    trcp[p] = guarded_rcp(tstep[p]);
+    rrcp[p] = guarded_rcp(rstep[p]);
+  }
+  if (wsub == 0 && tsub == 0) {
+    const int64_t so = b * s_sb + h * s_sh + static_cast<int64_t>(j + group_off) * kPairs + p0;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      rscale[so + p] = E::from_float(rstep[p]); rmn_out[so + p] = E::from_float(rmn[p]);
+      tscale[so + p] = E::from_float(tstep[p]); tmn_out[so + p] = E::from_float(tmn[p]);
+    }
+  }
+  const uint32_t tlo_w[2] = {pack2<DT16>(tmn[0], tmn[1]), pack2<DT16>(tmn[2], tmn[3])};
+  const uint32_t rlo_w[2] = {pack2<DT16>(rmn[0], rmn[1]), pack2<DT16>(rmn[2], rmn[3])};
+
+  const unsigned ttop = (1u << tbits) - 1u, rtop = (1u << rbits) - 1u;
+  const bool pack6 = (flags & PQ_QUANT_PACK6) != 0;
+  uint8_t* crow = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * kPairs + p0;
+  uint8_t* ctile = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * 48;   // packed container
+#pragma unroll 2
+  for (int i = 0; i < ni; ++i) {
+    const uint4 v = s_polar[i * kQuantThreads + threadIdx.x];
+    const float2 t01 = unpack2<DT16>(sub2_packed<DT16>(v.x, tlo_w[0])), t23 = unpack2<DT16>(sub2_packed<DT16>(v.y, tlo_w[1]));
+    const float2 r01 = unpack2<DT16>(sub2_packed<DT16>(v.z, rlo_w[0])), r23 = unpack2<DT16>(sub2_packed<DT16>(v.w, rlo_w[1]));
+    const float dt[4] = {t01.x, t01.y, t23.x, t23.y}, dr[4] = {r01.x, r01.y, r23.x, r23.y};
+    const uint32_t word = codes_of4<T>(dt, dr, tstep, trcp, rstep, rrcp, ttop, rtop, tbits);
+    const int tok = tok0 + tok_step * i;
+    if (!pack6) {
+      *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok) * kPairs) = word;
+    } else {
+      // the 16 lanes that share a token assemble the words of the packed container with shuffles (layout and
+      // roles of the lanes as in quantize_kernel's emit)
+      const int W = lane & 3, t = (lane >> 2) & 3;
+      uint32_t a = (word & 0x0f0f0f0fu) << (4 * (W & 1));
+      a |= __shfl_xor_sync(0xffffffffu, a, 1);
+      uint32_t hw = h_part(word, W);
+      hw |= __shfl_xor_sync(0xffffffffu, hw, 1);
+      hw |= __shfl_xor_sync(0xffffffffu, hw, 2);
+      const int r = tok & 15, l = 4 * (r & 7) + t, hi = r >> 3;
+      uint8_t* tl = ctile + static_cast<int64_t>(tok >> 4) * kPackedStepBytes;
+      if (W == 0) *reinterpret_cast<uint32_t*>(tl + 16 * l + 8 * hi) = a;
+      else if (W == 2) *reinterpret_cast<uint32_t*>(tl + 16 * l + 8 * hi + 4) = a;
+      else if (W == 1) *reinterpret_cast<uint32_t*>(tl + 512 + 8 * l + 4 * hi) = hw;
+    }
+  }
+}
 
 // NI > 0: the thread keeps phi and r of its NI tokens x 4 pairs in registers
 // (G == 16 * NI).  NI == 0: any G; phi and r are recomputed in the second pass.
@@ -283,20 +514,18 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
       const T* row = base + static_cast<int64_t>(tok0 + 16 * i) * sl;
-      float x[4], y[4];
+      float x[4], y[4], ph[4], rd[4];
       load4<T>(row + p0, x);
       load4<T>(row + p0 + kPairs, y);
+      polar_of4<T>(x, y, wrap, norm_sep, ph, rd);
 #pragma unroll
-      for (int p = 0; p < 4; p += 2) {
-        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
-        float ph[2], rd[2];
-        polar_of2<T>(xx, yy, wrap, norm_sep, ph, rd);
-        const uint32_t pw = pack2<DT16>(ph[0], ph[1]), rw = pack2<DT16>(rd[0], rd[1]);   // exact: already rounded
-        phi_w[i][p >> 1] = pw; rad_w[i][p >> 1] = rw;
-        if (i == 0) { tmx_w[p >> 1] = tmn_w[p >> 1] = pw; rmx_w[p >> 1] = rmn_w[p >> 1] = rw; }
+      for (int k = 0; k < 2; ++k) {
+        const uint32_t pw = pack2<DT16>(ph[2 * k], ph[2 * k + 1]), rw = pack2<DT16>(rd[2 * k], rd[2 * k + 1]);   // exact: already rounded
+        phi_w[i][k] = pw; rad_w[i][k] = rw;
+        if (i == 0) { tmx_w[k] = tmn_w[k] = pw; rmx_w[k] = rmn_w[k] = rw; }
         else {
-          tmx_w[p >> 1] = max2_nan<DT16>(tmx_w[p >> 1], pw); tmn_w[p >> 1] = min2_nan<DT16>(tmn_w[p >> 1], pw);
-          rmx_w[p >> 1] = max2_nan<DT16>(rmx_w[p >> 1], rw); rmn_w[p >> 1] = min2_nan<DT16>(rmn_w[p >> 1], rw);
+          tmx_w[k] = max2_nan<DT16>(tmx_w[k], pw); tmn_w[k] = min2_nan<DT16>(tmn_w[k], pw);
+          rmx_w[k] = max2_nan<DT16>(rmx_w[k], rw); rmn_w[k] = min2_nan<DT16>(rmn_w[k], rw);
         }
       }
     }
@@ -315,13 +544,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
       float x[4], y[4];
       load4<T>(row + p0, x);
       load4<T>(row + p0 + kPairs, y);
-#pragma unroll
-      for (int p = 0; p < 4; p += 2) {
-        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
-        float ph[2], rd[2];
-        polar_of2<T>(xx, yy, wrap, norm_sep, ph, rd);
-        phi[i][p] = ph[0]; phi[i][p + 1] = ph[1]; rad[i][p] = rd[0]; rad[i][p + 1] = rd[1];
-      }
+      polar_of4<T>(x, y, wrap, norm_sep, phi[i], rad[i]);
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
         tmx[p] = max_nan(tmx[p], phi[i][p]); tmn[p] = min_nan(tmn[p], phi[i][p]);
@@ -331,19 +554,14 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
   } else {
     for (int tok = tok0; tok < G; tok += 16) {
       const T* row = base + static_cast<int64_t>(tok) * sl;
-      float x[4], y[4];
+      float x[4], y[4], ph[4], rd[4];
       load4<T>(row + p0, x);
       load4<T>(row + p0 + kPairs, y);
+      polar_of4<T>(x, y, wrap, norm_sep, ph, rd);
 #pragma unroll
-      for (int p = 0; p < 4; p += 2) {
-        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
-        float ph[2], rd[2];
-        polar_of2<T>(xx, yy, wrap, norm_sep, ph, rd);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          tmx[p + k] = max_nan(tmx[p + k], ph[k]); tmn[p + k] = min_nan(tmn[p + k], ph[k]);
-          rmx[p + k] = max_nan(rmx[p + k], rd[k]); rmn[p + k] = min_nan(rmn[p + k], rd[k]);
-        }
+      for (int p = 0; p < 4; ++p) {
+        tmx[p] = max_nan(tmx[p], ph[p]); tmn[p] = min_nan(tmn[p], ph[p]);
+        rmx[p] = max_nan(rmx[p], rd[p]); rmn[p] = min_nan(rmn[p], rd[p]);
       }
     }
   }
@@ -417,49 +635,45 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
     else if (W == 1) *reinterpret_cast<uint32_t*>(tile + 512 + 8 * l + 4 * hi) = hw;
   };
   if constexpr (NI > 0) {
+    // the group's minima as packed pairs, for the packed subtraction
+    uint32_t tmn_w[2] = {0, 0}, rmn_w[2] = {0, 0};
+    if constexpr (kPacked) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        tmn_w[k] = pack2<DT16>(tmn[2 * k], tmn[2 * k + 1]); rmn_w[k] = pack2<DT16>(rmn[2 * k], rmn[2 * k + 1]);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
-      uint32_t word = 0;
+      float dt[4], dr[4];
+      if constexpr (kPacked) {
 #pragma unroll
-      for (int p = 0; p < 4; p += 2) {
-        float pv[2], rv[2];
-        if constexpr (kPacked) {
-          const float2 pf = unpack2<DT16>(phi_w[i][p >> 1]), rf = unpack2<DT16>(rad_w[i][p >> 1]);
-          pv[0] = pf.x; pv[1] = pf.y; rv[0] = rf.x; rv[1] = rf.y;
-        } else {
-          pv[0] = phi[i][p]; pv[1] = phi[i][p + 1]; rv[0] = rad[i][p]; rv[1] = rad[i][p + 1];
+        for (int k = 0; k < 2; ++k) {
+          const float2 a = unpack2<DT16>(sub2_packed<DT16>(phi_w[i][k], tmn_w[k]));
+          const float2 c = unpack2<DT16>(sub2_packed<DT16>(rad_w[i][k], rmn_w[k]));
+          dt[2 * k] = a.x; dt[2 * k + 1] = a.y; dr[2 * k] = c.x; dr[2 * k + 1] = c.y;
         }
-        const float tl[2] = {tmn[p], tmn[p + 1]}, ts[2] = {tstep[p], tstep[p + 1]}, tr[2] = {trcp[p], trcp[p + 1]};
-        const float rl[2] = {rmn[p], rmn[p + 1]}, rs[2] = {rstep[p], rstep[p + 1]}, rr[2] = {rrcp[p], rrcp[p + 1]};
-        unsigned th[2], rh[2];
-        level_of2<T>(pv, tl, ts, tr, ttop, th);
-        level_of2<T>(rv, rl, rs, rr, rtop, rh);
-        word |= (((rh[0] << tbits) + th[0]) & 0xffu) << (8 * p);
-        word |= (((rh[1] << tbits) + th[1]) & 0xffu) << (8 * p + 8);
+      } else {
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          dt[p] = E::round(__fsub_rn(phi[i][p], tmn[p])); dr[p] = E::round(__fsub_rn(rad[i][p], rmn[p]));
+        }
       }
-      emit(tok0 + 16 * i, word);
+      emit(tok0 + 16 * i, codes_of4<T>(dt, dr, tstep, trcp, rstep, rrcp, ttop, rtop, tbits));
     }
   } else {
     for (int tok = tok0; tok < G; tok += 16) {
       const T* row = base + static_cast<int64_t>(tok) * sl;
-      float x[4], y[4];
+      float x[4], y[4], pv[4], rv[4], dt[4], dr[4];
       load4<T>(row + p0, x);
       load4<T>(row + p0 + kPairs, y);
-      uint32_t word = 0;
+      polar_of4<T>(x, y, wrap, norm_sep, pv, rv);
 #pragma unroll
       for (int p = 0; p < 4; p += 2) {
-        const float xx[2] = {x[p], x[p + 1]}, yy[2] = {y[p], y[p + 1]};
-        float pv[2], rv[2];
-        polar_of2<T>(xx, yy, wrap, norm_sep, pv, rv);
-        const float tl[2] = {tmn[p], tmn[p + 1]}, ts[2] = {tstep[p], tstep[p + 1]}, tr[2] = {trcp[p], trcp[p + 1]};
-        const float rl[2] = {rmn[p], rmn[p + 1]}, rs[2] = {rstep[p], rstep[p + 1]}, rr[2] = {rrcp[p], rrcp[p + 1]};
-        unsigned th[2], rh[2];
-        level_of2<T>(pv, tl, ts, tr, ttop, th);
-        level_of2<T>(rv, rl, rs, rr, rtop, rh);
-        word |= (((rh[0] << tbits) + th[0]) & 0xffu) << (8 * p);
-        word |= (((rh[1] << tbits) + th[1]) & 0xffu) << (8 * p + 8);
+        round2<T>(__fsub_rn(pv[p], tmn[p]), __fsub_rn(pv[p + 1], tmn[p + 1]), dt[p], dt[p + 1]);
+        round2<T>(__fsub_rn(rv[p], rmn[p]), __fsub_rn(rv[p + 1], rmn[p + 1]), dr[p], dr[p + 1]);
       }
-      emit(tok, word);
+      emit(tok, codes_of4<T>(dt, dr, tstep, trcp, rstep, rrcp, ttop, rtop, tbits));
     }
   }
 }
@@ -470,6 +684,7 @@ quantize_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, 
 template <typename T>
 __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
   using E = Elem<T>;
+  constexpr int DT16 = E::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
   unsigned long long bad = 0;
   const unsigned long long total = 1ull << 32;
   for (unsigned long long i = blockIdx.x * static_cast<unsigned long long>(blockDim.x) + threadIdx.x; i < total;
@@ -477,20 +692,35 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
     const unsigned short xb = static_cast<unsigned short>(i & 0xffffu), yb = static_cast<unsigned short>(i >> 16);
     const float x = E::to_float(*reinterpret_cast<const T*>(&xb)), y = E::to_float(*reinterpret_cast<const T*>(&yb));
     if (which == 0) {
-      const float xx[2] = {x, y}, yy[2] = {y, x};             // the pair and its mirror image
-      float p0[2], r0[2], p1[2], r1[2];
-      polar_of2<T, true, true>(xx, yy, 6.283185307179586f, true, p0, r0);
-      polar_of2<T, false>(xx, yy, 6.283185307179586f, true, p1, r1);
+      // the pair, its mirror image and the two with the first channel negated
+      const float xx[4] = {x, y, -x, -y}, yy[4] = {y, x, y, x};
+      float p0[4], r0[4], p1[4], r1[4];
+      uint32_t pw[2], rw[2];
+      polar_of4_packed<T, true, true>(xx, yy, 6.283185307179586f, true, pw, rw);     // the kernel's form
+      const float2 pa = unpack2<DT16>(pw[0]), pb = unpack2<DT16>(pw[1]), ra = unpack2<DT16>(rw[0]), rb = unpack2<DT16>(rw[1]);
+      p0[0] = pa.x; p0[1] = pa.y; p0[2] = pb.x; p0[3] = pb.y; r0[0] = ra.x; r0[1] = ra.y; r0[2] = rb.x; r0[3] = rb.y;
+      polar_of4<T, false>(xx, yy, 6.283185307179586f, true, p1, r1);
       // values compare equal or both NaN; +0 and -0 count as equal, as they do for torch.equal
-      const bool same_p = (p0[0] == p1[0]) || (p0[0] != p0[0] && p1[0] != p1[0]);
-      const bool same_r = (r0[0] == r1[0]) || (r0[0] != r0[0] && r1[0] != r1[0]);
-      bad += !(same_p && same_r);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bool same_p = (p0[k] == p1[k]) || (p0[k] != p0[k] && p1[k] != p1[k]);
+        const bool same_r = (r0[k] == r1[k]) || (r0[k] != r0[k] && r1[k] != r1[k]);
+        bad += !(same_p && same_r);
+      }
+    } else if (which == 1) {
+      // value x as the rounded difference, y as the step: angle and radius slots, two bit widths
+      const float rc = guarded_rcp(y);
+      const float d[4] = {x, x, x, x}, st[4] = {y, y, y, y}, rcp[4] = {rc, rc, rc, rc};
+      const uint32_t fast = codes_of4<T, true>(d, d, st, rcp, st, rcp, 15u, 15u, 4);
+      const uint32_t exact = codes_of4<T, false>(d, d, st, rcp, st, rcp, 15u, 15u, 4);
+      const uint32_t fast8 = codes_of4<T, true>(d, d, st, rcp, st, rcp, 255u, 0u, 8);
+      const uint32_t exact8 = codes_of4<T, false>(d, d, st, rcp, st, rcp, 255u, 0u, 8);
+      bad += fast != exact || fast8 != exact8;
     } else {
-      const float v[2] = {x, x}, lo[2] = {0.0f, 0.0f}, st[2] = {y, y}, rc[2] = {guarded_rcp(y), guarded_rcp(y)};
-      unsigned a[2], b[2];
-      level_of2<T, true, true>(v, lo, st, rc, 255u, a);
-      level_of2<T, false>(v, lo, st, rc, 255u, b);
-      bad += a[0] != b[0];
+      // packed subtraction against the fp32 subtraction rounded to T
+      const uint32_t w = sub2_packed<DT16>(pack2<DT16>(x, x), pack2<DT16>(y, y));
+      const float got = unpack2<DT16>(w).x, want = E::round(__fsub_rn(x, y));
+      bad += !((got == want) || (got != got && want != want));
     }
   }
   if (bad) atomicAdd(mismatches, bad);
@@ -506,6 +736,28 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
   if (tiles > 0x7fffffffLL) return PQ_ERR_UNSUPPORTED;
   dim3 grid(static_cast<unsigned>(tiles)), block(kQuantThreads);
   const T* k = static_cast<const T*>(keys);
+  if constexpr (sizeof(T) == 2) {
+    if (G % 16 == 0 && G <= kMaxSmemGroup) {
+      const int gpc = (G == 16 || G == 32 || G == 64) ? 128 / G : 1;       // groups per CTA
+      const int wpg = (kQuantThreads / 32) / gpc;                          // warps per group
+      const size_t smem = static_cast<size_t>(G / (2 * wpg)) * kQuantThreads * sizeof(uint4);
+      const dim3 grid16(static_cast<unsigned>((tiles + gpc - 1) / gpc));
+#define PQ_LAUNCH_Q16(W)                                                                                         \
+  quantize_kernel16<T, W><<<grid16, block, smem, s>>>(k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, codes, \
+                                                      static_cast<T*>(rs), static_cast<T*>(rm), static_cast<T*>(ts), \
+                                                      static_cast<T*>(tm), os[0], os[1], os[2], os[3], gate,       \
+                                                      static_cast<int>(tiles))
+      switch (wpg) {
+        case 1: PQ_LAUNCH_Q16(1); break;
+        case 2: PQ_LAUNCH_Q16(2); break;
+        case 4: PQ_LAUNCH_Q16(4); break;
+        default: PQ_LAUNCH_Q16(8); break;
+      }
+#undef PQ_LAUNCH_Q16
+      PQ_CUDA_TRY(cudaGetLastError());
+      return PQ_OK;
+    }
+  }
 #define PQ_LAUNCH_Q(NI)                                                                                   \
   quantize_kernel<T, NI><<<grid, block, 0, s>>>(k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, \
                                                 codes, static_cast<T*>(rs), static_cast<T*>(rm),        \
@@ -700,7 +952,7 @@ int key_range_check_device(const void* rscale, const void* rmn, int64_t count, i
 }
 
 int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatches_dev, cudaStream_t stream) {
-  if (!mismatches_dev || which < 0 || which > 1) return PQ_ERR_INVALID;
+  if (!mismatches_dev || which < 0 || which > 2) return PQ_ERR_INVALID;
   if (dtype != PQ_F16 && dtype != PQ_BF16) return PQ_ERR_INVALID;
   PQ_CUDA_TRY(cudaMemsetAsync(mismatches_dev, 0, sizeof(unsigned long long), stream));
   if (dtype == PQ_F16) selftest_kernel<__half><<<148 * 8, 256, 0, stream>>>(which, mismatches_dev);

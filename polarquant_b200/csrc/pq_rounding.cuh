@@ -35,6 +35,23 @@ template <> __device__ __forceinline__ bool rounds_safely<__half>(float v) {
 }
 template <> __device__ __forceinline__ bool rounds_safely<float>(float) { return false; }
 
+// One test for an (angle, radius) pair from the approximations: both lie in the ordinary range (2^-100 .. 2^100
+// for bf16, the normal range of fp16) and both keep clear of a rounding tie of T by 32 fp32 units in the last place
+// (the zone [tie - 32, tie + 31] of the low bits, found by one addition and one mask).  The angle magnitude never
+// exceeds pi and is NaN only when the radius is NaN too, so its upper bound needs no test.
+template <typename T> __device__ __forceinline__ bool polar_safe(float a, float r);
+template <> __device__ __forceinline__ bool polar_safe<__nv_bfloat16>(float a, float r) {
+  const unsigned ua = __float_as_uint(a), ur = __float_as_uint(r);
+  const bool range = (ua & 0x7fffffffu) > 0x0d800000u && (ur - 0x0d800001u) < (0x71800000u - 0x0d800001u);
+  return range && ((ua + 0x8020u) & 0xffc0u) != 0u && ((ur + 0x8020u) & 0xffc0u) != 0u;
+}
+template <> __device__ __forceinline__ bool polar_safe<__half>(float a, float r) {
+  const unsigned ua = __float_as_uint(a), ur = __float_as_uint(r);
+  const bool range = (ua & 0x7fffffffu) >= 0x38800000u && (ur - 0x38800000u) < (0x47000000u - 0x38800000u);
+  return range && ((ua + 0x1020u) & 0x1fc0u) != 0u && ((ur + 0x1020u) & 0x1fc0u) != 0u;
+}
+template <> __device__ __forceinline__ bool polar_safe<float>(float, float) { return false; }
+
 // 2^-100 < |v| < 2^100 and not NaN: the range in which the approximations neither flush nor overflow.
 // It is tested on RESULTS: zero, NaN, inf or denormal inputs and underflowing ratios all surface there.
 __device__ __forceinline__ bool mid_range(float v) {
@@ -56,6 +73,34 @@ __device__ __forceinline__ float guarded_rcp(float step) {
 
 // exact IEEE quotient, out of line: taken by a fraction of a percent of the items
 __device__ __noinline__ float div_exact(float a, float b) { return __fdiv_rn(a, b); }
+
+// Quotient a / b from the correctly rounded reciprocal r = RN(1 / b): one product and one remainder correction,
+//   q0 = RN(a r);  e = a - b q0 (exact, one FMA);  q = RN(q0 + e r).
+// For ordinary operands this is the correctly rounded quotient - in particular it is exact whenever a / b is
+// exactly representable, which covers the only inputs for which a 16-bit rounding of the quotient could differ
+// from the rounding of an approximation: quotients of two 16-bit values that sit exactly on a rounding tie.  No
+// tie test and no branch are needed; operands outside the ordinary range arrive with r = NaN (guarded_rcp) and are
+// sent to the IEEE division by the caller's range test on q.  Checked against __fdiv_rn for every pair of 16-bit
+// operands by pq_selftest_quantizer (which = 1).
+__device__ __forceinline__ float div_refined(float a, float b, float r) {
+  const float q0 = a * r;
+  const float e = __fmaf_rn(-b, q0, a);
+  return __fmaf_rn(e, r, q0);
+}
+
+// a - b of two packed 16-bit pairs, rounded once to the same type.  torch computes RN_T(RN_fp32(a - b)); the fp32
+// difference of two 16-bit values is exact whenever the result is anywhere near a rounding tie of T (the operands'
+// exponents are then close), so the single rounding of the packed instruction gives the same value - checked for
+// every pair of 16-bit operands by pq_selftest_quantizer (which = 2).
+template <int DT> __device__ __forceinline__ uint32_t sub2_packed(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (DT == PQ_BF16) asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// floor of a value in [0, 2^22) by a round-toward-zero addition of 2^23: the integer sits in the low mantissa bits
+__device__ __forceinline__ uint32_t floor_bits(float v) { return __float_as_uint(__fadd_rz(v, 8388608.0f)); }
 
 }  // namespace
 }  // namespace pq

@@ -88,9 +88,10 @@ def test_edge_values_bit_exact():
 
 
 @pytest.mark.parametrize("dtype_name", ["bf16", "fp16"])
-@pytest.mark.parametrize("which", [0, 1])
+@pytest.mark.parametrize("which", [0, 1, 2])
 def test_fast_paths_agree_with_exact_paths_for_every_16_bit_input_pair(dtype_name, which):
-    """Exhaustive: all 2^32 (x, y) patterns.  which 0 = angle and radius of a key pair, 1 = quantisation level."""
+    """Exhaustive: all 2^32 (x, y) patterns.  which 0 = angle and radius of a key pair, 1 = quantisation level from
+    the refined division, 2 = the packed 16-bit subtraction."""
     from polarquant_b200 import _lib
     lib = _lib.load()
     counter = torch.zeros(1, dtype=torch.int64, device="cuda")
