@@ -16,6 +16,8 @@
 // ideal one pass: every key element is read once (8/16-byte loads, any token /
 // head / batch stride) and 64 code bytes per token plus four 64-wide scale rows
 // per group are written.
+#include <type_traits>
+
 #include "pq_common.cuh"
 #include "pq_rounding.cuh"
 
@@ -232,18 +234,20 @@ __device__ __forceinline__ uint32_t codes_of4(const float (&dt)[4], const float 
       all_ok = all_ok & (__float_as_uint(qt[k]) < 0x437f0000u) & (__float_as_uint(qr[k]) < 0x437f0000u);   // [0, 255)
     }
     if (all_ok) {
-      const float tf = static_cast<float>(ttop), rf = static_cast<float>(rtop);
+      // round to T and clamp to the top level on packed pairs (the clamp is exact: both operands are values of T),
+      // floor in fp32 by a round-toward-zero addition, gather the low bytes of the four codes with byte permutes
+      constexpr int DT16 = Elem<T>::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
+      const uint32_t tf2 = pack2<DT16>(static_cast<float>(ttop), static_cast<float>(ttop));
+      const uint32_t rf2 = pack2<DT16>(static_cast<float>(rtop), static_cast<float>(rtop));
+      uint32_t c[4];
 #pragma unroll
       for (int k = 0; k < 4; k += 2) {
-        round2<T>(qt[k], qt[k + 1], qt[k], qt[k + 1]);
-        round2<T>(qr[k], qr[k + 1], qr[k], qr[k + 1]);
+        const float2 t = unpack2<DT16>(min2_nan<DT16>(pack2<DT16>(qt[k], qt[k + 1]), tf2));
+        const float2 r = unpack2<DT16>(min2_nan<DT16>(pack2<DT16>(qr[k], qr[k + 1]), rf2));
+        c[k] = (floor_bits(r.x) << tbits) + floor_bits(t.x);
+        c[k + 1] = (floor_bits(r.y) << tbits) + floor_bits(t.y);
       }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t th = floor_bits(fminf(qt[k], tf)), rh = floor_bits(fminf(qr[k], rf));
-        word |= (((rh << tbits) + th) & 0xffu) << (8 * k);
-      }
-      return word;
+      return __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
     }
   }
 #pragma unroll
@@ -435,32 +439,38 @@ quantize_kernel16(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl
   const bool pack6 = (flags & PQ_QUANT_PACK6) != 0;
   uint8_t* crow = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * kPairs + p0;
   uint8_t* ctile = codes + b * c_sb + h * c_sh + static_cast<int64_t>(j + group_off) * G * 48;   // packed container
+  // one copy of the loop per container, so that the choice costs no branch per token
+  auto second_pass = [&](auto packed_container) {
+    constexpr bool kPack6 = decltype(packed_container)::value;
 #pragma unroll 2
-  for (int i = 0; i < ni; ++i) {
-    const uint4 v = s_polar[i * kQuantThreads + threadIdx.x];
-    const float2 t01 = unpack2<DT16>(sub2_packed<DT16>(v.x, tlo_w[0])), t23 = unpack2<DT16>(sub2_packed<DT16>(v.y, tlo_w[1]));
-    const float2 r01 = unpack2<DT16>(sub2_packed<DT16>(v.z, rlo_w[0])), r23 = unpack2<DT16>(sub2_packed<DT16>(v.w, rlo_w[1]));
-    const float dt[4] = {t01.x, t01.y, t23.x, t23.y}, dr[4] = {r01.x, r01.y, r23.x, r23.y};
-    const uint32_t word = codes_of4<T>(dt, dr, tstep, trcp, rstep, rrcp, ttop, rtop, tbits);
-    const int tok = tok0 + tok_step * i;
-    if (!pack6) {
-      *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok) * kPairs) = word;
-    } else {
-      // the 16 lanes that share a token assemble the words of the packed container with shuffles (layout and
-      // roles of the lanes as in quantize_kernel's emit)
-      const int W = lane & 3, t = (lane >> 2) & 3;
-      uint32_t a = (word & 0x0f0f0f0fu) << (4 * (W & 1));
-      a |= __shfl_xor_sync(0xffffffffu, a, 1);
-      uint32_t hw = h_part(word, W);
-      hw |= __shfl_xor_sync(0xffffffffu, hw, 1);
-      hw |= __shfl_xor_sync(0xffffffffu, hw, 2);
-      const int r = tok & 15, l = 4 * (r & 7) + t, hi = r >> 3;
-      uint8_t* tl = ctile + static_cast<int64_t>(tok >> 4) * kPackedStepBytes;
-      if (W == 0) *reinterpret_cast<uint32_t*>(tl + 16 * l + 8 * hi) = a;
-      else if (W == 2) *reinterpret_cast<uint32_t*>(tl + 16 * l + 8 * hi + 4) = a;
-      else if (W == 1) *reinterpret_cast<uint32_t*>(tl + 512 + 8 * l + 4 * hi) = hw;
+    for (int i = 0; i < ni; ++i) {
+      const uint4 v = s_polar[i * kQuantThreads + threadIdx.x];
+      const float2 t01 = unpack2<DT16>(sub2_packed<DT16>(v.x, tlo_w[0])), t23 = unpack2<DT16>(sub2_packed<DT16>(v.y, tlo_w[1]));
+      const float2 r01 = unpack2<DT16>(sub2_packed<DT16>(v.z, rlo_w[0])), r23 = unpack2<DT16>(sub2_packed<DT16>(v.w, rlo_w[1]));
+      const float dt[4] = {t01.x, t01.y, t23.x, t23.y}, dr[4] = {r01.x, r01.y, r23.x, r23.y};
+      const uint32_t word = codes_of4<T>(dt, dr, tstep, trcp, rstep, rrcp, ttop, rtop, tbits);
+      const int tok = tok0 + tok_step * i;
+      if constexpr (!kPack6) {
+        *reinterpret_cast<uint32_t*>(crow + static_cast<int64_t>(tok) * kPairs) = word;
+      } else {
+        // the 16 lanes that share a token assemble the words of the packed container with shuffles (layout and
+        // roles of the lanes as in quantize_kernel's emit)
+        const int W = lane & 3, t = (lane >> 2) & 3;
+        uint32_t a = (word & 0x0f0f0f0fu) << (4 * (W & 1));
+        a |= __shfl_xor_sync(0xffffffffu, a, 1);
+        uint32_t hw = h_part(word, W);
+        hw |= __shfl_xor_sync(0xffffffffu, hw, 1);
+        hw |= __shfl_xor_sync(0xffffffffu, hw, 2);
+        const int r = tok & 15, l = 4 * (r & 7) + t, hi = r >> 3;
+        uint8_t* tl = ctile + static_cast<int64_t>(tok >> 4) * kPackedStepBytes;
+        if (W == 0) *reinterpret_cast<uint32_t*>(tl + 16 * l + 8 * hi) = a;
+        else if (W == 2) *reinterpret_cast<uint32_t*>(tl + 16 * l + 8 * hi + 4) = a;
+        else if (W == 1) *reinterpret_cast<uint32_t*>(tl + 512 + 8 * l + 4 * hi) = hw;
+      }
     }
-  }
+  };
+  if (pack6) second_pass(std::true_type{});
+  else second_pass(std::false_type{});
 }
 
 // NI > 0: the thread keeps phi and r of its NI tokens x 4 pairs in registers
