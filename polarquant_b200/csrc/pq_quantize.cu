@@ -726,6 +726,13 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
       const uint32_t fast8 = codes_of4<T, true>(d, d, st, rcp, st, rcp, 255u, 0u, 8);
       const uint32_t exact8 = codes_of4<T, false>(d, d, st, rcp, st, rcp, 255u, 0u, 8);
       bad += fast != exact || fast8 != exact8;
+      // and the rounded quotient itself, wherever the refined division is accepted (below 256: the value quantiser's
+      // range test)
+      const float qf = div_refined(x, y, rc);
+      if (qf < 256.0f) {
+        const float a = E::round(qf), b = E::round(__fdiv_rn(x, y));
+        bad += !(a == b);
+      }
     } else {
       // packed subtraction against the fp32 subtraction rounded to T
       const uint32_t w = sub2_packed<DT16>(pack2<DT16>(x, x), pack2<DT16>(y, y));

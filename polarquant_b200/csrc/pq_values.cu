@@ -112,9 +112,9 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
       mx = max_nan(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
     const float scale = Elem<T>::round(__fmul_rn(Elem<T>::round(__fsub_rn(mx, mn)), a.inv_levels));
-    // RN(d / scale) by a multiplication with the correctly rounded reciprocal wherever that provably rounds to the
-    // same 16-bit value (the margin test validated for every (d, scale) pair by pq_selftest_quantizer, which = 1),
-    // the IEEE division otherwise and for fp32.  Roundings are packed conversions, the final round-half-even and the
+    // RN(d / scale) from the correctly rounded reciprocal and one remainder correction (div_refined: the IEEE
+    // quotient for ordinary operands, checked for every (d, scale) pair of 16-bit values by pq_selftest_quantizer,
+    // which = 1), the IEEE division itself for degenerate scales and for fp32.  Roundings are packed conversions, the final round-half-even and the
     // conversion to an integer are one addition of 1.5 * 2^23: nothing per element runs on the quarter-rate pipe.
     constexpr bool kFast = Elem<T>::kDtype != PQ_F32;
     const float rcp = guarded_rcp(scale);
@@ -126,10 +126,9 @@ __global__ void __launch_bounds__(kValThreads) quantize_values_kernel(const ValA
       float d0, d1, q0, q1;
       round2<T>(__fsub_rn(v[i], mn), __fsub_rn(v[i + 1], mn), d0, d1);
       if constexpr (kFast) {
-        q0 = d0 * rcp; q1 = d1 * rcp;
-        const bool ok0 = q0 < 256.0f && rounds_safely<T>(q0);
-        const bool ok1 = q1 < 256.0f && rounds_safely<T>(q1);
-        if (!(ok0 && ok1)) {
+        q0 = div_refined(d0, scale, rcp); q1 = div_refined(d1, scale, rcp);
+        const bool ok0 = q0 < 256.0f, ok1 = q1 < 256.0f;           // false for the NaN of a degenerate scale
+        if (!(ok0 & ok1)) {
           if (!ok0) q0 = div_exact(d0, scale);
           if (!ok1) q1 = div_exact(d1, scale);
         }
