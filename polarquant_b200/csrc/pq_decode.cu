@@ -159,39 +159,67 @@ __device__ __forceinline__ void wait_staged() {
 // word index = (row_pos << TBITS) + (level ^ x), row_pos = 4 * (d % 16) + d / 16, so the
 // four rows a warp gathers from in one instruction (pairs 16t + m, t = 0..3) are adjacent
 // and the lane-dependent part of the byte offset fits in the low byte.  The XOR with
-// x = (m / 2 + 8 * (t / 2)) mod 2^TBITS (m = d % 16, t = d / 16) spreads the stores of the
-// build, where lane l owns pairs 2l and 2l + 1, over all banks; the gather side folds
-// the same XOR into the constant it already applies to the code bytes.
+// x = (m / 2 + 8 * (t / 2)) mod 2^TBITS (m = d % 16, t = d / 16) spreads a gather's lanes over
+// the banks; the gather side folds the same XOR into the constant it already applies to the
+// code bytes.
 template <int TBITS> __device__ __forceinline__ uint32_t table_xor(int m, int t) {
   return static_cast<uint32_t>((m >> 1) + 8 * (t >> 1)) & ((1u << TBITS) - 1u);
 }
 
+// The build writes whole quads of adjacent positions with 128-bit stores.  Lane l = 8 a + 4 b + c owns the pairs
+// (m, t) = (4 a + 2 half + c / 2, b + 2 (c % 2)), half = 0, 1, and walks the quads of a row in the order
+// jq ^ (c or c / 2): in every quarter-warp phase of a store the eight lanes then hit eight different 16-byte bank
+// groups, for every table size.  Position p of a row holds level p ^ x; the level enters the angle as a float built
+// by bit insertion - 16 + level has the mantissa level / 16 - so phi = ts * ((16 + level) - 15.5) + tm is one FMA.
 template <int TBITS, int SDT>
 __device__ __forceinline__ void build_angle_table(uint32_t tbl_addr, const char* sc, int lane) {
   constexpr int A = 1 << TBITS;
-  constexpr int ROW = 64 * (SDT == PQ_F32 ? 4 : 2);          // bytes per staged scale row
-  float ts[2], tm[2];
-  if constexpr (SDT == PQ_F32) {
-    const float2 a = *reinterpret_cast<const float2*>(sc + 2 * ROW + 8 * lane);
-    const float2 b = *reinterpret_cast<const float2*>(sc + 3 * ROW + 8 * lane);
-    ts[0] = a.x; ts[1] = a.y; tm[0] = b.x; tm[1] = b.y;
+  constexpr int ES = SDT == PQ_F32 ? 4 : 2;
+  constexpr int ROW = 64 * ES;                               // bytes per staged scale row
+  auto scale_at = [&](int row, int d) {
+    if constexpr (SDT == PQ_F32) return *reinterpret_cast<const float*>(sc + row * ROW + 4 * d);
+    else if constexpr (SDT == PQ_F16) return __half2float(*reinterpret_cast<const __half*>(sc + row * ROW + 2 * d));
+    else return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sc + row * ROW + 2 * d));
+  };
+  if constexpr (A >= 4) {
+    const int a = lane >> 3, b = (lane >> 2) & 1, c = lane & 3;
+    const int t = b + 2 * (c & 1);
+    const uint32_t walk = TBITS == 4 ? c : TBITS == 3 ? (c >> 1) : 0;      // quad order of this lane
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = 4 * a + 2 * half + (c >> 1), d = 16 * t + m;
+      const float ts = scale_at(2, d), tm_c = fmaf(-15.5f, ts, scale_at(3, d));
+      const uint32_t base = tbl_addr + (static_cast<uint32_t>(4 * m + t) << (TBITS + 2));
+      const uint32_t xs = (table_xor<TBITS>(m, t) ^ (walk << 2)) << 19;      // level = (4 jq + i) ^ (4 walk) ^ x
+#pragma unroll
+      for (int jq = 0; jq < A / 4; ++jq) {
+        uint32_t cs[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          // |phi| stays small (a quantiser emits [0, 2 pi]); the hardware sine/cosine take the
+          // fraction of phi / (2 pi), precise to ~1e-6 for |phi| < 100, far below fp16 spacing
+          const float lv = __uint_as_float((0x41800000u | (static_cast<uint32_t>(4 * jq + i) << 19)) ^ xs);
+          const float phi = fmaf(ts, lv, tm_c);
+          cs[i] = pack2<PQ_F16>(__cosf(phi), __sinf(phi));
+        }
+        const uint32_t at = base + ((static_cast<uint32_t>(jq) ^ walk) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(at), "r"(cs[0]), "r"(cs[1]), "r"(cs[2]), "r"(cs[3])
+                     : "memory");
+      }
+    }
   } else {
-    const float2 a = unpack2<SDT>(*reinterpret_cast<const uint32_t*>(sc + 2 * ROW + 4 * lane));
-    const float2 b = unpack2<SDT>(*reinterpret_cast<const uint32_t*>(sc + 3 * ROW + 4 * lane));
-    ts[0] = a.x; ts[1] = a.y; tm[0] = b.x; tm[1] = b.y;
-  }
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int d = 2 * lane + half, m = d & 15, t = d >> 4;
-    const uint32_t base = tbl_addr + (static_cast<uint32_t>(4 * m + t) << (TBITS + 2));
-    const uint32_t bx = base ^ (table_xor<TBITS>(m, t) << 2);
+    for (int half = 0; half < 2; ++half) {
+      const int d = 2 * lane + half, m = d & 15, t = d >> 4;
+      const float ts = scale_at(2, d), tm = scale_at(3, d);
+      const uint32_t base = tbl_addr + (static_cast<uint32_t>(4 * m + t) << (TBITS + 2));
+      const uint32_t bx = base ^ (table_xor<TBITS>(m, t) << 2);
 #pragma unroll
-    for (int k = 0; k < A; ++k) {
-      // |phi| stays small (a quantiser emits [0, 2 pi]); the hardware sine/cosine take the
-      // fraction of phi / (2 pi), precise to ~1e-6 for |phi| < 100, far below fp16 spacing
-      const float phi = fmaf(ts[half], static_cast<float>(k) + 0.5f, tm[half]);
-      const uint32_t cs = pack2<PQ_F16>(__cosf(phi), __sinf(phi));
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(bx ^ (static_cast<uint32_t>(k) << 2)), "r"(cs) : "memory");
+      for (int k = 0; k < A; ++k) {
+        const float phi = fmaf(ts, static_cast<float>(k) + 0.5f, tm);
+        const uint32_t cs = pack2<PQ_F16>(__cosf(phi), __sinf(phi));
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(bx ^ (static_cast<uint32_t>(k) << 2)), "r"(cs) : "memory");
+      }
     }
   }
   __syncwarp();
