@@ -124,6 +124,25 @@ int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const
                    int value_cap, int res_pos, int ctx_pos, int dtype, void* stream);
 
 /*
+ * Prefill-side fusion: rotary embedding of the prompt's keys and their polar quantisation in one pass over the keys.
+ * In the reference the prefill rotates the keys (apply_rotary_pos_emb, models/modeling_llama_polar.py:57), runs the
+ * attention on them and then quantises all but the last L % 128 of them (:116-126): the rotated keys are written
+ * once and read again by the quantizer.  Here keys (B, Nk, L, hd) arrive UN-rotated (element strides[4], inner 1 -
+ * typically the (B, L, Nk, hd) projection output), cos / sin hold hd elements of `dtype` per position, element
+ * strides cs_strides = {batch (0 = shared by all sequences), position}; the rotated keys
+ * RN(RN(x * cos) + RN(rotate_half(x) * sin)) - every product and the sum rounded to `dtype` as the eager ops round
+ * them - are written to keys_out (element strides out_key_strides[4]; may be the input buffer itself; NULL only when
+ * Lq == L) and the first Lq tokens (a multiple of G) are quantised from registers exactly as pq_quantize[_into]
+ * quantises the rotated keys: codes and scales are bit-identical to quantising keys_out.  Tokens [Lq, L) are rotated
+ * only.  out_strides as in pq_quantize_into, or NULL for dense outputs of the Lq tokens.  16-bit dtypes, hd == 128,
+ * G a multiple of 16 up to 128; PQ_QUANT_PACK6 is honoured.
+ */
+int pq_rope_quantize(const void* keys, const int64_t strides[4], const void* cos, const void* sin,
+                     const int64_t cs_strides[2], void* keys_out, const int64_t out_key_strides[4], int B, int Nk, int L,
+                     int Lq, int hd, int G, int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale,
+                     void* rmn, void* tscale, void* tmn, const int64_t* out_strides, void* stream);
+
+/*
  * Self-test of the quantizer's fast paths (no reference counterpart).  The kernel replaces atan2f, sqrtf and the
  * IEEE division by cheaper approximations wherever the approximation provably rounds to the same 16-bit value,
  * and calls the exact routine otherwise.  This entry point checks that claim exhaustively on the device: for all

@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = (
     "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
     "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn", "pq_rope_append",
     "pq_quantize_into_dyn", "pq_quantize_values_dyn", "pq_lengths_advance", "pq_key_range_check",
-    "pq_keys_repack",
+    "pq_keys_repack", "pq_rope_quantize",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -68,6 +68,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_quantize.restype = _int
     lib.pq_quantize.argtypes = [_vp, ctypes.POINTER(_i64), _int, _int, _int, _int, _int, _int, _int, _int,
                                 ctypes.c_uint, _vp, _vp, _vp, _vp, _vp, _vp]
+    lib.pq_rope_quantize.restype = _int
+    lib.pq_rope_quantize.argtypes = [_vp, ctypes.POINTER(_i64), _vp, _vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64),
+                                     _int, _int, _int, _int, _int, _int, _int, _int, _int, ctypes.c_uint,
+                                     _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_i64), _vp]
     lib.pq_keys_repack.restype = _int
     lib.pq_keys_repack.argtypes = [_vp, _vp, _i64, _int, _vp]
     lib.pq_key_range_check.restype = _int

@@ -4,6 +4,7 @@
     python -m polarquant_b200.benchmarks sweep     # fused decode attention over bit widths / group sizes / shapes
     python -m polarquant_b200.benchmarks quant     # quantizer at prefill sizes
     python -m polarquant_b200.benchmarks values    # packed (4-bit) value cache: fused attention and value quantiser
+    python -m polarquant_b200.benchmarks packed_keys   # 6-bit key container (48 B/token) beside the byte container
     torchrun --nproc-per-node N -m polarquant_b200.benchmarks longctx   # 128k-context step sharded over N GPUs
 
 `qk` reproduces the grid of the reference's benchmark/benchmark_matmul.py (`test4polar`, lines 89-120: 32 heads on
@@ -94,6 +95,41 @@ def decode_sweep():
                 print(json.dumps({"bench": "decode", "shape": name, "bits": f"{rb}/{tb}", "group": G, "us": us,
                                   "mb": nbytes / 1e6, "gbs": nbytes / us / 1e3}))
                 del packed, v
+
+
+def packed_keys():
+    """The 48-byte-per-token key container beside the byte container, for the 6-bit splits: fused decode attention
+    (same codes, both containers; the results are bit-identical) and the quantizer writing either."""
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1007)
+    shapes = [("llama3-8b B16 ctx32k", 16, 32, 8, 32768), ("qwen2.5-7b B64 ctx8k", 64, 28, 4, 8192)]
+    for name, B, N, Nk, ctx in shapes:
+        for (rb, tb) in ((3, 3), (2, 4)):
+            G, R = 128, 128
+            Nb = (ctx - R) // G
+            q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.bfloat16)
+            v = torch.randn(B, Nk, ctx, 128, device=dev, generator=g).to(torch.bfloat16)
+            kres = torch.randn(B, Nk, R, 128, device=dev, generator=g).to(torch.bfloat16)
+            keys = torch.randn(B, Nk, Nb * G, 128, device=dev, generator=g).to(torch.bfloat16)
+            us_qb = _time_us(lambda: ops.quantize_and_pack_nbit(keys, rb, tb, G), reps=10)
+            us_qp = _time_us(lambda: ops.quantize_and_pack_nbit(keys, rb, tb, G, key_format="packed6"), reps=10)
+            byte = ops.quantize_and_pack_nbit(keys, rb, tb, G)
+            pack = ops.quantize_and_pack_nbit(keys, rb, tb, G, key_format="packed6")
+            del keys
+            us_b = _time_us(lambda: ops.decode_attention(q, kres, *byte, v, rbits=rb, tbits=tb), reps=20)
+            us_p = _time_us(lambda: ops.decode_attention(q, kres, *pack, v, rbits=rb, tbits=tb, key_format="packed6"),
+                            reps=20)
+            same = torch.equal(ops.decode_attention(q, kres, *byte, v, rbits=rb, tbits=tb),
+                               ops.decode_attention(q, kres, *pack, v, rbits=rb, tbits=tb, key_format="packed6"))
+            rest = 4 * byte[1].numel() * 2 + kres.numel() * 2 + v.numel() * 2 + q.numel() * 4
+            print(json.dumps({"bench": "packed_keys", "shape": name, "bits": f"{rb}/{tb}", "group": G,
+                              "us_byte_container": us_b, "us_packed_container": us_p,
+                              "key_bytes_per_token": {"byte": 64, "packed6": 48},
+                              "cache_bytes_per_token_per_kv_head": {"byte": 64 + 4 + 256, "packed6": 48 + 4 + 256},
+                              "gbs_byte": (rest + byte[0].numel()) / us_b / 1e3,
+                              "gbs_packed": (rest + pack[0].numel()) / us_p / 1e3,
+                              "quantizer_us_byte": us_qb, "quantizer_us_packed": us_qp, "bit_identical": same}))
+            del byte, pack, v
 
 
 def quant_sizes():
@@ -294,4 +330,4 @@ def long_context():
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "sweep"
     {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes, "values": packed_values,
-     "longctx": long_context}[what]()
+     "packed_keys": packed_keys, "longctx": long_context}[what]()

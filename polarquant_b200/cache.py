@@ -205,6 +205,59 @@ class PolarKVCache:
         else:
             self.values[sl, :, :length].copy_(value_states)
 
+    def prefill_rope(self, key_states: torch.Tensor, value_states: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                     batch_start: int = 0, rotated_out: torch.Tensor | None = None) -> torch.Tensor:
+        """``prefill`` for UN-rotated keys: the rotary embedding is applied while the keys are quantised into the
+        cache (one pass over the keys instead of a rotation pass plus a quantisation pass).  ``cos`` / ``sin``
+        (L, 128) or (b, L, 128).  Returns the rotated keys (for the prompt's own attention), written to
+        ``rotated_out`` if given - ``key_states`` itself is allowed - else to a new tensor."""
+        bsz, _, length, _ = key_states.shape
+        if length > self.max_tokens:
+            raise RuntimeError("prompt longer than the cache")
+        if batch_start < 0 or batch_start + bsz > self.B:
+            raise ValueError("batch chunk does not fit the cache")
+        if key_states.dtype != self.dtype:
+            raise ValueError("prefill_rope takes keys in the cache dtype")
+        dev = key_states.device
+        rest = length % self.RL
+        nq = length - rest
+        if not ops._vec_ok(key_states, 4):
+            key_states = key_states.contiguous()
+        cos, sin = cos.to(self.dtype), sin.to(self.dtype)
+        if cos.dim() == 2:
+            cos, sin = cos[None], sin[None]
+        if not ops._vec_ok(cos, 4) or not ops._vec_ok(sin, 4) or cos.stride() != sin.stride():
+            cos, sin = cos.contiguous(), sin.contiguous()
+        out = rotated_out if rotated_out is not None else torch.empty_like(key_states)
+        i64 = ctypes.c_int64
+        es = self.scales[0].element_size()
+        code_ptr = self.codes.data_ptr() + batch_start * self.codes.stride(0)
+        scale_ptrs = [s.data_ptr() + batch_start * s.stride(0) * es for s in self.scales]
+        out_strides = (i64 * 4)(self.codes.stride(0), self.codes.stride(1), self.scales[0].stride(0),
+                                self.scales[0].stride(1))
+        lib = _lib.load()
+        with ops._on_device(dev):
+            rc = lib.pq_rope_quantize(key_states.data_ptr(), (i64 * 4)(*key_states.stride()), cos.data_ptr(),
+                                      sin.data_ptr(), (i64 * 2)(0 if cos.shape[0] == 1 else cos.stride(0), cos.stride(1)),
+                                      out.data_ptr(), (i64 * 4)(*out.stride()), bsz, self.Nk, length, nq, 128, self.G,
+                                      self.rbits, self.tbits, self._dt, 0, code_ptr, *scale_ptrs, out_strides,
+                                      ops._stream(dev))
+        _lib.check(rc, "pq_rope_quantize")
+        sl = slice(batch_start, batch_start + bsz)
+        self.num_groups = nq // self.G
+        self.res_len = rest
+        if self.lengths is not None:
+            self.sync_lengths()
+        if rest:
+            self.k_res[sl, :, :rest].copy_(out[:, :, nq:])
+        if self.vbits:
+            self._quantize_values_into(value_states[:, :, :nq].to(self.dtype), 0, batch_start)
+            if rest:
+                self.values[sl, :, :rest].copy_(value_states[:, :, nq:])
+        else:
+            self.values[sl, :, :length].copy_(value_states)
+        return out
+
     def decode_step(self, query_states: torch.Tensor, key_new: torch.Tensor, value_new: torch.Tensor,
                     attention_mask=None, sm_scale=None, out_dtype=None) -> torch.Tensor:
         """Append one token per sequence and attend.  query_states (B, N, 1, 128); key_new / value_new

@@ -11,7 +11,12 @@ int& last_cuda_error() {
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G, int rbits,
                     int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn, void* tscale,
                     void* tmn, const int64_t* out_strides, cudaStream_t stream, const int* gate_lengths = nullptr,
-                    int gate_r_add = 0, int gate_full = 0, int gate_max_groups = 0);
+                    int gate_r_add = 0, int gate_full = 0, int gate_max_groups = 0, const void* rope_fusion = nullptr);
+int rope_quantize_device(const void* keys, const int64_t strides[4], const void* cosv, const void* sinv,
+                         const int64_t cs_strides[2], void* keys_out, const int64_t out_key_strides[4], int B, int Nk,
+                         int L, int Lq, int hd, int G, int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes,
+                         void* rscale, void* rmn, void* tscale, void* tmn, const int64_t* out_strides,
+                         cudaStream_t stream);
 int lengths_advance_device(int* lengths, int full, int G, cudaStream_t stream);
 int cache_append_device(const void* k_new, const void* v_new, const int64_t* in_strides, void* k_res,
                         const int64_t* kres_strides, void* values, const int64_t* v_strides, int B, int Nk, int hd,
@@ -135,6 +140,15 @@ int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const
   return rope_append_device(qkv, qkv_stride_b, cos, sin, cs_stride_b, q_out, k_res, kres_strides, values, v_strides,
                             B, N, Nk, hd, G, lengths, values_window, res_cap, value_cap, res_pos, ctx_pos, dtype,
                             static_cast<cudaStream_t>(stream));
+}
+
+int pq_rope_quantize(const void* keys, const int64_t strides[4], const void* cos, const void* sin,
+                     const int64_t cs_strides[2], void* keys_out, const int64_t out_key_strides[4], int B, int Nk, int L,
+                     int Lq, int hd, int G, int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale,
+                     void* rmn, void* tscale, void* tmn, const int64_t* out_strides, void* stream) {
+  return rope_quantize_device(keys, strides, cos, sin, cs_strides, keys_out, out_key_strides, B, Nk, L, Lq, hd, G, rbits,
+                              tbits, dtype, flags, codes, rscale, rmn, tscale, tmn, out_strides,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int pq_keys_repack(const uint8_t* codes_in, uint8_t* codes_out, int64_t steps, int to_format, void* stream) {

@@ -305,6 +305,48 @@ __global__ void keys_repack_kernel(const uint8_t* __restrict__ in, uint8_t* __re
 // lengths = {token groups, residual tokens} on the device; the kernel runs only when lengths[1] + r_add == full
 struct WindowGate { const int* lengths; int r_add, full, max_groups; };
 
+// Rotary embedding fused in front of the quantizer (prefill): keys arrive un-rotated, are rotated with the eager
+// arithmetic of apply_rotary_pos_emb (rotate-half: channel d pairs with d + 64, the quantizer's own pairing), written
+// out for the prefill attention and the residual window, and quantised from registers.
+template <typename T> struct RopeFusion {
+  const T* cos; const T* sin; int64_t cs_sb, cs_sl;       // (B or 1, L, 128): batch stride (0 = shared), token stride
+  T* out; int64_t o_sb, o_sh, o_sl;                        // rotated keys (may be the input buffer), or nullptr
+};
+__device__ __forceinline__ uint2 ldg8_nc(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+// out = RN(RN(x * cos) + RN(rotate_half(x) * sin)) for four pairs: xr = x c_lo - y s_lo, yr = y c_hi + x s_hi
+template <int DT>
+__device__ __forceinline__ void rope4_packed(uint2 xw, uint2 yw, uint2 clo, uint2 chi, uint2 slo, uint2 shi, uint2& xr,
+                                             uint2& yr) {
+  xr.x = sub2_packed<DT>(mul2_packed<DT>(xw.x, clo.x), mul2_packed<DT>(yw.x, slo.x));
+  xr.y = sub2_packed<DT>(mul2_packed<DT>(xw.y, clo.y), mul2_packed<DT>(yw.y, slo.y));
+  yr.x = add2_packed<DT>(mul2_packed<DT>(yw.x, chi.x), mul2_packed<DT>(xw.x, shi.x));
+  yr.y = add2_packed<DT>(mul2_packed<DT>(yw.y, chi.y), mul2_packed<DT>(xw.y, shi.y));
+}
+// rotation only, for the tokens behind the quantised ones (the residual window): one thread per (token, 4 pairs)
+template <typename T>
+__global__ void rope_rows_kernel(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, int Nk, int tok_first,
+                                 int tokens, const RopeFusion<T> rope) {
+  constexpr int DT16 = Elem<T>::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
+  const int bh = blockIdx.y, h = bh % Nk, b = bh / Nk;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int tok = idx >> 4, p0 = (idx & 15) * 4;
+  if (tok >= tokens) return;
+  const int64_t pos = tok_first + tok;
+  const T* row = keys + b * sb + h * sh + pos * sl + p0;
+  const T* c = rope.cos + b * rope.cs_sb + pos * rope.cs_sl + p0;
+  const T* sn = rope.sin + b * rope.cs_sb + pos * rope.cs_sl + p0;
+  uint2 xr, yr;
+  rope4_packed<DT16>(ldg8_nc(row), ldg8_nc(row + kPairs), ldg8_nc(c), ldg8_nc(c + kPairs), ldg8_nc(sn), ldg8_nc(sn + kPairs),
+                     xr, yr);
+  T* o = rope.out + b * rope.o_sb + h * rope.o_sh + pos * rope.o_sl + p0;
+  *reinterpret_cast<uint2*>(o) = xr;
+  *reinterpret_cast<uint2*>(o + kPairs) = yr;
+}
+
 // 16-bit keys, G a multiple of 16 up to kMaxSmemGroup: angle and radius of the group wait in shared memory between
 // the two passes (16 bytes per thread and token, conflict-free), so the token loops stay rolled - a small code
 // footprint that the instruction cache holds - and a thread needs 64 registers (four CTAs per SM).
@@ -316,12 +358,13 @@ constexpr int kMaxSmemGroup = 128;
 #ifndef PQ_QUANT16_MIN_CTAS
 #define PQ_QUANT16_MIN_CTAS 4
 #endif
-template <typename T, int WPG>
+template <typename T, int WPG, bool ROPE = false>
 __global__ void __launch_bounds__(kQuantThreads, PQ_QUANT16_MIN_CTAS)
 quantize_kernel16(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl, int Nk, int nb, int G,
                   int rbits, int tbits, unsigned flags, uint8_t* __restrict__ codes, T* __restrict__ rscale,
                   T* __restrict__ rmn_out, T* __restrict__ tscale, T* __restrict__ tmn_out,
-                  int64_t c_sb, int64_t c_sh, int64_t s_sb, int64_t s_sh, const WindowGate gate, int total_groups) {
+                  int64_t c_sb, int64_t c_sh, int64_t s_sb, int64_t s_sh, const WindowGate gate, int total_groups,
+                  const RopeFusion<T> rope) {
   constexpr int wpg = WPG;                                 // warps per group
   using E = Elem<T>;
   constexpr int DT16 = E::kDtype == PQ_BF16 ? PQ_BF16 : PQ_F16;
@@ -361,8 +404,24 @@ quantize_kernel16(const T* __restrict__ keys, int64_t sb, int64_t sh, int64_t sl
 #pragma unroll 2
   for (int i = 0; i < ni; ++i) {
     float x[4], y[4];
-    load4<T>(row, x);
-    load4<T>(row + kPairs, y);
+    if constexpr (ROPE) {
+      const int64_t pos = static_cast<int64_t>(j) * G + tok0 + i * tok_step;       // token of the sequence
+      const T* c = rope.cos + b * rope.cs_sb + pos * rope.cs_sl + p0;
+      const T* sn = rope.sin + b * rope.cs_sb + pos * rope.cs_sl + p0;
+      uint2 xr, yr;
+      rope4_packed<DT16>(ldg8_nc(row), ldg8_nc(row + kPairs), ldg8_nc(c), ldg8_nc(c + kPairs), ldg8_nc(sn),
+                         ldg8_nc(sn + kPairs), xr, yr);
+      if (rope.out) {
+        T* o = rope.out + b * rope.o_sb + h * rope.o_sh + pos * rope.o_sl + p0;
+        *reinterpret_cast<uint2*>(o) = xr;
+        *reinterpret_cast<uint2*>(o + kPairs) = yr;
+      }
+      const float2 x01 = unpack2<DT16>(xr.x), x23 = unpack2<DT16>(xr.y), y01 = unpack2<DT16>(yr.x), y23 = unpack2<DT16>(yr.y);
+      x[0] = x01.x; x[1] = x01.y; x[2] = x23.x; x[3] = x23.y; y[0] = y01.x; y[1] = y01.y; y[2] = y23.x; y[3] = y23.y;
+    } else {
+      load4<T>(row, x);
+      load4<T>(row + kPairs, y);
+    }
     row += row_step;
     uint32_t pw[2], rw[2];
     polar_of4_packed<T>(x, y, wrap, norm_sep, pw, rw);
@@ -746,7 +805,7 @@ __global__ void selftest_kernel(int which, unsigned long long* mismatches) {
 template <typename T>
 int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, int G, int rbits, int tbits,
                     unsigned flags, uint8_t* codes, void* rs, void* rm, void* ts, void* tm, const int64_t* os,
-                    const WindowGate& gate, cudaStream_t s) {
+                    const WindowGate& gate, cudaStream_t s, const void* rope_ptr = nullptr) {
   const int nb = L / G;
   const int64_t tiles = static_cast<int64_t>(B) * Nk * nb;
   if (tiles == 0) return PQ_OK;
@@ -759,11 +818,17 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
       const int wpg = (kQuantThreads / 32) / gpc;                          // warps per group
       const size_t smem = static_cast<size_t>(G / (2 * wpg)) * kQuantThreads * sizeof(uint4);
       const dim3 grid16(static_cast<unsigned>((tiles + gpc - 1) / gpc));
+      const RopeFusion<T> none{};
+      const RopeFusion<T>* rope = static_cast<const RopeFusion<T>*>(rope_ptr);
 #define PQ_LAUNCH_Q16(W)                                                                                         \
-  quantize_kernel16<T, W><<<grid16, block, smem, s>>>(k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, codes, \
-                                                      static_cast<T*>(rs), static_cast<T*>(rm), static_cast<T*>(ts), \
-                                                      static_cast<T*>(tm), os[0], os[1], os[2], os[3], gate,       \
-                                                      static_cast<int>(tiles))
+  if (rope)                                                                                                      \
+    quantize_kernel16<T, W, true><<<grid16, block, smem, s>>>(                                                   \
+        k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, codes, static_cast<T*>(rs), static_cast<T*>(rm), \
+        static_cast<T*>(ts), static_cast<T*>(tm), os[0], os[1], os[2], os[3], gate, static_cast<int>(tiles), *rope); \
+  else                                                                                                           \
+    quantize_kernel16<T, W, false><<<grid16, block, smem, s>>>(                                                  \
+        k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, codes, static_cast<T*>(rs), static_cast<T*>(rm), \
+        static_cast<T*>(ts), static_cast<T*>(tm), os[0], os[1], os[2], os[3], gate, static_cast<int>(tiles), none)
       switch (wpg) {
         case 1: PQ_LAUNCH_Q16(1); break;
         case 2: PQ_LAUNCH_Q16(2); break;
@@ -775,6 +840,7 @@ int launch_quantize(const void* keys, const int64_t* st, int B, int Nk, int L, i
       return PQ_OK;
     }
   }
+  if (rope_ptr) return PQ_ERR_UNSUPPORTED;   // the fused rotation exists for 16-bit keys and groups of 16 k <= 128 tokens
 #define PQ_LAUNCH_Q(NI)                                                                                   \
   quantize_kernel<T, NI><<<grid, block, 0, s>>>(k, st[0], st[1], st[2], Nk, nb, G, rbits, tbits, flags, \
                                                 codes, static_cast<T*>(rs), static_cast<T*>(rm),        \
@@ -983,7 +1049,8 @@ int selftest_quantizer_device(int dtype, int which, unsigned long long* mismatch
 int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, int L, int hd, int G,
                     int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes, void* rscale, void* rmn,
                     void* tscale, void* tmn, const int64_t* out_strides, cudaStream_t stream,
-                    const int* gate_lengths, int gate_r_add, int gate_full, int gate_max_groups) {
+                    const int* gate_lengths, int gate_r_add, int gate_full, int gate_max_groups,
+                    const void* rope_fusion) {
   if (!strides || B < 0 || Nk < 0 || L < 0 || G <= 0) return PQ_ERR_INVALID;
   const WindowGate gate{gate_lengths, gate_r_add, gate_full, gate_max_groups};
   if (gate_lengths && (!out_strides || gate_full <= 0 || gate_max_groups <= 0)) return PQ_ERR_INVALID;
@@ -1009,10 +1076,54 @@ int quantize_device(const void* keys, const int64_t strides[4], int B, int Nk, i
     if (os[0] % 4 || os[1] % 4 || os[1] < span * G * tok_bytes || os[3] < span * kPairs) return PQ_ERR_INVALID;
   }
   switch (dtype) {
-    case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
-    case PQ_BF16: return launch_quantize<__nv_bfloat16>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
-    default: return launch_quantize<float>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
+    case PQ_F16: return launch_quantize<__half>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream, rope_fusion);
+    case PQ_BF16: return launch_quantize<__nv_bfloat16>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream, rope_fusion);
+    default: return rope_fusion ? PQ_ERR_UNSUPPORTED
+                                : launch_quantize<float>(keys, strides, B, Nk, L, G, rbits, tbits, flags, codes, rscale, rmn, tscale, tmn, os, gate, stream);
   }
+}
+
+// Prefill-side fusion: rotate the prompt's keys and quantise the first Lq of them in the same pass; the tokens behind
+// them (the residual window) are rotated only.
+int rope_quantize_device(const void* keys, const int64_t strides[4], const void* cosv, const void* sinv,
+                         const int64_t cs_strides[2], void* keys_out, const int64_t out_key_strides[4], int B, int Nk,
+                         int L, int Lq, int hd, int G, int rbits, int tbits, int dtype, unsigned flags, uint8_t* codes,
+                         void* rscale, void* rmn, void* tscale, void* tmn, const int64_t* out_strides,
+                         cudaStream_t stream) {
+  if (!strides || !cs_strides || B < 0 || Nk < 0 || L < 0 || Lq < 0 || Lq > L || G <= 0 || Lq % G != 0) return PQ_ERR_INVALID;
+  if (dtype != PQ_F16 && dtype != PQ_BF16) return dtype == PQ_F32 ? PQ_ERR_UNSUPPORTED : PQ_ERR_INVALID;
+  if (hd != kHeadDim || G % 16 != 0 || G > kMaxSmemGroup) return PQ_ERR_UNSUPPORTED;
+  if (B == 0 || Nk == 0 || L == 0) return PQ_OK;
+  if (!keys || !cosv || !sinv) return PQ_ERR_INVALID;
+  if (keys_out && !out_key_strides) return PQ_ERR_INVALID;
+  if (L > Lq && !keys_out) return PQ_ERR_INVALID;            // rotating the tail needs somewhere to put it
+  if (strides[3] != 1 || (keys_out && out_key_strides[3] != 1)) return PQ_ERR_INVALID;
+  auto mis8 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 8 != 0; };
+  if (mis8(keys) || mis8(cosv) || mis8(sinv) || (keys_out && mis8(keys_out)) || strides[0] % 4 || strides[1] % 4 ||
+      strides[2] % 4 || cs_strides[0] % 4 || cs_strides[1] % 4 ||
+      (keys_out && (out_key_strides[0] % 4 || out_key_strides[1] % 4 || out_key_strides[2] % 4)))
+    return PQ_ERR_ALIGNMENT;
+  int rc = PQ_OK;
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    RopeFusion<T> rope{static_cast<const T*>(cosv), static_cast<const T*>(sinv), cs_strides[0], cs_strides[1],
+                       static_cast<T*>(keys_out), keys_out ? out_key_strides[0] : 0, keys_out ? out_key_strides[1] : 0,
+                       keys_out ? out_key_strides[2] : 0};
+    if (Lq > 0) {
+      rc = quantize_device(keys, strides, B, Nk, Lq, hd, G, rbits, tbits, dtype, flags, codes, rscale, rmn, tscale, tmn,
+                           out_strides, stream, nullptr, 0, 0, 0, &rope);
+      if (rc != PQ_OK) return;
+    }
+    if (L > Lq) {
+      const int tokens = L - Lq;
+      const dim3 grid((tokens * 16 + 255) / 256, static_cast<unsigned>(B) * Nk);
+      rope_rows_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(keys), strides[0], strides[1], strides[2], Nk, Lq,
+                                                   tokens, rope);
+      if (cudaGetLastError() != cudaSuccess) rc = PQ_ERR_CUDA;
+    }
+  };
+  if (dtype == PQ_F16) run(__half{}); else run(__nv_bfloat16{});
+  return rc;
 }
 
 }  // namespace pq

@@ -99,6 +99,21 @@ template <int DT> __device__ __forceinline__ uint32_t sub2_packed(uint32_t a, ui
   return d;
 }
 
+// a + b and a * b of packed 16-bit pairs, rounded once.  torch evaluates both in fp32 and rounds the result to T; a
+// product of two 16-bit values is exact in fp32, and the sum obeys the argument given at sub2_packed.
+template <int DT> __device__ __forceinline__ uint32_t add2_packed(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (DT == PQ_BF16) asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+template <int DT> __device__ __forceinline__ uint32_t mul2_packed(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (DT == PQ_BF16) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // floor of a value in [0, 2^22) by a round-toward-zero addition of 2^23: the integer sits in the low mantissa bits
 __device__ __forceinline__ uint32_t floor_bits(float v) { return __float_as_uint(__fadd_rz(v, 8388608.0f)); }
 

@@ -149,6 +149,62 @@ def qk_decode(query_states: torch.Tensor, indices: torch.Tensor, rscale, rmn, ts
 _KEY_FORMATS = {"byte": _lib.PQ_KEYS_BYTE, "packed6": _lib.PQ_KEYS_PACKED6}
 
 
+def rope_quantize(key_states: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rbits: int = 4, tbits: int = 4,
+                  group_size: int = 128, quantize_tokens: int | None = None, out: torch.Tensor | None = None,
+                  key_format: str = "byte"):
+    """Prefill-side fusion: rotate the prompt's keys and polar-quantise them in one pass.
+
+    ``key_states`` (B, Nk, L, 128) are the UN-rotated keys (fp16 / bf16, strided views allowed - the (B, L, Nk, hd)
+    layout of the projection); ``cos`` / ``sin`` (L, 128) or (B, L, 128) as ``apply_rotary_pos_emb`` takes them
+    (models/modeling_llama_polar.py:55-57).  Returns ``(rotated keys, (indices, rscale, rmn, tscale, tmn))``: the
+    rotated keys (written to ``out`` if given - it may be ``key_states`` itself - else to a new tensor in the
+    input's layout) equal the eager ``k * cos + rotate_half(k) * sin`` bit for bit, and the first
+    ``quantize_tokens`` of them (default: all but the last L % 128, as at :116-126) are quantised exactly as
+    ``quantize_and_pack_nbit`` quantises the rotated keys.
+    """
+    if key_states.dim() != 4:
+        raise ValueError("key_states must be (batch, kv_heads, length, head_dim)")
+    bsz, heads, length, hd = key_states.shape
+    dev = _require_cuda(key_states, cos, sin, out)
+    dt = _dtype_code(key_states, "rope_quantize")
+    if cos.dtype != key_states.dtype or sin.dtype != key_states.dtype:
+        cos, sin = cos.to(key_states.dtype), sin.to(key_states.dtype)
+    if cos.dim() == 2:
+        cos, sin = cos[None], sin[None]
+    if cos.shape[-2:] != (length, hd) or sin.shape != cos.shape or cos.shape[0] not in (1, bsz):
+        raise ValueError("cos / sin must be (L, head_dim) or (B, L, head_dim)")
+    lq = length - length % 128 if quantize_tokens is None else quantize_tokens
+    assert hd % 2 == 0 and lq % group_size == 0 and rbits + tbits <= 8
+    if not _vec_ok(key_states, 4):
+        key_states = key_states.contiguous()
+    if not _vec_ok(cos, 4) or not _vec_ok(sin, 4) or cos.stride() != sin.stride():
+        cos, sin = cos.contiguous(), sin.contiguous()
+    if out is None:
+        out = torch.empty_like(key_states)               # keeps the (dense) layout of a transposed projection output
+    elif out.shape != key_states.shape or out.dtype != key_states.dtype or not _vec_ok(out, 4):
+        raise ValueError("out must match key_states in shape and dtype, with aligned rows")
+    nb = lq // group_size
+    flags = 0
+    if key_format == "packed6":
+        if rbits + tbits != 6 or group_size % 16:
+            raise ValueError("the packed container holds 6-bit codes (rbits + tbits == 6) of groups of 16 k tokens")
+        flags |= _lib.PQ_QUANT_PACK6
+        codes = torch.empty((bsz, heads, nb, group_size // 16, 768), dtype=torch.uint8, device=dev)
+    else:
+        codes = torch.empty((bsz, heads, nb, group_size, hd // 2), dtype=torch.uint8, device=dev)
+    scales = [torch.empty((bsz, heads, nb, 1, hd // 2), dtype=key_states.dtype, device=dev) for _ in range(4)]
+    i64 = ctypes.c_int64
+    lib = _lib.load()
+    with _on_device(dev):
+        rc = lib.pq_rope_quantize(key_states.data_ptr(), (i64 * 4)(*key_states.stride()), cos.data_ptr(), sin.data_ptr(),
+                                  (i64 * 2)(0 if cos.shape[0] == 1 else cos.stride(0), cos.stride(1)), out.data_ptr(),
+                                  (i64 * 4)(*out.stride()), bsz, heads, length, lq, hd, group_size, rbits, tbits, dt,
+                                  flags, codes.data_ptr(), scales[0].data_ptr(), scales[1].data_ptr(),
+                                  scales[2].data_ptr(), scales[3].data_ptr(), None, _stream(dev))
+    _lib.check(rc, "pq_rope_quantize")
+    return out, (codes, *scales)
+
+
 def keys_repack(indices: torch.Tensor, to_format: str) -> torch.Tensor:
     """Convert key codes between the byte container (..., G, 64) and the 6-bit packed container
     (..., G/16, 768); returns a new tensor.  Lossless for 6-bit codes (bit splits 3/3 and 2/4)."""
