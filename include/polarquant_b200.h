@@ -361,6 +361,13 @@ int pq_values_matmul(const void* probs, const void* codes, const void* scale, co
  */
 int pq_merge_lse(const float* outs, const float* lses, int P, int64_t rows, int hd,
                  void* out, int out_dtype, float* lse_out, void* stream);
+/*
+ * The same with explicit strides (in elements) between the parts, so that the buffer an all-gather fills - every
+ * rank's [outs (rows, hd) | lses (rows)] block back to back - is merged in place: outs = buffer,
+ * out_part_stride = rows * (hd + 1), lses = buffer + rows * hd, lse_part_stride = rows * (hd + 1).
+ */
+int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float* lses, int64_t lse_part_stride, int P,
+                         int64_t rows, int hd, void* out, int out_dtype, float* lse_out, void* stream);
 
 /*
  * Host-buffer forms: the same operations for callers whose tensors live in host

@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = (
     "pq_quantize_values", "pq_values_relayout", "pq_values_matmul",
     "pq_cache_append_dyn", "pq_decode_workspace_bytes_dyn", "pq_rope_append",
     "pq_quantize_into_dyn", "pq_quantize_values_dyn", "pq_lengths_advance", "pq_key_range_check",
-    "pq_keys_repack", "pq_rope_quantize",
+    "pq_keys_repack", "pq_rope_quantize", "pq_merge_lse_strided",
 )
 
 _i64, _int, _vp, _sz, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
@@ -122,6 +122,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_decode_workspace_bytes.argtypes = [_int] * 7
     lib.pq_merge_lse.restype = _int
     lib.pq_merge_lse.argtypes = [_vp, _vp, _int, _i64, _int, _vp, _int, _vp, _vp]
+    lib.pq_merge_lse_strided.restype = _int
+    lib.pq_merge_lse_strided.argtypes = [_vp, _i64, _vp, _i64, _int, _i64, _int, _vp, _int, _vp, _vp]
     lib.pq_quantize_host.restype = _int
     lib.pq_quantize_host.argtypes = [_vp, _int, _int, _int, _int, _int, _int, _int, _int, ctypes.c_uint,
                                      _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]

@@ -146,6 +146,28 @@ def quant_sizes():
         print(json.dumps({"bench": "quantize", "batch": B, "kv_heads": Nk, "tokens": L, "group": G,
                           "dtype": str(dt).split(".")[-1], "us": us, "mb": nbytes / 1e6, "gbs": nbytes / us / 1e3}))
         del base, keys
+    # prefill-side fusion: rotation + quantisation in one pass against the two separate passes
+    B, Nk, L, G, dt = 16, 8, 32768, 128, torch.bfloat16
+    base = torch.randn(B, L, Nk, 128, device=dev, generator=g).to(dt)
+    keys = base.transpose(1, 2)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=dev, dtype=torch.float32) / 128))
+    ang = torch.arange(L, device=dev, dtype=torch.float32)[:, None] * inv
+    ang = torch.cat([ang, ang], dim=-1)
+    cos, sin = ang.cos().to(dt), ang.sin().to(dt)
+    out = torch.empty_like(keys)
+
+    def two_step():
+        half = 64
+        rot = keys * cos[None, None] + torch.cat([-keys[..., half:], keys[..., :half]], dim=-1) * sin[None, None]
+        return ops.quantize_and_pack_nbit(rot, 4, 4, G)
+
+    us_fused = _time_us(lambda: ops.rope_quantize(keys, cos, sin, 4, 4, G, out=out), reps=10)
+    us_quant = _time_us(lambda: ops.quantize_and_pack_nbit(keys, 4, 4, G), reps=10)
+    us_two = _time_us(two_step, reps=5, graph=False)
+    nbytes = B * Nk * L * 128 * 2 * 2 + B * Nk * (L * 64 + (L // G) * 4 * 64 * 2)
+    print(json.dumps({"bench": "rope_quantize", "batch": B, "kv_heads": Nk, "tokens": L, "group": G, "dtype": "bfloat16",
+                      "us_fused": us_fused, "mb_fused": nbytes / 1e6, "gbs_fused": nbytes / us_fused / 1e3,
+                      "us_quantizer_alone": us_quant, "us_eager_rotation_then_quantizer": us_two}))
 
 
 def packed_values():
@@ -296,13 +318,20 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
                         else ops.decode_attention(q, kres, *packed, v))
     agg = total(nbytes)
     out["sequence"] = {"us": us, "aggregate_gbs": agg / us / 1e3, "aggregate_mb": agg / 1e6,
-                       "collective": "all_gather of (B*N, 129) fp32 per rank + local merge", "cuda_graph": graphed}
+                       "collective": "one all_gather of (B*N, 129) fp32 per rank, merged in place by one kernel", "cuda_graph": graphed}
     if world > 1:
-        # the parts of the sequence-split step: local attention alone, and the exchange + merge alone
-        us_local, _ = timed(lambda: pqd.local_partial(q, kres, packed, v))
-        o, l = pqd.local_partial(q, kres, packed, v)
-        us_xchg, _ = timed(lambda: pqd.merge_across_ranks(o, l, out_dtype=torch.bfloat16))
-        out["sequence"].update(local_attention_us=us_local, exchange_and_merge_us=us_xchg)
+        # the parts of the sequence-split step, each replayed from a graph of its own: local attention, the
+        # all-gather of the (B N, 129) fp32 blocks, the merge over the gathered buffer
+        rows = B * N
+        mine = torch.zeros(rows * 129, dtype=torch.float32, device=dev)
+        gathered = torch.zeros(world * rows * 129, dtype=torch.float32, device=dev)
+        o_view, l_view = mine[:rows * 128].view(B, N, 1, 128), mine[rows * 128:].view(B, N)
+        us_local, _ = timed(lambda: ops.decode_attention(q, kres, *packed, v, out_dtype=torch.float32, out=o_view,
+                                                         lse_out=l_view))
+        us_gather, _ = timed(lambda: dist.all_gather_into_tensor(gathered, mine))
+        us_merge, _ = timed(lambda: ops.merge_lse_gathered(gathered, world, rows, out_dtype=torch.bfloat16))
+        out["sequence"].update(local_attention_us=us_local, all_gather_us=us_gather, merge_us=us_merge,
+                               exchange_bytes_per_rank=rows * 129 * 4)
     del q, kres, packed, v
     return out
 

@@ -20,6 +20,9 @@ when the window fills (:240-248):
     v_res   (B, Nk, residual_length, 128)
 136 bytes per token and kv head instead of 324.
 
+With ``key_format="packed6"`` (bit splits 3/3 and 2/4) the codes live in the 48-byte-per-token container instead of one
+byte per pair; everything else is unchanged and the attention results are bit-identical.
+
 CUDA-graph replay.  With ``lengths`` (an int32 device tensor ``[token groups, residual tokens]``, shared by the
 caches of all layers) ``decode_step_graph`` enqueues the append and the attention with the lengths read on the
 device, and changes nothing on the host: one captured graph of the whole model step is replayed for every token.
@@ -43,7 +46,7 @@ class PolarKVCache:
     def __init__(self, batch: int, kv_heads: int, max_tokens: int, dtype=torch.bfloat16, device="cuda",
                  rbits: int = 4, tbits: int = 4, group_size: int = 128, residual_length: int = 128,
                  head_dim: int = 128, vbits: int = 0, lengths: torch.Tensor | None = None,
-                 num_q_heads: int | None = None):
+                 num_q_heads: int | None = None, key_format: str = "byte"):
         if residual_length % group_size:
             raise ValueError("residual_length must be a multiple of group_size")
         if head_dim != 128:
@@ -56,7 +59,19 @@ class PolarKVCache:
         self.max_groups = max_tokens // group_size
         self.max_tokens = max_tokens
         dev = torch.device(device)
-        self.codes = torch.empty((batch, kv_heads, self.max_groups, group_size, 64), dtype=torch.uint8, device=dev)
+        if key_format == "packed6":
+            # 48 instead of 64 key bytes per token: the 6-bit container of the 3/3 and 2/4 bit splits
+            if rbits + tbits != 6 or group_size % 16:
+                raise ValueError("key_format='packed6' holds 6-bit codes (rbits + tbits == 6) of groups of 16 k tokens")
+            self.codes = torch.empty((batch, kv_heads, self.max_groups, group_size // 16, 768), dtype=torch.uint8,
+                                     device=dev)
+        elif key_format == "byte":
+            self.codes = torch.empty((batch, kv_heads, self.max_groups, group_size, 64), dtype=torch.uint8, device=dev)
+        else:
+            raise ValueError("key_format must be 'byte' or 'packed6'")
+        self.key_format = key_format
+        self._tok_bytes = 48 if key_format == "packed6" else 64          # code bytes per token
+        self._qflags = _lib.PQ_QUANT_PACK6 if key_format == "packed6" else 0
         self.scales = [torch.empty((batch, kv_heads, self.max_groups, 1, 64), dtype=dtype, device=dev)
                        for _ in range(4)]                     # rscale, rmn, tscale, tmn
         self.k_res = torch.empty((batch, kv_heads, residual_length, head_dim), dtype=dtype, device=dev)
@@ -94,6 +109,7 @@ class PolarKVCache:
         p.workspace, p.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
         p.B, p.Nk, p.G, p.hd = batch, kv_heads, group_size, head_dim
         p.rbits, p.tbits = rbits, tbits
+        p.key_format = ops._KEY_FORMATS[key_format]
         p.qk_dtype = p.v_dtype = self._dt
         if vbits:
             p.v_codes = self.v_codes.data_ptr()
@@ -146,11 +162,11 @@ class PolarKVCache:
         out_strides = (ctypes.c_int64 * 4)(self.codes.stride(0), self.codes.stride(1),
                                            self.scales[0].stride(0), self.scales[0].stride(1))
         es = self.scales[0].element_size()
-        code_ptr = self.codes.data_ptr() + first_group * self.G * 64 + batch_start * self.codes.stride(0)
+        code_ptr = self.codes.data_ptr() + first_group * self.G * self._tok_bytes + batch_start * self.codes.stride(0)
         scale_ptrs = [s.data_ptr() + (first_group * 64 + batch_start * s.stride(0)) * es for s in self.scales]
         with ops._on_device(dev):
             rc = lib.pq_quantize_into(keys.data_ptr(), in_strides, keys.shape[0], self.Nk, n * self.G, 128, self.G,
-                                      self.rbits, self.tbits, ops._DT[keys.dtype], 0, code_ptr, *scale_ptrs,
+                                      self.rbits, self.tbits, ops._DT[keys.dtype], self._qflags, code_ptr, *scale_ptrs,
                                       out_strides, ops._stream(dev))
         _lib.check(rc, "pq_quantize_into")
 
@@ -240,7 +256,7 @@ class PolarKVCache:
             rc = lib.pq_rope_quantize(key_states.data_ptr(), (i64 * 4)(*key_states.stride()), cos.data_ptr(),
                                       sin.data_ptr(), (i64 * 2)(0 if cos.shape[0] == 1 else cos.stride(0), cos.stride(1)),
                                       out.data_ptr(), (i64 * 4)(*out.stride()), bsz, self.Nk, length, nq, 128, self.G,
-                                      self.rbits, self.tbits, self._dt, 0, code_ptr, *scale_ptrs, out_strides,
+                                      self.rbits, self.tbits, self._dt, self._qflags, code_ptr, *scale_ptrs, out_strides,
                                       ops._stream(dev))
         _lib.check(rc, "pq_rope_quantize")
         sl = slice(batch_start, batch_start + bsz)
@@ -405,7 +421,7 @@ class PolarKVCache:
             kout = (ctypes.c_int64 * 4)(self.codes.stride(0), self.codes.stride(1),
                                         self.scales[0].stride(0), self.scales[0].stride(1))
             rc = lib.pq_quantize_into_dyn(self.k_res.data_ptr(), kin, self.B, self.Nk, self.RL, 128, self.G,
-                                          self.rbits, self.tbits, self._dt, 0, self.codes.data_ptr(),
+                                          self.rbits, self.tbits, self._dt, self._qflags, self.codes.data_ptr(),
                                           *(t.data_ptr() for t in self.scales), kout, self.max_groups, lp, 1, stream)
             _lib.check(rc, "pq_quantize_into_dyn")
 
@@ -460,7 +476,7 @@ class PolarKVCache:
         out = ops.decode_attention(query_states, self.k_res[:, :, :self.res_len], *packed,
                                    self.values[:, :, :vpos + 1], attention_mask=attention_mask, rbits=self.rbits,
                                    tbits=self.tbits, sm_scale=sm_scale, out_dtype=out_dtype,
-                                   workspace=self.workspace, **kw)
+                                   workspace=self.workspace, key_format=self.key_format, **kw)
         if self.res_len == self.RL:
             self._requantize_window()
             if self.lengths is not None:
@@ -470,9 +486,13 @@ class PolarKVCache:
         return out
 
     def as_reference_tuple(self):
-        """The reference's 8-tuple view of the cache (models/modeling_llama_polar.py:62,101): views, no copies."""
+        """The reference's 8-tuple view of the cache (models/modeling_llama_polar.py:62,101): views, no copies -
+        except the codes of a packed-key cache, which are unpacked into the reference's byte container."""
         ng = self.num_groups
-        packed = (self.codes[:, :, :ng], *(s[:, :, :ng] for s in self.scales)) if ng else (None,) * 5
+        codes = self.codes[:, :, :ng]
+        if ng and self.key_format == "packed6":
+            codes = ops.keys_repack(codes, "byte")
+        packed = (codes, *(s[:, :, :ng] for s in self.scales)) if ng else (None,) * 5
         k_full = self.k_res[:, :, :self.res_len] if self.res_len else None
         if self.vbits:
             # the mixed class's 11-tuple (models/modeling_llama_polar.py:190,246); its value codes are in the

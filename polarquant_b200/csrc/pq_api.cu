@@ -48,6 +48,9 @@ int values_matmul_device(const void* probs, const void* codes, const void* scale
                          int64_t BH, int M, int T, int hd, int vbits, int dtype, cudaStream_t stream);
 int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out, int out_dtype,
                      float* lse_out, cudaStream_t stream);
+int merge_lse_strided_device(const float* outs, int64_t out_part_stride, const float* lses, int64_t lse_part_stride,
+                             int P, int64_t rows, int hd, void* out, int out_dtype, float* lse_out,
+                             cudaStream_t stream);
 
 namespace {
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -140,6 +143,12 @@ int pq_rope_append(const void* qkv, int64_t qkv_stride_b, const void* cos, const
   return rope_append_device(qkv, qkv_stride_b, cos, sin, cs_stride_b, q_out, k_res, kres_strides, values, v_strides,
                             B, N, Nk, hd, G, lengths, values_window, res_cap, value_cap, res_pos, ctx_pos, dtype,
                             static_cast<cudaStream_t>(stream));
+}
+
+int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float* lses, int64_t lse_part_stride, int P,
+                         int64_t rows, int hd, void* out, int out_dtype, float* lse_out, void* stream) {
+  return merge_lse_strided_device(outs, out_part_stride, lses, lse_part_stride, P, rows, hd, out, out_dtype, lse_out,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int pq_rope_quantize(const void* keys, const int64_t strides[4], const void* cos, const void* sin,

@@ -1253,21 +1253,22 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
   }
 }
 
-// Merge P normalised partial results (outs (P, rows, 128), lses (P, rows)).
+// Merge P normalised partial results: part p holds outs (rows, 128) at outs + p * out_ps and lses (rows) at
+// lses + p * lse_ps (element strides between parts; dense tensors have out_ps = rows * 128, lse_ps = rows).
 template <int ODT>
 __global__ void __launch_bounds__(kHeadDim)
-merge_lse_kernel(const float* __restrict__ outs, const float* __restrict__ lses, int P, int64_t rows,
+merge_lse_kernel(const float* __restrict__ outs, int64_t out_ps, const float* __restrict__ lses, int64_t lse_ps, int P,
                  void* __restrict__ out, float* __restrict__ lse_out) {
   const int64_t row = blockIdx.x;
   const int ch = threadIdx.x;
   float M = -INFINITY;
-  for (int p = 0; p < P; ++p) M = fmaxf(M, lses[p * rows + row]);
+  for (int p = 0; p < P; ++p) M = fmaxf(M, lses[p * lse_ps + row]);
   float L = 0.f, acc = 0.f;
   for (int p = 0; p < P; ++p) {
-    const float l = lses[p * rows + row];
+    const float l = lses[p * lse_ps + row];
     const float w = l == -INFINITY ? 0.f : __expf(l - M);
     L += w;
-    acc = fmaf(w, outs[(p * rows + row) * kHeadDim + ch], acc);
+    acc = fmaf(w, outs[p * out_ps + row * kHeadDim + ch], acc);
   }
   const float val = acc / L;
   const int64_t off = row * kHeadDim + ch;
@@ -1523,8 +1524,9 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   return PQ_OK;
 }
 
-int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out,
-                     int out_dtype, float* lse_out, cudaStream_t stream) {
+int merge_lse_strided_device(const float* outs, int64_t out_part_stride, const float* lses, int64_t lse_part_stride,
+                             int P, int64_t rows, int hd, void* out, int out_dtype, float* lse_out,
+                             cudaStream_t stream) {
   if (P <= 0 || rows < 0 || !dtype_ok(out_dtype)) return PQ_ERR_INVALID;
   if (hd != kHeadDim) return PQ_ERR_UNSUPPORTED;
   if (rows == 0) return PQ_OK;
@@ -1532,12 +1534,17 @@ int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, 
   if (rows > 0x7fffffffLL) return PQ_ERR_UNSUPPORTED;
   const unsigned grid = static_cast<unsigned>(rows);
   switch (out_dtype) {
-    case PQ_F16: merge_lse_kernel<PQ_F16><<<grid, kHeadDim, 0, stream>>>(outs, lses, P, rows, out, lse_out); break;
-    case PQ_BF16: merge_lse_kernel<PQ_BF16><<<grid, kHeadDim, 0, stream>>>(outs, lses, P, rows, out, lse_out); break;
-    default: merge_lse_kernel<PQ_F32><<<grid, kHeadDim, 0, stream>>>(outs, lses, P, rows, out, lse_out); break;
+    case PQ_F16: merge_lse_kernel<PQ_F16><<<grid, kHeadDim, 0, stream>>>(outs, out_part_stride, lses, lse_part_stride, P, out, lse_out); break;
+    case PQ_BF16: merge_lse_kernel<PQ_BF16><<<grid, kHeadDim, 0, stream>>>(outs, out_part_stride, lses, lse_part_stride, P, out, lse_out); break;
+    default: merge_lse_kernel<PQ_F32><<<grid, kHeadDim, 0, stream>>>(outs, out_part_stride, lses, lse_part_stride, P, out, lse_out); break;
   }
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
+}
+
+int merge_lse_device(const float* outs, const float* lses, int P, int64_t rows, int hd, void* out,
+                     int out_dtype, float* lse_out, cudaStream_t stream) {
+  return merge_lse_strided_device(outs, rows * kHeadDim, lses, rows, P, rows, hd, out, out_dtype, lse_out, stream);
 }
 
 // ---------------------------------------------------------------------------------

@@ -280,7 +280,7 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
                      sm_scale: float | None = None, out_dtype: torch.dtype | None = None,
                      return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0,
                      mid_event=None, value_codes=None, value_scale=None, value_mn=None, vbits: int = 4,
-                     key_format: str = "byte"):
+                     key_format: str = "byte", out: torch.Tensor | None = None, lse_out: torch.Tensor | None = None):
     """One fused decode-attention step over the polar cache.
 
     Computes what the reference's decode branch computes with separate ops
@@ -304,6 +304,9 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     ``key_format="packed6"``: ``indices`` is the 48-byte-per-token container (B, Nk, Nb, G/16, 768) written by
     ``quantize_and_pack_nbit(key_format="packed6")`` or ``keys_repack`` (bit splits 3/3 and 2/4, fp16/bf16 caches);
     the result is bit-identical to the byte container's.
+
+    ``out`` (B, N, 1, 128) / ``lse_out`` (B, N) fp32: write the results into these tensors instead of new ones
+    (``out`` may have any batch / head strides with a dense last dimension; ``lse_out`` must be contiguous).
     """
     dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask, value_codes)
     bsz, nq, qlen, hd = query_states.shape
@@ -397,9 +400,17 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
         m = m.contiguous()
         p.mask, p.mask_stride_b = m.data_ptr(), m.stride(0)
         keep.append(m)
-    out = torch.empty((bsz, nq, 1, hd), dtype=out_dtype, device=dev)
+    if out is None:
+        out = torch.empty((bsz, nq, 1, hd), dtype=out_dtype, device=dev)
+    elif out.shape != (bsz, nq, 1, hd) or out.dtype != out_dtype or out.stride(-1) != 1 or out.device != dev:
+        raise ValueError("out must be (B, N, 1, 128) of the output dtype on the inputs' device")
     p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
-    lse = torch.empty((bsz, nq), dtype=torch.float32, device=dev) if return_lse else None
+    if lse_out is not None:
+        if lse_out.shape != (bsz, nq) or lse_out.dtype != torch.float32 or not lse_out.is_contiguous():
+            raise ValueError("lse_out must be a contiguous (B, N) float32 tensor")
+        return_lse = True
+    lse = lse_out if lse_out is not None else (torch.empty((bsz, nq), dtype=torch.float32, device=dev)
+                                               if return_lse else None)
     p.lse = lse.data_ptr() if return_lse else None
     p.B, p.N, p.Nk, p.Nb, p.G, p.R, p.hd = bsz, nq, kvh, nb, grp, res, hd
     p.rbits, p.tbits = rbits, tbits
@@ -436,6 +447,24 @@ def merge_lse(outs: torch.Tensor, lses: torch.Tensor, out_dtype: torch.dtype = t
                               lse.data_ptr() if return_lse else None, _stream(dev))
     _lib.check(rc, "pq_merge_lse")
     return (out, lse) if return_lse else out
+
+
+def merge_lse_gathered(gathered: torch.Tensor, parts: int, rows: int, out_dtype: torch.dtype = torch.float32,
+                       out_shape=None) -> torch.Tensor:
+    """Merge the buffer an all-gather fills: ``parts`` blocks of ``rows * 129`` fp32 back to back, each block
+    [outs (rows, 128) | lses (rows)] - the layout ``distributed.sequence_parallel_decode`` exchanges - without
+    slicing it apart first.  Returns (rows, 128) in ``out_dtype`` (reshaped to ``out_shape`` if given)."""
+    dev = _require_cuda(gathered)
+    if gathered.dtype != torch.float32 or not gathered.is_contiguous() or gathered.numel() != parts * rows * 129:
+        raise ValueError("gathered must be a contiguous float32 buffer of parts * rows * 129 elements")
+    out = torch.empty((rows, 128), dtype=out_dtype, device=dev)
+    lib = _lib.load()
+    base = gathered.data_ptr()
+    with _on_device(dev):
+        rc = lib.pq_merge_lse_strided(base, rows * 129, base + rows * 128 * 4, rows * 129, parts, rows, 128,
+                                      out.data_ptr(), _DT[out_dtype], None, _stream(dev))
+    _lib.check(rc, "pq_merge_lse_strided")
+    return out.reshape(out_shape) if out_shape is not None else out
 
 
 # ------------------------------------------------------------------------------------------------

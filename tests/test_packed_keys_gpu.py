@@ -107,3 +107,40 @@ def test_packed_container_at_the_qwen_shaped_full_size():
     a = pq.decode_attention(q, kres, *byte, v, rbits=3, tbits=3)
     b = pq.decode_attention(q, kres, *packed, v, rbits=3, tbits=3, key_format="packed6")
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("vbits", [0, 4])
+def test_in_place_cache_on_the_packed_container_tracks_the_byte_cache(vbits):
+    """PolarKVCache(key_format='packed6'): prefill, eager decode steps across a window boundary and the replayed
+    CUDA graph with device-side lengths all give the bits of the byte-container cache."""
+    from polarquant_b200.cache import PolarKVCache
+    dt = torch.bfloat16
+    B, N, Nk, prompt, steps = 2, 8, 2, 300, 100
+    g = torch.Generator(device=DEV).manual_seed(123)
+    keys = oracle.synth_keys(B, prompt, Nk, 128, dt, seed=124, device=DEV).transpose(1, 2)
+    vals = torch.randn(B, prompt, Nk, 128, device=DEV, generator=g).to(dt).transpose(1, 2)
+    caches = []
+    for fmt in ("byte", "packed6"):
+        lengths = torch.zeros(2, dtype=torch.int32, device=DEV)
+        c = PolarKVCache(B, Nk, max_tokens=prompt + steps + 128, dtype=dt, rbits=3, tbits=3, vbits=vbits,
+                         lengths=lengths, key_format=fmt)
+        c.prefill(keys, vals)
+        caches.append(c)
+    for step in range(steps):
+        q = torch.randn(B, N, 1, 128, device=DEV, generator=g).to(dt)
+        k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=3000 + step, device=DEV)
+        v_new = torch.randn(B, Nk, 1, 128, device=DEV, generator=g).to(dt)
+        if step % 2:
+            outs = [c.decode_step(q, k_new, v_new) for c in caches]
+        else:                                      # the device-side-lengths path, eagerly launched
+            outs = []
+            for c in caches:
+                outs.append(c.decode_step_graph(q, k_new, v_new))
+                c.lengths[1:2].add_(1)
+                if c.after_replay():
+                    c.sync_lengths()
+        assert torch.equal(outs[0], outs[1]), step
+    ta, tb = caches[0].as_reference_tuple(), caches[1].as_reference_tuple()
+    assert caches[1].codes.shape[-1] == 768 and caches[1].codes.numel() * 4 == caches[0].codes.numel() * 3
+    for x, y in zip(ta[1:6], tb[1:6]):
+        assert torch.equal(x, y)
