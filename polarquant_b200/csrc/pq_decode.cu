@@ -1061,8 +1061,10 @@ __device__ __forceinline__ long long warp_of(long long x, long long total, int n
 // stages, chunk by chunk, the weights 2^(m_i - M) and weighted sums once per (partial, head)
 // in shared memory, and 8 groups of 64 threads stride over the partial rows, four rows in
 // flight per thread, with one FMA per (partial, head, channel).  Every warp range of the
-// attention kernel is non-empty (total_warps <= total_slots), so the partials of a unit are
-// the consecutive warps w0..w1, all with segment 0 except possibly the first.
+// attention kernel is non-empty (total_warps <= total_slots), so a unit is covered by the
+// consecutive warps w0..w1; which of them left a partial follows from the CTA-level combine
+// of the attention kernel and is enumerated densely (see below), so every load issued is a
+// partial that exists.
 constexpr int kMergeGroups = 8;
 constexpr int kMergeCh = 64;
 constexpr int kMergeChunk = 128;      // partials whose weights are staged at a time
@@ -1109,23 +1111,24 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
   const long long w0 = warp_of(first, a.total_slots, a.total_warps);
   const long long w1 = warp_of(last, a.total_slots, a.total_warps);
   const int seg0 = static_cast<int>(unit - range_lo(w0, a.total_slots, a.total_warps) / a.slots_per_unit);
-  const int n = static_cast<int>(w1 - w0 + 1);
-  // warp i of the unit holds a partial unless its CTA lies in one unit and it is not the CTA's first warp
-  auto slot_of = [&](int i) { return (w0 + i) * a.max_seg + (i == 0 ? seg0 : 0); };
-  // the predicate costs 64-bit divisions: evaluate it once per CTA of the attention grid, into shared memory
-  constexpr int kMaxFlags = 1024;                      // CTAs of the attention grid a unit can span before falling back
-  __shared__ unsigned char s_single[kMaxFlags];
-  const long long cta0 = w0 >> 2;
-  const int ncta = static_cast<int>((w1 >> 2) - cta0 + 1);
-  for (int c = threadIdx.x; c < min(ncta, kMaxFlags); c += blockDim.x)
-    s_single[c] = cta_in_one_unit(cta0 + c, a.total_slots, a.total_warps, a.slots_per_unit);
-  __syncthreads();
-  auto has_partial = [&](int i) {
-    const long long w = w0 + i;
-    if ((w & 3) == 0) return true;
-    const long long c = (w >> 2) - cta0;
-    return c < kMaxFlags ? !s_single[c] : !cta_in_one_unit(w >> 2, a.total_slots, a.total_warps, a.slots_per_unit);
+  // The unit's partials, in a fixed order.  Warps strictly between w0 and w1 lie wholly inside the unit, so every
+  // CTA strictly between the first and the last one combined its four partials into one (in the slot of its
+  // first warp); only the two CTAs at the ends can straddle a unit boundary and hold one partial per warp.
+  //   [ nf partials of the first CTA | ni = one per interior CTA | nl partials of the last CTA ]
+  const long long c0 = w0 >> 2, c1 = w1 >> 2;
+  const bool single0 = cta_in_one_unit(c0, a.total_slots, a.total_warps, a.slots_per_unit);
+  const bool single1 = c1 != c0 && cta_in_one_unit(c1, a.total_slots, a.total_warps, a.slots_per_unit);
+  const long long wf_end = c1 == c0 ? w1 : 4 * c0 + 3;                 // last warp of the unit in the first CTA
+  const int nf = single0 ? 1 : static_cast<int>(wf_end - w0 + 1);
+  const int ni = c1 > c0 + 1 ? static_cast<int>(c1 - c0 - 1) : 0;
+  const int nl = c1 == c0 ? 0 : (single1 ? 1 : static_cast<int>(w1 - 4 * c1 + 1));
+  const int n = nf + ni + nl;
+  auto slot_of = [&](int k) -> long long {
+    if (k < nf) return (w0 + k) * a.max_seg + (k == 0 ? seg0 : 0);       // a single first CTA starts at w0 = 4 c0
+    if (k < nf + ni) return 4 * (c0 + 1 + (k - nf)) * a.max_seg;
+    return (4 * c1 + (k - nf - ni)) * a.max_seg;
   };
+  auto has_partial = [](int) { return true; };       // every index below n is a partial that exists
 
   // The first batch of partial rows is requested before anything else so that its DRAM round trip
   // overlaps the one of the (m, l) entries.
