@@ -68,6 +68,9 @@ def parse_args():
     ap.add_argument("--q-heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, quantizer and CPU legs (profiler runs)")
+    ap.add_argument("--key-format", default="byte", choices=["byte", "packed6"],
+                    help="packed6: the 48-byte-per-token key container (needs --rbits/--tbits 3/3 or 2/4); for "
+                         "profiler runs and side measurements, the headline configuration is the byte container")
     ap.add_argument("--e2e-new-tokens", type=int, default=64,
                     help="generated tokens of the end-to-end greedy-decode leg (batch 32, 8192-token prompts); "
                          "0 or 1 skips it")
@@ -77,10 +80,10 @@ def parse_args():
     return ap.parse_args()
 
 
-def algorithmic_bytes(B, N, Nk, Nb, G, R, e=2, e_out=2):
+def algorithmic_bytes(B, N, Nk, Nb, G, R, e=2, e_out=2, key_bytes=64):
     """Bytes one decode step must move: codes + scales + residual keys + values + query + output."""
     lq = Nb * G
-    return B * Nk * (lq * 64 + Nb * 4 * 64 * e + R * 128 * e + (lq + R) * 128 * e) + B * N * 128 * (e + e_out)
+    return B * Nk * (lq * key_bytes + Nb * 4 * 64 * e + R * 128 * e + (lq + R) * 128 * e) + B * N * 128 * (e + e_out)
 
 
 def measured_peak():
@@ -162,7 +165,8 @@ def make_inputs(args, device, seed):
     packed = [[] for _ in range(5)]
     for b in range(B):
         kb = (torch.randn(1, Nk, Nb * G, 128, device=device, generator=g) * scale[None, :, None]).to(torch.bfloat16)
-        for lst, t in zip(packed, pq.quantize_and_pack_nbit(kb, args.rbits, args.tbits, G)):
+        for lst, t in zip(packed, pq.quantize_and_pack_nbit(kb, args.rbits, args.tbits, G,
+                                                            key_format=getattr(args, "key_format", "byte"))):
             lst.append(t)
     packed = [torch.cat(lst, dim=0) for lst in packed]
     return dict(q=q, kres=kres, packed=packed, v=v, B=B, N=N, Nk=Nk, Nb=Nb, G=G, R=R)
@@ -273,7 +277,8 @@ def workload_config(args):
     return {"workload": f"Llama-3.1-8B-shaped GQA decode attention: batch {args.batch} per GPU, {args.q_heads} q / "
                         f"{args.kv_heads} kv heads, head_dim 128, ctx {args.ctx}, polar {args.rbits}/{args.tbits}, "
                         f"group {args.group}, residual 128, bf16"
-                        + (", values packed to 4 bits per token" if getattr(args, "packed_values", False) else ""),
+                        + (", values packed to 4 bits per token" if getattr(args, "packed_values", False) else "")
+                        + (", keys in the 48-byte container" if getattr(args, "key_format", "byte") == "packed6" else ""),
             "l2": "inputs of one step (1.36 GB at the default size) exceed the 126 MB L2; no flush needed",
             "sharding": "batch per GPU, no collective in the step"}
 
@@ -307,7 +312,9 @@ def main():
 
     inp = make_inputs(args, device, seed=1002 + rank)
     B, N, Nk, Nb, G, R = (inp[k] for k in ("B", "N", "Nk", "Nb", "G", "R"))
-    nbytes = algorithmic_bytes(B, N, Nk, Nb, G, R)
+    nbytes = algorithmic_bytes(B, N, Nk, Nb, G, R, key_bytes=48 if args.key_format == "packed6" else 64)
+    if args.key_format != "byte":
+        args.no_extras = True             # the side legs are written for the headline container
     ws = torch.empty(lib.pq_decode_workspace_bytes(B, N, Nk, Nb, G, R, 0) + 256, dtype=torch.uint8, device=device)
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -330,7 +337,7 @@ def main():
                                        tbits=args.tbits, workspace=ws, mid_event=mid, value_codes=vc, value_scale=vs,
                                        value_mn=vm)
         return pq.decode_attention(inp["q"], inp["kres"], *inp["packed"], inp["v"], rbits=args.rbits,
-                                   tbits=args.tbits, workspace=ws, mid_event=mid)
+                                   tbits=args.tbits, workspace=ws, mid_event=mid, key_format=args.key_format)
 
     def barrier():
         if world > 1:
@@ -407,7 +414,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT * B
                                      if (args.ctx, args.group, args.q_heads, args.kv_heads) == (32768, 128, 32, 8)
-                                     and not args.packed_values else None),
+                                     and not args.packed_values and args.key_format == "byte" else None),
                          "traffic_note": "bytes per launch; ncu capture at batch 4 scaled by the batch",
                          "kernel": "decode_kernel (fused attention over packed keys)",
                          "peak_source": f"{peak_kind} copy bandwidth", "kernel_us": kavg * 1e3,
