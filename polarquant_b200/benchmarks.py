@@ -1,7 +1,7 @@
 """Secondary timings of the polar key-cache kernels (the headline number is bench.py at the repository root).
 
     python -m polarquant_b200.benchmarks qk        # the reference's QK micro-benchmark grid
-    python -m polarquant_b200.benchmarks sweep     # fused decode attention over bit widths / group sizes / shapes
+    python -m polarquant_b200.benchmarks sweep [name]   # fused decode attention over bit widths / group sizes / shapes
     python -m polarquant_b200.benchmarks quant     # quantizer at prefill sizes
     python -m polarquant_b200.benchmarks values    # packed (4-bit) value cache: fused attention and value quantiser
     python -m polarquant_b200.benchmarks packed_keys   # 6-bit key container (48 B/token) beside the byte container
@@ -73,12 +73,15 @@ def qk_grid(group_size: int = 32, rbits: int = 4, tbits: int = 4, batches=(1, 2,
             del idx, sc
 
 
-def decode_sweep():
+def decode_sweep(only: str | None = None):
+    """`only`: run just the shapes whose name contains this string (e.g. "70b" for the long-context per-GPU share)."""
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(1003)
     shapes = [("llama3-8b B16 ctx32k", 16, 32, 8, 32768), ("qwen2.5-7b B64 ctx8k", 64, 28, 4, 8192),
               ("llama2-7b MHA B1 ctx4k", 1, 32, 32, 4096), ("70b-shaped 1 kv head/GPU B8 ctx128k", 8, 8, 1, 131072)]
     for name, B, N, Nk, ctx in shapes:
+        if only and only not in name:
+            continue
         for (rb, tb) in ((4, 4), (3, 3), (2, 4)):
             for G in (128, 32):
                 R = 128
@@ -358,5 +361,8 @@ def long_context():
 
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "sweep"
-    {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes, "values": packed_values,
-     "packed_keys": packed_keys, "longctx": long_context}[what]()
+    if what == "sweep" and len(sys.argv) > 2:
+        decode_sweep(sys.argv[2])
+    else:
+        {"qk": qk_grid, "sweep": decode_sweep, "quant": quant_sizes, "values": packed_values,
+         "packed_keys": packed_keys, "longctx": long_context}[what]()

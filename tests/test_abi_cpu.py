@@ -77,6 +77,37 @@ def test_argument_validation_needs_no_gpu():
     assert lib.pq_values_matmul(None, None, None, None, None, 2, 1, 10, 128, 8, 0, None) == -2
     assert lib.pq_decode_workspace_bytes(16, 32, 8, 255, 128, 128, 0) > 0
     assert lib.pq_decode_workspace_bytes(16, 32, 6, 255, 128, 128, 0) == 0
+    # packed key container, fused rotary + quantizer, strided merge, range check
+    assert lib.pq_quantize(None, st, 1, 1, 256, 128, 128, 4, 4, _lib.PQ_BF16, _lib.PQ_QUANT_PACK6, None, None, None, None,
+                           None, None) == -1                              # the packed container holds 6-bit codes only
+    assert lib.pq_quantize(None, st, 1, 1, 240, 128, 24, 3, 3, _lib.PQ_BF16, _lib.PQ_QUANT_PACK6, None, None, None, None,
+                           None, None) == -1                              # groups of 16 k tokens
+    assert lib.pq_keys_repack(None, None, 0, _lib.PQ_KEYS_PACKED6, None) == 0
+    assert lib.pq_keys_repack(None, None, 4, _lib.PQ_KEYS_PACKED6, None) == -1
+    assert lib.pq_keys_repack(None, None, 4, 7, None) == -1
+    p2 = _lib.DecodeParams()
+    p2.B, p2.N, p2.Nk, p2.Nb, p2.G, p2.R, p2.hd = 1, 8, 2, 1, 128, 0, 128
+    p2.rbits, p2.tbits, p2.v_dtype, p2.key_format = 4, 4, _lib.PQ_BF16, _lib.PQ_KEYS_PACKED6
+    assert lib.pq_decode_attention(ctypes.byref(p2), None) == -1          # 4/4 codes do not fit the 6-bit container
+    p2.key_format = 9
+    assert lib.pq_decode_attention(ctypes.byref(p2), None) == -1
+    cs = (ctypes.c_int64 * 2)(0, 128)
+    assert lib.pq_rope_quantize(None, st, None, None, cs, None, st, 1, 1, 256, 200, 128, 128, 4, 4, _lib.PQ_BF16, 0, None,
+                                None, None, None, None, None, None) == -1  # Lq must be whole groups
+    assert lib.pq_rope_quantize(None, st, None, None, cs, None, st, 1, 1, 256, 256, 128, 128, 4, 4, _lib.PQ_F32, 0, None,
+                                None, None, None, None, None, None) == -2  # 16-bit keys only
+    assert lib.pq_rope_quantize(None, st, None, None, cs, None, st, 0, 1, 256, 256, 128, 128, 4, 4, _lib.PQ_BF16, 0, None,
+                                None, None, None, None, None, None) == 0
+    assert lib.pq_merge_lse_strided(None, 0, None, 0, 0, 4, 128, None, 0, None, None) == -1
+    assert lib.pq_merge_lse_strided(None, 0, None, 0, 2, 0, 128, None, 0, None, None) == 0
+    assert lib.pq_key_range_check(None, None, 0, 4, _lib.PQ_BF16, None, None) == 0
+    assert lib.pq_key_range_check(None, None, 8, 4, _lib.PQ_BF16, None, None) == -1
+    # the built-in scratch array: a device-side-lengths call whose explicit grid cannot fit is refused up front
+    p3 = _lib.DecodeParams()
+    p3.B, p3.N, p3.Nk, p3.Nb, p3.G, p3.R, p3.hd = 16, 32, 8, 255, 128, 128, 128
+    p3.rbits, p3.tbits, p3.num_ctas = 4, 4, 444
+    p3.dyn_lengths = 8                                                     # any non-null address: never dereferenced here
+    assert lib.pq_decode_attention_static(ctypes.byref(p3), None) == -6
 
 
 def test_ops_refuse_cpu_tensors():

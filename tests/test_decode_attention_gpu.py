@@ -275,3 +275,21 @@ def test_full_size_step():
         sl = slice(b, b + 2)
         want = oracle.decode_attention(q[sl], kres[sl], *[t[sl] for t in quant], v[sl])
         _check(got[sl], want, f"batch {b}")
+
+
+def test_strided_merge_reads_an_all_gather_buffer_in_place():
+    """pq_merge_lse_strided over [out | lse] blocks back to back equals pq_merge_lse over the tensors sliced apart."""
+    import polarquant_b200 as pq
+    from polarquant_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(55)
+    parts, b, n = 3, 2, 8
+    rows = b * n
+    outs = torch.randn(parts, rows, 128, device="cuda", generator=g)
+    lses = torch.randn(parts, rows, device="cuda", generator=g) * 3.0
+    lses[1, 3] = float("-inf")                                   # a part without keys for that row
+    gathered = torch.cat([torch.cat([outs[p].reshape(-1), lses[p]]) for p in range(parts)]).contiguous()
+    want = pq.merge_lse(outs, lses, out_dtype=torch.bfloat16)
+    got = ops.merge_lse_gathered(gathered, parts, rows, out_dtype=torch.bfloat16)
+    assert torch.equal(got, want)
+    ref, _ = oracle.merge_lse(outs.cpu(), lses.cpu())
+    assert float((got.float().cpu() - ref).abs().max()) <= 2e-2

@@ -130,9 +130,16 @@ def test_in_place_cache_on_the_packed_container_tracks_the_byte_cache(vbits):
         q = torch.randn(B, N, 1, 128, device=DEV, generator=g).to(dt)
         k_new = oracle.synth_keys(B, Nk, 1, 128, dt, seed=3000 + step, device=DEV)
         v_new = torch.randn(B, Nk, 1, 128, device=DEV, generator=g).to(dt)
-        if step % 2:
+        if step % 3 == 1:
             outs = [c.decode_step(q, k_new, v_new) for c in caches]
-        else:                                      # the device-side-lengths path, eagerly launched
+        elif step % 3 == 2:                        # everything on the device: append, attend, re-quantise, advance
+            outs = []
+            for c in caches:
+                outs.append(c.decode_step_graph(q, k_new, v_new))
+                c.requantize_graph()
+                c.advance_graph()
+                c.after_replay(device_requantized=True)
+        else:                                      # the device-side-lengths path with the host re-quantising
             outs = []
             for c in caches:
                 outs.append(c.decode_step_graph(q, k_new, v_new))
