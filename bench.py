@@ -45,9 +45,9 @@ if ROOT not in sys.path:
 METRIC = "polar-KV decode-attn GB/s (% HBM peak) & µs/step @32k ctx; e2e decode tokens/s"
 NOMINAL_HBM_GBS = 8000.0
 # DRAM bytes (read + write) of one attention-kernel launch per batch element of the benchmark shape, from the
-# ncu capture of the batch-4 case (dram__bytes_read.sum 342.03 MB + dram__bytes_write.sum 4.20 MB per launch);
+# ncu capture of the batch-4 case (dram__bytes_read.sum 341.99 MB + dram__bytes_write.sum 3.85 MB per launch);
 # traffic grows in proportion to the batch, so a full-size launch is this figure times the batch
-NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT = (342.04e6 + 4.45e6) / 4
+NCU_TRAFFIC_BYTES_PER_BATCH_ELEMENT = (341.99e6 + 3.85e6) / 4
 FALLBACK_HBM_GBS = 6650.0
 
 

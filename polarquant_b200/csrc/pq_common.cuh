@@ -86,14 +86,10 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // warp-level tensor-core primitives (mma.sync path; see the decode kernel for
 // why the single-query decode shape does not fit tcgen05's M >= 64 tiles)
 // ---------------------------------------------------------------------------
-#ifdef PQ_MMA_NOVOL
-#define PQ_MMA_ASM asm
-#else
-#define PQ_MMA_ASM asm volatile
-#endif
+// plain (not volatile) asm: an MMA has no effect beyond its outputs, so the compiler may schedule it freely
 __device__ __forceinline__ void mma_16816_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                               uint32_t a3, uint32_t b0, uint32_t b1) {
-  PQ_MMA_ASM(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -101,7 +97,7 @@ __device__ __forceinline__ void mma_16816_f16(float (&c)[4], uint32_t a0, uint32
 }
 __device__ __forceinline__ void mma_16816_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
-  PQ_MMA_ASM(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])

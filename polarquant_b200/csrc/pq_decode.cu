@@ -283,14 +283,11 @@ __device__ __forceinline__ uint32_t hmul2_hi(uint32_t cs, uint32_t rr) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-#ifdef PQ_LDS_NOVOL
-#define PQ_LDS_ASM asm
-#else
-#define PQ_LDS_ASM asm volatile
-#endif
+// The gathers are plain (movable) asm so the compiler may schedule them freely inside a step; the step loop ties
+// them to the table build that precedes it.
 template <int IMM> __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
   uint32_t v;
-  PQ_LDS_ASM("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
   return v;
 }
 
@@ -485,11 +482,7 @@ __device__ __forceinline__ void softmax_step(float (&S)[4], float scale_log2, bo
   // Raising the reference exponent costs a warp-wide reduction and a rescale of O; it is only needed when a
   // logit exceeds it by more than kMaxSlack (any exponent gives the same softmax, the slack only bounds the
   // magnitude of the unnormalised probabilities).  The guarded form always takes the exact maximum.
-#ifdef PQ_EAGER_MAX
-  const bool raise = true;
-#else
   const bool raise = GUARDED || mx0 > st.t0 || mx1 > st.t1;
-#endif
   if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll
     for (int o = 4; o <= 16; o <<= 1) {
@@ -831,27 +824,17 @@ decode_kernel(const DecodeArgs a_in) {
         if (grp < last_grp) stage_group(grp + 1, buf ^ 1);
         build_angle_table<TBITS, QDT>(tbl_addr, s_sc_w + buf * kStageBytes, lane);
         uint32_t tbl_run = tbl_addr;
-#ifdef PQ_LDS_NOVOL
         // the gathers are plain (movable) asm: tie them to this build of the table
         asm volatile("" : "+r"(tbl_run) :: "memory");
-#endif
         load_radius_consts<RBITS, QDT>(s_sc_w + buf * kStageBytes, t, rs2, rc2);
         buf ^= 1;
 #pragma unroll 1
         for (; s < run_end; ++s) {
-#ifdef PQ_PREFETCH_PAIRS
-          // two tiles every second step
-          if (kPrefetch > 0 && ((s - pos) & 1) == 0 && s + kPrefetch < qs_end)
-            prefetch_tiles(s + kPrefetch, min(2, qs_end - s - kPrefetch));
-#else
           if (kPrefetch > 0 && s + kPrefetch < qs_end) prefetch_tiles(s + kPrefetch, 1);
-#endif
           // next tile; the last step of the segment re-reads its own tile rather than branching
           const bool more = s + 1 < qs_end;
           if (more) c_lane += kCodeStep;
-#ifndef PQ_CODES_INPLACE
           const uint4 ng = ldg_stream(c_lane), nh = load_second(c_lane);
-#endif
           if constexpr (kVPipe) {
             if (next_tile < last_tile) { ++next_tile; v_tile += v_step; }
             int fill = vstage + kVStages - 1;
@@ -870,10 +853,6 @@ decode_kernel(const DecodeArgs a_in) {
             qk_step_packed6<RBITS, TBITS>(S, cg, make_uint2(ch.x, ch.y), tbl_run, lane_xor, rs2, rc2, qb);
           else
             qk_step_quant<RBITS, TBITS>(S, cg, ch, tbl_run, lane_xor, rs2, rc2, qb);
-#ifdef PQ_CODES_INPLACE
-          // the code registers are free again: refill them for the next step (its lines are in L2 already)
-          cg = ldg_stream(c_lane); ch = load_second(c_lane);
-#endif
 
           if constexpr (QK_ONLY) {
             // logits (B, N, Nb*G): lane holds tokens (g, g+8) x heads (2t, 2t+1)
@@ -901,9 +880,7 @@ decode_kernel(const DecodeArgs a_in) {
               if (++vstage == kVStages) vstage = 0;
             }
           }
-#ifndef PQ_CODES_INPLACE
           cg = ng; ch = nh;
-#endif
         }
         in_group = 0;
         ++grp;

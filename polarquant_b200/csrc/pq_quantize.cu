@@ -113,9 +113,6 @@ __device__ __noinline__ float2 polar_exact(float x, float y, bool norm_separate)
 // prefill shape), so fp16 - like fp32, where nothing is rounded - stays on the exact routines.
 template <typename T> struct FastPathPays { static constexpr bool value = false; };
 template <> struct FastPathPays<__nv_bfloat16> { static constexpr bool value = true; };
-#ifdef PQ_FAST_FP16
-template <> struct FastPathPays<__half> { static constexpr bool value = true; };
-#endif
 
 // Angle and radius of the four pairs a thread holds of one token, each rounded to T where torch rounds:
 //   phi = RN(atan2f(y, x)); if (phi < 0) phi = RN(phi + wrap);   rad = RN(sqrtf(x^2 + y^2)).

@@ -77,6 +77,16 @@ def test_random_configuration(case):
     assert float(diff.max()) <= ATTN_MAX_ABS and float(diff.mean()) <= ATTN_MEAN_ABS, \
         (float(diff.max()), float(diff.mean()))
 
+    # the 48-byte container holds the same codes: repacked or written directly, attention must not change by a bit
+    if Nb and dt != torch.float32 and (rb, tb) in ((3, 3), (2, 4)) and G % 16 == 0:
+        repacked = pq.keys_repack(packed[0], "packed6")
+        direct = pq.quantize_and_pack_nbit(kq, rb, tb, G, key_format="packed6")
+        assert torch.equal(repacked, direct[0])
+        assert torch.equal(pq.keys_repack(repacked, "byte"), packed[0])
+        got6 = pq.decode_attention(q, kres, repacked, *packed[1:], vv, attention_mask=mask, rbits=rb, tbits=tb,
+                                   key_format="packed6")
+        assert torch.equal(got6, got)
+
     # packed values and device-side lengths over the same random configuration (16-bit caches only)
     if Nb and dt != torch.float32:
         tq = Nb * G
