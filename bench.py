@@ -101,15 +101,30 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
+    _instant_ok = None          # does this driver report power.draw.instant (power.draw is a one-second average)
+
     def __init__(self, index: int):
         self.rows = []
         self.proc = None
         self.index = index
 
+    @classmethod
+    def _has_instant(cls, index: int) -> bool:
+        if cls._instant_ok is None:
+            try:
+                r = subprocess.run(["nvidia-smi", f"--id={index}", "--query-gpu=power.draw.instant",
+                                    "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=20)
+                float(r.stdout.strip().splitlines()[0])
+                cls._instant_ok = r.returncode == 0
+            except Exception:
+                cls._instant_ok = False
+        return cls._instant_ok
+
     def start(self):
         try:
+            fields = self.FIELDS + (",power.draw.instant" if self._has_instant(self.index) else "")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={fields}", "--format=csv,noheader,nounits",
                  "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -139,15 +154,18 @@ class ClockSampler:
                         reasons.add(name)
             except Exception:
                 continue
-        powers = []
+        powers, instant = [], []
         for r in self.rows:
             try:
                 powers.append(float(r[2]))
+                if len(r) > 7:
+                    instant.append(float(r[7]))
             except Exception:
                 continue
         return {"sm_mhz": statistics.median(clocks) if clocks else None,
                 "sm_max_mhz": max(maxes) if maxes else None, "samples": len(clocks), "reasons": sorted(reasons),
-                "power_w_median": statistics.median(powers) if powers else None}
+                "power_w_median": statistics.median(powers) if powers else None,
+                "power_w_instant_median": statistics.median(instant) if instant else None}
 
 
 def make_inputs(args, device, seed):

@@ -5,7 +5,8 @@
  * explicit sizes and strides, and a CUDA stream handle (cudaStream_t passed as
  * void*).  Work is enqueued on that stream and the call returns without
  * synchronising.  The library owns no memory: outputs and scratch are the
- * caller's.  Return value: PQ_OK (0) or a negative pq_status; nothing throws or
+ * caller's (one exception: the peer-mappable exchange buffer of pq_peer_alloc,
+ * freed by pq_peer_free).  Return value: PQ_OK (0) or a negative pq_status; nothing throws or
  * aborts.  Strides are in ELEMENTS of the tensor's dtype.
  *
  * The reference project (ericshwu/PolarQuant) is Python; the interface each
@@ -368,6 +369,47 @@ int pq_merge_lse(const float* outs, const float* lses, int P, int64_t rows, int 
  */
 int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float* lses, int64_t lse_part_stride, int P,
                          int64_t rows, int hd, void* out, int out_dtype, float* lse_out, void* stream);
+
+/*
+ * Sequence split across the GPUs of one node without a library collective: ONE kernel per step pushes this rank's
+ * partial ([out (rows, hd) fp32 | lse (rows) fp32], the block pq_decode_attention writes when out / lse point into it)
+ * into every peer's exchange buffer with plain peer stores over NVLink, waits for the peers' pushes on flag words in
+ * local memory, and merges all partials by log-sum-exp - the same arithmetic, in rank order, as pq_merge_lse_strided
+ * over an all-gathered buffer (bit-identical results).  No counterpart in the reference, which never splits the
+ * sequence (test4long.py:38-43 runs one replica per GPU).
+ *
+ * Every rank owns one exchange buffer of pq_exchange_bytes(world, rows, hd) bytes, created with pq_peer_alloc (the
+ * one allocation this library makes: peer mapping needs an allocation of its own; it is zero-filled, which is the
+ * protocol's initial state), exports its handle (PQ_IPC_HANDLE_BYTES bytes, to be carried to the peers by the host
+ * program, e.g. an all-gather of bytes) and opens the peers' handles with pq_peer_open.  `bufs` lists the `world`
+ * buffers in rank order as seen from this process: bufs[rank] the local one, the others the opened mappings.  The
+ * attention output of the step goes to bufs[rank] + pq_exchange_slot_offset(world, rows, hd, rank).
+ *
+ * pq_exchange_merge enqueues the kernel (grid rows / 4, 128 threads; hd must be 128; world <= PQ_EXCHANGE_MAX_RANKS).
+ * All ranks must call it once per step with the same world / rows; calls on one buffer must not overlap.  The epoch
+ * lives in the buffer, so the call can be captured in a CUDA graph and replayed.  Every wait on a peer is bounded
+ * (about a second): if a peer never arrives the kernel finishes with a wrong result and sets a status bit
+ * (1: a peer did not release the previous step's data, 2: a peer's data did not arrive), which
+ * pq_exchange_status reads back (it synchronises the stream).  Ranks may only leave between steps: free the buffer
+ * (pq_peer_close on the mappings, pq_peer_free on the own one) after all ranks finished their last call.
+ *
+ * pq_exchange_merge_emulated runs all `world` ranks' CTAs in ONE cooperative launch on one GPU over `world` local
+ * buffers (plain allocations of the same layout, zero-filled) - the protocol's test on a single GPU, where separate
+ * launches that wait on one another must not be used.
+ */
+#define PQ_EXCHANGE_MAX_RANKS 8
+#define PQ_IPC_HANDLE_BYTES 64
+int64_t pq_exchange_bytes(int world, int64_t rows, int hd);
+int64_t pq_exchange_slot_offset(int world, int64_t rows, int hd, int rank);
+int pq_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle);
+int pq_peer_open(const unsigned char* handle, void** ptr);
+int pq_peer_close(void* ptr);
+int pq_peer_free(void* ptr);
+int pq_exchange_merge(void* const* bufs, int world, int rank, int64_t rows, int hd, void* out, int out_dtype,
+                      float* lse_out, void* stream);
+int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int hd, void* const* outs, int out_dtype,
+                               float* const* lse_outs, void* stream);
+int pq_exchange_status(const void* local_buf, int world, int64_t rows, int hd, unsigned* status, void* stream);
 
 /*
  * Host-buffer forms: the same operations for callers whose tensors live in host

@@ -19,6 +19,8 @@ PQ_OK = 0
 PQ_QUANT_WRAP_DTYPE = 1
 PQ_QUANT_NORM_FMA = 2
 PQ_VALUES_KIVI, PQ_VALUES_TILED = 0, 1
+PQ_IPC_HANDLE_BYTES = 64
+PQ_EXCHANGE_MAX_RANKS = 8
 PQ_KEYS_BYTE, PQ_KEYS_PACKED6 = 0, 1
 PQ_QUANT_PACK6 = 4
 
@@ -124,6 +126,25 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_merge_lse.argtypes = [_vp, _vp, _int, _i64, _int, _vp, _int, _vp, _vp]
     lib.pq_merge_lse_strided.restype = _int
     lib.pq_merge_lse_strided.argtypes = [_vp, _i64, _vp, _i64, _int, _i64, _int, _vp, _int, _vp, _vp]
+    lib.pq_exchange_bytes.restype = _i64
+    lib.pq_exchange_bytes.argtypes = [_int, _i64, _int]
+    lib.pq_exchange_slot_offset.restype = _i64
+    lib.pq_exchange_slot_offset.argtypes = [_int, _i64, _int, _int]
+    lib.pq_peer_alloc.restype = _int
+    lib.pq_peer_alloc.argtypes = [_i64, ctypes.POINTER(_vp), ctypes.c_char_p]
+    lib.pq_peer_open.restype = _int
+    lib.pq_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(_vp)]
+    lib.pq_peer_close.restype = _int
+    lib.pq_peer_close.argtypes = [_vp]
+    lib.pq_peer_free.restype = _int
+    lib.pq_peer_free.argtypes = [_vp]
+    lib.pq_exchange_merge.restype = _int
+    lib.pq_exchange_merge.argtypes = [ctypes.POINTER(_vp), _int, _int, _i64, _int, _vp, _int, _vp, _vp]
+    lib.pq_exchange_merge_emulated.restype = _int
+    lib.pq_exchange_merge_emulated.argtypes = [ctypes.POINTER(_vp), _int, _i64, _int, ctypes.POINTER(_vp), _int,
+                                               ctypes.POINTER(_vp), _vp]
+    lib.pq_exchange_status.restype = _int
+    lib.pq_exchange_status.argtypes = [_vp, _int, _i64, _int, ctypes.POINTER(ctypes.c_uint), _vp]
     lib.pq_quantize_host.restype = _int
     lib.pq_quantize_host.argtypes = [_vp, _int, _int, _int, _int, _int, _int, _int, _int, ctypes.c_uint,
                                      _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]
@@ -164,7 +185,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 5:
+        if lib.pq_abi_version() != 6:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

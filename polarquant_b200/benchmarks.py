@@ -261,6 +261,8 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
         return q, kres, packed, v, nbytes
 
     def timed(fn):
+        if world > 1:
+            dist.barrier()                             # ranks enter a leg together (the peer-memory waits are bounded)
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
@@ -278,6 +280,8 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
         except Exception:                              # capture not possible: time the eager calls
             torch.cuda.synchronize()
             run, graphed = fn, False
+        if world > 1:
+            dist.barrier()
         for _ in range(5):
             run()
         torch.cuda.synchronize()
@@ -335,6 +339,23 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
         us_merge, _ = timed(lambda: ops.merge_lse_gathered(gathered, world, rows, out_dtype=torch.bfloat16))
         out["sequence"].update(local_attention_us=us_local, all_gather_us=us_gather, merge_us=us_merge,
                                exchange_bytes_per_rank=rows * 129 * 4)
+        # the same step with the exchange done by ONE kernel over NVLink peer memory instead of the all-gather + merge
+        try:
+            ex = pqd.PeerExchange(B, N, device=dev)
+        except Exception as e:                         # raised on every rank alike (see PeerExchange)
+            out["sequence_peer_memory"] = {"unavailable": str(e)[:200]}
+        else:
+            want = pqd.sequence_parallel_decode(q, kres, packed, v)
+            us_p2p, graphed = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex))
+            got = pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex)
+            us_x, _ = timed(lambda: ex.merge(out_dtype=torch.bfloat16))
+            flags = torch.tensor([float(torch.equal(got, want)), float(ex.status() == 0)], device=dev)
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            out["sequence_peer_memory"] = {
+                "us": us_p2p, "aggregate_gbs": agg / us_p2p / 1e3, "cuda_graph": graphed, "exchange_kernel_us": us_x,
+                "collective": "none: one kernel stores the (B*N, 129) fp32 block into every peer, waits on flags, merges",
+                "bit_identical_to_all_gather_path": bool(flags[0].item()), "no_wait_timed_out": bool(flags[1].item())}
+            ex.close()
     del q, kres, packed, v
     return out
 

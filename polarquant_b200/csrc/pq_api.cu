@@ -67,7 +67,7 @@ using namespace pq;
 
 extern "C" {
 
-int pq_abi_version(void) { return 5; }
+int pq_abi_version(void) { return 6; }
 size_t pq_decode_params_size(void) { return sizeof(pq_decode_params); }
 int pq_last_cuda_error(void) { return last_cuda_error(); }
 

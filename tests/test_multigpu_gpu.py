@@ -1,7 +1,9 @@
-"""Sequence-split decode attention over NCCL on 2+ GPUs of one node (skipped on a single-GPU box).
+"""Sequence-split decode attention on 2+ GPUs of one node (skipped on a single-GPU box).
 
-Each rank holds a slice of the keys, runs the fused CUDA kernel on it, all-gathers one (output, log-sum-exp) pair
-per query head and merges with the CUDA merge kernel; the result must equal single-GPU attention over all keys."""
+Each rank holds a slice of the keys and runs the fused CUDA kernel on it; the (output, log-sum-exp) pairs are exchanged
+either by one NCCL all-gather followed by the merge kernel, or by the one-kernel peer-memory exchange
+(`PeerExchange`: plain peer-to-peer stores over NVLink, bounded waits).  Both must equal single-GPU attention
+over all keys, and each other bit for bit."""
 import os
 import sys
 
@@ -38,13 +40,23 @@ def _worker(rank, world, port, queue):
         got = pqd.sequence_parallel_decode(q, kres if owns else None, mine, torch.cat(my_v, dim=2).contiguous(),
                                            out_dtype=torch.float32)
         torch.cuda.synchronize()
-        queue.put((rank, float((got - full).abs().max())))
+        # the same step through the peer-memory exchange, several times on the same buffers
+        ex = pqd.PeerExchange(B, N, device=dev)
+        same = True
+        for _ in range(5):
+            got_p = pqd.sequence_parallel_decode(q, kres if owns else None, mine, torch.cat(my_v, dim=2).contiguous(),
+                                                 out_dtype=torch.float32, exchange=ex)
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(got_p, got))
+        status = ex.status()
+        ex.close()
+        queue.put((rank, float((got - full).abs().max()), same, status))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-def test_sequence_split_over_nccl_equals_single_gpu_attention():
+def test_sequence_split_over_nccl_and_over_peer_memory_equals_single_gpu_attention():
     world = min(torch.cuda.device_count(), 4)
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
@@ -56,5 +68,6 @@ def test_sequence_split_over_nccl_equals_single_gpu_attention():
         p.join(timeout=300)
         assert p.exitcode == 0
     for _ in range(world):
-        _, err = queue.get(timeout=5)
+        _, err, same, status = queue.get(timeout=5)
         assert err <= 8e-3         # bf16 rounding of the probabilities differs between the split and unsplit runs
+        assert same and status == 0
