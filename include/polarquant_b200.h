@@ -373,10 +373,11 @@ int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float
 /*
  * Sequence split across the GPUs of one node without a library collective: ONE kernel per step pushes this rank's
  * partial ([out (rows, hd) fp32 | lse (rows) fp32], the block pq_decode_attention writes when out / lse point into it)
- * into every peer's exchange buffer with plain peer stores over NVLink, waits for the peers' pushes on flag words in
- * local memory, and merges all partials by log-sum-exp - the same arithmetic, in rank order, as pq_merge_lse_strided
- * over an all-gathered buffer (bit-identical results).  No counterpart in the reference, which never splits the
- * sequence (test4long.py:38-43 runs one replica per GPU).
+ * into every peer's exchange buffer with plain peer stores over NVLink, picks up the peers' pushes from local memory
+ * and merges all partials by log-sum-exp - the same arithmetic, in rank order, as pq_merge_lse_strided over an
+ * all-gathered buffer (bit-identical results).  Pushed values travel paired with the step's epoch in 16-byte stores,
+ * so the receiver validates every word by itself and no fence or "ready" flag sits on the critical path.  No
+ * counterpart in the reference, which never splits the sequence (test4long.py:38-43 runs one replica per GPU).
  *
  * Every rank owns one exchange buffer of pq_exchange_bytes(world, rows, hd) bytes, created with pq_peer_alloc (the
  * one allocation this library makes: peer mapping needs an allocation of its own; it is zero-filled, which is the
@@ -385,11 +386,11 @@ int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float
  * buffers in rank order as seen from this process: bufs[rank] the local one, the others the opened mappings.  The
  * attention output of the step goes to bufs[rank] + pq_exchange_slot_offset(world, rows, hd, rank).
  *
- * pq_exchange_merge enqueues the kernel (grid rows / 4, 128 threads; hd must be 128; world <= PQ_EXCHANGE_MAX_RANKS).
- * All ranks must call it once per step with the same world / rows; calls on one buffer must not overlap.  The epoch
- * lives in the buffer, so the call can be captured in a CUDA graph and replayed.  Every wait on a peer is bounded
- * (about a second): if a peer never arrives the kernel finishes with a wrong result and sets a status bit
- * (1: a peer did not release the previous step's data, 2: a peer's data did not arrive), which
+ * pq_exchange_merge enqueues the kernel (grid rows / 4, 128 threads; hd must be 128; world <= PQ_EXCHANGE_MAX_RANKS;
+ * out 16-byte aligned).  All ranks must call it once per step with the same world / rows; calls on one buffer must
+ * not overlap.  The epoch lives in the buffer, so the call can be captured in a CUDA graph and replayed.  Every wait
+ * on a peer is bounded (one second): if a peer never arrives the kernel finishes with a wrong result and sets a
+ * status bit (1: a peer did not consume the data of two steps ago, 2: a peer's data did not arrive), which
  * pq_exchange_status reads back (it synchronises the stream).  Ranks may only leave between steps: free the buffer
  * (pq_peer_close on the mappings, pq_peer_free on the own one) after all ranks finished their last call.
  *

@@ -1059,6 +1059,8 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
   __shared__ float s_acc[kMergeGroups][kHeadTile][kMergeCh];
   __shared__ float s_max[kHeadTile], s_sum[kHeadTile];
 
+  // a dependent of this kernel (the peer-memory exchange of a sequence split) may become resident now
+  asm volatile("griddepcontrol.launch_dependents;");
   // no-op unless launched with programmatic stream serialisation: wait until the attention kernel has
   // completed and its partials are visible
   asm volatile("griddepcontrol.wait;" ::: "memory");

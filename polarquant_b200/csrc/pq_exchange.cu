@@ -1,25 +1,33 @@
 // Sequence-split exchange over NVLink peer memory (sm_100a): one kernel pushes this GPU's partial attention result
-// into every peer's buffer, waits for the peers' pushes and merges all partials by log-sum-exp.  It replaces the
+// into every peer's buffer, picks up the peers' pushes and merges all partials by log-sum-exp.  It replaces the
 // all-gather + merge pair of the sequence split (two launches, one of them a library collective) by one launch whose
-// only remote operations are plain stores into peer memory and two flag words per (peer, row slice).
+// only remote operations are plain stores into peer memory.
 //
-// Every rank owns one exchange buffer of the same layout (float / 32-bit units):
+// The pushed data validates itself: every 16-byte store carries two (value, epoch) pairs, and the receiver polls
+// the words in its own memory until both epochs match (8-byte halves of an aligned 16-byte store arrive whole).  No
+// fence, no separate "data ready" flag and no second round trip sit on the critical path: the latency of the
+// exchange is one store's flight over NVLink plus whatever the ranks' attention kernels are apart.
 //
-//   slots   world x block      block = [out (rows, 128) | lse (rows)], padded to a multiple of 4 floats; slot r holds
-//                              rank r's partial.  A rank's attention kernel writes its own slot of its own buffer.
-//   ready   world x slices     ready[r][s] = epoch once rank r's rows of slice s have landed in THIS buffer
-//   free    world x slices     free[r][s]  = epoch once rank r has finished reading what THIS rank pushed to it
-//   ctrl    4 words            epoch of the last finished call, finished-CTA counter, status bits, unused
+// Every rank owns one exchange buffer of the same layout (32-bit words):
 //
-// CTA s of the kernel owns the row slice s (kRowsPerCta rows) on every rank, so CTAs of one launch never wait on each
-// other - only on the CTA of the same index on the peers - and the protocol needs no grid-wide barrier:
-//   1. wait until every peer released the slice pushed in the previous call (free[p][s] >= epoch - 1, flags in the
-//      local buffer), 2. store the slice into slot `rank` of every peer, 3. system-scope fence, then ready[rank][s] =
-//   epoch on every peer, 4. wait for ready[p][s] == epoch from every peer (local flags), 5. merge the slice from the
-//   local slots, 6. free[rank][s] = epoch on every peer.  The epoch lives in the buffer and is advanced by the last
-//   CTA to finish, so a captured CUDA graph replays the call unchanged.
-// Every wait is bounded (about a second); on expiry the kernel records a status bit and carries on, so that a peer
-// that never arrives leaves a wrong result and a readable status rather than a hung GPU.
+//   own     block                 [out (rows, 128) | lse (rows)] fp32, padded to a multiple of 4: this rank's partial,
+//                                 written in place by its attention kernel
+//   inbox   2 x world x rows*260  per epoch parity and sending rank: rows x 64 stores {v0, e, v1, e} of the output
+//                                 and rows stores {lse, e, 0, e}
+//   free    world x slices        free[r][s] = e once rank r has consumed the slice this rank pushed to it in epoch e
+//   ctrl    4 words               epoch of the last finished call, finished-CTA counter, status bits, unused
+//
+// CTA s owns the row slice s (kRowsPerCta rows) on every rank, so CTAs of one launch never wait on each other - only
+// on the CTA of the same index on the peers - and no grid-wide barrier exists.  Per call (epoch e, parity e & 1):
+//   1. tell every peer that the slice it pushed in epoch e - 1 is consumed (that was the previous launch), and wait
+//      until every peer has consumed what this rank pushed in epoch e - 2 (the inbox slot about to be overwritten);
+//   2. store the slice, paired with e, into this rank's inbox slot on every peer;
+//   3. poll the local inbox slots of the peers until the slice has arrived, merge in rank order with the arithmetic
+//      of the gathered merge (bit-identical results), write the output.
+// The epoch lives in the buffer and is advanced by the last CTA to finish, so a captured CUDA graph replays the call.
+// Every wait is bounded (one second); on expiry the kernel records a status bit and carries on, so that a peer that
+// never arrives leaves a wrong result and a readable status rather than a hung GPU.
+#include <stdlib.h>
 #include <string.h>
 
 #include "pq_common.cuh"
@@ -29,6 +37,7 @@ namespace {
 
 constexpr int kRowsPerCta = 4;
 static_assert(kRowsPerCta * 32 == kHeadDim, "one float4 per thread covers the output rows of a slice");
+constexpr int kInboxRowWords = 2 * kHeadDim + 4;             // 64 + 1 stores of 4 words per row
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // a wait on a peer gives up after one second ...
 constexpr int kSpinLimit = 1 << 24;                          // ... or after this many polls, whichever comes first
 
@@ -37,39 +46,64 @@ struct ExchangeArgs {
   void* out[PQ_EXCHANGE_MAX_RANKS];        // a real launch uses entry `rank` only
   float* lse_out[PQ_EXCHANGE_MAX_RANKS];
   int world, rank;                         // rank < 0: all ranks emulated by one launch, rank = blockIdx.y
-  long long rows, block_f;
+  long long rows, block_f, inbox_words;    // inbox_words: one (parity, sender) slot
   int slices;
 };
 
 inline long long block_floats(long long rows) { return (rows * (kHeadDim + 1) + 3) / 4 * 4; }
 inline int slices_of(long long rows) { return static_cast<int>((rows + kRowsPerCta - 1) / kRowsPerCta); }
+inline long long inbox_slot_words(long long rows) { return rows * kInboxRowWords; }
 inline long long buffer_words(int world, long long rows) {
-  return world * block_floats(rows) + 2ll * world * slices_of(rows) + 4;
+  return block_floats(rows) + 2ll * world * inbox_slot_words(rows) + static_cast<long long>(world) * slices_of(rows) + 4;
 }
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
   unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// true once *flag has reached `want` (epochs only grow; the signed difference tolerates wrap-around)
+__device__ __forceinline__ void st_pairs(float* p, float a, float b, unsigned e) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(__float_as_uint(a)), "r"(e),
+               "r"(__float_as_uint(b)) : "memory");
+}
+__device__ __forceinline__ uint4 ld_pairs(const float* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// true once *flag has reached `want` (epochs only grow; the signed difference tolerates wrap-around)
 __device__ __forceinline__ bool wait_reached(const unsigned* flag, unsigned want) {
-  if (static_cast<int>(ld_acquire_sys(flag) - want) >= 0) return true;
+  if (static_cast<int>(ld_relaxed_sys(flag) - want) >= 0) return true;
   const unsigned long long t0 = global_ns();
   for (int it = 0; it < kSpinLimit; ++it) {
     __nanosleep(100);
-    if (static_cast<int>(ld_acquire_sys(flag) - want) >= 0) return true;
+    if (static_cast<int>(ld_relaxed_sys(flag) - want) >= 0) return true;
     if (global_ns() - t0 > kWaitLimitNs) break;
   }
   return false;
+}
+// the two values of a pushed 16-byte word once both halves carry epoch e; false when the wait ran out
+__device__ __forceinline__ bool wait_pairs(const float* p, unsigned e, float& a, float& b) {
+  uint4 v = ld_pairs(p);
+  if (v.y != e || v.w != e) {
+    const unsigned long long t0 = global_ns();
+    for (int it = 0; it < kSpinLimit; ++it) {
+      v = ld_pairs(p);
+      if (v.y == e && v.w == e) break;
+      if (global_ns() - t0 > kWaitLimitNs) break;
+    }
+  }
+  a = __uint_as_float(v.x); b = __uint_as_float(v.z);
+  return v.y == e && v.w == e;
 }
 
 template <int ODT>
@@ -77,78 +111,89 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
   const int rank = a.rank < 0 ? static_cast<int>(blockIdx.y) : a.rank;
   const int s = blockIdx.x, tid = threadIdx.x;
   float* mine = a.buf[rank];
-  const long long flags0 = a.world * a.block_f;
-  unsigned* ready = reinterpret_cast<unsigned*>(mine) + flags0;
-  unsigned* freed = ready + static_cast<long long>(a.world) * a.slices;
+  const long long inbox0 = a.block_f;
+  const long long free0 = inbox0 + 2ll * a.world * a.inbox_words;
+  unsigned* freed = reinterpret_cast<unsigned*>(mine) + free0;
   unsigned* ctrl = freed + static_cast<long long>(a.world) * a.slices;
   __shared__ unsigned s_epoch;
   if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned*>(ctrl) + 1u;
   __syncthreads();
   const unsigned epoch = s_epoch;
+  const long long slot = static_cast<long long>(epoch & 1u) * a.world;     // inbox slots of this epoch's parity
   const long long r0 = static_cast<long long>(s) * kRowsPerCta;
-  const int nr = static_cast<int>(min(static_cast<long long>(kRowsPerCta), a.rows - r0));
+  const int row = tid >> 5, col = tid & 31;
+  const bool active = r0 + row < a.rows;
+  const long long grow = r0 + row;
 
-  // 1. the peers have consumed what the previous call pushed into their slot `rank`
-  if (tid < a.world && tid != rank && !wait_reached(freed + tid * a.slices + s, epoch - 1u)) atomicOr(ctrl + 2, 1u);
-  __syncthreads();
-
-  // 2. push the slice: 32 float4 per output row, one float per lse row
-  {
-    const float* src = mine + rank * a.block_f;
-    const int row = tid >> 5, col = tid & 31;
-    if (row < nr) {
-      const long long off = (r0 + row) * kHeadDim + 4 * col;
-      const float4 v = *reinterpret_cast<const float4*>(src + off);
-      for (int p = 0; p < a.world; ++p)
-        if (p != rank) *reinterpret_cast<float4*>(a.buf[p] + rank * a.block_f + off) = v;
-    }
-    if (tid < nr) {
-      const long long off = a.rows * kHeadDim + r0 + tid;
-      const float v = src[off];
-      for (int p = 0; p < a.world; ++p)
-        if (p != rank) a.buf[p][rank * a.block_f + off] = v;
-    }
+  // 1. the previous launch consumed the peers' epoch - 1 slices: tell them; and the inbox slot written below was
+  // last used in epoch - 2: the peers must have consumed that
+  if (tid < a.world && tid != rank) {
+    st_relaxed_sys(reinterpret_cast<unsigned*>(a.buf[tid]) + free0 + rank * a.slices + s, epoch - 1u);
+    if (!wait_reached(freed + tid * a.slices + s, epoch - 2u)) atomicOr(ctrl + 2, 1u);
   }
   __syncthreads();
-  // 3. publish: the fence orders every thread's stores (observed through the barrier) before the flags
-  if (tid == 0) {
-    __threadfence_system();
-    for (int p = 0; p < a.world; ++p)
-      if (p != rank)
-        st_release_sys(reinterpret_cast<unsigned*>(a.buf[p]) + flags0 + rank * a.slices + s, epoch);
-  }
-  // 4. the peers' slices have landed here
-  if (tid < a.world && tid != rank && !wait_reached(ready + tid * a.slices + s, epoch)) atomicOr(ctrl + 2, 2u);
-  __syncthreads();
 
-  // 5. merge, in rank order (the same arithmetic as the merge of a gathered buffer).  Remote ranks wrote these lines
-  // into local memory: read them past L1.
-  for (int r = 0; r < nr; ++r) {
-    const long long row = r0 + r;
-    float M = -INFINITY;
-    for (int p = 0; p < a.world; ++p) M = fmaxf(M, __ldcg(mine + p * a.block_f + a.rows * kHeadDim + row));
-    float L = 0.f, acc = 0.f;
+  // launched as a programmatic dependent of the kernel that writes this rank's partial: everything above overlaps
+  // that kernel's tail (a no-op for an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (active) {
+    // 2. push: this thread's four output values (and, once per row, the log-sum-exp), each pair with the epoch
+    const float4 v = *reinterpret_cast<const float4*>(mine + grow * kHeadDim + 4 * col);
+    const float l = mine[a.rows * kHeadDim + grow];
     for (int p = 0; p < a.world; ++p) {
-      const float l = __ldcg(mine + p * a.block_f + a.rows * kHeadDim + row);
-      const float w = l == -INFINITY ? 0.f : __expf(l - M);
-      L += w;
-      acc = fmaf(w, __ldcg(mine + p * a.block_f + row * kHeadDim + tid), acc);
+      if (p == rank) continue;
+      float* dst = a.buf[p] + inbox0 + (slot + rank) * a.inbox_words;
+      st_pairs(dst + grow * 2 * kHeadDim + 8 * col, v.x, v.y, epoch);
+      st_pairs(dst + grow * 2 * kHeadDim + 8 * col + 4, v.z, v.w, epoch);
+      if (col == 0) st_pairs(dst + a.rows * 2 * kHeadDim + grow * 4, l, 0.f, epoch);
     }
-    const float val = acc / L;
-    const long long off = row * kHeadDim + tid;
-    if constexpr (ODT == PQ_F32) static_cast<float*>(a.out[rank])[off] = val;
-    else if constexpr (ODT == PQ_F16) static_cast<__half*>(a.out[rank])[off] = __float2half_rn(val);
-    else static_cast<__nv_bfloat16*>(a.out[rank])[off] = __float2bfloat16_rn(val);
-    if (a.lse_out[rank] && tid == 0) a.lse_out[rank][row] = M + __logf(L);
+
+    // 3. collect the peers' values of this row and these four channels from the local inbox
+    float4 vp[PQ_EXCHANGE_MAX_RANKS];
+    float lp[PQ_EXCHANGE_MAX_RANKS];
+    bool ok = true;
+#pragma unroll
+    for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
+      if (p >= a.world) break;
+      if (p == rank) { vp[p] = v; lp[p] = l; continue; }
+      const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
+      float unused;
+      ok &= wait_pairs(src + a.rows * 2 * kHeadDim + grow * 4, epoch, lp[p], unused);
+      ok &= wait_pairs(src + grow * 2 * kHeadDim + 8 * col, epoch, vp[p].x, vp[p].y);
+      ok &= wait_pairs(src + grow * 2 * kHeadDim + 8 * col + 4, epoch, vp[p].z, vp[p].w);
+    }
+    if (!ok) atomicOr(ctrl + 2, 2u);
+
+    // merge in rank order: the arithmetic of the merge over a gathered buffer, four channels per thread
+    float M = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p)
+      if (p < a.world) M = fmaxf(M, lp[p]);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
+      if (p >= a.world) break;
+      const float w = lp[p] == -INFINITY ? 0.f : __expf(lp[p] - M);
+      L += w;
+      acc.x = fmaf(w, vp[p].x, acc.x); acc.y = fmaf(w, vp[p].y, acc.y);
+      acc.z = fmaf(w, vp[p].z, acc.z); acc.w = fmaf(w, vp[p].w, acc.w);
+    }
+    const float4 val = make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
+    const long long off = grow * kHeadDim + 4 * col;
+    if constexpr (ODT == PQ_F32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(a.out[rank]) + off) = val;
+    } else {
+      constexpr int DT16 = ODT == PQ_F16 ? PQ_F16 : PQ_BF16;
+      *reinterpret_cast<uint2*>(static_cast<char*>(a.out[rank]) + off * 2) =
+          make_uint2(pack2<DT16>(val.x, val.y), pack2<DT16>(val.z, val.w));
+    }
+    if (a.lse_out[rank] && col == 0) a.lse_out[rank][grow] = M + __logf(L);
   }
   __syncthreads();
 
-  // 6. release the peers' slices; the last CTA of this rank advances the epoch
+  // the last CTA of this rank advances the epoch
   if (tid == 0) {
-    for (int p = 0; p < a.world; ++p)
-      if (p != rank)
-        st_release_sys(reinterpret_cast<unsigned*>(a.buf[p]) + flags0 + static_cast<long long>(a.world) * a.slices +
-                           rank * a.slices + s, epoch);
     __threadfence();
     if (atomicAdd(ctrl + 1, 1u) == gridDim.x - 1) {
       ctrl[1] = 0u;
@@ -173,8 +218,20 @@ int launch(const ExchangeArgs& a, int out_dtype, dim3 grid, bool cooperative, cu
   const void* fn = out_dtype == PQ_F16    ? reinterpret_cast<const void*>(exchange_merge_kernel<PQ_F16>)
                    : out_dtype == PQ_BF16 ? reinterpret_cast<const void*>(exchange_merge_kernel<PQ_BF16>)
                                           : reinterpret_cast<const void*>(exchange_merge_kernel<PQ_F32>);
-  if (cooperative) PQ_CUDA_TRY(cudaLaunchCooperativeKernel(fn, grid, dim3(kHeadDim), params, 0, stream));
-  else PQ_CUDA_TRY(cudaLaunchKernel(fn, grid, dim3(kHeadDim), params, 0, stream));
+  if (cooperative) {
+    PQ_CUDA_TRY(cudaLaunchCooperativeKernel(fn, grid, dim3(kHeadDim), params, 0, stream));
+  } else {
+    // programmatic dependent launch: the grid may become resident while the preceding kernel of the stream (the
+    // merge of the attention partials) drains; it waits for that kernel's results on the device
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kHeadDim); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool no_pdl = getenv("POLARQUANT_B200_NO_PDL") != nullptr;   // field switch: plain launches only
+    cfg.attrs = attr; cfg.numAttrs = no_pdl ? 0 : 1;
+    PQ_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, params));
+  }
   return PQ_OK;
 }
 
@@ -192,7 +249,7 @@ int64_t pq_exchange_bytes(int world, int64_t rows, int hd) {
 
 int64_t pq_exchange_slot_offset(int world, int64_t rows, int hd, int rank) {
   if (world < 1 || world > PQ_EXCHANGE_MAX_RANKS || rows <= 0 || hd != kHeadDim || rank < 0 || rank >= world) return -1;
-  return rank * block_floats(rows) * 4;
+  return 0;      // the rank's own partial opens its buffer; the peers' partials arrive in the inbox behind it
 }
 
 int pq_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle) {
@@ -235,10 +292,12 @@ int pq_exchange_merge(void* const* bufs, int world, int rank, int64_t rows, int 
   const int rc = check_common(bufs, world, rows, hd, out_dtype);
   if (rc != PQ_OK) return rc;
   if (rank < 0 || rank >= world || !out) return PQ_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return PQ_ERR_ALIGNMENT;      // four channels per vector store
   ExchangeArgs a{};
   for (int p = 0; p < world; ++p) a.buf[p] = static_cast<float*>(bufs[p]);
   a.out[rank] = out; a.lse_out[rank] = lse_out;
   a.world = world; a.rank = rank; a.rows = rows; a.block_f = block_floats(rows); a.slices = slices_of(rows);
+  a.inbox_words = inbox_slot_words(rows);
   return launch(a, out_dtype, dim3(a.slices), false, static_cast<cudaStream_t>(stream));
 }
 
@@ -250,11 +309,13 @@ int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int h
   ExchangeArgs a{};
   for (int p = 0; p < world; ++p) {
     if (!outs[p]) return PQ_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(outs[p]) & 15) return PQ_ERR_ALIGNMENT;
     a.buf[p] = static_cast<float*>(bufs[p]);
     a.out[p] = outs[p];
     a.lse_out[p] = lse_outs ? lse_outs[p] : nullptr;
   }
   a.world = world; a.rank = -1; a.rows = rows; a.block_f = block_floats(rows); a.slices = slices_of(rows);
+  a.inbox_words = inbox_slot_words(rows);
   // the emulated ranks wait on one another inside one launch: a cooperative launch guarantees that all of its CTAs
   // are resident together (and is refused, not deadlocked, when they cannot be)
   return launch(a, out_dtype, dim3(a.slices, world), true, static_cast<cudaStream_t>(stream));

@@ -83,8 +83,11 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit():
     assert lib.pq_exchange_status(bufs[0].data_ptr(), world, rows, 128, ctypes.byref(word), stream) == 0
     assert time.time() - t0 < 10.0
     assert word.value & 2                        # the peer's data never arrived
-    # rank 0 did push its rows and raise its flag in the peer's buffer
-    assert torch.equal(bufs[1][:rows * 129], slots[0])
+    # rank 0 did push its rows, paired with epoch 1, into its inbox slot (parity 1, sender 0) of the peer's buffer
+    inbox = bufs[1].view(torch.int32)[(rows * 129 + 3) // 4 * 4:]
+    sent = inbox[(1 * world + 0) * rows * 260:][:rows * 256].view(rows * 64, 4)
+    assert bool((sent[:, 1] == 1).all()) and bool((sent[:, 3] == 1).all())
+    assert torch.equal(sent[:, 0::2].reshape(-1).view(torch.float32), slots[0][:rows * 128])
     assert torch.equal(torch.ones(4, device=DEV) + 1, torch.full((4,), 2.0, device=DEV))     # context still works
 
 
