@@ -91,9 +91,10 @@ __device__ __forceinline__ bool wait_reached(const unsigned* flag, unsigned want
   }
   return false;
 }
-// the two values of a pushed 16-byte word once both halves carry epoch e; false when the wait ran out
-__device__ __forceinline__ bool wait_pairs(const float* p, unsigned e, float& a, float& b) {
-  uint4 v = ld_pairs(p);
+// the two values of a pushed 16-byte word once both halves carry epoch e; `v` is a first look at the word taken
+// earlier (all of a thread's first looks are issued together so that their latencies overlap); false when the wait
+// ran out
+__device__ __forceinline__ bool wait_pairs(uint4 v, const float* p, unsigned e, float& a, float& b) {
   if (v.y != e || v.w != e) {
     const unsigned long long t0 = global_ns();
     for (int it = 0; it < kSpinLimit; ++it) {
@@ -148,19 +149,29 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
       if (col == 0) st_pairs(dst + a.rows * 2 * kHeadDim + grow * 4, l, 0.f, epoch);
     }
 
-    // 3. collect the peers' values of this row and these four channels from the local inbox
+    // 3. collect the peers' values of this row and these four channels from the local inbox: a first look at every
+    // word, all loads in flight together, then a bounded wait on whatever has not arrived yet
     float4 vp[PQ_EXCHANGE_MAX_RANKS];
     float lp[PQ_EXCHANGE_MAX_RANKS];
+    uint4 look[PQ_EXCHANGE_MAX_RANKS][3];
+#pragma unroll
+    for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
+      if (p >= a.world || p == rank) continue;
+      const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
+      look[p][0] = ld_pairs(src + a.rows * 2 * kHeadDim + grow * 4);
+      look[p][1] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col);
+      look[p][2] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col + 4);
+    }
     bool ok = true;
 #pragma unroll
     for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
-      if (p >= a.world) break;
+      if (p >= a.world) continue;
       if (p == rank) { vp[p] = v; lp[p] = l; continue; }
       const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
       float unused;
-      ok &= wait_pairs(src + a.rows * 2 * kHeadDim + grow * 4, epoch, lp[p], unused);
-      ok &= wait_pairs(src + grow * 2 * kHeadDim + 8 * col, epoch, vp[p].x, vp[p].y);
-      ok &= wait_pairs(src + grow * 2 * kHeadDim + 8 * col + 4, epoch, vp[p].z, vp[p].w);
+      ok &= wait_pairs(look[p][0], src + a.rows * 2 * kHeadDim + grow * 4, epoch, lp[p], unused);
+      ok &= wait_pairs(look[p][1], src + grow * 2 * kHeadDim + 8 * col, epoch, vp[p].x, vp[p].y);
+      ok &= wait_pairs(look[p][2], src + grow * 2 * kHeadDim + 8 * col + 4, epoch, vp[p].z, vp[p].w);
     }
     if (!ok) atomicOr(ctrl + 2, 2u);
 
@@ -173,7 +184,7 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
-      if (p >= a.world) break;
+      if (p >= a.world) continue;
       const float w = lp[p] == -INFINITY ? 0.f : __expf(lp[p] - M);
       L += w;
       acc.x = fmaf(w, vp[p].x, acc.x); acc.y = fmaf(w, vp[p].y, acc.y);
