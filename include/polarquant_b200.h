@@ -399,6 +399,10 @@ int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float
  * launches that wait on one another must not be used.
  */
 #define PQ_EXCHANGE_MAX_RANKS 8
+/* flag of pq_exchange_merge: the kernel directly before it on the stream is pq_decode_attention's own merge (the call
+   that wrote this rank's block): the exchange is then launched as its programmatic dependent and its prologue overlaps
+   that kernel's tail.  Leave it clear after anything else. */
+#define PQ_EXCHANGE_AFTER_ATTENTION 1u
 #define PQ_IPC_HANDLE_BYTES 64
 int64_t pq_exchange_bytes(int world, int64_t rows, int hd);
 int64_t pq_exchange_slot_offset(int world, int64_t rows, int hd, int rank);
@@ -407,7 +411,7 @@ int pq_peer_open(const unsigned char* handle, void** ptr);
 int pq_peer_close(void* ptr);
 int pq_peer_free(void* ptr);
 int pq_exchange_merge(void* const* bufs, int world, int rank, int64_t rows, int hd, void* out, int out_dtype,
-                      float* lse_out, void* stream);
+                      float* lse_out, unsigned flags, void* stream);
 int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int hd, void* const* outs, int out_dtype,
                                float* const* lse_outs, void* stream);
 int pq_exchange_status(const void* local_buf, int world, int64_t rows, int hd, unsigned* status, void* stream);

@@ -21,6 +21,7 @@ PQ_QUANT_NORM_FMA = 2
 PQ_VALUES_KIVI, PQ_VALUES_TILED = 0, 1
 PQ_IPC_HANDLE_BYTES = 64
 PQ_EXCHANGE_MAX_RANKS = 8
+PQ_EXCHANGE_AFTER_ATTENTION = 1
 PQ_KEYS_BYTE, PQ_KEYS_PACKED6 = 0, 1
 PQ_QUANT_PACK6 = 4
 
@@ -139,7 +140,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_peer_free.restype = _int
     lib.pq_peer_free.argtypes = [_vp]
     lib.pq_exchange_merge.restype = _int
-    lib.pq_exchange_merge.argtypes = [ctypes.POINTER(_vp), _int, _int, _i64, _int, _vp, _int, _vp, _vp]
+    lib.pq_exchange_merge.argtypes = [ctypes.POINTER(_vp), _int, _int, _i64, _int, _vp, _int, _vp, ctypes.c_uint, _vp]
     lib.pq_exchange_merge_emulated.restype = _int
     lib.pq_exchange_merge_emulated.argtypes = [ctypes.POINTER(_vp), _int, _i64, _int, ctypes.POINTER(_vp), _int,
                                                ctypes.POINTER(_vp), _vp]

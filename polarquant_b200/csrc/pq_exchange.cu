@@ -91,22 +91,6 @@ __device__ __forceinline__ bool wait_reached(const unsigned* flag, unsigned want
   }
   return false;
 }
-// the two values of a pushed 16-byte word once both halves carry epoch e; `v` is a first look at the word taken
-// earlier (all of a thread's first looks are issued together so that their latencies overlap); false when the wait
-// ran out
-__device__ __forceinline__ bool wait_pairs(uint4 v, const float* p, unsigned e, float& a, float& b) {
-  if (v.y != e || v.w != e) {
-    const unsigned long long t0 = global_ns();
-    for (int it = 0; it < kSpinLimit; ++it) {
-      v = ld_pairs(p);
-      if (v.y == e && v.w == e) break;
-      if (global_ns() - t0 > kWaitLimitNs) break;
-    }
-  }
-  a = __uint_as_float(v.x); b = __uint_as_float(v.z);
-  return v.y == e && v.w == e;
-}
-
 template <int ODT>
 __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const ExchangeArgs a) {
   const int rank = a.rank < 0 ? static_cast<int>(blockIdx.y) : a.rank;
@@ -149,29 +133,41 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
       if (col == 0) st_pairs(dst + a.rows * 2 * kHeadDim + grow * 4, l, 0.f, epoch);
     }
 
-    // 3. collect the peers' values of this row and these four channels from the local inbox: a first look at every
-    // word, all loads in flight together, then a bounded wait on whatever has not arrived yet
+    // 3. collect the peers' values of this row and these four channels from the local inbox.  One poll looks at
+    // every word (all loads in flight together: one L2 round trip per poll whatever the number of peers) and the
+    // loop ends once each carries this epoch in both halves, or when the time limit is reached.
+    uint4 look[PQ_EXCHANGE_MAX_RANKS][3];
+    bool ok = false;
+    unsigned long long t0 = 0;
+    for (int it = 0; it < kSpinLimit; ++it) {
+      ok = true;
+#pragma unroll
+      for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
+        if (p >= a.world || p == rank) continue;
+        const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
+        look[p][0] = ld_pairs(src + a.rows * 2 * kHeadDim + grow * 4);
+        look[p][1] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col);
+        look[p][2] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col + 4);
+      }
+#pragma unroll
+      for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
+        if (p >= a.world || p == rank) continue;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) ok &= look[p][k].y == epoch && look[p][k].w == epoch;
+      }
+      if (ok) break;
+      if (it == 0) t0 = global_ns();
+      else if (global_ns() - t0 > kWaitLimitNs) break;
+    }
     float4 vp[PQ_EXCHANGE_MAX_RANKS];
     float lp[PQ_EXCHANGE_MAX_RANKS];
-    uint4 look[PQ_EXCHANGE_MAX_RANKS][3];
-#pragma unroll
-    for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
-      if (p >= a.world || p == rank) continue;
-      const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
-      look[p][0] = ld_pairs(src + a.rows * 2 * kHeadDim + grow * 4);
-      look[p][1] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col);
-      look[p][2] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col + 4);
-    }
-    bool ok = true;
 #pragma unroll
     for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
       if (p >= a.world) continue;
       if (p == rank) { vp[p] = v; lp[p] = l; continue; }
-      const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
-      float unused;
-      ok &= wait_pairs(look[p][0], src + a.rows * 2 * kHeadDim + grow * 4, epoch, lp[p], unused);
-      ok &= wait_pairs(look[p][1], src + grow * 2 * kHeadDim + 8 * col, epoch, vp[p].x, vp[p].y);
-      ok &= wait_pairs(look[p][2], src + grow * 2 * kHeadDim + 8 * col + 4, epoch, vp[p].z, vp[p].w);
+      lp[p] = __uint_as_float(look[p][0].x);
+      vp[p] = make_float4(__uint_as_float(look[p][1].x), __uint_as_float(look[p][1].z),
+                          __uint_as_float(look[p][2].x), __uint_as_float(look[p][2].z));
     }
     if (!ok) atomicOr(ctrl + 2, 2u);
 
@@ -204,11 +200,10 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
   __syncthreads();
 
   // the last CTA of this rank advances the epoch
+  // (no fence: the counter only elects the last CTA, and what it writes is read by the next launch)
   if (tid == 0) {
-    __threadfence();
     if (atomicAdd(ctrl + 1, 1u) == gridDim.x - 1) {
       ctrl[1] = 0u;
-      __threadfence();
       *reinterpret_cast<volatile unsigned*>(ctrl) = epoch;
     }
   }
@@ -224,7 +219,7 @@ int check_common(void* const* bufs, int world, long long rows, int hd, int out_d
   return PQ_OK;
 }
 
-int launch(const ExchangeArgs& a, int out_dtype, dim3 grid, bool cooperative, cudaStream_t stream) {
+int launch(const ExchangeArgs& a, int out_dtype, dim3 grid, bool cooperative, bool dependent, cudaStream_t stream) {
   void* params[] = {const_cast<ExchangeArgs*>(&a)};
   const void* fn = out_dtype == PQ_F16    ? reinterpret_cast<const void*>(exchange_merge_kernel<PQ_F16>)
                    : out_dtype == PQ_BF16 ? reinterpret_cast<const void*>(exchange_merge_kernel<PQ_BF16>)
@@ -232,15 +227,16 @@ int launch(const ExchangeArgs& a, int out_dtype, dim3 grid, bool cooperative, cu
   if (cooperative) {
     PQ_CUDA_TRY(cudaLaunchCooperativeKernel(fn, grid, dim3(kHeadDim), params, 0, stream));
   } else {
-    // programmatic dependent launch: the grid may become resident while the preceding kernel of the stream (the
-    // merge of the attention partials) drains; it waits for that kernel's results on the device
+    // programmatic dependent launch, when the caller says the preceding kernel of the stream is the merge of the
+    // attention partials: the grid may become resident while that kernel drains and waits for its results on the
+    // device.  (Behind another exchange kernel it must not be used: the epoch is read before that wait.)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(kHeadDim); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     static const bool no_pdl = getenv("POLARQUANT_B200_NO_PDL") != nullptr;   // field switch: plain launches only
-    cfg.attrs = attr; cfg.numAttrs = no_pdl ? 0 : 1;
+    cfg.attrs = attr; cfg.numAttrs = (dependent && !no_pdl) ? 1 : 0;
     PQ_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, params));
   }
   return PQ_OK;
@@ -299,17 +295,18 @@ int pq_peer_free(void* ptr) {
 }
 
 int pq_exchange_merge(void* const* bufs, int world, int rank, int64_t rows, int hd, void* out, int out_dtype,
-                      float* lse_out, void* stream) {
+                      float* lse_out, unsigned flags, void* stream) {
   const int rc = check_common(bufs, world, rows, hd, out_dtype);
   if (rc != PQ_OK) return rc;
-  if (rank < 0 || rank >= world || !out) return PQ_ERR_INVALID;
+  if (rank < 0 || rank >= world || !out || (flags & ~PQ_EXCHANGE_AFTER_ATTENTION)) return PQ_ERR_INVALID;
   if (reinterpret_cast<uintptr_t>(out) & 15) return PQ_ERR_ALIGNMENT;      // four channels per vector store
   ExchangeArgs a{};
   for (int p = 0; p < world; ++p) a.buf[p] = static_cast<float*>(bufs[p]);
   a.out[rank] = out; a.lse_out[rank] = lse_out;
   a.world = world; a.rank = rank; a.rows = rows; a.block_f = block_floats(rows); a.slices = slices_of(rows);
   a.inbox_words = inbox_slot_words(rows);
-  return launch(a, out_dtype, dim3(a.slices), false, static_cast<cudaStream_t>(stream));
+  return launch(a, out_dtype, dim3(a.slices), false, (flags & PQ_EXCHANGE_AFTER_ATTENTION) != 0,
+                static_cast<cudaStream_t>(stream));
 }
 
 int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int hd, void* const* outs, int out_dtype,
@@ -329,7 +326,7 @@ int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int h
   a.inbox_words = inbox_slot_words(rows);
   // the emulated ranks wait on one another inside one launch: a cooperative launch guarantees that all of its CTAs
   // are resident together (and is refused, not deadlocked, when they cannot be)
-  return launch(a, out_dtype, dim3(a.slices, world), true, static_cast<cudaStream_t>(stream));
+  return launch(a, out_dtype, dim3(a.slices, world), true, false, static_cast<cudaStream_t>(stream));
 }
 
 int pq_exchange_status(const void* local_buf, int world, int64_t rows, int hd, unsigned* status, void* stream) {

@@ -148,8 +148,11 @@ class PeerExchange:
         self.lse_view = flat[self.rows * head_dim:].view(batch, heads)
         self._closed = False
 
-    def merge(self, out_dtype=torch.float32, out: torch.Tensor | None = None) -> torch.Tensor:
-        """Push this rank's slot to the peers, wait for theirs, merge: (B, N, 1, 128) in `out_dtype`."""
+    def merge(self, out_dtype=torch.float32, out: torch.Tensor | None = None,
+              after_attention: bool = False) -> torch.Tensor:
+        """Push this rank's slot to the peers, wait for theirs, merge: (B, N, 1, 128) in `out_dtype`.
+        `after_attention`: the call directly follows the ``decode_attention`` that wrote the slot, on the same
+        stream - the kernel is then launched as a programmatic dependent of that call's merge."""
         from . import _lib
         from .ops import _DT, _on_device, _stream
         if out is None:
@@ -158,7 +161,9 @@ class PeerExchange:
             raise ValueError("out must be contiguous, of out_dtype, with batch * heads * 128 elements")
         with _on_device(self.device):
             rc = self._lib.pq_exchange_merge(self._bufs, self.world, self.rank, self.rows, 128, out.data_ptr(),
-                                             _DT[out_dtype], None, _stream(self.device))
+                                             _DT[out_dtype], None,
+                                             _lib.PQ_EXCHANGE_AFTER_ATTENTION if after_attention else 0,
+                                             _stream(self.device))
         _lib.check(rc, "pq_exchange_merge")
         return out
 
@@ -220,14 +225,15 @@ def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, att
         lse_view = mine[rows * hd:].view(b, n)
     have_q = packed is not None and packed[0] is not None and packed[0].shape[2] > 0
     have_r = kres is not None and kres.shape[2] > 0
-    if not have_q and not have_r:                        # a rank without keys: weight zero in the merge
+    attended = have_q or have_r
+    if not attended:                                     # a rank without keys: weight zero in the merge
         out_view.zero_()
         lse_view.fill_(float("-inf"))
     else:
         ops.decode_attention(q, kres if have_r else None, *(packed if have_q else (None,) * 5), v,
                              out_dtype=torch.float32, out=out_view, lse_out=lse_view, **kw)
     if exchange is not None:
-        return exchange.merge(out_dtype=out_dtype or q.dtype)
+        return exchange.merge(out_dtype=out_dtype or q.dtype, after_attention=attended)
     gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=q.device)
     dist.all_gather_into_tensor(gathered, mine, group=group)
     return ops.merge_lse_gathered(gathered, world, rows, out_dtype=out_dtype or q.dtype, out_shape=(b, n, 1, hd))

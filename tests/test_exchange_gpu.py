@@ -77,7 +77,7 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit():
     arr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     t0 = time.time()
-    rc = lib.pq_exchange_merge(arr, world, 0, rows, 128, out.data_ptr(), ops._DT[torch.float32], None, stream)
+    rc = lib.pq_exchange_merge(arr, world, 0, rows, 128, out.data_ptr(), ops._DT[torch.float32], None, 0, stream)
     assert rc == 0, lib.pq_strerror(rc)
     word = ctypes.c_uint(0)
     assert lib.pq_exchange_status(bufs[0].data_ptr(), world, rows, 128, ctypes.byref(word), stream) == 0
@@ -99,6 +99,6 @@ def test_argument_validation():
     assert lib.pq_exchange_slot_offset(2, 4, 128, 2) == -1
     buf = torch.zeros(4096, dtype=torch.float32, device=DEV)
     arr = (ctypes.c_void_p * 2)(buf.data_ptr(), None)
-    assert lib.pq_exchange_merge(arr, 2, 0, 4, 128, buf.data_ptr(), 2, None, None) == -1
+    assert lib.pq_exchange_merge(arr, 2, 0, 4, 128, buf.data_ptr(), 2, None, 0, None) == -1
     arr = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr() + 4)
-    assert lib.pq_exchange_merge(arr, 2, 0, 4, 128, buf.data_ptr(), 2, None, None) == -5
+    assert lib.pq_exchange_merge(arr, 2, 0, 4, 128, buf.data_ptr(), 2, None, 0, None) == -5
