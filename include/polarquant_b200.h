@@ -282,6 +282,15 @@ typedef struct pq_decode_params {
      PQ_KEYS_PACKED6 (48 bytes per token, see pq_keys_repack; rbits + tbits must be 6: 3/3 or 2/4; 16-bit caches
      with qk_dtype == v_dtype).  A unit then holds Nb * G * 48 contiguous bytes. */
   int key_format;
+  /* Sequence split over peer memory (pq_exchange_merge below): with exchange_world > 0 the merge that ends this call
+     also stores every result row, paired with the exchange's epoch, into the inboxes of the peers - the push of
+     pq_exchange_merge done by the producer, so that the transfer is in flight before the exchange kernel starts; call
+     pq_exchange_merge with PQ_EXCHANGE_PUSHED afterwards.  exchange_bufs: the `world` exchange buffers in rank order
+     as this process sees them (host array, read during the call); out must be exchange_bufs[exchange_rank] (fp32,
+     dense (B N, 128)), lse must be out + B * N * 128.  Zero / NULL: off. */
+  void* const* exchange_bufs;
+  int exchange_world;
+  int exchange_rank;
 } pq_decode_params;
 
 int pq_decode_attention(const pq_decode_params* p, void* stream);
@@ -403,6 +412,9 @@ int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float
    that wrote this rank's block): the exchange is then launched as its programmatic dependent and its prologue overlaps
    that kernel's tail.  Leave it clear after anything else. */
 #define PQ_EXCHANGE_AFTER_ATTENTION 1u
+/* flag of pq_exchange_merge: this rank's block was already pushed to the peers by the pq_decode_attention call that
+   wrote it (pq_decode_params.exchange_bufs); the kernel then only collects and merges. */
+#define PQ_EXCHANGE_PUSHED 2u
 #define PQ_IPC_HANDLE_BYTES 64
 int64_t pq_exchange_bytes(int world, int64_t rows, int hd);
 int64_t pq_exchange_slot_offset(int world, int64_t rows, int hd, int rank);
@@ -413,7 +425,7 @@ int pq_peer_free(void* ptr);
 int pq_exchange_merge(void* const* bufs, int world, int rank, int64_t rows, int hd, void* out, int out_dtype,
                       float* lse_out, unsigned flags, void* stream);
 int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int hd, void* const* outs, int out_dtype,
-                               float* const* lse_outs, void* stream);
+                               float* const* lse_outs, unsigned flags, void* stream);
 int pq_exchange_status(const void* local_buf, int world, int64_t rows, int hd, unsigned* status, void* stream);
 
 /*

@@ -22,6 +22,7 @@ PQ_VALUES_KIVI, PQ_VALUES_TILED = 0, 1
 PQ_IPC_HANDLE_BYTES = 64
 PQ_EXCHANGE_MAX_RANKS = 8
 PQ_EXCHANGE_AFTER_ATTENTION = 1
+PQ_EXCHANGE_PUSHED = 2
 PQ_KEYS_BYTE, PQ_KEYS_PACKED6 = 0, 1
 PQ_QUANT_PACK6 = 4
 
@@ -64,6 +65,7 @@ class DecodeParams(ctypes.Structure):
         ("vbits", _int),
         ("dyn_lengths", _vp), ("dyn_r_add", _int),
         ("key_format", _int),
+        ("exchange_bufs", ctypes.POINTER(_vp)), ("exchange_world", _int), ("exchange_rank", _int),
     ]
 
 
@@ -143,7 +145,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pq_exchange_merge.argtypes = [ctypes.POINTER(_vp), _int, _int, _i64, _int, _vp, _int, _vp, ctypes.c_uint, _vp]
     lib.pq_exchange_merge_emulated.restype = _int
     lib.pq_exchange_merge_emulated.argtypes = [ctypes.POINTER(_vp), _int, _i64, _int, ctypes.POINTER(_vp), _int,
-                                               ctypes.POINTER(_vp), _vp]
+                                               ctypes.POINTER(_vp), ctypes.c_uint, _vp]
     lib.pq_exchange_status.restype = _int
     lib.pq_exchange_status.argtypes = [_vp, _int, _i64, _int, ctypes.POINTER(ctypes.c_uint), _vp]
     lib.pq_quantize_host.restype = _int
@@ -186,7 +188,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 6:
+        if lib.pq_abi_version() != 7:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

@@ -43,7 +43,7 @@
 
 #include <mutex>
 
-#include "pq_common.cuh"
+#include "pq_exchange.cuh"
 
 namespace pq {
 namespace {
@@ -1050,7 +1050,7 @@ static_assert(kMergeGroups == kHeadTile, "each thread group finishes one head");
 template <int ODT>
 __global__ void __launch_bounds__(kMergeCh * kMergeGroups)
 merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_sb, int64_t o_sh,
-                      float* __restrict__ lse) {
+                      float* __restrict__ lse, const __grid_constant__ PushArgs px) {
   DecodeArgs a = a_in;
   if (a.dyn) plan_on_device(a);
   constexpr int kThreadsM = kMergeCh * kMergeGroups;
@@ -1083,6 +1083,7 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
       else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(0.f);
       else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(0.f);
       if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + hh] = -INFINITY;
+      if (px.world > 0) push_row_value(px, static_cast<long long>(b) * a.N + head0 + hh, ch, 0.f, -INFINITY);
     }
     return;
   }
@@ -1231,7 +1232,10 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
     if constexpr (ODT == PQ_F32) static_cast<float*>(out)[off] = val;
     else if constexpr (ODT == PQ_F16) static_cast<__half*>(out)[off] = __float2half_rn(val);
     else static_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
-    if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + h] = (s_max[h] + log2f(l)) * 0.6931471805599453f;
+    const float lse_val = (s_max[h] + log2f(l)) * 0.6931471805599453f;
+    if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + h] = lse_val;
+    // sequence split over peer memory: the row goes straight into the peers' inboxes, paired with the epoch
+    if (px.world > 0) push_row_value(px, static_cast<long long>(b) * a.N + head0 + h, ch, val, lse_val);
   }
 }
 
@@ -1419,6 +1423,21 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   if (!p->q || !p->out || (!p->v && !(packed_v && p->R == 0))) return PQ_ERR_INVALID;
   if (p->Nb > 0 && (!p->codes || !p->rscale || !p->rmn || !p->tscale || !p->tmn)) return PQ_ERR_INVALID;
   if (p->R > 0 && !p->k_res) return PQ_ERR_INVALID;
+  // Sequence split over peer memory: the merge pushes the result rows into the peers' exchange buffers.  The result
+  // itself must then be this rank's block of its own buffer: fp32 rows (B N, 128) at its start, log-sum-exps behind.
+  PushArgs px{};
+  if (p->exchange_world > 0) {
+    const long long rows = static_cast<long long>(p->B) * p->N;
+    const int rc = exchange_push_args(reinterpret_cast<const void* const*>(p->exchange_bufs), p->exchange_world,
+                                      p->exchange_rank, rows, &px);
+    if (rc != PQ_OK) return rc;
+    if (p->out_dtype != PQ_F32 || p->out != p->exchange_bufs[p->exchange_rank] || !p->lse ||
+        p->lse != static_cast<float*>(p->out) + rows * kHeadDim || p->out_stride_h != kHeadDim ||
+        p->out_stride_b != static_cast<int64_t>(p->N) * kHeadDim)
+      return PQ_ERR_INVALID;
+  } else if (p->exchange_world < 0) {
+    return PQ_ERR_INVALID;
+  }
   const int qes = static_cast<int>(dtype_bytes(p->qk_dtype));
   auto mis = [](const void* ptr, size_t al) { return reinterpret_cast<uintptr_t>(ptr) % al != 0; };
   // 128-bit loads: pointers 16-byte aligned, strides multiples of 16 bytes
@@ -1499,9 +1518,9 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   int64_t osb = p->out_stride_b, osh = p->out_stride_h;
   float* lse_ptr = p->lse;
   switch (p->out_dtype) {
-    case PQ_F16: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_F16>, a, out_ptr, osb, osh, lse_ptr)); break;
-    case PQ_BF16: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_BF16>, a, out_ptr, osb, osh, lse_ptr)); break;
-    default: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_F32>, a, out_ptr, osb, osh, lse_ptr)); break;
+    case PQ_F16: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_F16>, a, out_ptr, osb, osh, lse_ptr, px)); break;
+    case PQ_BF16: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_BF16>, a, out_ptr, osb, osh, lse_ptr, px)); break;
+    default: PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel<PQ_F32>, a, out_ptr, osb, osh, lse_ptr, px)); break;
   }
   return PQ_OK;
 }

@@ -30,14 +30,13 @@
 #include <stdlib.h>
 #include <string.h>
 
-#include "pq_common.cuh"
+#include "pq_exchange.cuh"
 
 namespace pq {
 namespace {
 
-constexpr int kRowsPerCta = 4;
+constexpr int kRowsPerCta = kExchangeRowsPerCta;
 static_assert(kRowsPerCta * 32 == kHeadDim, "one float4 per thread covers the output rows of a slice");
-constexpr int kInboxRowWords = 2 * kHeadDim + 4;             // 64 + 1 stores of 4 words per row
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // a wait on a peer gives up after one second ...
 constexpr int kSpinLimit = 1 << 24;                          // ... or after this many polls, whichever comes first
 
@@ -48,14 +47,13 @@ struct ExchangeArgs {
   int world, rank;                         // rank < 0: all ranks emulated by one launch, rank = blockIdx.y
   long long rows, block_f, inbox_words;    // inbox_words: one (parity, sender) slot
   int slices;
+  int pushed;                              // the producer of this rank's block already pushed it to the peers
 };
 
-inline long long block_floats(long long rows) { return (rows * (kHeadDim + 1) + 3) / 4 * 4; }
-inline int slices_of(long long rows) { return static_cast<int>((rows + kRowsPerCta - 1) / kRowsPerCta); }
-inline long long inbox_slot_words(long long rows) { return rows * kInboxRowWords; }
-inline long long buffer_words(int world, long long rows) {
-  return block_floats(rows) + 2ll * world * inbox_slot_words(rows) + static_cast<long long>(world) * slices_of(rows) + 4;
-}
+inline long long block_floats(long long rows) { return exchange_block_floats(rows); }
+inline int slices_of(long long rows) { return exchange_slices(rows); }
+inline long long inbox_slot_words(long long rows) { return exchange_inbox_words(rows); }
+inline long long buffer_words(int world, long long rows) { return exchange_buffer_words(world, rows); }
 
 __device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
   unsigned v;
@@ -126,7 +124,7 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
     const float4 v = *reinterpret_cast<const float4*>(mine + grow * kHeadDim + 4 * col);
     const float l = mine[a.rows * kHeadDim + grow];
     for (int p = 0; p < a.world; ++p) {
-      if (p == rank) continue;
+      if (p == rank || a.pushed) continue;
       float* dst = a.buf[p] + inbox0 + (slot + rank) * a.inbox_words;
       st_pairs(dst + grow * 2 * kHeadDim + 8 * col, v.x, v.y, epoch);
       st_pairs(dst + grow * 2 * kHeadDim + 8 * col + 4, v.z, v.w, epoch);
@@ -208,6 +206,25 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
     }
   }
 }
+
+}  // namespace
+
+int exchange_push_args(const void* const* bufs, int world, int rank, long long rows, PushArgs* px) {
+  if (!bufs || !px || world < 1 || world > PQ_EXCHANGE_MAX_RANKS || rank < 0 || rank >= world || rows <= 0)
+    return PQ_ERR_INVALID;
+  *px = PushArgs{};
+  for (int p = 0; p < world; ++p) {
+    if (!bufs[p]) return PQ_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(bufs[p]) & 15) return PQ_ERR_ALIGNMENT;
+    px->inbox[p] = static_cast<float*>(const_cast<void*>(bufs[p])) + block_floats(rows) + rank * inbox_slot_words(rows);
+  }
+  px->ctrl = static_cast<const unsigned*>(bufs[rank]) + buffer_words(world, rows) - 4;
+  px->parity_stride = world * inbox_slot_words(rows);
+  px->rows = rows; px->world = world; px->rank = rank;
+  return PQ_OK;
+}
+
+namespace {
 
 int check_common(void* const* bufs, int world, long long rows, int hd, int out_dtype) {
   if (!bufs || world < 1 || world > PQ_EXCHANGE_MAX_RANKS || rows <= 0 || hd != kHeadDim) return PQ_ERR_INVALID;
@@ -298,22 +315,24 @@ int pq_exchange_merge(void* const* bufs, int world, int rank, int64_t rows, int 
                       float* lse_out, unsigned flags, void* stream) {
   const int rc = check_common(bufs, world, rows, hd, out_dtype);
   if (rc != PQ_OK) return rc;
-  if (rank < 0 || rank >= world || !out || (flags & ~PQ_EXCHANGE_AFTER_ATTENTION)) return PQ_ERR_INVALID;
+  if (rank < 0 || rank >= world || !out || (flags & ~(PQ_EXCHANGE_AFTER_ATTENTION | PQ_EXCHANGE_PUSHED)))
+    return PQ_ERR_INVALID;
   if (reinterpret_cast<uintptr_t>(out) & 15) return PQ_ERR_ALIGNMENT;      // four channels per vector store
   ExchangeArgs a{};
   for (int p = 0; p < world; ++p) a.buf[p] = static_cast<float*>(bufs[p]);
   a.out[rank] = out; a.lse_out[rank] = lse_out;
   a.world = world; a.rank = rank; a.rows = rows; a.block_f = block_floats(rows); a.slices = slices_of(rows);
   a.inbox_words = inbox_slot_words(rows);
+  a.pushed = (flags & PQ_EXCHANGE_PUSHED) != 0;
   return launch(a, out_dtype, dim3(a.slices), false, (flags & PQ_EXCHANGE_AFTER_ATTENTION) != 0,
                 static_cast<cudaStream_t>(stream));
 }
 
 int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int hd, void* const* outs, int out_dtype,
-                               float* const* lse_outs, void* stream) {
+                               float* const* lse_outs, unsigned flags, void* stream) {
   const int rc = check_common(bufs, world, rows, hd, out_dtype);
   if (rc != PQ_OK) return rc;
-  if (!outs) return PQ_ERR_INVALID;
+  if (!outs || (flags & ~PQ_EXCHANGE_PUSHED)) return PQ_ERR_INVALID;
   ExchangeArgs a{};
   for (int p = 0; p < world; ++p) {
     if (!outs[p]) return PQ_ERR_INVALID;
@@ -324,6 +343,7 @@ int pq_exchange_merge_emulated(void* const* bufs, int world, int64_t rows, int h
   }
   a.world = world; a.rank = -1; a.rows = rows; a.block_f = block_floats(rows); a.slices = slices_of(rows);
   a.inbox_words = inbox_slot_words(rows);
+  a.pushed = (flags & PQ_EXCHANGE_PUSHED) != 0;
   // the emulated ranks wait on one another inside one launch: a cooperative launch guarantees that all of its CTAs
   // are resident together (and is refused, not deadlocked, when they cannot be)
   return launch(a, out_dtype, dim3(a.slices, world), true, false, static_cast<cudaStream_t>(stream));

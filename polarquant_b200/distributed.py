@@ -149,10 +149,11 @@ class PeerExchange:
         self._closed = False
 
     def merge(self, out_dtype=torch.float32, out: torch.Tensor | None = None,
-              after_attention: bool = False) -> torch.Tensor:
+              after_attention: bool = False, pushed: bool = False) -> torch.Tensor:
         """Push this rank's slot to the peers, wait for theirs, merge: (B, N, 1, 128) in `out_dtype`.
         `after_attention`: the call directly follows the ``decode_attention`` that wrote the slot, on the same
-        stream - the kernel is then launched as a programmatic dependent of that call's merge."""
+        stream - the kernel is then launched as a programmatic dependent of that call's merge.
+        `pushed`: that ``decode_attention`` call was given ``push_to=self`` and has pushed the slot already."""
         from . import _lib
         from .ops import _DT, _on_device, _stream
         if out is None:
@@ -162,8 +163,8 @@ class PeerExchange:
         with _on_device(self.device):
             rc = self._lib.pq_exchange_merge(self._bufs, self.world, self.rank, self.rows, 128, out.data_ptr(),
                                              _DT[out_dtype], None,
-                                             _lib.PQ_EXCHANGE_AFTER_ATTENTION if after_attention else 0,
-                                             _stream(self.device))
+                                             (_lib.PQ_EXCHANGE_AFTER_ATTENTION if after_attention else 0)
+                                             | (_lib.PQ_EXCHANGE_PUSHED if pushed else 0), _stream(self.device))
         _lib.check(rc, "pq_exchange_merge")
         return out
 
@@ -195,7 +196,7 @@ class PeerExchange:
 
 
 def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, attend=None, merge=None, exchange=None,
-                             **kw):
+                             push_in_attention=True, **kw):
     """Decode attention with the keys split along the sequence across the ranks of `group`.
 
     Each rank passes ITS slice: `packed` = codes/scales of its token groups (or None), `kres` = the residual keys on
@@ -205,7 +206,9 @@ def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, att
     With the default CUDA entry points the step is four launches: the attention kernel and its merge write this
     rank's fp32 output and log-sum-exp straight into one exchange block [out (B N, 128) | lse (B N)], one
     all-gather moves every rank's block, and one merge kernel reads the gathered buffer in place.  With
-    ``exchange=PeerExchange(batch, heads, group)`` the last two become one kernel over NVLink peer memory.
+    ``exchange=PeerExchange(batch, heads, group)`` the attention's own merge also stores the block into the peers'
+    buffers over NVLink, and one kernel collects the peers' blocks and merges (``push_in_attention=False``: that
+    kernel does the stores itself).
     """
     if attend is not None or merge is not None:          # injected compute (CPU tests): the generic path
         out, lse = local_partial(q, kres, packed, v, attend=attend, **kw)
@@ -231,9 +234,11 @@ def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, att
         lse_view.fill_(float("-inf"))
     else:
         ops.decode_attention(q, kres if have_r else None, *(packed if have_q else (None,) * 5), v,
-                             out_dtype=torch.float32, out=out_view, lse_out=lse_view, **kw)
+                             out_dtype=torch.float32, out=out_view, lse_out=lse_view,
+                             push_to=exchange if push_in_attention else None, **kw)
     if exchange is not None:
-        return exchange.merge(out_dtype=out_dtype or q.dtype, after_attention=attended)
+        return exchange.merge(out_dtype=out_dtype or q.dtype, after_attention=attended,
+                              pushed=attended and push_in_attention)
     gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=q.device)
     dist.all_gather_into_tensor(gathered, mine, group=group)
     return ops.merge_lse_gathered(gathered, world, rows, out_dtype=out_dtype or q.dtype, out_shape=(b, n, 1, hd))

@@ -280,7 +280,8 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
                      sm_scale: float | None = None, out_dtype: torch.dtype | None = None,
                      return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0,
                      mid_event=None, value_codes=None, value_scale=None, value_mn=None, vbits: int = 4,
-                     key_format: str = "byte", out: torch.Tensor | None = None, lse_out: torch.Tensor | None = None):
+                     key_format: str = "byte", out: torch.Tensor | None = None, lse_out: torch.Tensor | None = None,
+                     push_to=None):
     """One fused decode-attention step over the polar cache.
 
     Computes what the reference's decode branch computes with separate ops
@@ -307,6 +308,10 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
 
     ``out`` (B, N, 1, 128) / ``lse_out`` (B, N) fp32: write the results into these tensors instead of new ones
     (``out`` may have any batch / head strides with a dense last dimension; ``lse_out`` must be contiguous).
+
+    ``push_to``: a ``distributed.PeerExchange``; the results are written to its ``out_view`` / ``lse_view`` and the
+    merge that ends the call also stores every row into the peers' exchange buffers (sequence split over peer
+    memory: follow with ``push_to.merge(after_attention=True, pushed=True)``).
     """
     dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask, value_codes)
     bsz, nq, qlen, hd = query_states.shape
@@ -415,6 +420,10 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
     p.B, p.N, p.Nk, p.Nb, p.G, p.R, p.hd = bsz, nq, kvh, nb, grp, res, hd
     p.rbits, p.tbits = rbits, tbits
     p.key_format = _KEY_FORMATS[key_format]
+    if push_to is not None:
+        if out is not push_to.out_view or lse_out is not push_to.lse_view:
+            raise ValueError("push_to: pass the exchange's out_view / lse_view as out / lse_out")
+        p.exchange_bufs, p.exchange_world, p.exchange_rank = push_to._bufs, push_to.world, push_to.rank
     p.qk_dtype, p.v_dtype, p.out_dtype = qdt, vdt, _DT[out_dtype]
     p.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
     p.num_ctas = num_ctas

@@ -52,7 +52,7 @@ def test_emulated_ranks_reproduce_the_gathered_merge_bit_for_bit(world, rows, ou
         rc = lib.pq_exchange_merge_emulated(arr, world, rows, 128,
                                             (ctypes.c_void_p * world)(*[o.data_ptr() for o in outs]),
                                             ops._DT[out_dtype],
-                                            (ctypes.c_void_p * world)(*[t.data_ptr() for t in lses]), stream)
+                                            (ctypes.c_void_p * world)(*[t.data_ptr() for t in lses]), 0, stream)
         assert rc == 0, lib.pq_strerror(rc)
         torch.cuda.synchronize()
         for r in range(world):
@@ -63,6 +63,82 @@ def test_emulated_ranks_reproduce_the_gathered_merge_bit_for_bit(world, rows, ou
         m = gathered[:, rows * 128:].max(dim=0).values
         ref_lse = m + torch.log(torch.exp(gathered[:, rows * 128:] - m).sum(dim=0))
         assert torch.allclose(lses[0], ref_lse, atol=1e-5, rtol=1e-5)
+
+
+class _LocalExchange:
+    """The attributes `decode_attention(push_to=...)` reads from a PeerExchange, over buffers of one GPU."""
+
+    def __init__(self, bufs, rank, batch, heads):
+        self.world, self.rank = len(bufs), rank
+        self._bufs = (ctypes.c_void_p * len(bufs))(*[b.data_ptr() for b in bufs])
+        rows = batch * heads
+        self.out_view = bufs[rank][:rows * 128].view(batch, heads, 1, 128)
+        self.lse_view = bufs[rank][rows * 128: rows * 129].view(batch, heads)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_attention_pushes_its_rows_and_the_exchange_only_collects(world):
+    """Producer-side push: every emulated rank runs the fused attention on its slice of the keys with
+    `push_to` set - its merge stores the rows, paired with the epoch, into the other ranks' inboxes - and the
+    exchange kernel, told that the rows are pushed, only collects and merges.  Three steps on the same buffers;
+    bitwise equal to the merge of the gathered blocks and within the bar of attention over all keys."""
+    import polarquant_b200 as pq
+    from polarquant_b200 import _lib, ops
+    from polarquant_b200 import distributed as pqd
+    from oracle import polar_oracle as oracle
+    lib = _lib.load()
+    B, N, Nk, Nb, G, R = 2, 8, 2, 6, 64, 20
+    rows = B * N
+    bufs, _ = _buffers(lib, world, rows)
+    ranks = [_LocalExchange(bufs, r, B, N) for r in range(world)]
+    arr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for step in range(3):
+        keys = oracle.synth_keys(B, Nk, Nb * G + R, 128, torch.bfloat16, seed=300 + step, device=DEV)
+        g = torch.Generator(device=DEV).manual_seed(310 + step)
+        q = torch.randn(B, N, 1, 128, device=DEV, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, Nk, Nb * G + R, 128, device=DEV, generator=g).to(torch.bfloat16)
+        packed = pq.quantize_and_pack_nbit(keys[:, :, :Nb * G].contiguous(), 4, 4, G)
+        kres = keys[:, :, Nb * G:].contiguous()
+        full = pq.decode_attention(q, kres, *packed, v, out_dtype=torch.float32)
+        for r, ex in enumerate(ranks):
+            g0, g1, owns = pqd.split_sequence(Nb, R, r, world)
+            mine = [t[:, :, g0:g1].contiguous() for t in packed]
+            my_v = torch.cat([v[:, :, g0 * G:g1 * G]] + ([v[:, :, Nb * G:]] if owns else []), dim=2).contiguous()
+            pq.decode_attention(q, kres if owns else None, *mine, my_v, out_dtype=torch.float32, out=ex.out_view,
+                                lse_out=ex.lse_view, push_to=ex)
+        gathered = torch.stack([b[:rows * 129] for b in bufs]).reshape(-1).clone()
+        want = ops.merge_lse_gathered(gathered, world, rows, out_dtype=torch.float32)
+        outs = [torch.full((rows, 128), float("nan"), device=DEV) for _ in range(world)]
+        rc = lib.pq_exchange_merge_emulated(arr, world, rows, 128,
+                                            (ctypes.c_void_p * world)(*[o.data_ptr() for o in outs]),
+                                            ops._DT[torch.float32], None, _lib.PQ_EXCHANGE_PUSHED, stream)
+        assert rc == 0, lib.pq_strerror(rc)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(outs[r], want), f"step {step}, rank {r}"
+            word = ctypes.c_uint(7)
+            assert lib.pq_exchange_status(bufs[r].data_ptr(), world, rows, 128, ctypes.byref(word), stream) == 0
+            assert word.value == 0
+        assert float((outs[0].view(B, N, 1, 128) - full).abs().max()) <= 8e-3
+
+
+def test_push_arguments_are_validated():
+    import polarquant_b200 as pq
+    from polarquant_b200 import _lib
+    from oracle import polar_oracle as oracle
+    lib = _lib.load()
+    B, N, Nk = 1, 4, 1
+    bufs, _ = _buffers(lib, 2, B * N)
+    ex = _LocalExchange(bufs, 0, B, N)
+    keys = oracle.synth_keys(B, Nk, 64, 128, torch.bfloat16, seed=5, device=DEV)
+    q = torch.randn(B, N, 1, 128, device=DEV).to(torch.bfloat16)
+    v = torch.randn(B, Nk, 64, 128, device=DEV).to(torch.bfloat16)
+    with pytest.raises(ValueError):        # results must go to the exchange's own views
+        pq.decode_attention(q, keys, None, None, None, None, None, v, out_dtype=torch.float32, push_to=ex)
+    with pytest.raises(ValueError):        # the own block is fp32
+        pq.decode_attention(q, keys, None, None, None, None, None, v, out_dtype=torch.bfloat16, out=ex.out_view,
+                            lse_out=ex.lse_view, push_to=ex)
 
 
 def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit():
