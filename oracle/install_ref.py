@@ -1,6 +1,6 @@
 """Recipe that puts the reference's own files for the key-cache path next to the oracle, untouched.
 
-    python oracle/install_ref.py [/path/to/PolarQuant-checkout]      (default: $POLARQUANT_REFERENCE, /root/reference)
+    python oracle/install_ref.py [/path/to/PolarQuant-checkout]      (default: $POLARQUANT_REFERENCE, else the checkout beside the home directory's repository)
 
 Test infrastructure, like everything under ``oracle/``: the copies land in ``oracle/_ref/`` (listed in
 ``.gitignore``, so they never enter the history, and imported by nothing in the ``polarquant_b200`` package).  They

@@ -129,16 +129,16 @@ class PeerExchange:
                     self._ptrs[r] = peer.value
                     opened.append(peer.value)
             torch.cuda.synchronize(self.device)
-            verdicts = [None] * self.world
-            dist.all_gather_object(verdicts, rc, group=group)
-            if failed or any(code != 0 for code in verdicts):
+            mapped = [None] * self.world
+            dist.all_gather_object(mapped, rc, group=group)
+            if failed or any(code != 0 for code in mapped):
                 for ptr in opened:
                     self._lib.pq_peer_close(ptr)
                 dist.barrier(group=group)
                 if mine.value:
                     self._lib.pq_peer_free(mine.value)
                 raise RuntimeError(f"PeerExchange: peer memory unavailable (allocation status per rank "
-                                   f"{[code for code, _ in handles]}, mapping status per rank {verdicts})")
+                                   f"{[code for code, _ in handles]}, mapping status per rank {mapped})")
         dist.barrier(group=group)          # every buffer exists, is zeroed and is mapped before anyone stores into it
         self._bufs = (ctypes.c_void_p * self.world)(*self._ptrs)
         slot = self._lib.pq_exchange_slot_offset(self.world, self.rows, head_dim, self.rank)
