@@ -86,18 +86,31 @@ def decode_sweep(only: str | None = None):
             for G in (128, 32):
                 R = 128
                 Nb = (ctx - R) // G
-                q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.bfloat16)
-                v = torch.randn(B, Nk, ctx, 128, device=dev, generator=g).to(torch.bfloat16)
-                kres = torch.randn(B, Nk, R, 128, device=dev, generator=g).to(torch.bfloat16)
-                keys = torch.randn(B, Nk, Nb * G, 128, device=dev, generator=g).to(torch.bfloat16)
-                packed = ops.quantize_and_pack_nbit(keys, rb, tb, G)
-                del keys
-                us = _time_us(lambda: ops.decode_attention(q, kres, *packed, v, rbits=rb, tbits=tb), reps=20)
+
+                def one_set():
+                    q = torch.randn(B, N, 1, 128, device=dev, generator=g).to(torch.bfloat16)
+                    v = torch.randn(B, Nk, ctx, 128, device=dev, generator=g).to(torch.bfloat16)
+                    kres = torch.randn(B, Nk, R, 128, device=dev, generator=g).to(torch.bfloat16)
+                    keys = torch.randn(B, Nk, Nb * G, 128, device=dev, generator=g).to(torch.bfloat16)
+                    return q, kres, ops.quantize_and_pack_nbit(keys, rb, tb, G), v
+
+                sets = [one_set()]
+                q, kres, packed, v = sets[0]
                 nbytes = (packed[0].numel() + 4 * packed[1].numel() * 2 + kres.numel() * 2 + v.numel() * 2
                           + q.numel() * 4)
+                # a footprint below 512 MB is rotated over four input sets, so that no launch finds its
+                # predecessor's lines in the 126 MB L2
+                while nbytes < 512e6 and len(sets) < 4:
+                    sets.append(one_set())
+
+                def step():
+                    for q_, kres_, packed_, v_ in sets:
+                        ops.decode_attention(q_, kres_, *packed_, v_, rbits=rb, tbits=tb)
+
+                us = _time_us(step, reps=20) / len(sets)
                 print(json.dumps({"bench": "decode", "shape": name, "bits": f"{rb}/{tb}", "group": G, "us": us,
-                                  "mb": nbytes / 1e6, "gbs": nbytes / us / 1e3}))
-                del packed, v
+                                  "mb": nbytes / 1e6, "gbs": nbytes / us / 1e3, "input_sets_rotated": len(sets)}))
+                del sets, packed, v, q, kres
 
 
 def packed_keys():
@@ -307,22 +320,34 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
         return float(tot.item())
 
     out = {"shape": f"batch {B}, {N} q / {Nk} kv heads, ctx {ctx}, polar 4/4, group {G}, bf16", "n_gpus": world}
+    # A rank's share below 512 MB (8 GPUs: 340 MB) is rotated over four input sets, so that no launch finds its
+    # predecessor's lines in the 126 MB L2; the criterion is the same on every rank.
+    copies = 4 if B * Nk * ctx * 324 / world < 512e6 else 1
+    out["input_sets_rotated"] = copies
+
+    def over(sets, call):
+        return lambda: [call(*s[:4]) for s in sets]
+
     # --- kv heads over ranks ---
     h0, h1 = pqd.shard_range(Nk, rank, world)
-    q, kres, packed, v, nbytes = build(h1 - h0, (h1 - h0) * (N // Nk), Nb, R)
-    us, graphed = timed(lambda: ops.decode_attention(q, kres, *packed, v))
-    agg = total(nbytes)
+    sets = [build(h1 - h0, (h1 - h0) * (N // Nk), Nb, R) for _ in range(copies)]
+    us, graphed = timed(over(sets, lambda q, kres, packed, v: ops.decode_attention(q, kres, *packed, v)))
+    us /= copies
+    agg = total(sets[0][4])
     out["heads"] = {"us": us, "aggregate_gbs": agg / us / 1e3, "aggregate_mb": agg / 1e6, "collective": "none",
                     "cuda_graph": graphed}
-    del q, kres, packed, v
+    del sets
 
     # --- sequence over ranks ---
     g0, g1, owns = pqd.split_sequence(Nb, R, rank, world)
-    q, kres, packed, v, nbytes = build(Nk, N, g1 - g0, R if owns else 0)
+    sets = [build(Nk, N, g1 - g0, R if owns else 0) for _ in range(copies)]
     if world > 1:
-        dist.broadcast(q, 0)                           # one query for all ranks
-    us, graphed = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v) if world > 1
-                        else ops.decode_attention(q, kres, *packed, v))
+        for s_ in sets:
+            dist.broadcast(s_[0], 0)                   # one query for all ranks
+    q, kres, packed, v, nbytes = sets[0]
+    us, graphed = timed(over(sets, (lambda q, kres, packed, v: pqd.sequence_parallel_decode(q, kres, packed, v))
+                             if world > 1 else (lambda q, kres, packed, v: ops.decode_attention(q, kres, *packed, v))))
+    us /= copies
     agg = total(nbytes)
     out["sequence"] = {"us": us, "aggregate_gbs": agg / us / 1e3, "aggregate_mb": agg / 1e6,
                        "collective": "one all_gather of (B*N, 129) fp32 per rank, merged in place by one kernel", "cuda_graph": graphed}
@@ -333,23 +358,27 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
         mine = torch.zeros(rows * 129, dtype=torch.float32, device=dev)
         gathered = torch.zeros(world * rows * 129, dtype=torch.float32, device=dev)
         o_view, l_view = mine[:rows * 128].view(B, N, 1, 128), mine[rows * 128:].view(B, N)
-        us_local, _ = timed(lambda: ops.decode_attention(q, kres, *packed, v, out_dtype=torch.float32, out=o_view,
-                                                         lse_out=l_view))
+        us_local, _ = timed(over(sets, lambda q, kres, packed, v: ops.decode_attention(
+            q, kres, *packed, v, out_dtype=torch.float32, out=o_view, lse_out=l_view)))
+        us_local /= copies
         us_gather, _ = timed(lambda: dist.all_gather_into_tensor(gathered, mine))
         us_merge, _ = timed(lambda: ops.merge_lse_gathered(gathered, world, rows, out_dtype=torch.bfloat16))
         out["sequence"].update(local_attention_us=us_local, all_gather_us=us_gather, merge_us=us_merge,
                                exchange_bytes_per_rank=rows * 129 * 4)
-        # the same step with the exchange done by ONE kernel over NVLink peer memory instead of the all-gather + merge
+        # the same step with the exchange done over NVLink peer memory instead of the all-gather + merge
         try:
             ex = pqd.PeerExchange(B, N, device=dev)
         except Exception as e:                         # raised on every rank alike (see PeerExchange)
             out["sequence_peer_memory"] = {"unavailable": str(e)[:200]}
         else:
             want = pqd.sequence_parallel_decode(q, kres, packed, v)
-            us_p2p, graphed = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex))
+            us_p2p, graphed = timed(over(sets, lambda q, kres, packed, v: pqd.sequence_parallel_decode(
+                q, kres, packed, v, exchange=ex)))
+            us_p2p /= copies
             got = pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex)
-            us_kp, _ = timed(lambda: pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex,
-                                                                  push_in_attention=False))
+            us_kp, _ = timed(over(sets, lambda q, kres, packed, v: pqd.sequence_parallel_decode(
+                q, kres, packed, v, exchange=ex, push_in_attention=False)))
+            us_kp /= copies
             got_kp = pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex, push_in_attention=False)
             us_x, _ = timed(lambda: ex.merge(out_dtype=torch.bfloat16))
             flags = torch.tensor([float(torch.equal(got, want) and torch.equal(got_kp, want)),
@@ -362,7 +391,7 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
                               "epoch, into every peer; one kernel collects the peers' blocks and merges",
                 "bit_identical_to_all_gather_path": bool(flags[0].item()), "no_wait_timed_out": bool(flags[1].item())}
             ex.close()
-    del q, kres, packed, v
+    del sets, q, kres, packed, v
     return out
 
 
