@@ -178,3 +178,67 @@ def test_argument_validation():
     assert lib.pq_exchange_merge(arr, 2, 0, 4, 128, buf.data_ptr(), 2, None, 0, None) == -1
     arr = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr() + 4)
     assert lib.pq_exchange_merge(arr, 2, 0, 4, 128, buf.data_ptr(), 2, None, 0, None) == -5
+
+
+def _single_rank_worker(port, queue):
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    try:
+        import polarquant_b200 as pq
+        from polarquant_b200 import distributed as pqd
+        from oracle import polar_oracle as oracle
+        B, N, Nk, Nb, G, R = 2, 8, 2, 3, 128, 40
+        keys = oracle.synth_keys(B, Nk, Nb * G + R, 128, torch.bfloat16, seed=41).to(dev)
+        g = torch.Generator().manual_seed(42)
+        q = torch.randn(B, N, 1, 128, generator=g).to(torch.bfloat16).to(dev)
+        v = torch.randn(B, Nk, Nb * G + R, 128, generator=g).to(torch.bfloat16).to(dev)
+        packed = pq.quantize_and_pack_nbit(keys[:, :, :Nb * G].contiguous(), 4, 4, G)
+        kres = keys[:, :, Nb * G:].contiguous()
+        full = pq.decode_attention(q, kres, *packed, v, out_dtype=torch.float32)
+        ex = pqd.PeerExchange(B, N, device=dev)
+        same = True
+        for push in (True, False, True):
+            got = pqd.sequence_parallel_decode(q, kres, packed, v, out_dtype=torch.float32, exchange=ex,
+                                               push_in_attention=push)
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(got, full))
+        # the step captured in a CUDA graph and replayed (the epoch lives on the device)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            pqd.sequence_parallel_decode(q, kres, packed, v, out_dtype=torch.float32, exchange=ex)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = pqd.sequence_parallel_decode(q, kres, packed, v, out_dtype=torch.float32, exchange=ex)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(captured, full))
+        status = ex.status()
+        ex.close()
+        queue.put((same, status))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_exchange_object_with_a_single_rank():
+    """The host class end to end on one GPU (a group of one rank has no peers): allocation through the library, the
+    views torch gets over it, both push variants, CUDA-graph replay, status and release.  With one rank the merged
+    result is the rank's own partial, i.e. plain attention, bit for bit."""
+    import os
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    proc = ctx.Process(target=_single_rank_worker, args=(35500 + os.getpid() % 2000, queue))
+    proc.start()
+    proc.join(timeout=300)
+    assert proc.exitcode == 0
+    same, status = queue.get(timeout=5)
+    assert same and status == 0
