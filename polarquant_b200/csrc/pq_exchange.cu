@@ -24,6 +24,11 @@
 //   2. store the slice, paired with e, into this rank's inbox slot on every peer;
 //   3. poll the local inbox slots of the peers until the slice has arrived, merge in rank order with the arithmetic
 //      of the gathered merge (bit-identical results), write the output.
+// Step 2 is normally done by the producer instead: the merge kernel that ends the attention call stores each result
+// value as a {v, e} pair into the peers' inboxes as it writes it locally (push_row_value, pq_exchange.cuh), and this
+// kernel is told so (PQ_EXCHANGE_PUSHED).  Those stores need no "consumed" check of their own: the slot of epoch e
+// was last read by the peer's call of epoch e - 2, which had ended before the peer produced the rows of e - 1 that
+// this rank's call of e - 1 waited for.
 // The epoch lives in the buffer and is advanced by the last CTA to finish, so a captured CUDA graph replays the call.
 // Every wait is bounded (one second); on expiry the kernel records a status bit and carries on, so that a peer that
 // never arrives leaves a wrong result and a readable status rather than a hung GPU.
