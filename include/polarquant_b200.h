@@ -291,6 +291,14 @@ typedef struct pq_decode_params {
   void* const* exchange_bufs;
   int exchange_world;
   int exchange_rank;
+  /* With exchange_out set the merge that ends this call does the whole exchange: after pushing its rows it waits
+     (bounded) for the peers' rows in this rank's own buffer, merges them in rank order and writes the final result
+     (B N, 128) of exchange_out_dtype to exchange_out (and its log-sum-exp to exchange_lse_out unless NULL); no
+     pq_exchange_merge follows on this rank.  A rank that has no keys in a step calls pq_exchange_merge instead (after
+     writing zeros / -inf to its block); the two forms interoperate. */
+  void* exchange_out;
+  int exchange_out_dtype;
+  float* exchange_lse_out;
 } pq_decode_params;
 
 int pq_decode_attention(const pq_decode_params* p, void* stream);
@@ -399,7 +407,7 @@ int pq_merge_lse_strided(const float* outs, int64_t out_part_stride, const float
  * out 16-byte aligned).  All ranks must call it once per step with the same world / rows; calls on one buffer must
  * not overlap.  The epoch lives in the buffer, so the call can be captured in a CUDA graph and replayed.  Every wait
  * on a peer is bounded (one second): if a peer never arrives the kernel finishes with a wrong result and sets a
- * status bit (1: a peer did not consume the data of two steps ago, 2: a peer's data did not arrive), which
+ * status bit (2: a peer's data did not arrive), which
  * pq_exchange_status reads back (it synchronises the stream).  Ranks may only leave between steps: free the buffer
  * (pq_peer_close on the mappings, pq_peer_free on the own one) after all ranks finished their last call.
  *

@@ -66,6 +66,7 @@ class DecodeParams(ctypes.Structure):
         ("dyn_lengths", _vp), ("dyn_r_add", _int),
         ("key_format", _int),
         ("exchange_bufs", ctypes.POINTER(_vp)), ("exchange_world", _int), ("exchange_rank", _int),
+        ("exchange_out", _vp), ("exchange_out_dtype", _int), ("exchange_lse_out", _vp),
     ]
 
 
@@ -188,7 +189,7 @@ def load() -> ctypes.CDLL:
                 "Run `make -C polarquant_b200/csrc` (needs nvcc); there is no CPU fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
-        if lib.pq_abi_version() != 7:
+        if lib.pq_abi_version() != 8:
             raise RuntimeError("polarquant_b200: library ABI version does not match this package")
         if lib.pq_decode_params_size() != ctypes.sizeof(DecodeParams):
             raise RuntimeError("polarquant_b200: pq_decode_params layout differs between library and binding")

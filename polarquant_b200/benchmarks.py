@@ -376,19 +376,24 @@ def long_context_legs(dev, rank: int, world: int, reps: int = 30) -> dict:
                 q, kres, packed, v, exchange=ex)))
             us_p2p /= copies
             got = pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex)
+            us_pp, _ = timed(over(sets, lambda q, kres, packed, v: pqd.sequence_parallel_decode(
+                q, kres, packed, v, exchange=ex, collect_in_attention=False)))
+            us_pp /= copies
+            got_pp = pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex, collect_in_attention=False)
             us_kp, _ = timed(over(sets, lambda q, kres, packed, v: pqd.sequence_parallel_decode(
                 q, kres, packed, v, exchange=ex, push_in_attention=False)))
             us_kp /= copies
             got_kp = pqd.sequence_parallel_decode(q, kres, packed, v, exchange=ex, push_in_attention=False)
             us_x, _ = timed(lambda: ex.merge(out_dtype=torch.bfloat16))
-            flags = torch.tensor([float(torch.equal(got, want) and torch.equal(got_kp, want)),
+            flags = torch.tensor([float(torch.equal(got, want) and torch.equal(got_kp, want) and torch.equal(got_pp, want)),
                                   float(ex.status() == 0)], device=dev)
             dist.all_reduce(flags, op=dist.ReduceOp.MIN)
             out["sequence_peer_memory"] = {
                 "us": us_p2p, "aggregate_gbs": agg / us_p2p / 1e3, "cuda_graph": graphed,
-                "us_with_the_push_in_the_exchange_kernel": us_kp, "exchange_kernel_us": us_x,
+                "us_with_a_separate_collecting_kernel": us_pp,
+                "us_with_the_push_in_that_kernel_too": us_kp, "exchange_kernel_us": us_x,
                 "collective": "none: the attention's merge stores the (B*N, 129) fp32 block, paired with the step's "
-                              "epoch, into every peer; one kernel collects the peers' blocks and merges",
+                              "epoch, into every peer, collects the peers' blocks from local memory and merges",
                 "bit_identical_to_all_gather_path": bool(flags[0].item()), "no_wait_timed_out": bool(flags[1].item())}
             ex.close()
     del sets, q, kres, packed, v

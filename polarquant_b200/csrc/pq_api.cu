@@ -67,7 +67,7 @@ using namespace pq;
 
 extern "C" {
 
-int pq_abi_version(void) { return 7; }
+int pq_abi_version(void) { return 8; }
 size_t pq_decode_params_size(void) { return sizeof(pq_decode_params); }
 int pq_last_cuda_error(void) { return last_cuda_error(); }
 
@@ -326,6 +326,7 @@ int pq_decode_attention_host(const pq_decode_params* hp, void* staging, size_t s
   d.num_ctas = 0;
   d.mid_event = nullptr;
   d.exchange_bufs = nullptr; d.exchange_world = 0; d.exchange_rank = 0;      // device-buffer feature only
+  d.exchange_out = nullptr; d.exchange_lse_out = nullptr;
 
   PQ_CUDA_TRY(cudaMemcpyAsync(dq, hp->q, q_b, cudaMemcpyHostToDevice, s));
   if (Nb > 0) {

@@ -1085,6 +1085,10 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
       if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + hh] = -INFINITY;
       if (px.world > 0) push_row_value(px, static_cast<long long>(b) * a.N + head0 + hh, ch, 0.f, -INFINITY);
     }
+    if (px.world > 0) {
+      __syncthreads();
+      if (threadIdx.x == 0) finish_exchange_cta(px, gridDim.x * gridDim.y);
+    }
     return;
   }
   const long long first = unit * a.slots_per_unit, last = first + a.slots_per_unit - 1;
@@ -1236,6 +1240,10 @@ merge_partials_kernel(const DecodeArgs a_in, void* __restrict__ out, int64_t o_s
     if (lse && ch == 0) lse[static_cast<int64_t>(b) * a.N + head0 + h] = lse_val;
     // sequence split over peer memory: the row goes straight into the peers' inboxes, paired with the epoch
     if (px.world > 0) push_row_value(px, static_cast<long long>(b) * a.N + head0 + h, ch, val, lse_val);
+  }
+  if (px.world > 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) finish_exchange_cta(px, gridDim.x * gridDim.y);
   }
 }
 
@@ -1428,13 +1436,18 @@ int decode_attention_device(const pq_decode_params* p, cudaStream_t stream) {
   PushArgs px{};
   if (p->exchange_world > 0) {
     const long long rows = static_cast<long long>(p->B) * p->N;
-    const int rc = exchange_push_args(reinterpret_cast<const void* const*>(p->exchange_bufs), p->exchange_world,
+    const int rc = exchange_push_args(p->exchange_bufs, p->exchange_world,
                                       p->exchange_rank, rows, &px);
     if (rc != PQ_OK) return rc;
     if (p->out_dtype != PQ_F32 || p->out != p->exchange_bufs[p->exchange_rank] || !p->lse ||
         p->lse != static_cast<float*>(p->out) + rows * kHeadDim || p->out_stride_h != kHeadDim ||
         p->out_stride_b != static_cast<int64_t>(p->N) * kHeadDim)
       return PQ_ERR_INVALID;
+    if (p->exchange_out) {                     // the merge also collects the peers' rows and writes the final result
+      if (!dtype_ok(p->exchange_out_dtype)) return PQ_ERR_INVALID;
+      px.collect = 1;
+      px.final_out = p->exchange_out; px.final_lse = p->exchange_lse_out; px.final_dtype = p->exchange_out_dtype;
+    }
   } else if (p->exchange_world < 0) {
     return PQ_ERR_INVALID;
   }

@@ -14,21 +14,19 @@
 //                                 written in place by its attention kernel
 //   inbox   2 x world x rows*260  per epoch parity and sending rank: rows x 64 stores {v0, e, v1, e} of the output
 //                                 and rows stores {lse, e, 0, e}
-//   free    world x slices        free[r][s] = e once rank r has consumed the slice this rank pushed to it in epoch e
 //   ctrl    4 words               epoch of the last finished call, finished-CTA counter, status bits, unused
 //
 // CTA s owns the row slice s (kRowsPerCta rows) on every rank, so CTAs of one launch never wait on each other - only
 // on the CTA of the same index on the peers - and no grid-wide barrier exists.  Per call (epoch e, parity e & 1):
-//   1. tell every peer that the slice it pushed in epoch e - 1 is consumed (that was the previous launch), and wait
-//      until every peer has consumed what this rank pushed in epoch e - 2 (the inbox slot about to be overwritten);
-//   2. store the slice, paired with e, into this rank's inbox slot on every peer;
-//   3. poll the local inbox slots of the peers until the slice has arrived, merge in rank order with the arithmetic
+//   1. store the slice, paired with e, into this rank's inbox slot on every peer;
+//   2. poll the local inbox slots of the peers until the slice has arrived, merge in rank order with the arithmetic
 //      of the gathered merge (bit-identical results), write the output.
-// Step 2 is normally done by the producer instead: the merge kernel that ends the attention call stores each result
+// No "slot consumed" handshake is needed before a slot is overwritten: the slot of epoch e was last read by the peer's
+// call of epoch e - 2, and that call had ended before the peer produced the rows of epoch e - 1, which this rank's
+// call of epoch e - 1 waited for before it ended.  (It does rely on the calls of one rank being ordered on a stream.)
+// Step 1 is normally done by the producer instead: the merge kernel that ends the attention call stores each result
 // value as a {v, e} pair into the peers' inboxes as it writes it locally (push_row_value, pq_exchange.cuh), and this
-// kernel is told so (PQ_EXCHANGE_PUSHED).  Those stores need no "consumed" check of their own: the slot of epoch e
-// was last read by the peer's call of epoch e - 2, which had ended before the peer produced the rows of e - 1 that
-// this rank's call of e - 1 waited for.
+// kernel is told so (PQ_EXCHANGE_PUSHED).
 // The epoch lives in the buffer and is advanced by the last CTA to finish, so a captured CUDA graph replays the call.
 // Every wait is bounded (one second); on expiry the kernel records a status bit and carries on, so that a peer that
 // never arrives leaves a wrong result and a readable status rather than a hung GPU.
@@ -42,8 +40,8 @@ namespace {
 
 constexpr int kRowsPerCta = kExchangeRowsPerCta;
 static_assert(kRowsPerCta * 32 == kHeadDim, "one float4 per thread covers the output rows of a slice");
-constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // a wait on a peer gives up after one second ...
-constexpr int kSpinLimit = 1 << 24;                          // ... or after this many polls, whichever comes first
+constexpr unsigned long long kWaitLimitNs = kExchangeWaitLimitNs;
+constexpr int kSpinLimit = kExchangeSpinLimit;
 
 struct ExchangeArgs {
   float* buf[PQ_EXCHANGE_MAX_RANKS];
@@ -60,49 +58,13 @@ inline int slices_of(long long rows) { return exchange_slices(rows); }
 inline long long inbox_slot_words(long long rows) { return exchange_inbox_words(rows); }
 inline long long buffer_words(int world, long long rows) { return exchange_buffer_words(world, rows); }
 
-__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
-  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void st_pairs(float* p, float a, float b, unsigned e) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(__float_as_uint(a)), "r"(e),
-               "r"(__float_as_uint(b)) : "memory");
-}
-__device__ __forceinline__ uint4 ld_pairs(const float* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// true once *flag has reached `want` (epochs only grow; the signed difference tolerates wrap-around)
-__device__ __forceinline__ bool wait_reached(const unsigned* flag, unsigned want) {
-  if (static_cast<int>(ld_relaxed_sys(flag) - want) >= 0) return true;
-  const unsigned long long t0 = global_ns();
-  for (int it = 0; it < kSpinLimit; ++it) {
-    __nanosleep(100);
-    if (static_cast<int>(ld_relaxed_sys(flag) - want) >= 0) return true;
-    if (global_ns() - t0 > kWaitLimitNs) break;
-  }
-  return false;
-}
 template <int ODT>
 __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const ExchangeArgs a) {
   const int rank = a.rank < 0 ? static_cast<int>(blockIdx.y) : a.rank;
   const int s = blockIdx.x, tid = threadIdx.x;
   float* mine = a.buf[rank];
   const long long inbox0 = a.block_f;
-  const long long free0 = inbox0 + 2ll * a.world * a.inbox_words;
-  unsigned* freed = reinterpret_cast<unsigned*>(mine) + free0;
-  unsigned* ctrl = freed + static_cast<long long>(a.world) * a.slices;
+  unsigned* ctrl = reinterpret_cast<unsigned*>(mine) + inbox0 + 2ll * a.world * a.inbox_words;
   __shared__ unsigned s_epoch;
   if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned*>(ctrl) + 1u;
   __syncthreads();
@@ -113,30 +75,22 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
   const bool active = r0 + row < a.rows;
   const long long grow = r0 + row;
 
-  // 1. the previous launch consumed the peers' epoch - 1 slices: tell them; and the inbox slot written below was
-  // last used in epoch - 2: the peers must have consumed that
-  if (tid < a.world && tid != rank) {
-    st_relaxed_sys(reinterpret_cast<unsigned*>(a.buf[tid]) + free0 + rank * a.slices + s, epoch - 1u);
-    if (!wait_reached(freed + tid * a.slices + s, epoch - 2u)) atomicOr(ctrl + 2, 1u);
-  }
-  __syncthreads();
-
   // launched as a programmatic dependent of the kernel that writes this rank's partial: everything above overlaps
   // that kernel's tail (a no-op for an ordinary launch)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (active) {
-    // 2. push: this thread's four output values (and, once per row, the log-sum-exp), each pair with the epoch
+    // 1. push: this thread's four output values (and, once per row, the log-sum-exp), each pair with the epoch
     const float4 v = *reinterpret_cast<const float4*>(mine + grow * kHeadDim + 4 * col);
     const float l = mine[a.rows * kHeadDim + grow];
     for (int p = 0; p < a.world; ++p) {
       if (p == rank || a.pushed) continue;
       float* dst = a.buf[p] + inbox0 + (slot + rank) * a.inbox_words;
-      st_pairs(dst + grow * 2 * kHeadDim + 8 * col, v.x, v.y, epoch);
-      st_pairs(dst + grow * 2 * kHeadDim + 8 * col + 4, v.z, v.w, epoch);
-      if (col == 0) st_pairs(dst + a.rows * 2 * kHeadDim + grow * 4, l, 0.f, epoch);
+      push_pairs(dst + grow * 2 * kHeadDim + 8 * col, v.x, v.y, epoch);
+      push_pairs(dst + grow * 2 * kHeadDim + 8 * col + 4, v.z, v.w, epoch);
+      if (col == 0) push_pairs(dst + a.rows * 2 * kHeadDim + grow * 4, l, 0.f, epoch);
     }
 
-    // 3. collect the peers' values of this row and these four channels from the local inbox.  One poll looks at
+    // 2. collect the peers' values of this row and these four channels from the local inbox.  One poll looks at
     // every word (all loads in flight together: one L2 round trip per poll whatever the number of peers) and the
     // loop ends once each carries this epoch in both halves, or when the time limit is reached.
     uint4 look[PQ_EXCHANGE_MAX_RANKS][3];
@@ -148,9 +102,9 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
       for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
         if (p >= a.world || p == rank) continue;
         const float* src = mine + inbox0 + (slot + p) * a.inbox_words;
-        look[p][0] = ld_pairs(src + a.rows * 2 * kHeadDim + grow * 4);
-        look[p][1] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col);
-        look[p][2] = ld_pairs(src + grow * 2 * kHeadDim + 8 * col + 4);
+        look[p][0] = look_pairs(src + a.rows * 2 * kHeadDim + grow * 4);
+        look[p][1] = look_pairs(src + grow * 2 * kHeadDim + 8 * col);
+        look[p][2] = look_pairs(src + grow * 2 * kHeadDim + 8 * col + 4);
       }
 #pragma unroll
       for (int p = 0; p < PQ_EXCHANGE_MAX_RANKS; ++p) {
@@ -159,8 +113,8 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
         for (int k = 0; k < 3; ++k) ok &= look[p][k].y == epoch && look[p][k].w == epoch;
       }
       if (ok) break;
-      if (it == 0) t0 = global_ns();
-      else if (global_ns() - t0 > kWaitLimitNs) break;
+      if (it == 0) t0 = exchange_ns();
+      else if (exchange_ns() - t0 > kWaitLimitNs) break;
     }
     float4 vp[PQ_EXCHANGE_MAX_RANKS];
     float lp[PQ_EXCHANGE_MAX_RANKS];
@@ -214,18 +168,20 @@ __global__ void __launch_bounds__(kHeadDim) exchange_merge_kernel(const Exchange
 
 }  // namespace
 
-int exchange_push_args(const void* const* bufs, int world, int rank, long long rows, PushArgs* px) {
+int exchange_push_args(void* const* bufs, int world, int rank, long long rows, PushArgs* px) {
   if (!bufs || !px || world < 1 || world > PQ_EXCHANGE_MAX_RANKS || rank < 0 || rank >= world || rows <= 0)
     return PQ_ERR_INVALID;
   *px = PushArgs{};
   for (int p = 0; p < world; ++p) {
     if (!bufs[p]) return PQ_ERR_INVALID;
     if (reinterpret_cast<uintptr_t>(bufs[p]) & 15) return PQ_ERR_ALIGNMENT;
-    px->inbox[p] = static_cast<float*>(const_cast<void*>(bufs[p])) + block_floats(rows) + rank * inbox_slot_words(rows);
+    px->inbox[p] = static_cast<float*>(bufs[p]) + block_floats(rows) + rank * inbox_slot_words(rows);
   }
-  px->ctrl = static_cast<const unsigned*>(bufs[rank]) + buffer_words(world, rows) - 4;
+  px->ctrl = static_cast<unsigned*>(bufs[rank]) + buffer_words(world, rows) - 4;
   px->parity_stride = world * inbox_slot_words(rows);
   px->rows = rows; px->world = world; px->rank = rank;
+  px->local_inbox = static_cast<const float*>(bufs[rank]) + block_floats(rows);
+  px->inbox_words = inbox_slot_words(rows);
   return PQ_OK;
 }
 

@@ -196,7 +196,7 @@ class PeerExchange:
 
 
 def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, attend=None, merge=None, exchange=None,
-                             push_in_attention=True, **kw):
+                             push_in_attention=True, collect_in_attention=True, **kw):
     """Decode attention with the keys split along the sequence across the ranks of `group`.
 
     Each rank passes ITS slice: `packed` = codes/scales of its token groups (or None), `kres` = the residual keys on
@@ -207,8 +207,9 @@ def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, att
     rank's fp32 output and log-sum-exp straight into one exchange block [out (B N, 128) | lse (B N)], one
     all-gather moves every rank's block, and one merge kernel reads the gathered buffer in place.  With
     ``exchange=PeerExchange(batch, heads, group)`` the attention's own merge also stores the block into the peers'
-    buffers over NVLink, and one kernel collects the peers' blocks and merges (``push_in_attention=False``: that
-    kernel does the stores itself).
+    buffers over NVLink, waits for the peers' blocks and merges: the step is the attention call alone, two launches
+    (``collect_in_attention=False``: a separate kernel collects and merges; ``push_in_attention=False``: that kernel
+    also does the stores).
     """
     if attend is not None or merge is not None:          # injected compute (CPU tests): the generic path
         out, lse = local_partial(q, kres, packed, v, attend=attend, **kw)
@@ -233,9 +234,14 @@ def sequence_parallel_decode(q, kres, packed, v, group=None, out_dtype=None, att
         out_view.zero_()
         lse_view.fill_(float("-inf"))
     else:
+        final = None
+        if exchange is not None and push_in_attention and collect_in_attention:
+            final = torch.empty((b, n, 1, hd), dtype=out_dtype or q.dtype, device=q.device)
         ops.decode_attention(q, kres if have_r else None, *(packed if have_q else (None,) * 5), v,
                              out_dtype=torch.float32, out=out_view, lse_out=lse_view,
-                             push_to=exchange if push_in_attention else None, **kw)
+                             push_to=exchange if push_in_attention else None, collect_out=final, **kw)
+        if final is not None:
+            return final
     if exchange is not None:
         return exchange.merge(out_dtype=out_dtype or q.dtype, after_attention=attended,
                               pushed=attended and push_in_attention)

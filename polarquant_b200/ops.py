@@ -281,7 +281,7 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
                      return_lse: bool = False, workspace: torch.Tensor | None = None, num_ctas: int = 0,
                      mid_event=None, value_codes=None, value_scale=None, value_mn=None, vbits: int = 4,
                      key_format: str = "byte", out: torch.Tensor | None = None, lse_out: torch.Tensor | None = None,
-                     push_to=None):
+                     push_to=None, collect_out: torch.Tensor | None = None):
     """One fused decode-attention step over the polar cache.
 
     Computes what the reference's decode branch computes with separate ops
@@ -311,7 +311,9 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
 
     ``push_to``: a ``distributed.PeerExchange``; the results are written to its ``out_view`` / ``lse_view`` and the
     merge that ends the call also stores every row into the peers' exchange buffers (sequence split over peer
-    memory: follow with ``push_to.merge(after_attention=True, pushed=True)``).
+    memory: follow with ``push_to.merge(after_attention=True, pushed=True)``).  With ``collect_out`` (B, N, 1, 128)
+    as well, that merge also waits for the peers' rows, merges them and writes the final result there: the call is
+    the whole sequence-split step and nothing follows it.
     """
     dev = _require_cuda(query_states, key_residual, indices, value_states, attention_mask, value_codes)
     bsz, nq, qlen, hd = query_states.shape
@@ -424,6 +426,13 @@ def decode_attention(query_states: torch.Tensor, key_residual, indices, rscale, 
         if out is not push_to.out_view or lse_out is not push_to.lse_view:
             raise ValueError("push_to: pass the exchange's out_view / lse_view as out / lse_out")
         p.exchange_bufs, p.exchange_world, p.exchange_rank = push_to._bufs, push_to.world, push_to.rank
+        if collect_out is not None:
+            if (collect_out.numel() != bsz * nq * hd or not collect_out.is_contiguous() or collect_out.device != dev
+                    or collect_out.dtype not in _DT):
+                raise ValueError("collect_out must be a contiguous (B, N, 1, 128) tensor on the inputs' device")
+            p.exchange_out, p.exchange_out_dtype = collect_out.data_ptr(), _DT[collect_out.dtype]
+    elif collect_out is not None:
+        raise ValueError("collect_out needs push_to")
     p.qk_dtype, p.v_dtype, p.out_dtype = qdt, vdt, _DT[out_dtype]
     p.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
     p.num_ctas = num_ctas

@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_mirror_and_status_strings():
     from polarquant_b200 import _lib
     lib = _lib.load()
-    assert lib.pq_abi_version() == 7
+    assert lib.pq_abi_version() == 8
     assert lib.pq_decode_params_size() == ctypes.sizeof(_lib.DecodeParams)
     for code in (0, -1, -2, -3, -4, -5):
         assert lib.pq_strerror(code)

@@ -123,6 +123,54 @@ def test_attention_pushes_its_rows_and_the_exchange_only_collects(world):
         assert float((outs[0].view(B, N, 1, 128) - full).abs().max()) <= 8e-3
 
 
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("final_dtype", [torch.float32, torch.bfloat16])
+def test_attention_call_can_do_the_whole_exchange(world, final_dtype):
+    """`collect_out`: the attention call's merge pushes its rows, waits for the peers' rows and writes the merged
+    result - no exchange kernel.  On one GPU the emulated ranks cannot wait for one another in separate launches, so
+    every rank first pushes its rows with a push-only call and then repeats the call with `collect_out`: the rows it
+    waits for are already there.  Bitwise equal to the merge of the gathered blocks, three steps on the same buffers."""
+    import polarquant_b200 as pq
+    from polarquant_b200 import _lib, ops
+    from polarquant_b200 import distributed as pqd
+    from oracle import polar_oracle as oracle
+    lib = _lib.load()
+    B, N, Nk, Nb, G, R = 2, 14, 2, 6, 64, 20            # 7 query heads per kv head: rows not aligned to anything
+    rows = B * N
+    bufs, _ = _buffers(lib, world, rows)
+    ranks = [_LocalExchange(bufs, r, B, N) for r in range(world)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for step in range(3):
+        keys = oracle.synth_keys(B, Nk, Nb * G + R, 128, torch.bfloat16, seed=400 + step, device=DEV)
+        g = torch.Generator(device=DEV).manual_seed(410 + step)
+        q = torch.randn(B, N, 1, 128, device=DEV, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, Nk, Nb * G + R, 128, device=DEV, generator=g).to(torch.bfloat16)
+        packed = pq.quantize_and_pack_nbit(keys[:, :, :Nb * G].contiguous(), 4, 4, G)
+        kres = keys[:, :, Nb * G:].contiguous()
+
+        def call(r, collect_out=None):
+            ex = ranks[r]
+            g0, g1, owns = pqd.split_sequence(Nb, R, r, world)
+            mine = [t[:, :, g0:g1].contiguous() for t in packed]
+            my_v = torch.cat([v[:, :, g0 * G:g1 * G]] + ([v[:, :, Nb * G:]] if owns else []), dim=2).contiguous()
+            pq.decode_attention(q, kres if owns else None, *mine, my_v, out_dtype=torch.float32, out=ex.out_view,
+                                lse_out=ex.lse_view, push_to=ex, collect_out=collect_out)
+
+        for r in range(world):
+            call(r)                                        # rows of this step land in every inbox
+        torch.cuda.synchronize()
+        gathered = torch.stack([b[:rows * 129] for b in bufs]).reshape(-1).clone()
+        want = ops.merge_lse_gathered(gathered, world, rows, out_dtype=final_dtype)
+        for r in range(world):
+            final = torch.full((B, N, 1, 128), float("nan"), dtype=final_dtype, device=DEV)
+            call(r, collect_out=final)
+            torch.cuda.synchronize()
+            assert torch.equal(final.view(rows, 128), want), f"step {step}, rank {r}"
+            word = ctypes.c_uint(7)
+            assert lib.pq_exchange_status(bufs[r].data_ptr(), world, rows, 128, ctypes.byref(word), stream) == 0
+            assert word.value == 0
+
+
 def test_push_arguments_are_validated():
     import polarquant_b200 as pq
     from polarquant_b200 import _lib
@@ -203,9 +251,9 @@ def _single_rank_worker(port, queue):
         full = pq.decode_attention(q, kres, *packed, v, out_dtype=torch.float32)
         ex = pqd.PeerExchange(B, N, device=dev)
         same = True
-        for push in (True, False, True):
+        for push, collect in ((True, True), (True, False), (False, False), (True, True)):
             got = pqd.sequence_parallel_decode(q, kres, packed, v, out_dtype=torch.float32, exchange=ex,
-                                               push_in_attention=push)
+                                               push_in_attention=push, collect_in_attention=collect)
             torch.cuda.synchronize()
             same = same and bool(torch.equal(got, full))
         # the step captured in a CUDA graph and replayed (the epoch lives on the device)

@@ -43,9 +43,11 @@ def _worker(rank, world, port, queue):
         # the same step through the peer-memory exchange, several times on the same buffers
         ex = pqd.PeerExchange(B, N, device=dev)
         same = True
-        for _ in range(5):
+        # the attention call does the whole exchange / a separate kernel collects / that kernel also pushes
+        for push, collect in ((True, True), (True, True), (True, False), (False, False), (True, True), (True, False)):
             got_p = pqd.sequence_parallel_decode(q, kres if owns else None, mine, torch.cat(my_v, dim=2).contiguous(),
-                                                 out_dtype=torch.float32, exchange=ex)
+                                                 out_dtype=torch.float32, exchange=ex, push_in_attention=push,
+                                                 collect_in_attention=collect)
             torch.cuda.synchronize()
             same = same and bool(torch.equal(got_p, got))
         status = ex.status()
