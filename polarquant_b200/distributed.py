@@ -8,9 +8,10 @@ locally (`sequence_parallel_decode`).  The reference has no counterpart: it runs
 (`test4long.py:38-43`) and never splits the sequence.
 
 Two forms of that exchange exist.  The default one moves the partials with one NCCL all-gather and merges the
-gathered buffer with one kernel; kernels then only ever touch local memory.  `PeerExchange` replaces both by ONE
-kernel that stores this rank's partial into every peer's buffer over NVLink (plain peer-to-peer stores), waits
-for the peers' stores on flag words in local memory - every wait bounded - and merges; the results are bit-identical.
+gathered buffer with one kernel; kernels then only ever touch local memory.  With a `PeerExchange` the attention
+call does the exchange itself: the kernel that ends it stores this rank's partial into every peer's buffer over
+NVLink (plain peer-to-peer stores, each value paired with the step's epoch), waits for the peers' stores in local
+memory - every wait bounded - and merges; the results are bit-identical.
 """
 from __future__ import annotations
 
@@ -88,9 +89,11 @@ class PeerExchange:
 
     Construction is collective over `group`: every rank allocates its buffer through the library
     (``pq_peer_alloc``), the 64-byte handles travel by ``all_gather_object``, and each rank maps the peers' buffers
-    (``pq_peer_open``).  ``out_view`` / ``lse_view`` are this rank's slot - pass them to ``decode_attention(out=,
-    lse_out=)`` - and ``merge`` enqueues the push / wait / merge kernel.  Call ``close`` on every rank after the last
-    step (it is collective too: a barrier first, so that no peer is still storing into a buffer that is freed).
+    (``pq_peer_open``).  ``out_view`` / ``lse_view`` are this rank's block - ``decode_attention(out=, lse_out=,
+    push_to=self, collect_out=...)`` writes it, pushes it and merges the peers' blocks - and ``merge`` enqueues the
+    stand-alone push / wait / merge kernel (a rank without keys in a step; the staged forms).  Call ``close`` on every
+    rank after the last step (it is collective too: a barrier first, so that no peer is still storing into a buffer
+    that is freed).
     """
 
     def __init__(self, batch: int, heads: int, group=None, device=None, head_dim: int = 128):
