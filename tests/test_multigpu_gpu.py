@@ -50,9 +50,25 @@ def _worker(rank, world, port, queue):
                                                  collect_in_attention=collect)
             torch.cuda.synchronize()
             same = same and bool(torch.equal(got_p, got))
+        # a context so short that some ranks hold no keys at all (3+ ranks): they contribute weight zero through the
+        # stand-alone exchange kernel while the others exchange inside their attention call - the forms interoperate
+        Nb2 = 2
+        full2 = pq.decode_attention(q, kres, *[t[:, :, :Nb2].contiguous() for t in packed],
+                                    torch.cat([v[:, :, :Nb2 * G], v[:, :, Nb * G:]], dim=2).contiguous(),
+                                    out_dtype=torch.float32)
+        g0, g1, owns = pqd.split_sequence(Nb2, R, rank, world)
+        mine2 = [t[:, :, g0:g1].contiguous() for t in packed] if g1 > g0 else None
+        v2 = [v[:, :, g0 * G:g1 * G]] + ([v[:, :, Nb * G:]] if owns else [])
+        v2 = torch.cat(v2, dim=2).contiguous()
+        err2 = 0.0
+        for collect in (True, False, True):
+            got2 = pqd.sequence_parallel_decode(q, kres if owns else None, mine2, v2, out_dtype=torch.float32,
+                                                exchange=ex, collect_in_attention=collect)
+            torch.cuda.synchronize()
+            err2 = max(err2, float((got2 - full2).abs().max()))
         status = ex.status()
         ex.close()
-        queue.put((rank, float((got - full).abs().max()), same, status))
+        queue.put((rank, max(float((got - full).abs().max()), err2), same, status))
     finally:
         dist.destroy_process_group()
 
