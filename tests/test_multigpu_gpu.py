@@ -35,6 +35,7 @@ def _worker(rank, world, port, queue):
         kres = keys[:, :, Nb * G:].contiguous()
         full = pq.decode_attention(q, kres, *packed, v, out_dtype=torch.float32)
         g0, g1, owns = pqd.split_sequence(Nb, R, rank, world)
+        owns1 = owns
         mine = [t[:, :, g0:g1].contiguous() for t in packed] if g1 > g0 else None
         my_v = [v[:, :, g0 * G:g1 * G]] + ([v[:, :, Nb * G:]] if owns else [])
         got = pqd.sequence_parallel_decode(q, kres if owns else None, mine, torch.cat(my_v, dim=2).contiguous(),
@@ -66,6 +67,25 @@ def _worker(rank, world, port, queue):
                                                 exchange=ex, collect_in_attention=collect)
             torch.cuda.synchronize()
             err2 = max(err2, float((got2 - full2).abs().max()))
+        # a few hundred steps with host-side skew between the ranks, the three forms interleaved, a fresh query every
+        # step: the buffers' two parities and the epochs see every order of arrival
+        import random
+        import time
+        rng = random.Random(500 + rank)
+        my_v1 = torch.cat(my_v, dim=2).contiguous()
+        for i in range(300):
+            qi = torch.randn(B, N, 1, 128, generator=torch.Generator().manual_seed(i)).to(torch.bfloat16).to(dev)
+            if rng.random() < 0.1:
+                time.sleep(rng.random() * 0.003)
+            got_i = pqd.sequence_parallel_decode(qi, kres if owns1 else None, mine, my_v1, out_dtype=torch.float32,
+                                                 exchange=ex, push_in_attention=i % 3 != 2,
+                                                 collect_in_attention=i % 3 == 0)
+            if i % 25 == 0:
+                want_i = pqd.sequence_parallel_decode(qi, kres if owns1 else None, mine, my_v1,
+                                                      out_dtype=torch.float32)
+                torch.cuda.synchronize()
+                same = same and bool(torch.equal(got_i, want_i))
+        torch.cuda.synchronize()
         status = ex.status()
         ex.close()
         queue.put((rank, max(float((got - full).abs().max()), err2), same, status))
